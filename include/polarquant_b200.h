@@ -1,0 +1,184 @@
+/*
+ * polarquant_b200 — C ABI of the B200 (sm_100a) implementation of the PolarQuant-KV
+ * block_pq4 hot path: compress, dequantise, decode attention, prefill attention and the
+ * cross-GPU partial merge.
+ *
+ * Conventions (all entry points):
+ *   - every pointer is a DEVICE pointer owned by the caller unless it says HOST
+ *     (the small tables: thresholds and codebooks, at most 16 floats each, are read on
+ *     the host during the call and travel to the kernel as launch parameters);
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued on it and the call
+ *     returns without synchronising; nothing is allocated or freed;
+ *   - the return value is a pq_status; 0 is success; pq_strerror() names the others;
+ *   - the device the pointers live on must be the current device.
+ *
+ * Storage layout ("block_pq4", README.md:73-78 of hilllief/polarquant-kv):
+ *   a vector of head_dim elements is head_dim/32 consecutive blocks; one block is
+ *       struct { __half d; uint8_t qs[32*n_bits/8]; }        18 bytes (4-bit), 10 (2-bit)
+ *   d is the float16 Euclidean norm of the 32 rotated elements, qs holds the Lloyd-Max
+ *   centroid indices: 4-bit  byte k = idx[2k] | idx[2k+1] << 4,
+ *                     2-bit  byte k = idx[4k] | idx[4k+1] << 2 | idx[4k+2] << 4 | idx[4k+3] << 6
+ *   (src/polarquant_kv_cuda/compress_kernel.py:34-50 of the reference).
+ *   A cache tensor is uint8 [rows, seq, head_dim/32, block_bytes], rows = batch*kv_heads.
+ *   QJL side band per key vector: jl_dim/8 sign bytes (bit k of byte j = sign[8j+k],
+ *   src/polarquant_kv_cuda/qjl_kernel.py:87-92) and one float16 residual norm.
+ *
+ * The precedent for a C ABI on this path is the reference's llama.cpp bridge
+ * (integration/polarquant-kv.patch, `polarquant_*_cuda_c`, lines 695-763 of the decoded
+ * patch): raw device pointers, caller-owned buffers, stream as void*.
+ */
+#ifndef POLARQUANT_B200_H
+#define POLARQUANT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum pq_status {
+    PQ_OK = 0,
+    PQ_ERR_NULL_POINTER = 1,     /* a required pointer is NULL                         */
+    PQ_ERR_BAD_HEAD_DIM = 2,     /* head_dim is not 64 or 128                          */
+    PQ_ERR_BAD_BITS = 3,         /* n_bits is not 2 or 4                               */
+    PQ_ERR_BAD_SHAPE = 4,        /* negative size, q_heads not a multiple of kv_heads… */
+    PQ_ERR_BAD_JL_DIM = 5,       /* jl_dim is not a multiple of 16 in [16, 128]        */
+    PQ_ERR_MISALIGNED = 6,       /* a buffer does not have the required alignment      */
+    PQ_ERR_SCRATCH_TOO_SMALL = 7,/* scratch_bytes is below pq_decode_attn_scratch_bytes */
+    PQ_ERR_CUDA = 8,             /* a CUDA runtime call failed (launch error, …)       */
+    PQ_ERR_TOO_LARGE = 9         /* a size exceeds what the entry point supports       */
+} pq_status;
+
+/* Library version: major*10000 + minor*100 + patch. */
+int pq_version(void);
+
+/* Static string for a pq_status value (never NULL). */
+const char* pq_strerror(int status);
+
+/* ---------------------------------------------------------------------------------
+ * pq_compress — fused rotate + per-32 radius + nearest-centroid + pack [+ QJL sketch].
+ *
+ * Replaces, on the block_pq4 layout: polarquant_kv.quantizer.compress / compress_batch
+ * (python/polarquant_kv/quantizer.py:88-134, 161-195), compress_gpu
+ * (src/polarquant_kv_cuda/compress_kernel.py:100-189), turboquant_compress_kernel
+ * (csrc/flash_turboquant.cu:111-175) and polarquant_compress_cuda_c (patch:695-763);
+ * with jl_split != NULL also compute_signatures_gpu (src/polarquant_kv_cuda/qjl_kernel.py:6-37).
+ *
+ *   x           float16 [n_vec, head_dim], 16-byte aligned
+ *   rot_split   float16 [head_dim, 2*head_dim]: row i = [hi(4096*R[i,:]) | lo(4096*R[i,:])],
+ *               the two-term float16 split of the rotation (R as used by v @ R^T);
+ *               built by the host helper polarquant_kv.rotation.split_for_device
+ *   thresholds  HOST float32 [2^n_bits - 1]: index = number of thresholds strictly below the
+ *               normalised coordinate; exact decision points of argmin|v - c_i| in float32
+ *   codebook    HOST float32 [2^n_bits] centroids (used for the QJL residual only)
+ *   blocks_out  uint8 [n_vec, head_dim/32, block_bytes], 16-byte aligned
+ *   jl_split    float16 [jl_dim, 2*head_dim] split of 1024*(P @ R^T), or NULL for no sketch;
+ *               jl_dim a multiple of 16 in [16, 128]
+ *   qjl_bits_out  uint8 [n_vec, jl_dim/8]      (required when jl_split != NULL)
+ *   qjl_norm_out  float16 [n_vec]              (required when jl_split != NULL)
+ */
+int pq_compress(const void* x, int64_t n_vec, int head_dim, int n_bits,
+                const void* rot_split, const float* thresholds, const float* codebook,
+                void* blocks_out,
+                const void* jl_split, int jl_dim, void* qjl_bits_out, void* qjl_norm_out,
+                void* stream);
+
+/* ---------------------------------------------------------------------------------
+ * pq_dequant — blocks -> centroid * d -> inverse rotation (v @ R).
+ *
+ * Replaces quantizer.decompress / decompress_batch (python/polarquant_kv/quantizer.py:137-158,
+ * 198-219), decompress_gpu (src/polarquant_kv_cuda/decompress_kernel.py:10-51),
+ * batch_dequant_4bit (src/polarquant_kv_cuda/fused_cuda_kernels.py:405-435).
+ *
+ *   blocks     uint8 [n_vec, head_dim/32, block_bytes]
+ *   codebook   HOST float32 [2^n_bits]
+ *   rot        float32 [head_dim, head_dim] row-major R
+ *   out        [n_vec, head_dim], float32 (out_is_fp16 == 0) or float16 clamped to +-65504
+ */
+int pq_dequant(const void* blocks, int64_t n_vec, int head_dim, int n_bits,
+               const float* codebook, const float* rot, void* out, int out_is_fp16,
+               void* stream);
+
+/* ---------------------------------------------------------------------------------
+ * pq_decode_attn — one query token per sequence against the compressed cache (GQA).
+ *
+ * Replaces attention.compressed_attention for seq_q == 1
+ * (python/polarquant_kv/attention.py:83-191), compressed_attention_gpu
+ * (src/polarquant_kv_cuda/attention_kernel.py:11-113), turboquant_attention_kernel
+ * (csrc/flash_turboquant.cu:27-105), rotate_query/inverse_rotate kernels
+ * (csrc/polarquant_full.cu:25-40, 125-140) and polarquant_fused_attention_cuda_c.
+ * Non-causal, as the reference.  The query is rotated once inside the kernel, only
+ * packed blocks are read, the sequence is cut into `n_splits` ranges whose (m, l, o)
+ * partials are merged by the last CTA to finish, and the result is rotated back.
+ *
+ *   q          float16 [batch, q_heads, head_dim]
+ *   k_blocks   uint8 [batch*kv_heads, seq_capacity, head_dim/32, block_bytes(k_bits)]
+ *   v_blocks   uint8 [batch*kv_heads, seq_capacity, head_dim/32, block_bytes(v_bits)]
+ *   seq_len    tokens to attend to (<= seq_capacity); 0 gives an all-zero output
+ *   codebook_k/codebook_v  HOST float32 [2^bits]
+ *   rot        float32 [head_dim, head_dim] row-major R
+ *   scale      softmax scale (1/sqrt(head_dim) in the reference)
+ *   jl_qproj   NULL, or float16 split of the JL matrix for the QJL score correction:
+ *              float32 [jl_dim, head_dim] row-major P (scores += corr * scale,
+ *              attention.py:150-155); then qjl_bits [rows, seq_capacity, jl_dim/8] and
+ *              qjl_norms float16 [rows, seq_capacity] are required
+ *   out        [batch, q_heads, head_dim] float32 (out_is_fp16 == 0) or float16
+ *   partial_out NULL, or float32 [batch, q_heads, head_dim + 2]: when given, the kernel
+ *              skips the final normalisation and inverse rotation and writes
+ *              (m, l, o_rotated[head_dim]) per query head instead of `out`
+ *              (m in log2 units) — the per-GPU partial of a sequence-sharded decode
+ *   n_splits   >= 1 sequence ranges per (batch, kv head); 0 lets the library choose
+ *   scratch    device buffer of at least pq_decode_attn_scratch_bytes(...) bytes,
+ *              256-byte aligned, ZERO-FILLED ONCE before its first use; the kernel
+ *              leaves its counters at zero again, so it can be reused by later calls
+ *              on the same stream (concurrent calls need separate scratch buffers)
+ */
+int pq_decode_attn(const void* q, const void* k_blocks, const void* v_blocks,
+                   int batch, int q_heads, int kv_heads, int64_t seq_len, int64_t seq_capacity,
+                   int head_dim, int k_bits, int v_bits,
+                   const float* codebook_k, const float* codebook_v, const float* rot, float scale,
+                   const float* jl_matrix, int jl_dim, const void* qjl_bits, const void* qjl_norms,
+                   void* out, int out_is_fp16, void* partial_out,
+                   int n_splits, void* scratch, size_t scratch_bytes, void* stream);
+
+/* Bytes of scratch pq_decode_attn needs for this shape (n_splits == 0: library default). */
+size_t pq_decode_attn_scratch_bytes(int batch, int q_heads, int kv_heads, int64_t seq_len,
+                                    int head_dim, int n_splits);
+
+/* The number of splits the library would choose for n_splits == 0 on the current device. */
+int pq_decode_attn_default_splits(int batch, int q_heads, int kv_heads, int64_t seq_len, int head_dim);
+
+/* ---------------------------------------------------------------------------------
+ * pq_lse_merge — merge per-GPU (m, l, o_rotated) partials of a sequence-sharded decode
+ * (after an all-gather) and rotate back.  No counterpart in the reference, which has no
+ * multi-GPU path; it completes pq_decode_attn(partial_out=...) for the long-context case.
+ *
+ *   partials   float32 [n_parts, n_rows, head_dim + 2] as written through partial_out
+ *   out        [n_rows, head_dim] float32 or float16
+ */
+int pq_lse_merge(const float* partials, int n_parts, int64_t n_rows, int head_dim,
+                 const float* rot, void* out, int out_is_fp16, void* stream);
+
+/* ---------------------------------------------------------------------------------
+ * pq_prefill_attn — seq_q >= 1 query tokens per head against the compressed cache:
+ * K/V tiles are dequantised into shared memory and contracted on tensor cores.
+ *
+ * Replaces attention.compressed_attention for seq_q > 1 and compressed_attention_gpu's
+ * dequantise-everything path (src/polarquant_kv_cuda/attention_kernel.py:70-113).
+ *
+ *   q          float16 [batch, q_heads, seq_q, head_dim]
+ *   causal     0: every query sees all seq_len tokens (the reference's behaviour);
+ *              1: query i sees tokens [0, seq_len - seq_q + i]
+ *   out        [batch, q_heads, seq_q, head_dim] float32 or float16
+ */
+int pq_prefill_attn(const void* q, const void* k_blocks, const void* v_blocks,
+                    int batch, int q_heads, int kv_heads, int seq_q, int64_t seq_len,
+                    int64_t seq_capacity, int head_dim, int k_bits, int v_bits,
+                    const float* codebook_k, const float* codebook_v, const float* rot,
+                    float scale, int causal, void* out, int out_is_fp16, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* POLARQUANT_B200_H */

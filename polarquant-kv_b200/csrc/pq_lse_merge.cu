@@ -1,0 +1,79 @@
+// pq_lse_merge, pq_version, pq_strerror.
+//
+// pq_lse_merge combines the per-GPU partials of a sequence-sharded decode: every rank ran
+// pq_decode_attn(partial_out=...) on its slice of the sequence and the ranks all-gathered
+// the [rows, D+2] records (m in log2 units, l, o in rotated space).  The merge is the usual
+// log-sum-exp combination followed by the inverse rotation o @ R.  Parts with l == 0 (an
+// empty slice) carry no weight and are ignored when the running maximum is taken.
+#include "pq_common.cuh"
+
+namespace pq {
+
+template <int D>
+__global__ void __launch_bounds__(D) pq_lse_merge_kernel(const float* __restrict__ parts, int n_parts,
+                                                         int64_t n_rows, const float* __restrict__ rot,
+                                                         void* out, int out_is_fp16) {
+    __shared__ float o_s[D];
+    const int i = threadIdx.x;
+    for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
+        float mx = -INFINITY;
+        for (int s = 0; s < n_parts; ++s) {
+            const float* r = parts + ((size_t)s * n_rows + row) * (D + 2);
+            if (r[1] > 0.f) mx = fmaxf(mx, r[0]);
+        }
+        float l = 0.f, o = 0.f;
+        for (int s = 0; s < n_parts; ++s) {
+            const float* r = parts + ((size_t)s * n_rows + row) * (D + 2);
+            if (r[1] > 0.f) {
+                const float sc = fast_exp2(r[0] - mx);
+                l = fmaf(sc, r[1], l);
+                o = fmaf(sc, r[2 + i], o);
+            }
+        }
+        __syncthreads();
+        o_s[i] = l > 0.f ? o / l : 0.f;
+        __syncthreads();
+        float acc = 0.f;
+#pragma unroll 8
+        for (int j = 0; j < D; ++j) acc = fmaf(o_s[j], __ldg(rot + (size_t)j * D + i), acc);
+        if (out_is_fp16)
+            static_cast<__half*>(out)[row * D + i] = __float2half_rn(fminf(fmaxf(acc, -65504.f), 65504.f));
+        else
+            static_cast<float*>(out)[row * D + i] = acc;
+    }
+}
+
+}  // namespace pq
+
+extern "C" int pq_lse_merge(const float* partials, int n_parts, int64_t n_rows, int head_dim,
+                            const float* rot, void* out, int out_is_fp16, void* stream) {
+    if (n_parts <= 0 || n_rows < 0) return PQ_ERR_BAD_SHAPE;
+    if (head_dim != 64 && head_dim != 128) return PQ_ERR_BAD_HEAD_DIM;
+    if (n_rows == 0) return PQ_OK;
+    if (!partials || !rot || !out) return PQ_ERR_NULL_POINTER;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = (int)(n_rows < 4096 ? n_rows : 4096);
+    if (head_dim == 64)
+        pq::pq_lse_merge_kernel<64><<<grid, 64, 0, st>>>(partials, n_parts, n_rows, rot, out, out_is_fp16);
+    else
+        pq::pq_lse_merge_kernel<128><<<grid, 128, 0, st>>>(partials, n_parts, n_rows, rot, out, out_is_fp16);
+    return cudaGetLastError() == cudaSuccess ? PQ_OK : PQ_ERR_CUDA;
+}
+
+extern "C" int pq_version(void) { return 100; }   // 0.1.0
+
+extern "C" const char* pq_strerror(int status) {
+    switch (status) {
+        case PQ_OK: return "ok";
+        case PQ_ERR_NULL_POINTER: return "a required pointer is NULL";
+        case PQ_ERR_BAD_HEAD_DIM: return "head_dim must be 64 or 128";
+        case PQ_ERR_BAD_BITS: return "n_bits must be 2 or 4";
+        case PQ_ERR_BAD_SHAPE: return "invalid shape argument";
+        case PQ_ERR_BAD_JL_DIM: return "jl_dim must be a multiple of 16 in [16, 128]";
+        case PQ_ERR_MISALIGNED: return "a buffer is not aligned as required";
+        case PQ_ERR_SCRATCH_TOO_SMALL: return "scratch buffer is smaller than pq_decode_attn_scratch_bytes()";
+        case PQ_ERR_CUDA: return "a CUDA runtime call failed";
+        case PQ_ERR_TOO_LARGE: return "a size exceeds what this entry point supports";
+        default: return "unknown pq_status";
+    }
+}

@@ -1,0 +1,170 @@
+"""Attention over a block_pq4 cache.
+
+``compressed_attention`` keeps the reference's GPU signature
+(src/polarquant_kv_cuda/attention_kernel.py:11-36, compressor.py:19-25) and the semantics
+of python/polarquant_kv/attention.py:83-191: non-causal softmax(q K^T / sqrt(d)) V on the
+dequantised cache with GQA (query head h reads kv head h // (Hq/Hkv)) and the optional QJL
+score correction.  seq_q == 1 runs pq_decode_attn, seq_q > 1 runs pq_prefill_attn.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _ext
+from .quantizer import _require_cuda, _stream, compress, tables
+from .rotation import device_plan
+from .types import CompressedKV
+
+_SCRATCH: dict = {}
+
+
+def _scratch(device, nbytes: int) -> torch.Tensor:
+    """Zero-initialised scratch for pq_decode_attn, one per (device, stream); grown on demand.
+    The kernel leaves its tickets at zero, so the buffer is reused without clearing."""
+    key = (str(device), torch.cuda.current_stream(device).cuda_stream)
+    buf = _SCRATCH.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _SCRATCH[key] = buf
+    return buf
+
+
+def standard_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                       num_kv_heads: int | None = None) -> torch.Tensor:
+    """Uncompressed float64 reference on the GPU, for checks: [B, Hq, Sq, D] x [B, Hkv, S, D]
+    (attention.py:20-73 of the reference; non-causal; GQA by repetition)."""
+    B, Hq, Sq, D = query.shape
+    Hkv = key.shape[1]
+    if num_kv_heads is not None and num_kv_heads != Hkv:
+        raise ValueError(f"key heads {Hkv} != num_kv_heads {num_kv_heads}")
+    if key.shape[2] == 0:
+        return torch.zeros((B, Hq, Sq, D), dtype=torch.float32, device=query.device)
+    rep = Hq // Hkv
+    k = key.double().repeat_interleave(rep, dim=1)
+    v = value.double().repeat_interleave(rep, dim=1)
+    s = query.double() @ k.transpose(-2, -1) / math.sqrt(D)
+    return (torch.softmax(s, dim=-1) @ v).float()
+
+
+def decode_attention(query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, plan,
+                     enable_qjl: bool = True, scale: float | None = None,
+                     out_dtype: torch.dtype = torch.float32, n_splits: int = 0,
+                     partial: bool = False, seq_range: tuple[int, int] | None = None) -> torch.Tensor:
+    """One query token per sequence.  query [B, Hq, D] float16 -> [B, Hq, D] (or, with
+    ``partial``, float32 [B, Hq, D+2] = (m, l, o_rotated) for a cross-GPU merge).
+    ``seq_range`` restricts attention to tokens [begin, end) of the cache."""
+    _require_cuda(query, "query")
+    B, Hq, D = query.shape
+    Hkv = ck.blocks.shape[1]
+    if Hq % Hkv:
+        raise ValueError(f"q heads {Hq} not a multiple of kv heads {Hkv}")
+    dev = query.device
+    kb, vb = ck.blocks, cv.blocks
+    S, cap = ck.seq_len, ck.max_seq_len
+    bits_t, norms_t = ck.qjl_signs, ck.residual_norms
+    if seq_range is not None:
+        lo, hi = seq_range
+        kb, vb = kb[:, :, lo:hi], vb[:, :, lo:hi]
+        if bits_t is not None:
+            bits_t, norms_t = bits_t[:, :, lo:hi], norms_t[:, :, lo:hi]
+        S = max(0, min(hi, S) - lo)
+    if not kb.is_contiguous() or not vb.is_contiguous():
+        kb, vb = kb.contiguous(), vb.contiguous()
+        if bits_t is not None:
+            bits_t, norms_t = bits_t.contiguous(), norms_t.contiguous()
+    cap = kb.shape[2]
+    use_qjl = bool(enable_qjl and plan.jl is not None and bits_t is not None)
+    q = query.to(torch.float16).contiguous()
+    lib = _ext.lib()
+    if n_splits <= 0:
+        n_splits = lib.pq_decode_attn_default_splits(B, Hq, Hkv, S, D)
+    need = lib.pq_decode_attn_scratch_bytes(B, Hq, Hkv, S, D, n_splits)
+    scratch = _scratch(dev, need)
+    if partial:
+        out = torch.empty((B, Hq, D + 2), dtype=torch.float32, device=dev)
+    else:
+        out = torch.empty((B, Hq, D), dtype=out_dtype, device=dev)
+    cbk, _, _ = tables(ck.n_bits)
+    cbv, _, _ = tables(cv.n_bits)
+    st = lib.pq_decode_attn(
+        q.data_ptr(), kb.data_ptr(), vb.data_ptr(), B, Hq, Hkv, S, cap, D, ck.n_bits, cv.n_bits,
+        cbk, cbv, plan.rot.data_ptr(), ctypes.c_float(scale if scale is not None else 1.0 / math.sqrt(D)),
+        plan.jl.data_ptr() if use_qjl else None, plan.jl_dim if use_qjl else 0,
+        bits_t.data_ptr() if use_qjl else None, norms_t.data_ptr() if use_qjl else None,
+        None if partial else out.data_ptr(), 1 if out_dtype == torch.float16 else 0,
+        out.data_ptr() if partial else None, n_splits, scratch.data_ptr(), scratch.numel(), _stream(dev))
+    _ext.check(st, "pq_decode_attn")
+    return out
+
+
+def prefill_attention(query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, plan,
+                      scale: float | None = None, causal: bool = False,
+                      out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """query [B, Hq, Sq, D] float16 -> [B, Hq, Sq, D]; K/V tiles are dequantised into shared
+    memory and contracted on tensor cores (pq_prefill_attn)."""
+    _require_cuda(query, "query")
+    B, Hq, Sq, D = query.shape
+    Hkv = ck.blocks.shape[1]
+    dev = query.device
+    out = torch.empty((B, Hq, Sq, D), dtype=out_dtype, device=dev)
+    if out.numel() == 0:
+        return out
+    kb, vb = ck.blocks, cv.blocks
+    if not kb.is_contiguous() or not vb.is_contiguous():
+        kb, vb = kb.contiguous(), vb.contiguous()
+    q = query.to(torch.float16).contiguous()
+    cbk, _, _ = tables(ck.n_bits)
+    cbv, _, _ = tables(cv.n_bits)
+    st = _ext.lib().pq_prefill_attn(
+        q.data_ptr(), kb.data_ptr(), vb.data_ptr(), B, Hq, Hkv, Sq, ck.seq_len, ck.max_seq_len, D,
+        ck.n_bits, cv.n_bits, cbk, cbv, plan.rot.data_ptr(),
+        ctypes.c_float(scale if scale is not None else 1.0 / math.sqrt(D)), 1 if causal else 0,
+        out.data_ptr(), 1 if out_dtype == torch.float16 else 0, _stream(dev))
+    _ext.check(st, "pq_prefill_attn")
+    return out
+
+
+def compressed_attention(query: torch.Tensor, compressed_keys, compressed_values, rotation_matrix,
+                         jl_matrix=None, enable_qjl: bool = True, num_kv_heads: int | None = None,
+                         n_bits: int = 4, group_size: int = 32,
+                         out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """query [B, Hq, Sq, D] (or [Hq, Sq, D]) float16 on the GPU; keys/values either
+    CompressedKV caches (the GPU facade's signature) or raw float16 tensors
+    [B, Hkv, S, D] / [Hkv, S, D], which are compressed first as the numpy reference does
+    (attention.py:138-144).  Returns [B, Hq, Sq, D] (same rank as the query), float32 by
+    default since float16 cannot hold the 2e-3 parity the path is checked to.
+    An empty cache gives zeros (attention.py:127-131)."""
+    _require_cuda(query, "query")
+    squeeze = query.dim() == 3
+    q4 = query.unsqueeze(0) if squeeze else query
+    if q4.dim() != 4:
+        raise ValueError(f"unsupported query shape {tuple(query.shape)}")
+    dev = query.device
+    plan = device_plan(rotation_matrix, dev, jl_matrix if enable_qjl else None)
+
+    def as_cache(x, with_qjl):
+        if isinstance(x, CompressedKV):
+            return x
+        x4 = x.unsqueeze(0) if x.dim() == 3 else x
+        return compress(x4, plan if not with_qjl else rotation_matrix, n_bits, group_size,
+                        jl_matrix if with_qjl else None)
+
+    ck = as_cache(compressed_keys, enable_qjl and jl_matrix is not None)
+    cv = as_cache(compressed_values, False)
+    Hkv = ck.blocks.shape[1]
+    if num_kv_heads is not None and num_kv_heads != Hkv:
+        raise ValueError(f"key heads {Hkv} != num_kv_heads {num_kv_heads}")
+    B, Hq, Sq, D = q4.shape
+    if ck.seq_len == 0 or q4.numel() == 0:
+        out = torch.zeros((B, Hq, Sq, D), dtype=out_dtype, device=dev)
+    elif Sq == 1:
+        out = decode_attention(q4[:, :, 0], ck, cv, plan, enable_qjl, out_dtype=out_dtype).unsqueeze(2)
+    else:
+        if enable_qjl and jl_matrix is not None and ck.qjl_signs is not None:
+            raise ValueError("the QJL score correction is implemented for decode (seq_q == 1) only")
+        out = prefill_attention(q4, ck, cv, plan, out_dtype=out_dtype)
+    return out[0] if squeeze else out
