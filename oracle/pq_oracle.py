@@ -379,10 +379,13 @@ def attention_from_blocks(q, k_blocks, v_blocks, R, codebook_k, codebook_v, bits
     rep = Hq // Hkv
     sc = 1.0 / math.sqrt(d) if scale is None else scale
     out = np.zeros((Hq, Sq, d), dtype=np.float64)
+    cache = {}
     for h in range(Hq):
         g = h // rep
-        k_hat = decompress(k_blocks[g], R, codebook_k, bits_k).astype(np.float64)
-        v_hat = decompress(v_blocks[g], R, codebook_v, bits_v).astype(np.float64)
+        if g not in cache:
+            cache = {g: (decompress(k_blocks[g], R, codebook_k, bits_k).astype(np.float64),
+                         decompress(v_blocks[g], R, codebook_v, bits_v).astype(np.float64))}
+        k_hat, v_hat = cache[g]
         if k_hat.shape[0] == 0:
             continue
         s = q[h].astype(np.float64) @ k_hat.T * sc

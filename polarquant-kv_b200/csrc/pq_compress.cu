@@ -153,10 +153,17 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
                 int j = lane >> 3;
                 ldmatrix_x4(b0, b1, b2, b3,
                             Rs + (wn * (D / 2) + nt * 8 + (lane & 7)) * RS + ks * 16 + (j & 1) * 8 + (j >> 1) * D);
+                // The tensor core truncates when it aligns addends to the running sum, so a
+                // long in-MMA accumulation chain drifts by several ulp.  Each k-step is
+                // therefore summed from zero (hi then lo term) and added to the running sum
+                // with a round-to-nearest float32 add.
 #pragma unroll
                 for (int mt = 0; mt < 2; ++mt) {
-                    mma_16816(acc[mt][nt], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
-                    mma_16816(acc[mt][nt], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b2, b3);
+                    float part[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma_16816(part, a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
+                    mma_16816(part, a[mt][0], a[mt][1], a[mt][2], a[mt][3], b2, b3);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[mt][nt][i] = __fadd_rn(acc[mt][nt][i], part[i]);
                 }
             }
         }
@@ -307,13 +314,14 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
 
         // ---- coalesced copy-out of the tile
         {
-            const int n_bytes = n_valid * VB;                       // multiple of 8
+            const int n_bytes = n_valid * VB;                       // multiple of 4
             uint8_t* dst = p.blocks_out + v0 * VB;                  // 16-byte aligned (v0 % 128 == 0)
             const int n16 = n_bytes / 16;
             for (int c = tid; c < n16; c += kCompressThreads)
                 reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(outs)[c];
-            if ((n_bytes & 15) && tid == 0)
-                reinterpret_cast<uint2*>(dst)[n_bytes / 8 - 1] = reinterpret_cast<const uint2*>(outs)[n_bytes / 8 - 1];
+            const int rest4 = (n_bytes & 15) >> 2;                  // ragged end in 4-byte words
+            if (tid < rest4)
+                reinterpret_cast<uint32_t*>(dst)[n16 * 4 + tid] = reinterpret_cast<const uint32_t*>(outs)[n16 * 4 + tid];
             if (QJL) {
                 const int M8 = p.jl_dim / 8;
                 uint8_t* bd = p.qjl_bits_out + v0 * M8;

@@ -45,12 +45,12 @@ __global__ void __launch_bounds__(D) pq_dequant_kernel(const DequantParams p) {
         const int64_t v0 = tile * kDqVecs;
         const int n_valid = (int)((p.n_vec - v0) < kDqVecs ? (p.n_vec - v0) : kDqVecs);
         __syncthreads();
-        // stored bytes of the tile (8-byte granules: VB is a multiple of 8)
+        // stored bytes of the tile (4-byte granules: VB is a multiple of 4)
         {
-            const uint2* src = reinterpret_cast<const uint2*>(p.blocks + v0 * VB);
-            const int n8 = n_valid * VB / 8;
-            for (int c = tid; c < kDqVecs * VB / 8; c += D)
-                reinterpret_cast<uint2*>(raw)[c] = c < n8 ? src[c] : make_uint2(0, 0);
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(p.blocks + v0 * VB);
+            const int n4 = n_valid * VB / 4;
+            for (int c = tid; c < kDqVecs * VB / 4; c += D)
+                reinterpret_cast<uint32_t*>(raw)[c] = c < n4 ? src[c] : 0u;
         }
         __syncthreads();
         // dequantise: thread j handles element j of every vector
@@ -124,7 +124,7 @@ extern "C" int pq_dequant(const void* blocks, int64_t n_vec, int head_dim, int n
     if (n_bits != 2 && n_bits != 4) return PQ_ERR_BAD_BITS;
     if (n_vec == 0) return PQ_OK;
     if (!blocks || !codebook || !rot || !out) return PQ_ERR_NULL_POINTER;
-    if ((reinterpret_cast<uintptr_t>(blocks) & 7) || (reinterpret_cast<uintptr_t>(rot) & 15))
+    if ((reinterpret_cast<uintptr_t>(blocks) & 3) || (reinterpret_cast<uintptr_t>(rot) & 15))
         return PQ_ERR_MISALIGNED;
     DequantParams p{};
     p.blocks = static_cast<const uint8_t*>(blocks);
