@@ -74,7 +74,7 @@ class ClockSampler:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
                  "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
@@ -107,8 +107,11 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        out = {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax,
+               "samples": len(sm), "reasons": sorted(reasons)}
+        if not sm and self.lines:
+            out["error"] = self.lines[0][:200]
+        return out
 
 
 # ----------------------------------------------------------------------------- CPU arm
@@ -235,12 +238,12 @@ def run_ours(args):
 
     def step(i):
         _, ck, cv = sets[i & 1]
-        return attention.decode_attention(q_dev, ck, cv, plan, enable_qjl=False)
+        return attention.decode_attention(q_dev, ck, cv, plan, enable_qjl=False, n_splits=args.splits)
 
     def step_e2e(i):
         _, ck, cv = sets[i & 1]
         q_stage.copy_(q_host, non_blocking=True)
-        out = attention.decode_attention(q_stage, ck, cv, plan, enable_qjl=False)
+        out = attention.decode_attention(q_stage, ck, cv, plan, enable_qjl=False, n_splits=args.splits)
         out_host.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()     # the caller reads the result on the host
 
@@ -278,13 +281,13 @@ def run_ours(args):
     # ---- secondary: bulk compress throughput (4-bit, with and without the QJL sketch)
     from polarquant_kv.qjl import generate_jl_matrix
     from polarquant_kv.rotation import device_plan, generate_rotation_matrix
-    n = COMPRESS_VECS
+    n = 1024 if args.only_decode else COMPRESS_VECS
     x = (torch.randn((n, D), generator=gen, device=dev) * torch.exp(torch.randn(D, generator=gen, device=dev))).to(torch.float16)
     x2 = x.flip(0).contiguous()
     Rm = generate_rotation_matrix(D, 0)
     plan_q = device_plan(Rm, dev, generate_jl_matrix(D, D, 1))
     comp = {}
-    for label, pl, jl in (("4bit", plan, None), ("4bit_qjl", plan_q, True)):
+    for label, pl, jl in (() if args.only_decode else (("4bit", plan, None), ("4bit_qjl", plan_q, True))):
         outs = [quantizer.allocate_cache(1, 1, n, D, 4, D if jl else 0, dev) for _ in range(2)]
         xs = [x.view(1, 1, n, D), x2.view(1, 1, n, D)]
 
@@ -316,7 +319,7 @@ def run_ours(args):
     # ---- CPU baseline on a bounded sample (one process, as the oracle is written)
     t0 = time.perf_counter()
     rows = 0
-    while time.perf_counter() - t0 < 10.0:
+    while time.perf_counter() - t0 < (0.0 if args.only_decode else 10.0) or rows == 0:
         _cpu_rows((1, rows, w))
         rows += 1
     cpu_dt = time.perf_counter() - t0
@@ -366,7 +369,13 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=WORKLOAD["batch"],
+                    help="sequences per GPU (default: the headline workload's 32; smaller for profiler captures)")
+    ap.add_argument("--only-decode", action="store_true",
+                    help="skip the compress and CPU-baseline measurements (profiler captures)")
+    ap.add_argument("--splits", type=int, default=0, help="sequence splits per (batch, kv head); 0 = library default")
     args = ap.parse_args()
+    WORKLOAD["batch"] = args.batch
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -8,29 +8,37 @@
 // KV head: all query heads of a KV head (up to 8 per CTA) share it.
 //
 // Why tensor cores in a bandwidth-bound kernel: with G query heads per KV head the
-// centroid products cost 2*G FMAs per stored nibble, more than the FP32 pipe can issue
-// at HBM speed.  Both contractions therefore run as mma.sync.m16n8k16 with two-term
-// float16 operands (value = hi + lo, ~22 mantissa bits) and float32 accumulation, which
-// keeps the float32-level accuracy the 2e-3 output tolerance needs (a single float16
-// rounding of the dequantised K is 15x too coarse on outlier-channel data).  Centroids
-// come from a shared-memory table indexed by a whole byte (two nibbles / four crumbs per
-// lookup, hi and lo terms in one entry), replicated per lane so lookups never conflict.
+// centroid products cost 2*G FMAs per stored nibble, more than the FP32 pipe can issue at
+// HBM speed.  Both contractions therefore run as mma.sync.m16n8k16 with two-term float16
+// operands (value = hi + lo, ~22 mantissa bits) and float32 accumulation, which keeps the
+// float32-level accuracy the 2e-3 output tolerance needs (one float16 rounding of the
+// dequantised K is 15x too coarse on outlier-channel data).
+//   scores:  A = centroids of 16 tokens x 16 dims, B = the query heads as MMA columns
+//            (4 heads x {hi, lo} in one n-tile, or 8 heads as a hi tile and a lo tile);
+//            the block radius multiplies the per-block partial sum in float32.
+//   values:  A = centroids^T of 16 dims x 16 tokens, B = p * radius per (token, head)
+//            with the same column arrangement.
+// Centroids come from a shared-memory table indexed by a whole byte of packed indices
+// (two nibbles / four crumbs per lookup, hi and lo terms in one entry), one private copy
+// per lane so lookups never bank-conflict; a byte is moved into address position with a
+// single byte-permute.
 //
-// Work split: grid = (n_splits, batch*kv_heads, ceil(G/8)); 8 warps per CTA; a warp owns
-// 16-token tiles of its CTA's range, streamed through a private 3-stage cp.async ring.
-// Each CTA reduces its warps' partials in shared memory and writes one (m, l, o) record
-// per query head; the last CTA of a (row, head-group) to arrive (atomic ticket, no
-// spinning) merges all records, normalises, rotates back and resets the ticket.
+// Work split: grid = (n_splits, batch*kv_heads, head groups); 16 warps per CTA, one CTA per
+// SM; a warp owns 16-token tiles of its CTA's range, streamed through a private 3-stage
+// cp.async ring.  Each CTA reduces its warps' partials in shared memory and writes one
+// (m, l, o) record per query head; the last CTA of a (row, head group) to arrive (atomic
+// ticket, no spinning) merges all records, normalises, rotates back and resets the ticket.
 #include "pq_common.cuh"
 
 namespace pq {
 
-constexpr int kDecWarps = 8;
+constexpr int kDecWarps = 16;
 constexpr int kDecThreads = kDecWarps * 32;
 constexpr int kTileTok = 16;
 constexpr int kStages = 3;
-constexpr int kHeadsPerCta = 8;
+constexpr int kRecHeads = 8;        // head slots per record in the scratch buffer
 constexpr float kCbScale = 64.0f;   // centroids are stored x64 in the table (keeps lo terms normal)
+constexpr int kTabBytes = 65536;    // 256 byte values x 256 B: K copies at +0, V copies at +128
 
 struct DecodeParams {
     const __half* q;           // [B, Hq, D]
@@ -53,126 +61,164 @@ struct DecodeParams {
     float cbk[16], cbv[16];
 };
 
+// ------------------------------------------------------------------ shared-memory access
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
+    uint32_t v;
+    asm volatile("{ .reg .u16 t; ld.shared.u16 t, [%1]; cvt.u32.u16 %0, t; }\n" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u8(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];\n" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds_v2(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ float lds_half_as_float(uint32_t a) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(lds_u16(a))));
+}
+// byte j of w moved to bits 8..15, everything else zero: the table row offset (byte * 256)
+template <int J>
+__device__ __forceinline__ uint32_t row_of_byte(uint32_t w) {
+    return __byte_perm(w, 0u, 0x4404u | (J << 4));
+}
+// 32 bits of packed indices at a shared address whose alignment class is known statically
+template <bool ALIGNED4>
+__device__ __forceinline__ uint32_t lds_word(uint32_t a) {
+    if (ALIGNED4) return lds_u32(a);
+    return lds_u16(a) | (lds_u16(a + 2) << 16);
+}
+
 // ------------------------------------------------------------------ centroid tables
-// 4-bit: entry(byte) = {half2(c[b&15], c[b>>4]) hi, same lo}, 8 bytes, 16 lane copies.
-// 2-bit: entry(byte) = {c[b&3], c[b>>2&3] | c[b>>4&3], c[b>>6] hi ; same lo}, 16 bytes, 8 copies.
+// Row r (256 B) belongs to byte value r.  4-bit: entry = {half2(c[r&15], c[r>>4]) hi, same lo},
+// 8 bytes, 16 lane copies.  2-bit: entry = {c[r&3], c[r>>2&3] | c[r>>4&3], c[r>>6] hi; same lo},
+// 16 bytes, 8 lane copies.  `half_off` is 0 for the K copies and 128 for the V copies.
 template <int BITS>
-struct Table {
-    static constexpr int kBytes = 32768;
-    __device__ static void build(uint8_t* tab, const float* cb, int tid) {
-        if (BITS == 4) {
-            for (int e = tid; e < 256 * 16; e += kDecThreads) {
-                const int b = e >> 4;
-                __half h0, l0, h1, l1;
-                split_half(cb[b & 15] * kCbScale, h0, l0);
-                split_half(cb[b >> 4] * kCbScale, h1, l1);
-                __half2 hi = __halves2half2(h0, h1), lo = __halves2half2(l0, l1);
-                uint2 v = make_uint2(*reinterpret_cast<uint32_t*>(&hi), *reinterpret_cast<uint32_t*>(&lo));
-                reinterpret_cast<uint2*>(tab)[e] = v;
-            }
-        } else {
-            for (int e = tid; e < 256 * 8; e += kDecThreads) {
-                const int b = e >> 3;
-                __half h[4], l[4];
+__device__ __forceinline__ void build_table(uint8_t* tab, int half_off, const float* cb, int tid) {
+    if (BITS == 4) {
+        for (int e = tid; e < 256 * 16; e += kDecThreads) {
+            const int b = e >> 4, copy = e & 15;
+            __half h0, l0, h1, l1;
+            split_half(cb[b & 15] * kCbScale, h0, l0);
+            split_half(cb[b >> 4] * kCbScale, h1, l1);
+            __half2 hi = __halves2half2(h0, h1), lo = __halves2half2(l0, l1);
+            *reinterpret_cast<uint2*>(tab + b * 256 + half_off + copy * 8) =
+                make_uint2(*reinterpret_cast<uint32_t*>(&hi), *reinterpret_cast<uint32_t*>(&lo));
+        }
+    } else {
+        for (int e = tid; e < 256 * 8; e += kDecThreads) {
+            const int b = e >> 3, copy = e & 7;
+            __half h[4], l[4];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) split_half(cb[(b >> (2 * k)) & 3] * kCbScale, h[k], l[k]);
-                __half2 h01 = __halves2half2(h[0], h[1]), h23 = __halves2half2(h[2], h[3]);
-                __half2 l01 = __halves2half2(l[0], l[1]), l23 = __halves2half2(l[2], l[3]);
-                uint4 v = make_uint4(*reinterpret_cast<uint32_t*>(&h01), *reinterpret_cast<uint32_t*>(&h23),
-                                     *reinterpret_cast<uint32_t*>(&l01), *reinterpret_cast<uint32_t*>(&l23));
-                reinterpret_cast<uint4*>(tab)[e] = v;
-            }
+            for (int k = 0; k < 4; ++k) split_half(cb[(b >> (2 * k)) & 3] * kCbScale, h[k], l[k]);
+            __half2 h01 = __halves2half2(h[0], h[1]), h23 = __halves2half2(h[2], h[3]);
+            __half2 l01 = __halves2half2(l[0], l[1]), l23 = __halves2half2(l[2], l[3]);
+            *reinterpret_cast<uint4*>(tab + b * 256 + half_off + copy * 16) =
+                make_uint4(*reinterpret_cast<uint32_t*>(&h01), *reinterpret_cast<uint32_t*>(&h23),
+                           *reinterpret_cast<uint32_t*>(&l01), *reinterpret_cast<uint32_t*>(&l23));
         }
     }
-};
-
-// 4-bit lookup: byte value already multiplied by 128 (entry stride of 16 copies x 8 bytes).
-__device__ __forceinline__ uint2 lut4(const uint8_t* tab_lane, uint32_t byte_x128) {
-    return *reinterpret_cast<const uint2*>(tab_lane + byte_x128);
-}
-__device__ __forceinline__ uint4 lut2(const uint8_t* tab_lane, uint32_t byte_x128) {
-    return *reinterpret_cast<const uint4*>(tab_lane + byte_x128);
 }
 
 // ------------------------------------------------------------------ tile staging
 // Copies `n` bytes (multiple of 4) from global `src` (4-byte aligned) to `dst_base +
 // (src & 15)`, so source and destination share their 16-byte phase; the middle goes as
-// 16-byte cp.async, the ragged ends as 4-byte ones.  Returns nothing; the caller commits.
+// 16-byte cp.async, the ragged ends as 4-byte ones.  The caller commits the group.
 __device__ __forceinline__ void stage_bytes(uint8_t* dst_base, const uint8_t* src, int n, int lane) {
     const uint32_t phase = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(src)) & 15u;
     uint8_t* dst = dst_base + phase;
+    if (phase == 0 && (n & 15) == 0) {                      // the common, fully aligned case
+        for (int c = lane; c < (n >> 4); c += 32) cp_async_16(dst + c * 16, src + c * 16);
+        return;
+    }
     int head = phase ? (int)(16u - phase) : 0;
     if (head > n) head = n;
     const int mid = (n - head) & ~15;
     const int tail = n - head - mid;
     if (lane < (head >> 2)) {
-        uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst + lane * 4));
+        uint32_t d = smem_addr(dst + lane * 4);
         asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src + lane * 4));
     }
     for (int c = lane; c < (mid >> 4); c += 32) cp_async_16(dst + head + c * 16, src + head + c * 16);
     if (lane < (tail >> 2)) {
-        uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst + head + mid + lane * 4));
+        uint32_t d = smem_addr(dst + head + mid + lane * 4);
         asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src + head + mid + lane * 4));
     }
 }
 
-// 32 bits at a 2-byte aligned shared address.
-__device__ __forceinline__ uint32_t lds32_align2(const uint8_t* p) {
-    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-    if ((a & 2) == 0) return *reinterpret_cast<const uint32_t*>(p);
-    const uint32_t* w = reinterpret_cast<const uint32_t*>(p - 2);
-    return __funnelshift_r(w[0], w[1], 16);
-}
-
-template <int D, int KBITS, int VBITS, bool QJL>
+template <int D, int KBITS, int VBITS, int NH, bool QJL>
 struct DecodeCfg {
     static constexpr int NBLK = D / 32;
+    static constexpr int HPC = 4 * NH;                            // query heads per CTA
     static constexpr int BBK = block_bytes(KBITS), BBV = block_bytes(VBITS);
     static constexpr int TBK = NBLK * BBK, TBV = NBLK * BBV;     // bytes per token
     static constexpr int kStageK = kTileTok * TBK + 16;
     static constexpr int kStageV = kTileTok * TBV + 16;
     static constexpr int kStageN = 48;                            // 16 float16 norms + slack
-    static constexpr int kTabK = Table<KBITS>::kBytes;
-    static constexpr int kTabV = (KBITS == VBITS) ? 0 : Table<VBITS>::kBytes;
     static constexpr int kSignTab = QJL ? 16 * 16 * 8 : 0;
     __host__ __device__ static int stage_bits(int jl_dim) { return QJL ? kTileTok * (jl_dim / 8) + 16 : 0; }
     __host__ __device__ static int stage_bytes_total(int jl_dim) {
         return kStageK + kStageV + (QJL ? stage_bits(jl_dim) + kStageN : 0);
     }
+    __host__ __device__ static int qjl_frag_bytes(int jl_dim) { return QJL ? (jl_dim / 16) * 32 * 16 : 0; }
     __host__ __device__ static size_t smem_bytes(int jl_dim) {
         size_t ring = (size_t)kDecWarps * kStages * stage_bytes_total(jl_dim);
-        size_t work = kTabK + kTabV + kSignTab + ring;
-        size_t merge = (size_t)kDecWarps * kHeadsPerCta * (D + 2) * 4;   // aliases tables + ring
-        size_t qbuf = (size_t)kHeadsPerCta * (D + (QJL ? jl_dim : 0)) * 4 + 2 * kHeadsPerCta * D * 4;
+        size_t work = kTabBytes + kSignTab + qjl_frag_bytes(jl_dim) + ring;
+        size_t merge = (size_t)kDecWarps * kRecHeads * (D + 2) * 4;      // aliases tables + ring
+        size_t qbuf = (size_t)HPC * (3 * D + (QJL ? jl_dim : 0)) * 4;
         return (work > merge ? work : merge) + qbuf + 64;
     }
 };
 
-template <int D, int KBITS, int VBITS, bool QJL>
-__global__ void __launch_bounds__(kDecThreads, 2) pq_decode_attn_kernel(const DecodeParams p) {
-    using C = DecodeCfg<D, KBITS, VBITS, QJL>;
+// float -> the float16 term this lane contributes: hi, or lo = v - hi
+__device__ __forceinline__ float term_of(float v, bool want_lo) {
+    const float hi = __half2float(__float2half_rn(v));
+    return want_lo ? v - hi : v;
+}
+
+template <int D, int KBITS, int VBITS, int NH, bool QJL>
+__global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const DecodeParams p) {
+    using C = DecodeCfg<D, KBITS, VBITS, NH, QJL>;
     constexpr int NBLK = C::NBLK;
+    constexpr int HPC = C::HPC;
     extern __shared__ __align__(16) uint8_t smem[];
-    // layout: [q buffers][tables][ring]  (merge area aliases tables + ring afterwards)
-    float* q_in = reinterpret_cast<float*>(smem);                        // [8][D]   original-space q
-    float* q_rot = q_in + kHeadsPerCta * D;                              // [8][D]   rotated, scaled
-    float* q_jl = q_rot + kHeadsPerCta * D;                              // [8][M]   (QJL)
-    float* o_fin = q_jl + (QJL ? kHeadsPerCta * p.jl_dim : 0);           // [8][D]   final stage
-    uint8_t* work = reinterpret_cast<uint8_t*>(o_fin + kHeadsPerCta * D);
+    // layout: [q buffers][table][sign table][qjl fragments][rings]; the merge area reuses
+    // everything after the q buffers once the main loop is over
+    float* q_in = reinterpret_cast<float*>(smem);                        // [HPC][D] original-space q
+    float* q_rot = q_in + HPC * D;                                       // [HPC][D] rotated, scaled
+    float* o_fin = q_rot + HPC * D;                                      // [HPC][D] final stage
+    float* q_jl = o_fin + HPC * D;                                       // [HPC][M] (QJL)
+    uint8_t* work = reinterpret_cast<uint8_t*>(q_jl + (QJL ? HPC * p.jl_dim : 0));
     work = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(work) + 15) & ~uintptr_t(15));
-    uint8_t* tabk = work;
-    uint8_t* tabv = (KBITS == VBITS) ? tabk : tabk + C::kTabK;
-    uint8_t* signtab = work + C::kTabK + C::kTabV;
-    uint8_t* ring = signtab + C::kSignTab;
-    float* merge = reinterpret_cast<float*>(work);                       // [8 warps][8][D+2]
+    uint8_t* tab = work;
+    uint8_t* signtab = tab + kTabBytes;
+    uint8_t* qjl_frag = signtab + C::kSignTab;
+    uint8_t* ring = qjl_frag + C::qjl_frag_bytes(QJL ? p.jl_dim : 0);
+    float* merge = reinterpret_cast<float*>(work);                       // [16 warps][8][D+2]
     __shared__ unsigned int s_ticket;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int split = blockIdx.x, row = blockIdx.y, hg = blockIdx.z;
     const int b = row / p.Hkv, hkv = row % p.Hkv;
-    const int Gp = min(kHeadsPerCta, p.G - hg * kHeadsPerCta);           // query heads of this CTA
-    const int head0 = hkv * p.G + hg * kHeadsPerCta;                      // first query head
+    const int Gp = min(HPC, p.G - hg * HPC);                             // query heads of this CTA
+    const int head0 = hkv * p.G + hg * HPC;                              // first query head
     const int M = QJL ? p.jl_dim : 0;
 
     // ---- token range of this CTA and of this warp
@@ -194,11 +240,10 @@ __global__ void __launch_bounds__(kDecThreads, 2) pq_decode_attn_kernel(const De
             stage_bytes(st, k_row + tok0 * C::TBK, ntok * C::TBK, lane);
             stage_bytes(st + C::kStageK, v_row + tok0 * C::TBV, ntok * C::TBV, lane);
             if (QJL) {
-                stage_bytes(st + C::kStageK + C::kStageV, bits_row + tok0 * (M / 8), ntok * (M / 8), lane);
-                // norms: 2 bytes per token; copy whole 4-byte words around them (the row is
-                // 4-byte aligned at even tokens, tok0 is a multiple of 16)
+                stage_bytes(st + C::kStageK + C::kStageV, bits_row + tok0 * (M / 8),
+                            (ntok * (M / 8) + 3) & ~3, lane);
                 stage_bytes(st + C::kStageK + C::kStageV + C::stage_bits(M), norm_row + tok0 * 2,
-                            ((ntok * 2 + 3) & ~3), lane);
+                            (ntok * 2 + 3) & ~3, lane);
             }
         }
         cp_async_commit();
@@ -208,8 +253,8 @@ __global__ void __launch_bounds__(kDecThreads, 2) pq_decode_attn_kernel(const De
     issue_tile(tile_begin + warp + kDecWarps, 1);
 
     // ---- prologue: tables, query rotation (and JL projection of the query)
-    Table<KBITS>::build(tabk, p.cbk, tid);
-    if (KBITS != VBITS) Table<VBITS>::build(tabv, p.cbv, tid);
+    build_table<KBITS>(tab, 0, p.cbk, tid);
+    build_table<VBITS>(tab, 128, p.cbv, tid);
     if (QJL) {
         // sign table: nibble -> 4 halves of +-1; entry 8 bytes, 16 lane copies
         for (int e = tid; e < 16 * 16; e += kDecThreads) {
@@ -220,12 +265,12 @@ __global__ void __launch_bounds__(kDecThreads, 2) pq_decode_attn_kernel(const De
                 make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&c));
         }
     }
-    for (int e = tid; e < kHeadsPerCta * D; e += kDecThreads) {
+    for (int e = tid; e < HPC * D; e += kDecThreads) {
         const int h = e / D, j = e % D;
         q_in[e] = h < Gp ? __half2float(p.q[((size_t)b * p.Hq + head0 + h) * D + j]) : 0.f;
     }
     __syncthreads();
-    // q_rot[h][i] = sum_j q[h][j] * R[i][j]; a warp takes rows i = warp, warp+8, ...
+    // q_rot[h][i] = sum_j q[h][j] * R[i][j]; a warp takes matrix rows i = warp, warp+16, ...
     {
         constexpr int JP = D / 32;
         for (int i = warp; i < D + M; i += kDecWarps) {
@@ -234,7 +279,7 @@ __global__ void __launch_bounds__(kDecThreads, 2) pq_decode_attn_kernel(const De
 #pragma unroll
             for (int k = 0; k < JP; ++k) r[k] = mrow[lane + 32 * k];
 #pragma unroll
-            for (int h = 0; h < kHeadsPerCta; ++h) {
+            for (int h = 0; h < HPC; ++h) {
                 float s = 0.f;
 #pragma unroll
                 for (int k = 0; k < JP; ++k) s = fmaf(r[k], q_in[h * D + lane + 32 * k], s);
@@ -249,32 +294,63 @@ __global__ void __launch_bounds__(kDecThreads, 2) pq_decode_attn_kernel(const De
     }
     __syncthreads();
 
-    // ---- A fragments of the query: rows 0-7 carry hi(q[head]), rows 8-15 lo(q[head]).
+    // ---- B fragments of the query.  MMA column n = lane group g.
+    //   NH == 1: column g is head g>>1, term hi (g even) or lo (g odd);
+    //   NH == 2: column g is head g; a hi tile and a lo tile.
     // k-slot mapping inside a 32-dim block, k-step ks: slots (2t,2t+1) <-> dims 8t+4ks+(0,1),
-    // slots (2t+8,2t+9) <-> dims 8t+4ks+(2,3): the 8 nibbles of this lane's 32-bit word.
-    uint32_t qa[NBLK][2][4];
+    // slots (2t+8,2t+9) <-> dims 8t+4ks+(2,3): the 8 nibbles of the 32-bit word lane t reads.
+    uint32_t qb[NBLK][2][2 * NH];
+    {
+        const int hq = NH == 1 ? (g >> 1) : g;
+        const bool lo1 = (g & 1) != 0;
 #pragma unroll
-    for (int blk = 0; blk < NBLK; ++blk)
+        for (int blk = 0; blk < NBLK; ++blk)
 #pragma unroll
-        for (int ks = 0; ks < 2; ++ks) {
-            const float* src = q_rot + g * D + blk * 32 + 8 * t + 4 * ks;
-            __half h[4], l[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) split_half(src[k], h[k], l[k]);
-            __half2 v;
-            v = __halves2half2(h[0], h[1]); qa[blk][ks][0] = *reinterpret_cast<uint32_t*>(&v);
-            v = __halves2half2(l[0], l[1]); qa[blk][ks][1] = *reinterpret_cast<uint32_t*>(&v);
-            v = __halves2half2(h[2], h[3]); qa[blk][ks][2] = *reinterpret_cast<uint32_t*>(&v);
-            v = __halves2half2(l[2], l[3]); qa[blk][ks][3] = *reinterpret_cast<uint32_t*>(&v);
+            for (int ks = 0; ks < 2; ++ks) {
+                const float* src = q_rot + hq * D + blk * 32 + 8 * t + 4 * ks;
+                if (NH == 1) {
+                    qb[blk][ks][0] = pack_half2(term_of(src[0], lo1), term_of(src[1], lo1));
+                    qb[blk][ks][1] = pack_half2(term_of(src[2], lo1), term_of(src[3], lo1));
+                } else {
+                    qb[blk][ks][0] = pack_half2(src[0], src[1]);
+                    qb[blk][ks][1] = pack_half2(src[2], src[3]);
+                    qb[blk][ks][2] = pack_half2(term_of(src[0], true), term_of(src[1], true));
+                    qb[blk][ks][3] = pack_half2(term_of(src[2], true), term_of(src[3], true));
+                }
+            }
+        if (QJL) {
+            // fragments of the projected query, one uint4 per (k-step, lane): {b0, b1 | lo b0, lo b1}
+            for (int ks = warp; ks < M / 16; ks += kDecWarps) {
+                const float* src = q_jl + hq * M + ks * 16 + 4 * t;
+                uint4 f;
+                if (NH == 1) {
+                    f.x = pack_half2(term_of(src[0], lo1), term_of(src[1], lo1));
+                    f.y = pack_half2(term_of(src[2], lo1), term_of(src[3], lo1));
+                    f.z = 0u; f.w = 0u;
+                } else {
+                    f.x = pack_half2(src[0], src[1]);
+                    f.y = pack_half2(src[2], src[3]);
+                    f.z = pack_half2(term_of(src[0], true), term_of(src[1], true));
+                    f.w = pack_half2(term_of(src[2], true), term_of(src[3], true));
+                }
+                reinterpret_cast<uint4*>(qjl_frag)[ks * 32 + lane] = f;
+            }
         }
+    }
+    __syncthreads();
 
-    // table base for this lane's private copy
-    const uint8_t* tabk_lane = tabk + (KBITS == 4 ? (lane & 15) * 8 : (lane & 7) * 16);
-    const uint8_t* tabv_lane = tabv + (VBITS == 4 ? (lane & 15) * 8 : (lane & 7) * 16);
-    const uint8_t* sign_lane = signtab + (lane & 15) * 8;
+    // this lane's private table copies (shared-memory byte addresses)
+    const uint32_t tabk_lane = smem_addr(tab) + (KBITS == 4 ? (lane & 15) * 8 : (lane & 7) * 16);
+    const uint32_t tabv_lane = smem_addr(tab) + 128 + (VBITS == 4 ? (lane & 15) * 8 : (lane & 7) * 16);
+    const uint32_t sign_lane = smem_addr(signtab) + (lane & 15) * 8;
+    const uint32_t qjl_frag_lane = smem_addr(qjl_frag) + lane * 16;
+    const uint32_t ring_addr = smem_addr(my_ring);
 
-    // ---- running softmax state of head g (m shared by the 4 lanes of a row, l per lane)
-    float m_run = -INFINITY, l_run = 0.f;
+    // ---- running softmax state.  A lane holds scores of NH heads (NH == 1: head t;
+    // NH == 2: heads 2t, 2t+1) for tokens g and g+8 of the tile.
+    float m_run[NH], l_run[NH];
+#pragma unroll
+    for (int h = 0; h < NH; ++h) { m_run[h] = -INFINITY; l_run[h] = 0.f; }
     float o_acc[NBLK][2][4];
 #pragma unroll
     for (int blk = 0; blk < NBLK; ++blk)
@@ -285,162 +361,203 @@ __global__ void __launch_bounds__(kDecThreads, 2) pq_decode_attn_kernel(const De
 
     int slot = 0;
     for (int64_t tile = tile_begin + warp; tile < tile_end; tile += kDecWarps) {
-        issue_tile(tile + 2 * kDecWarps, (slot + 2) % kStages);
+        issue_tile(tile + 2 * kDecWarps, slot >= 1 ? slot - 1 : kStages - 1);
         cp_async_wait<2>();
         __syncwarp();
-        const uint8_t* st = my_ring + slot * stage_sz;
         const int64_t tok0 = tile * kTileTok;
         const int ntok = (int)min((int64_t)kTileTok, p.S - tok0);
-        const uint8_t* ks_base = st + (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(k_row + tok0 * C::TBK)) & 15u);
-        const uint8_t* vs_base = st + C::kStageK +
+        const uint32_t st = ring_addr + slot * stage_sz;
+        const uint32_t ks_base = st + (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(k_row + tok0 * C::TBK)) & 15u);
+        const uint32_t vs_base = st + C::kStageK +
                                  (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(v_row + tok0 * C::TBV)) & 15u);
 
-        // ================= scores: 2 sub-tiles of 8 tokens, token = 8*sub + g as MMA column
-        float sc[2][2];
+        // ================= scores: MMA rows = tokens (g, g+8), columns = query heads
+        float sc[NH][2];
 #pragma unroll
-        for (int sub = 0; sub < 2; ++sub) {
-            const uint8_t* tokp = ks_base + (sub * 8 + g) * C::TBK;
-            float s0 = 0.f, s1 = 0.f;
+        for (int h = 0; h < NH; ++h) { sc[h][0] = 0.f; sc[h][1] = 0.f; }
+        {
+            const uint32_t tok_a = ks_base + g * C::TBK;            // token g
+            const uint32_t tok_b = tok_a + 8 * C::TBK;              // token g + 8
 #pragma unroll
             for (int blk = 0; blk < NBLK; ++blk) {
                 float c[4] = {0.f, 0.f, 0.f, 0.f};
+                uint32_t ah[2][4], al[2][4];                        // [k-step][a0..a3]
                 if (KBITS == 4) {
-                    const uint32_t w = lds32_align2(tokp + blk * C::BBK + 2 + 4 * t);
-                    const uint2 e0 = lut4(tabk_lane, (w << 7) & 0x7F80u);
-                    const uint2 e1 = lut4(tabk_lane, (w >> 1) & 0x7F80u);
-                    const uint2 e2 = lut4(tabk_lane, (w >> 9) & 0x7F80u);
-                    const uint2 e3 = lut4(tabk_lane, (w >> 17) & 0x7F80u);
-                    mma_16816(c, qa[blk][0][0], qa[blk][0][1], qa[blk][0][2], qa[blk][0][3], e0.x, e1.x);
-                    mma_16816(c, qa[blk][0][0], qa[blk][0][1], qa[blk][0][2], qa[blk][0][3], e0.y, e1.y);
-                    mma_16816(c, qa[blk][1][0], qa[blk][1][1], qa[blk][1][2], qa[blk][1][3], e2.x, e3.x);
-                    mma_16816(c, qa[blk][1][0], qa[blk][1][1], qa[blk][1][2], qa[blk][1][3], e2.y, e3.y);
+                    constexpr bool A4 = true;
+                    const uint32_t off = blk * C::BBK + 2 + 4 * t;
+                    const bool al4 = ((blk * C::BBK + 2) & 3) == 0; // tile base and token stride are 4-aligned
+                    const uint32_t wa = al4 ? lds_word<true>(tok_a + off) : lds_word<false>(tok_a + off);
+                    const uint32_t wb = al4 ? lds_word<true>(tok_b + off) : lds_word<false>(tok_b + off);
+                    (void)A4;
+                    const uint2 a0 = lds_v2(tabk_lane + row_of_byte<0>(wa)), a1 = lds_v2(tabk_lane + row_of_byte<1>(wa));
+                    const uint2 a2 = lds_v2(tabk_lane + row_of_byte<2>(wa)), a3 = lds_v2(tabk_lane + row_of_byte<3>(wa));
+                    const uint2 b0 = lds_v2(tabk_lane + row_of_byte<0>(wb)), b1 = lds_v2(tabk_lane + row_of_byte<1>(wb));
+                    const uint2 b2 = lds_v2(tabk_lane + row_of_byte<2>(wb)), b3 = lds_v2(tabk_lane + row_of_byte<3>(wb));
+                    ah[0][0] = a0.x; ah[0][1] = b0.x; ah[0][2] = a1.x; ah[0][3] = b1.x;
+                    al[0][0] = a0.y; al[0][1] = b0.y; al[0][2] = a1.y; al[0][3] = b1.y;
+                    ah[1][0] = a2.x; ah[1][1] = b2.x; ah[1][2] = a3.x; ah[1][3] = b3.x;
+                    al[1][0] = a2.y; al[1][1] = b2.y; al[1][2] = a3.y; al[1][3] = b3.y;
                 } else {
-                    const uint32_t h = *reinterpret_cast<const uint16_t*>(tokp + blk * C::BBK + 2 + 2 * t);
-                    const uint4 e0 = lut2(tabk_lane, (h << 7) & 0x7F80u);
-                    const uint4 e1 = lut2(tabk_lane, (h >> 1) & 0x7F80u);
-                    mma_16816(c, qa[blk][0][0], qa[blk][0][1], qa[blk][0][2], qa[blk][0][3], e0.x, e0.y);
-                    mma_16816(c, qa[blk][0][0], qa[blk][0][1], qa[blk][0][2], qa[blk][0][3], e0.z, e0.w);
-                    mma_16816(c, qa[blk][1][0], qa[blk][1][1], qa[blk][1][2], qa[blk][1][3], e1.x, e1.y);
-                    mma_16816(c, qa[blk][1][0], qa[blk][1][1], qa[blk][1][2], qa[blk][1][3], e1.z, e1.w);
+                    const uint32_t off = blk * C::BBK + 2 + 2 * t;
+                    const uint32_t ha = lds_u16(tok_a + off), hb = lds_u16(tok_b + off);
+                    const uint4 a0 = lds_v4(tabk_lane + row_of_byte<0>(ha)), a1 = lds_v4(tabk_lane + row_of_byte<1>(ha));
+                    const uint4 b0 = lds_v4(tabk_lane + row_of_byte<0>(hb)), b1 = lds_v4(tabk_lane + row_of_byte<1>(hb));
+                    ah[0][0] = a0.x; ah[0][1] = b0.x; ah[0][2] = a0.y; ah[0][3] = b0.y;
+                    al[0][0] = a0.z; al[0][1] = b0.z; al[0][2] = a0.w; al[0][3] = b0.w;
+                    ah[1][0] = a1.x; ah[1][1] = b1.x; ah[1][2] = a1.y; ah[1][3] = b1.y;
+                    al[1][0] = a1.z; al[1][1] = b1.z; al[1][2] = a1.w; al[1][3] = b1.w;
                 }
-                // C: rows g (hi of head g) and g+8 (lo), columns = tokens 8*sub + 2t, 2t+1
-                const uint8_t* dp = ks_base + (sub * 8 + 2 * t) * C::TBK + blk * C::BBK;
-                const float d0 = __half2float(*reinterpret_cast<const __half*>(dp));
-                const float d1 = __half2float(*reinterpret_cast<const __half*>(dp + C::TBK));
-                s0 = fmaf(d0, c[0] + c[2], s0);
-                s1 = fmaf(d1, c[1] + c[3], s1);
+#pragma unroll
+                for (int ks = 0; ks < 2; ++ks) {
+                    mma_16816(c, ah[ks][0], ah[ks][1], ah[ks][2], ah[ks][3], qb[blk][ks][0], qb[blk][ks][1]);
+                    mma_16816(c, al[ks][0], al[ks][1], al[ks][2], al[ks][3], qb[blk][ks][0], qb[blk][ks][1]);
+                    if (NH == 2)
+                        mma_16816(c, ah[ks][0], ah[ks][1], ah[ks][2], ah[ks][3], qb[blk][ks][2], qb[blk][ks][3]);
+                }
+                const float d0 = lds_half_as_float(tok_a + blk * C::BBK);
+                const float d1 = lds_half_as_float(tok_b + blk * C::BBK);
+                if (NH == 1) {      // columns 2t, 2t+1 = hi and lo term of head t
+                    sc[0][0] = fmaf(d0, c[0] + c[1], sc[0][0]);
+                    sc[0][1] = fmaf(d1, c[2] + c[3], sc[0][1]);
+                } else {            // columns 2t, 2t+1 = heads 2t, 2t+1
+                    sc[0][0] = fmaf(d0, c[0], sc[0][0]);
+                    sc[NH - 1][0] = fmaf(d0, c[1], sc[NH - 1][0]);
+                    sc[0][1] = fmaf(d1, c[2], sc[0][1]);
+                    sc[NH - 1][1] = fmaf(d1, c[3], sc[NH - 1][1]);
+                }
             }
-            sc[sub][0] = s0 * (1.0f / kCbScale);
-            sc[sub][1] = s1 * (1.0f / kCbScale);
+#pragma unroll
+            for (int h = 0; h < NH; ++h) { sc[h][0] *= (1.0f / kCbScale); sc[h][1] *= (1.0f / kCbScale); }
         }
 
         if (QJL) {
-            // corr[head][token] = sum_i (+-1) * qp[head][i] (already scaled by scale*log2e/M)
-            const uint8_t* bs_base = st + C::kStageK + C::kStageV +
+            // corr[token][head] = sum_i (+-1) * qp[head][i] (qp already scaled by scale*log2e/M)
+            const uint32_t bs_base = st + C::kStageK + C::kStageV +
                                      (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(bits_row + tok0 * (M / 8))) & 15u);
-            const uint8_t* ns_base = st + C::kStageK + C::kStageV + C::stage_bits(M) +
+            const uint32_t ns_base = st + C::kStageK + C::kStageV + C::stage_bits(M) +
                                      (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(norm_row + tok0 * 2)) & 15u);
-#pragma unroll
-            for (int sub = 0; sub < 2; ++sub) {
-                float c[4] = {0.f, 0.f, 0.f, 0.f};
-                const uint8_t* tb = bs_base + (sub * 8 + g) * (M / 8);
-                for (int ks = 0; ks < M / 16; ++ks) {
-                    const uint32_t h = *reinterpret_cast<const uint16_t*>(tb + 2 * ks);
-                    const uint2 e = *reinterpret_cast<const uint2*>(sign_lane + (((h >> (4 * t)) & 0xFu) << 7));
-                    const float* src = q_jl + g * M + ks * 16 + 4 * t;
-                    __half hh[4], ll[4];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) split_half(src[k], hh[k], ll[k]);
-                    __half2 v0 = __halves2half2(hh[0], hh[1]), v1 = __halves2half2(ll[0], ll[1]);
-                    __half2 v2 = __halves2half2(hh[2], hh[3]), v3 = __halves2half2(ll[2], ll[3]);
-                    mma_16816(c, *reinterpret_cast<uint32_t*>(&v0), *reinterpret_cast<uint32_t*>(&v1),
-                              *reinterpret_cast<uint32_t*>(&v2), *reinterpret_cast<uint32_t*>(&v3), e.x, e.y);
-                }
-                const __half* np = reinterpret_cast<const __half*>(ns_base) + sub * 8 + 2 * t;
-                // a zero residual norm switches the correction off (qjl.py:49-50)
-                if (__half2float(np[0]) != 0.f) sc[sub][0] += c[0] + c[2];
-                if (__half2float(np[1]) != 0.f) sc[sub][1] += c[1] + c[3];
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t ta = bs_base + g * (M / 8), tb = ta + 8 * (M / 8);
+            for (int ks = 0; ks < M / 16; ++ks) {
+                const uint32_t ha = lds_u16(ta + 2 * ks), hb = lds_u16(tb + 2 * ks);
+                const uint2 ea = lds_v2(sign_lane + (((ha >> (4 * t)) & 0xFu) << 7));
+                const uint2 eb = lds_v2(sign_lane + (((hb >> (4 * t)) & 0xFu) << 7));
+                const uint4 f = lds_v4(qjl_frag_lane + ks * 512);
+                mma_16816(c, ea.x, eb.x, ea.y, eb.y, f.x, f.y);
+                if (NH == 2) mma_16816(c, ea.x, eb.x, ea.y, eb.y, f.z, f.w);
+            }
+            // a zero residual norm switches the correction off (qjl.py:49-50)
+            const bool on0 = lds_u16(ns_base + 2 * g) != 0u;
+            const bool on1 = lds_u16(ns_base + 2 * (g + 8)) != 0u;
+            if (NH == 1) {
+                if (on0) sc[0][0] += c[0] + c[1];
+                if (on1) sc[0][1] += c[2] + c[3];
+            } else {
+                if (on0) { sc[0][0] += c[0]; sc[NH - 1][0] += c[1]; }
+                if (on1) { sc[0][1] += c[2]; sc[NH - 1][1] += c[3]; }
             }
         }
 
         // mask tokens past the end of the sequence
+        if (g >= ntok) {
 #pragma unroll
-        for (int sub = 0; sub < 2; ++sub)
+            for (int h = 0; h < NH; ++h) sc[h][0] = -INFINITY;
+        }
+        if (g + 8 >= ntok) {
 #pragma unroll
-            for (int e = 0; e < 2; ++e)
-                if (sub * 8 + 2 * t + e >= ntok) sc[sub][e] = -INFINITY;
+            for (int h = 0; h < NH; ++h) sc[h][1] = -INFINITY;
+        }
 
-        // ================= online softmax for head g over the 16 tokens of the tile
-        float tmax = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
-        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
-        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
-        const float m_new = fmaxf(m_run, tmax);
-        const float alpha = fast_exp2(m_run - m_new);      // exp2(-inf) = 0 on the first tile
-        float pr[2][2];
+        // ================= online softmax over the 16 tokens of the tile (lanes with equal t)
+        float pr[NH][2], alpha[NH];
+        bool rescale = false;
 #pragma unroll
-        for (int sub = 0; sub < 2; ++sub)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) pr[sub][e] = fast_exp2(sc[sub][e] - m_new);
-        l_run = l_run * alpha + (pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]);
-        m_run = m_new;
-        // rescale the accumulators: their columns are heads 2t, 2t+1
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-            const float a0 = __shfl_sync(0xffffffffu, alpha, (2 * t) * 4);
-            const float a1 = __shfl_sync(0xffffffffu, alpha, (2 * t + 1) * 4);
+        for (int h = 0; h < NH; ++h) {
+            float tmax = fmaxf(sc[h][0], sc[h][1]);
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 8));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 16));
+            const float m_new = fmaxf(m_run[h], tmax);
+            alpha[h] = fast_exp2(m_run[h] - m_new);          // exp2(-inf) = 0 on the first tile
+            pr[h][0] = fast_exp2(sc[h][0] - m_new);
+            pr[h][1] = fast_exp2(sc[h][1] - m_new);
+            l_run[h] = l_run[h] * alpha[h] + pr[h][0] + pr[h][1];
+            m_run[h] = m_new;
+            rescale |= alpha[h] != 1.0f;
+        }
+        // accumulator columns 2t, 2t+1 belong to this lane's own head(s)
+        if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
             for (int blk = 0; blk < NBLK; ++blk)
 #pragma unroll
                 for (int mt = 0; mt < 2; ++mt) {
-                    o_acc[blk][mt][0] *= a0; o_acc[blk][mt][1] *= a1;
-                    o_acc[blk][mt][2] *= a0; o_acc[blk][mt][3] *= a1;
+                    o_acc[blk][mt][0] *= alpha[0]; o_acc[blk][mt][1] *= alpha[NH - 1];
+                    o_acc[blk][mt][2] *= alpha[0]; o_acc[blk][mt][3] *= alpha[NH - 1];
                 }
         }
 
-        // ================= values: O[dim][head] += V^T[dim][token] * (p*d)[token][head]
-        // A rows: g <-> dim 4g+2mt, g+8 <-> dim 4g+2mt+1 of the block; k slots = tokens
-        // (2t, 2t+1 | 8+2t, 9+2t); B column g = head g with the same token slots.
+        // ================= values: O[dim][column] += V^T[dim][token] * (p*d)[token][column]
+        // B column g needs p of its head for tokens (2t, 2t+1 | 8+2t, 9+2t); the lane that
+        // holds p[head h][token tau] is (tau % 8) * 4 + (NH == 1 ? h : h >> 1).
+        float pv[4];
+        {
+            const int hsel = NH == 1 ? (g >> 1) : (g >> 1);
+            const int la = (2 * t) * 4 + hsel, lb = (2 * t + 1) * 4 + hsel;
+            float x0 = __shfl_sync(0xffffffffu, pr[0][0], la), x1 = __shfl_sync(0xffffffffu, pr[0][0], lb);
+            float x2 = __shfl_sync(0xffffffffu, pr[0][1], la), x3 = __shfl_sync(0xffffffffu, pr[0][1], lb);
+            if (NH == 2) {
+                const float y0 = __shfl_sync(0xffffffffu, pr[NH - 1][0], la), y1 = __shfl_sync(0xffffffffu, pr[NH - 1][0], lb);
+                const float y2 = __shfl_sync(0xffffffffu, pr[NH - 1][1], la), y3 = __shfl_sync(0xffffffffu, pr[NH - 1][1], lb);
+                if (g & 1) { x0 = y0; x1 = y1; x2 = y2; x3 = y3; }
+            }
+            pv[0] = (2 * t < ntok) ? x0 : 0.f;
+            pv[1] = (2 * t + 1 < ntok) ? x1 : 0.f;
+            pv[2] = (2 * t + 8 < ntok) ? x2 : 0.f;
+            pv[3] = (2 * t + 9 < ntok) ? x3 : 0.f;
+        }
+        const bool lo_col = NH == 1 && (g & 1);
+        const uint32_t vtok = vs_base + (2 * t) * C::TBV;            // tokens 2t, 2t+1, 2t+8, 2t+9
 #pragma unroll
         for (int blk = 0; blk < NBLK; ++blk) {
-            // weights of this lane's 4 tokens for head g, times the block radius
             float w[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const int tok = (k >> 1) * 8 + 2 * t + (k & 1);
-                const float d = __half2float(*reinterpret_cast<const __half*>(vs_base + tok * C::TBV + blk * C::BBV));
-                w[k] = tok < ntok ? pr[k >> 1][k & 1] * d : 0.f;
+                const uint32_t a = vtok + ((k >> 1) * 8 + (k & 1)) * C::TBV + blk * C::BBV;
+                const float d = lds_half_as_float(a);
+                w[k] = pv[k] != 0.f ? pv[k] * d : 0.f;               // masked tokens may hold stale bytes
             }
-            __half wh[4], wl[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) split_half(w[k], wh[k], wl[k]);
-            __half2 t0 = __halves2half2(wh[0], wh[1]), t1 = __halves2half2(wh[2], wh[3]);
-            __half2 t2 = __halves2half2(wl[0], wl[1]), t3 = __halves2half2(wl[2], wl[3]);
-            const uint32_t bh0 = *reinterpret_cast<uint32_t*>(&t0), bh1 = *reinterpret_cast<uint32_t*>(&t1);
-            const uint32_t bl0 = *reinterpret_cast<uint32_t*>(&t2), bl1 = *reinterpret_cast<uint32_t*>(&t3);
-
-            uint32_t ahi[2][4], alo[2][4];   // [m-tile][a0..a3]
+            uint32_t bh0, bh1, bl0 = 0u, bl1 = 0u;
+            if (NH == 1) {
+                bh0 = pack_half2(term_of(w[0], lo_col), term_of(w[1], lo_col));
+                bh1 = pack_half2(term_of(w[2], lo_col), term_of(w[3], lo_col));
+            } else {
+                bh0 = pack_half2(w[0], w[1]);
+                bh1 = pack_half2(w[2], w[3]);
+                bl0 = pack_half2(term_of(w[0], true), term_of(w[1], true));
+                bl1 = pack_half2(term_of(w[2], true), term_of(w[3], true));
+            }
+            // A rows: g <-> dim 4g+2mt, g+8 <-> dim 4g+2mt+1 of the block; k slots = tokens
+            uint32_t ahi[2][4], alo[2][4];
 #pragma unroll
             for (int pair = 0; pair < 2; ++pair) {
-                const uint8_t* pa = vs_base + (pair * 8 + 2 * t) * C::TBV + blk * C::BBV + 2;
+                const uint32_t pa = vtok + pair * 8 * C::TBV + blk * C::BBV + 2;
                 if (VBITS == 4) {
-                    const uint32_t ha = *reinterpret_cast<const uint16_t*>(pa + 2 * g);
-                    const uint32_t hb = *reinterpret_cast<const uint16_t*>(pa + C::TBV + 2 * g);
-                    const uint32_t m1 = (ha & 0x0F0Fu) | ((hb & 0x0F0Fu) << 4);          // dims 0, 2
-                    const uint32_t m2 = ((ha >> 4) & 0x0F0Fu) | (hb & 0xF0F0u);           // dims 1, 3
-                    const uint2 e0 = lut4(tabv_lane, (m1 << 7) & 0x7F80u);
-                    const uint2 e1 = lut4(tabv_lane, (m2 << 7) & 0x7F80u);
-                    const uint2 e2 = lut4(tabv_lane, (m1 >> 1) & 0x7F80u);
-                    const uint2 e3 = lut4(tabv_lane, (m2 >> 1) & 0x7F80u);
+                    const uint32_t ha = lds_u16(pa + 2 * g), hb = lds_u16(pa + C::TBV + 2 * g);
+                    // byte k of m1: dims 0 / 2, byte k of m2: dims 1 / 3; low nibble token a, high token b
+                    const uint32_t m1 = (ha & 0x0F0Fu) | ((hb << 4) & 0xF0F0u);
+                    const uint32_t m2 = ((ha >> 4) & 0x0F0Fu) | (hb & 0xF0F0u);
+                    const uint2 e0 = lds_v2(tabv_lane + row_of_byte<0>(m1)), e1 = lds_v2(tabv_lane + row_of_byte<0>(m2));
+                    const uint2 e2 = lds_v2(tabv_lane + row_of_byte<1>(m1)), e3 = lds_v2(tabv_lane + row_of_byte<1>(m2));
                     ahi[0][pair * 2 + 0] = e0.x; ahi[0][pair * 2 + 1] = e1.x;
                     alo[0][pair * 2 + 0] = e0.y; alo[0][pair * 2 + 1] = e1.y;
                     ahi[1][pair * 2 + 0] = e2.x; ahi[1][pair * 2 + 1] = e3.x;
                     alo[1][pair * 2 + 0] = e2.y; alo[1][pair * 2 + 1] = e3.y;
                 } else {
-                    const uint32_t ba = pa[g], bb = pa[C::TBV + g];
+                    const uint32_t ba = lds_u8(pa + g), bb = lds_u8(pa + C::TBV + g);
                     const uint32_t m1 = (ba & 3u) | ((bb & 3u) << 2) | ((ba & 0xCu) << 2) | ((bb & 0xCu) << 4);
                     const uint32_t ua = ba >> 4, ub = bb >> 4;
                     const uint32_t m2 = (ua & 3u) | ((ub & 3u) << 2) | ((ua & 0xCu) << 2) | ((ub & 0xCu) << 4);
-                    const uint4 e0 = lut2(tabv_lane, m1 << 7);
-                    const uint4 e1 = lut2(tabv_lane, m2 << 7);
+                    const uint4 e0 = lds_v4(tabv_lane + (m1 << 8)), e1 = lds_v4(tabv_lane + (m2 << 8));
                     ahi[0][pair * 2 + 0] = e0.x; ahi[0][pair * 2 + 1] = e0.y;
                     alo[0][pair * 2 + 0] = e0.z; alo[0][pair * 2 + 1] = e0.w;
                     ahi[1][pair * 2 + 0] = e1.x; ahi[1][pair * 2 + 1] = e1.y;
@@ -450,48 +567,63 @@ __global__ void __launch_bounds__(kDecThreads, 2) pq_decode_attn_kernel(const De
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt) {
                 mma_16816(o_acc[blk][mt], ahi[mt][0], ahi[mt][1], ahi[mt][2], ahi[mt][3], bh0, bh1);
-                mma_16816(o_acc[blk][mt], ahi[mt][0], ahi[mt][1], ahi[mt][2], ahi[mt][3], bl0, bl1);
                 mma_16816(o_acc[blk][mt], alo[mt][0], alo[mt][1], alo[mt][2], alo[mt][3], bh0, bh1);
+                if (NH == 2)
+                    mma_16816(o_acc[blk][mt], ahi[mt][0], ahi[mt][1], ahi[mt][2], ahi[mt][3], bl0, bl1);
             }
         }
         __syncwarp();
-        slot = (slot + 1) % kStages;
+        slot = slot + 1 == kStages ? 0 : slot + 1;
     }
     cp_async_wait<0>();
 
-    // ---- reduce the row sum over the 4 lanes of a head
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    // ---- reduce the row sums over the 8 lanes that share a head
+#pragma unroll
+    for (int h = 0; h < NH; ++h) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 4);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 8);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 16);
+    }
     __syncthreads();   // tables and rings are dead: the merge area takes their place
 
-    // per-warp record: merge[warp][head][0]=m, [1]=l, [2+dim]=o
+    // per-warp record: merge[warp][head][0] = m, [1] = l, [2 + dim] = o
     {
-        float* rec = merge + (size_t)warp * kHeadsPerCta * (D + 2);
-        if (t == 0) {
-            rec[g * (D + 2) + 0] = m_run;
-            rec[g * (D + 2) + 1] = l_run;
+        float* rec = merge + (size_t)warp * kRecHeads * (D + 2);
+        if (g == 0) {
+#pragma unroll
+            for (int h = 0; h < NH; ++h) {
+                const int head = NH == 1 ? t : 2 * t + h;
+                rec[head * (D + 2) + 0] = m_run[h];
+                rec[head * (D + 2) + 1] = l_run[h];
+            }
         }
 #pragma unroll
         for (int blk = 0; blk < NBLK; ++blk)
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int head = 2 * t + (i & 1);
-                    const int dim = blk * 32 + 4 * g + 2 * mt + (i >> 1);
-                    rec[head * (D + 2) + 2 + dim] = o_acc[blk][mt][i] * (1.0f / kCbScale);
+            for (int mt = 0; mt < 2; ++mt) {
+                const int dim = blk * 32 + 4 * g + 2 * mt;
+                const float* o = o_acc[blk][mt];
+                if (NH == 1) {     // columns 2t, 2t+1 are the hi and lo parts of head t
+                    rec[t * (D + 2) + 2 + dim] = (o[0] + o[1]) * (1.0f / kCbScale);
+                    rec[t * (D + 2) + 2 + dim + 1] = (o[2] + o[3]) * (1.0f / kCbScale);
+                } else {
+                    rec[(2 * t) * (D + 2) + 2 + dim] = o[0] * (1.0f / kCbScale);
+                    rec[(2 * t + 1) * (D + 2) + 2 + dim] = o[1] * (1.0f / kCbScale);
+                    rec[(2 * t) * (D + 2) + 2 + dim + 1] = o[2] * (1.0f / kCbScale);
+                    rec[(2 * t + 1) * (D + 2) + 2 + dim + 1] = o[3] * (1.0f / kCbScale);
                 }
+            }
     }
     __syncthreads();
 
-    // ---- CTA record = merge of the 8 warp records
+    // ---- CTA record = merge of the warp records
     const size_t group = (size_t)row * p.HG + hg;
-    float* cta_rec = p.records + (group * p.splits + split) * kHeadsPerCta * (D + 2);
-    for (int e = tid; e < kHeadsPerCta * (D + 2); e += kDecThreads) {
+    float* cta_rec = p.records + (group * p.splits + split) * kRecHeads * (D + 2);
+    for (int e = tid; e < HPC * (D + 2); e += kDecThreads) {
         const int head = e / (D + 2), col = e % (D + 2);
         float mx = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kDecWarps; ++w) mx = fmaxf(mx, merge[(w * kHeadsPerCta + head) * (D + 2)]);
+        for (int w = 0; w < kDecWarps; ++w) mx = fmaxf(mx, merge[(w * kRecHeads + head) * (D + 2)]);
         float val;
         if (col == 0) {
             val = mx;
@@ -499,9 +631,9 @@ __global__ void __launch_bounds__(kDecThreads, 2) pq_decode_attn_kernel(const De
             val = 0.f;
 #pragma unroll
             for (int w = 0; w < kDecWarps; ++w) {
-                const float mw = merge[(w * kHeadsPerCta + head) * (D + 2)];
+                const float mw = merge[(w * kRecHeads + head) * (D + 2)];
                 const float s = (mw == -INFINITY) ? 0.f : fast_exp2(mw - mx);
-                val = fmaf(s, merge[(w * kHeadsPerCta + head) * (D + 2) + col], val);
+                val = fmaf(s, merge[(w * kRecHeads + head) * (D + 2) + col], val);
             }
         }
         __stcg(cta_rec + e, val);
@@ -514,14 +646,14 @@ __global__ void __launch_bounds__(kDecThreads, 2) pq_decode_attn_kernel(const De
     __threadfence();
 
     // ---- last CTA of this (row, head group): merge the split records
-    const float* recs = p.records + group * p.splits * kHeadsPerCta * (D + 2);
-    for (int e = tid; e < kHeadsPerCta * D; e += kDecThreads) {
+    const float* recs = p.records + group * p.splits * kRecHeads * (D + 2);
+    for (int e = tid; e < HPC * D; e += kDecThreads) {
         const int head = e / D, dim = e % D;
         float mx = -INFINITY;
-        for (int s = 0; s < p.splits; ++s) mx = fmaxf(mx, __ldcg(recs + (s * kHeadsPerCta + head) * (D + 2)));
+        for (int s = 0; s < p.splits; ++s) mx = fmaxf(mx, __ldcg(recs + (s * kRecHeads + head) * (D + 2)));
         float l = 0.f, o = 0.f;
         for (int s = 0; s < p.splits; ++s) {
-            const float* r = recs + (s * kHeadsPerCta + head) * (D + 2);
+            const float* r = recs + (s * kRecHeads + head) * (D + 2);
             const float ms = __ldcg(r);
             const float sc = (ms == -INFINITY) ? 0.f : fast_exp2(ms - mx);
             l = fmaf(sc, __ldcg(r + 1), l);
@@ -541,7 +673,7 @@ __global__ void __launch_bounds__(kDecThreads, 2) pq_decode_attn_kernel(const De
     if (p.partial_out) return;
     __syncthreads();
     // out[head][i] = sum_j o_fin[head][j] * R[j][i]
-    for (int e = tid; e < kHeadsPerCta * D; e += kDecThreads) {
+    for (int e = tid; e < HPC * D; e += kDecThreads) {
         const int head = e / D, i = e % D;
         if (head >= Gp) continue;
         float acc = 0.f;
@@ -561,25 +693,37 @@ static int device_sms() {
     return sms;
 }
 
+// query heads per CTA: 4 (one MMA n-tile holds 4 heads x {hi, lo}) or 8 (a hi and a lo tile)
+static int heads_per_cta(int G) { return G <= 4 ? 4 : 8; }
+
+static int head_groups(int G) { const int h = heads_per_cta(G); return (G + h - 1) / h; }
+
+// One CTA per SM: pick the split count whose CTA total fills whole waves best, with at
+// least two tiles per warp and no more than 64 splits.
 static int choose_splits(int batch, int q_heads, int kv_heads, int64_t seq_len, int sms) {
     if (sms <= 0) sms = 148;
     const int G = q_heads / kv_heads;
-    const int64_t groups = (int64_t)batch * kv_heads * ((G + kHeadsPerCta - 1) / kHeadsPerCta);
+    const int64_t groups = (int64_t)batch * kv_heads * head_groups(G);
     const int64_t tiles = (seq_len + kTileTok - 1) / kTileTok;
-    // aim for about 4 CTAs per SM in total (2 resident x 2 waves), at least 2 tiles per warp
-    int64_t want = (4LL * sms + groups - 1) / groups;
-    const int64_t max_by_work = tiles / (2 * kDecWarps);
-    if (want > max_by_work) want = max_by_work;
-    if (want < 1) want = 1;
-    if (want > 1024) want = 1024;
-    return (int)want;
+    int64_t max_s = tiles / (2 * kDecWarps);
+    if (max_s > 64) max_s = 64;
+    if (max_s < 1) max_s = 1;
+    int best = 1;
+    double best_eff = -1.0;
+    for (int s = 1; s <= max_s; ++s) {
+        const double waves = (double)(groups * s) / sms;
+        const double full = waves < 1.0 ? 1.0 : (double)(int64_t)(waves + 0.999999);
+        const double eff = waves / full;
+        if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+    }
+    return best;
 }
 
-template <int D, int KBITS, int VBITS, bool QJL>
+template <int D, int KBITS, int VBITS, int NH, bool QJL>
 static int launch_decode(const DecodeParams& p, int rows, cudaStream_t st) {
-    using C = DecodeCfg<D, KBITS, VBITS, QJL>;
+    using C = DecodeCfg<D, KBITS, VBITS, NH, QJL>;
     const size_t smem = C::smem_bytes(p.jl_dim);
-    auto kern = pq_decode_attn_kernel<D, KBITS, VBITS, QJL>;
+    auto kern = pq_decode_attn_kernel<D, KBITS, VBITS, NH, QJL>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return PQ_ERR_CUDA;
     dim3 grid(p.splits, rows, p.HG);
@@ -600,9 +744,9 @@ extern "C" size_t pq_decode_attn_scratch_bytes(int batch, int q_heads, int kv_he
     if (batch <= 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads) return 0;
     if (n_splits <= 0) n_splits = pq::choose_splits(batch, q_heads, kv_heads, seq_len, pq::device_sms());
     const int G = q_heads / kv_heads;
-    const size_t groups = (size_t)batch * kv_heads * ((G + pq::kHeadsPerCta - 1) / pq::kHeadsPerCta);
+    const size_t groups = (size_t)batch * kv_heads * pq::head_groups(G);
     const size_t tickets = (groups * sizeof(unsigned int) + 255) & ~size_t(255);
-    return tickets + groups * n_splits * pq::kHeadsPerCta * (head_dim + 2) * sizeof(float);
+    return tickets + groups * n_splits * pq::kRecHeads * (head_dim + 2) * sizeof(float);
 }
 
 extern "C" int pq_decode_attn(const void* q, const void* k_blocks, const void* v_blocks,
@@ -665,7 +809,7 @@ extern "C" int pq_decode_attn(const void* q, const void* k_blocks, const void* v
     p.Hq = q_heads;
     p.Hkv = kv_heads;
     p.G = q_heads / kv_heads;
-    p.HG = (p.G + kHeadsPerCta - 1) / kHeadsPerCta;
+    p.HG = head_groups(p.G);
     p.splits = n_splits;
     p.tiles_per_split = (int)((tiles + n_splits - 1) / n_splits);
     p.jl_dim = qjl ? jl_dim : 0;
@@ -679,9 +823,14 @@ extern "C" int pq_decode_attn(const void* q, const void* k_blocks, const void* v
     p.tickets = static_cast<unsigned int*>(scratch);
     p.records = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + ((groups * sizeof(unsigned int) + 255) & ~size_t(255)));
 
-#define PQ_DEC(DD, KB, VB)                                                                     \
-    if (head_dim == DD && k_bits == KB && v_bits == VB)                                        \
-        return qjl ? launch_decode<DD, KB, VB, true>(p, rows, st) : launch_decode<DD, KB, VB, false>(p, rows, st);
+    const bool wide = heads_per_cta(p.G) == 8;
+#define PQ_DEC(DD, KB, VB)                                                                            \
+    if (head_dim == DD && k_bits == KB && v_bits == VB) {                                             \
+        if (wide) return qjl ? launch_decode<DD, KB, VB, 2, true>(p, rows, st)                        \
+                             : launch_decode<DD, KB, VB, 2, false>(p, rows, st);                      \
+        return qjl ? launch_decode<DD, KB, VB, 1, true>(p, rows, st)                                  \
+                   : launch_decode<DD, KB, VB, 1, false>(p, rows, st);                                \
+    }
     PQ_DEC(64, 4, 4) PQ_DEC(64, 4, 2) PQ_DEC(64, 2, 4) PQ_DEC(64, 2, 2)
     PQ_DEC(128, 4, 4) PQ_DEC(128, 4, 2) PQ_DEC(128, 2, 4) PQ_DEC(128, 2, 2)
 #undef PQ_DEC
