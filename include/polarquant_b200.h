@@ -47,7 +47,9 @@ typedef enum pq_status {
     PQ_ERR_MISALIGNED = 6,       /* a buffer does not have the required alignment      */
     PQ_ERR_SCRATCH_TOO_SMALL = 7,/* scratch_bytes is below pq_decode_attn_scratch_bytes */
     PQ_ERR_CUDA = 8,             /* a CUDA runtime call failed (launch error, …)       */
-    PQ_ERR_TOO_LARGE = 9         /* a size exceeds what the entry point supports       */
+    PQ_ERR_TOO_LARGE = 9,        /* a size exceeds what the entry point supports       */
+    PQ_ERR_STATIC_SCRATCH_EXCEEDED = 10 /* pq_decode_attn_static: the shape needs more scratch
+                                           than the library's built-in array holds           */
 } pq_status;
 
 /* Library version: major*10000 + minor*100 + patch. */
@@ -148,6 +150,43 @@ size_t pq_decode_attn_scratch_bytes(int batch, int q_heads, int kv_heads, int64_
 
 /* The number of splits the library would choose for n_splits == 0 on the current device. */
 int pq_decode_attn_default_splits(int batch, int q_heads, int kv_heads, int64_t seq_len, int head_dim);
+
+/* ---------------------------------------------------------------------------------
+ * pq_decode_attn_static — pq_decode_attn for callers that cannot allocate device memory.
+ *
+ * This entry point has no counterpart in the reference.  It exists for hosts that have
+ * no way to provide the `scratch` buffer of pq_decode_attn: an operator callback inside an
+ * inference runtime that owns all device memory and passes the operator nothing but its
+ * input and output tensors, code that runs while the device allocator is frozen, or a
+ * serving loop that must not risk the device-wide stall of a cudaMalloc.  The split-merge
+ * scratch lives in an array built into the library instead (8 MiB of device memory on
+ * every GPU that loads the library, held until the process exits; its size is returned by
+ * pq_decode_attn_static_scratch_capacity()).
+ *
+ * Arguments and results are those of pq_decode_attn without `scratch`/`scratch_bytes`.
+ * It calls no cudaMalloc/cudaFree and no allocating library routine.
+ *   - A shape whose scratch need (pq_decode_attn_scratch_bytes) exceeds the capacity is
+ *     rejected with PQ_ERR_STATIC_SCRATCH_EXCEEDED; nothing is launched.  Fewer splits
+ *     (`n_splits`) need less scratch.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current).  Make that first call outside any
+ *     stream capture.
+ *   - All calls on a device share the one array, and it keeps the previous call's
+ *     contents; the entry point re-zeroes the part that must start at zero (the ticket
+ *     counters) on `stream` before each launch.  Two calls that overlap on the GPU (other
+ *     streams, other host threads) would race on the array: serialise them, or use
+ *     pq_decode_attn with separate scratch buffers.
+ */
+int pq_decode_attn_static(const void* q, const void* k_blocks, const void* v_blocks,
+                          int batch, int q_heads, int kv_heads, int64_t seq_len, int64_t seq_capacity,
+                          int head_dim, int k_bits, int v_bits,
+                          const float* codebook_k, const float* codebook_v, const float* rot, float scale,
+                          const float* jl_matrix, int jl_dim, const void* qjl_bits, const void* qjl_norms,
+                          void* out, int out_is_fp16, void* partial_out,
+                          int n_splits, void* stream);
+
+/* Bytes of the built-in scratch array pq_decode_attn_static can use. */
+size_t pq_decode_attn_static_scratch_capacity(void);
 
 /* ---------------------------------------------------------------------------------
  * pq_lse_merge — merge per-GPU (m, l, o_rotated) partials of a sequence-sharded decode

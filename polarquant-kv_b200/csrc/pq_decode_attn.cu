@@ -836,3 +836,74 @@ extern "C" int pq_decode_attn(const void* q, const void* k_blocks, const void* v
 #undef PQ_DEC
     return PQ_ERR_BAD_HEAD_DIM;
 }
+
+// ------------------------------------------------------------------ no-allocation variant
+// pq_decode_attn_static: the same decode attention, for hosts that are not allowed to
+// allocate device memory around the call.  Examples: an operator callback of an inference
+// runtime that owns every device buffer and hands the operator only its input and output
+// tensors; code running while a memory pool is frozen; latency-critical serving loops where
+// a cudaMalloc would stall every stream of the device.  Such callers have nowhere to get
+// the split-merge scratch from, so this entry point keeps it inside the library: a
+// file-scope device array of kStaticScratchBytes that every GPU which loads the library
+// carries until the process exits.
+//
+// The array's name is only a host-side handle; its device address is fetched once per
+// device with cudaGetSymbolAddress (with that device current) and that pointer is what the
+// kernel receives.
+namespace pq {
+
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;   // 8 MiB per GPU
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_static_scratch_ptr[kMaxDevices] = {};
+static bool g_static_scratch_ready[kMaxDevices] = {};
+
+// Device address of the static scratch on the current device, or nullptr on failure.
+static void* static_scratch_for_current_device() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    if (!g_static_scratch_ready[dev]) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return nullptr;
+        g_static_scratch_ptr[dev] = ptr;
+        g_static_scratch_ready[dev] = true;
+    }
+    return g_static_scratch_ptr[dev];
+}
+
+}  // namespace pq
+
+extern "C" size_t pq_decode_attn_static_scratch_capacity(void) { return pq::kStaticScratchBytes; }
+
+extern "C" int pq_decode_attn_static(const void* q, const void* k_blocks, const void* v_blocks,
+                                     int batch, int q_heads, int kv_heads, int64_t seq_len, int64_t seq_capacity,
+                                     int head_dim, int k_bits, int v_bits,
+                                     const float* codebook_k, const float* codebook_v, const float* rot, float scale,
+                                     const float* jl_matrix, int jl_dim, const void* qjl_bits, const void* qjl_norms,
+                                     void* out, int out_is_fp16, void* partial_out,
+                                     int n_splits, void* stream) {
+    using namespace pq;
+    if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads || seq_len < 0) return PQ_ERR_BAD_SHAPE;
+    if (head_dim != 64 && head_dim != 128) return PQ_ERR_BAD_HEAD_DIM;
+    if (batch == 0) return PQ_OK;
+    // Fix the split count here so the size check below and the launch agree.
+    const int64_t tiles = (seq_len + kTileTok - 1) / kTileTok;
+    if (n_splits <= 0) n_splits = choose_splits(batch, q_heads, kv_heads, seq_len, device_sms());
+    if (n_splits > tiles) n_splits = tiles > 0 ? (int)tiles : 1;
+    const size_t need = pq_decode_attn_scratch_bytes(batch, q_heads, kv_heads, seq_len, head_dim, n_splits);
+    if (need > kStaticScratchBytes) return PQ_ERR_STATIC_SCRATCH_EXCEEDED;
+    void* scratch = static_scratch_for_current_device();
+    if (!scratch) return PQ_ERR_CUDA;
+    // The array is shared by all calls and keeps whatever the previous call left.  The
+    // only part that must read zero at launch is the ticket counters: clear them on the
+    // caller's stream (an aborted earlier launch could have left a count behind).
+    const size_t groups = (size_t)batch * kv_heads * head_groups(q_heads / kv_heads);
+    const size_t ticket_bytes = (groups * sizeof(unsigned int) + 255) & ~size_t(255);
+    if (seq_len > 0 &&
+        cudaMemsetAsync(scratch, 0, ticket_bytes, static_cast<cudaStream_t>(stream)) != cudaSuccess)
+        return PQ_ERR_CUDA;
+    return pq_decode_attn(q, k_blocks, v_blocks, batch, q_heads, kv_heads, seq_len, seq_capacity, head_dim,
+                          k_bits, v_bits, codebook_k, codebook_v, rot, scale, jl_matrix, jl_dim, qjl_bits,
+                          qjl_norms, out, out_is_fp16, partial_out, n_splits, scratch, kStaticScratchBytes, stream);
+}

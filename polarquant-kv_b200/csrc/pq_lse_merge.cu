@@ -74,6 +74,9 @@ extern "C" const char* pq_strerror(int status) {
         case PQ_ERR_SCRATCH_TOO_SMALL: return "scratch buffer is smaller than pq_decode_attn_scratch_bytes()";
         case PQ_ERR_CUDA: return "a CUDA runtime call failed";
         case PQ_ERR_TOO_LARGE: return "a size exceeds what this entry point supports";
+        case PQ_ERR_STATIC_SCRATCH_EXCEEDED:
+            return "this shape needs more scratch than the library's built-in array holds (8 MiB); "
+                   "use fewer splits or pq_decode_attn with a caller-provided buffer";
         default: return "unknown pq_status";
     }
 }

@@ -28,6 +28,11 @@ SIGNATURES = {
                                c_int, c_int, c_int, c_float_p, c_float_p, c_void_p, c_float,
                                c_void_p, c_int, c_void_p, c_void_p,
                                c_void_p, c_int, c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
+    "pq_decode_attn_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64,
+                                      c_int, c_int, c_int, c_float_p, c_float_p, c_void_p, c_float,
+                                      c_void_p, c_int, c_void_p, c_void_p,
+                                      c_void_p, c_int, c_void_p, c_int, c_void_p]),
+    "pq_decode_attn_static_scratch_capacity": (c_size_t, []),
     "pq_decode_attn_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int64, c_int, c_int]),
     "pq_decode_attn_default_splits": (c_int, [c_int, c_int, c_int, c_int64, c_int]),
     "pq_lse_merge": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p]),
