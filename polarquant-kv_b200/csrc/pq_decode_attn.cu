@@ -91,12 +91,17 @@ __device__ __forceinline__ uint4 lds_v4(uint32_t a) {
     return v;
 }
 __device__ __forceinline__ float lds_half_as_float(uint32_t a) {
-    return __half2float(__ushort_as_half(static_cast<unsigned short>(lds_u16(a))));
+    float v;
+    asm volatile("{ .reg .b16 h; ld.shared.b16 h, [%1]; cvt.f32.f16 %0, h; }\n" : "=f"(v) : "r"(a));
+    return v;
 }
-// byte j of w moved to bits 8..15, everything else zero: the table row offset (byte * 256)
+// The centroid table sits at shared address kTabAddr (a multiple of 64 KB), one 256-byte row
+// per byte value.  `lane_const` = kTabAddr | offset of this lane's copy inside a row (< 256),
+// so byte J of w dropped into bits 8..15 of lane_const IS the address of the entry.
+constexpr uint32_t kTabAddr = 0x10000u;
 template <int J>
-__device__ __forceinline__ uint32_t row_of_byte(uint32_t w) {
-    return __byte_perm(w, 0u, 0x4404u | (J << 4));
+__device__ __forceinline__ uint32_t entry_addr(uint32_t w, uint32_t lane_const) {
+    return __byte_perm(w, lane_const, 0x7604u | (J << 4));
 }
 // 32 bits of packed indices at a shared address whose alignment class is known statically
 template <bool ALIGNED4>
@@ -109,29 +114,23 @@ __device__ __forceinline__ uint32_t lds_word(uint32_t a) {
 // Row r (256 B) belongs to byte value r.  4-bit: entry = {half2(c[r&15], c[r>>4]) hi, same lo},
 // 8 bytes, 16 lane copies.  2-bit: entry = {c[r&3], c[r>>2&3] | c[r>>4&3], c[r>>6] hi; same lo},
 // 16 bytes, 8 lane copies.  `half_off` is 0 for the K copies and 128 for the V copies.
+// `cs` holds the split centroids as bit patterns: cs[i] = hi16(64*c[i]) | lo16 << 16.
 template <int BITS>
-__device__ __forceinline__ void build_table(uint8_t* tab, int half_off, const float* cb, int tid) {
+__device__ __forceinline__ void build_table(uint8_t* tab, int half_off, const uint32_t* cs, int tid) {
     if (BITS == 4) {
         for (int e = tid; e < 256 * 16; e += kDecThreads) {
             const int b = e >> 4, copy = e & 15;
-            __half h0, l0, h1, l1;
-            split_half(cb[b & 15] * kCbScale, h0, l0);
-            split_half(cb[b >> 4] * kCbScale, h1, l1);
-            __half2 hi = __halves2half2(h0, h1), lo = __halves2half2(l0, l1);
+            const uint32_t c0 = cs[b & 15], c1 = cs[b >> 4];
             *reinterpret_cast<uint2*>(tab + b * 256 + half_off + copy * 8) =
-                make_uint2(*reinterpret_cast<uint32_t*>(&hi), *reinterpret_cast<uint32_t*>(&lo));
+                make_uint2(__byte_perm(c0, c1, 0x5410), __byte_perm(c0, c1, 0x7632));
         }
     } else {
         for (int e = tid; e < 256 * 8; e += kDecThreads) {
             const int b = e >> 3, copy = e & 7;
-            __half h[4], l[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) split_half(cb[(b >> (2 * k)) & 3] * kCbScale, h[k], l[k]);
-            __half2 h01 = __halves2half2(h[0], h[1]), h23 = __halves2half2(h[2], h[3]);
-            __half2 l01 = __halves2half2(l[0], l[1]), l23 = __halves2half2(l[2], l[3]);
+            const uint32_t c0 = cs[b & 3], c1 = cs[(b >> 2) & 3], c2 = cs[(b >> 4) & 3], c3 = cs[b >> 6];
             *reinterpret_cast<uint4*>(tab + b * 256 + half_off + copy * 16) =
-                make_uint4(*reinterpret_cast<uint32_t*>(&h01), *reinterpret_cast<uint32_t*>(&h23),
-                           *reinterpret_cast<uint32_t*>(&l01), *reinterpret_cast<uint32_t*>(&l23));
+                make_uint4(__byte_perm(c0, c1, 0x5410), __byte_perm(c2, c3, 0x5410),
+                           __byte_perm(c0, c1, 0x7632), __byte_perm(c2, c3, 0x7632));
         }
     }
 }
@@ -177,12 +176,25 @@ struct DecodeCfg {
         return kStageK + kStageV + (QJL ? stage_bits(jl_dim) + kStageN : 0);
     }
     __host__ __device__ static int qjl_frag_bytes(int jl_dim) { return QJL ? (jl_dim / 16) * 32 * 16 : 0; }
+    // Shared-memory plan (byte addresses in the shared window):
+    //   [base, 64K)        query buffers, split codebooks, the rings of the first n_low warps
+    //   [64K, 128K)        centroid table (its address is baked into the lookups)
+    //   [128K, ...)        sign table, JL query fragments, the rings of the remaining warps
+    // After the main loop the merge area ([16 warps][8][D+2] floats) reuses [64K, ...).
+    __host__ __device__ static int ring_bytes(int jl_dim) { return kStages * stage_bytes_total(jl_dim); }
+    __host__ __device__ static int low_fixed(int jl_dim) {
+        return ((HPC * (3 * D + (QJL ? jl_dim : 0)) * 4 + 2 * 16 * 4) + 15) & ~15;
+    }
+    // rings that fit below the table when the dynamic window starts at or below 8 KB
+    __host__ __device__ static int n_low(int jl_dim) {
+        int n = (65536 - 8192 - low_fixed(jl_dim)) / ring_bytes(jl_dim);
+        return n > kDecWarps ? kDecWarps : n;
+    }
     __host__ __device__ static size_t smem_bytes(int jl_dim) {
-        size_t ring = (size_t)kDecWarps * kStages * stage_bytes_total(jl_dim);
-        size_t work = kTabBytes + kSignTab + qjl_frag_bytes(jl_dim) + ring;
-        size_t merge = (size_t)kDecWarps * kRecHeads * (D + 2) * 4;      // aliases tables + ring
-        size_t qbuf = (size_t)HPC * (3 * D + (QJL ? jl_dim : 0)) * 4;
-        return (work > merge ? work : merge) + qbuf + 64;
+        size_t high = kSignTab + qjl_frag_bytes(jl_dim) + (size_t)(kDecWarps - n_low(jl_dim)) * ring_bytes(jl_dim);
+        size_t merge = (size_t)kDecWarps * kRecHeads * (D + 2) * 4;
+        if (kTabBytes + high < merge) high = merge - kTabBytes;
+        return 2 * 65536 + high + 16;
     }
 };
 
@@ -198,19 +210,19 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
     constexpr int NBLK = C::NBLK;
     constexpr int HPC = C::HPC;
     extern __shared__ __align__(16) uint8_t smem[];
-    // layout: [q buffers][table][sign table][qjl fragments][rings]; the merge area reuses
-    // everything after the q buffers once the main loop is over
-    float* q_in = reinterpret_cast<float*>(smem);                        // [HPC][D] original-space q
+    float* q_in = reinterpret_cast<float*>(smem);                        // [HPC][D] (spare)
     float* q_rot = q_in + HPC * D;                                       // [HPC][D] rotated, scaled
     float* o_fin = q_rot + HPC * D;                                      // [HPC][D] final stage
     float* q_jl = o_fin + HPC * D;                                       // [HPC][M] (QJL)
-    uint8_t* work = reinterpret_cast<uint8_t*>(q_jl + (QJL ? HPC * p.jl_dim : 0));
-    work = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(work) + 15) & ~uintptr_t(15));
-    uint8_t* tab = work;
+    uint32_t* cs_k = reinterpret_cast<uint32_t*>(q_jl + (QJL ? HPC * p.jl_dim : 0));   // split centroids
+    uint32_t* cs_v = cs_k + 16;
+    const uint32_t smem_base = smem_addr(smem);
+    uint8_t* low_ring = smem + C::low_fixed(QJL ? p.jl_dim : 0);
+    uint8_t* tab = smem + (kTabAddr - smem_base);                        // shared address 64K exactly
     uint8_t* signtab = tab + kTabBytes;
     uint8_t* qjl_frag = signtab + C::kSignTab;
-    uint8_t* ring = qjl_frag + C::qjl_frag_bytes(QJL ? p.jl_dim : 0);
-    float* merge = reinterpret_cast<float*>(work);                       // [16 warps][8][D+2]
+    uint8_t* high_ring = qjl_frag + C::qjl_frag_bytes(QJL ? p.jl_dim : 0);
+    float* merge = reinterpret_cast<float*>(tab);                        // [16 warps][8][D+2]
     __shared__ unsigned int s_ticket;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -226,19 +238,47 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
     const int64_t tile_begin = (int64_t)split * p.tiles_per_split;
     const int64_t tile_end = min(tiles_total, tile_begin + p.tiles_per_split);
     const int stage_sz = C::stage_bytes_total(M);
-    uint8_t* my_ring = ring + (size_t)warp * kStages * stage_sz;
+    const int n_low = C::n_low(M);
+    if (smem_base + C::low_fixed(M) + n_low * C::ring_bytes(M) > kTabAddr) return;   // window starts too high
+    uint8_t* my_ring = warp < n_low ? low_ring + (size_t)warp * C::ring_bytes(M)
+                                    : high_ring + (size_t)(warp - n_low) * C::ring_bytes(M);
     const uint8_t* k_row = p.kb + (size_t)row * p.Scap * C::TBK;
     const uint8_t* v_row = p.vb + (size_t)row * p.Scap * C::TBV;
     const uint8_t* bits_row = QJL ? p.qjl_bits + (size_t)row * p.Scap * (M / 8) : nullptr;
     const uint8_t* norm_row = QJL ? reinterpret_cast<const uint8_t*>(p.qjl_norms + (size_t)row * p.Scap) : nullptr;
 
+    // Rows whose byte streams start on a 16-byte boundary take the short path: every full
+    // tile is copied as whole 16-byte chunks at fixed per-lane offsets.
+    const bool k_al = ((reinterpret_cast<uintptr_t>(k_row) & 15) == 0), v_al = ((reinterpret_cast<uintptr_t>(v_row) & 15) == 0);
     auto issue_tile = [&](int64_t tile, int slot) {
         if (tile < tile_end) {
             const int64_t tok0 = tile * kTileTok;
             const int ntok = (int)min((int64_t)kTileTok, p.S - tok0);
             uint8_t* st = my_ring + slot * stage_sz;
-            stage_bytes(st, k_row + tok0 * C::TBK, ntok * C::TBK, lane);
-            stage_bytes(st + C::kStageK, v_row + tok0 * C::TBV, ntok * C::TBV, lane);
+            if (ntok == kTileTok && k_al && v_al) {
+                const uint8_t* ks = k_row + tok0 * C::TBK + lane * 16;
+                const uint8_t* vs = v_row + tok0 * C::TBV + lane * 16;
+                uint8_t* kd = st + lane * 16;
+                uint8_t* vd = st + C::kStageK + lane * 16;
+#pragma unroll
+                for (int c = 0; c < (C::TBK + 31) / 32; ++c)
+                    if (c * 32 + 32 <= C::TBK || lane + c * 32 < C::TBK) cp_async_16(kd + c * 512, ks + c * 512);
+#pragma unroll
+                for (int c = 0; c < (C::TBV + 31) / 32; ++c)
+                    if (c * 32 + 32 <= C::TBV || lane + c * 32 < C::TBV) cp_async_16(vd + c * 512, vs + c * 512);
+            } else {
+                const uint8_t* ksrc = k_row + tok0 * C::TBK;
+                const uint8_t* vsrc = v_row + tok0 * C::TBV;
+                if (ntok < kTileTok) {
+                    // tokens past the end must read as finite numbers (radius 0): clear their bytes
+                    uint8_t* kz = st + (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(ksrc)) & 15u) + ntok * C::TBK;
+                    uint8_t* vz = st + C::kStageK + (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(vsrc)) & 15u) + ntok * C::TBV;
+                    for (int c = lane; c < (kTileTok - ntok) * C::TBK / 4; c += 32) reinterpret_cast<uint32_t*>(kz)[c] = 0u;
+                    for (int c = lane; c < (kTileTok - ntok) * C::TBV / 4; c += 32) reinterpret_cast<uint32_t*>(vz)[c] = 0u;
+                }
+                stage_bytes(st, ksrc, ntok * C::TBK, lane);
+                stage_bytes(st + C::kStageK, vsrc, ntok * C::TBV, lane);
+            }
             if (QJL) {
                 stage_bytes(st + C::kStageK + C::kStageV, bits_row + tok0 * (M / 8),
                             (ntok * (M / 8) + 3) & ~3, lane);
@@ -253,8 +293,12 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
     issue_tile(tile_begin + warp + kDecWarps, 1);
 
     // ---- prologue: tables, query rotation (and JL projection of the query)
-    build_table<KBITS>(tab, 0, p.cbk, tid);
-    build_table<VBITS>(tab, 128, p.cbv, tid);
+    if (tid < 32) {
+        const float c = (tid < 16 ? p.cbk[tid] : p.cbv[tid - 16]) * kCbScale;
+        __half h, l;
+        split_half(c, h, l);
+        cs_k[tid] = (uint32_t)__half_as_ushort(h) | ((uint32_t)__half_as_ushort(l) << 16);   // cs_v = cs_k + 16
+    }
     if (QJL) {
         // sign table: nibble -> 4 halves of +-1; entry 8 bytes, 16 lane copies
         for (int e = tid; e < 16 * 16; e += kDecThreads) {
@@ -265,30 +309,40 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
                 make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&c));
         }
     }
-    for (int e = tid; e < HPC * D; e += kDecThreads) {
-        const int h = e / D, j = e % D;
-        q_in[e] = h < Gp ? __half2float(p.q[((size_t)b * p.Hq + head0 + h) * D + j]) : 0.f;
-    }
     __syncthreads();
-    // q_rot[h][i] = sum_j q[h][j] * R[i][j]; a warp takes matrix rows i = warp, warp+16, ...
-    {
-        constexpr int JP = D / 32;
-        for (int i = warp; i < D + M; i += kDecWarps) {
-            const float* mrow = i < D ? p.rot + (size_t)i * D : p.jl + (size_t)(i - D) * D;
-            float r[JP];
-#pragma unroll
-            for (int k = 0; k < JP; ++k) r[k] = mrow[lane + 32 * k];
-#pragma unroll
-            for (int h = 0; h < HPC; ++h) {
-                float s = 0.f;
-#pragma unroll
-                for (int k = 0; k < JP; ++k) s = fmaf(r[k], q_in[h * D + lane + 32 * k], s);
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                if (lane == 0) {
-                    if (i < D) q_rot[h * D + i] = s * p.scale_log2;
-                    else q_jl[h * M + (i - D)] = s * (QJL ? p.scale_log2 / (float)p.jl_dim : 0.f);
-                }
+    build_table<KBITS>(tab, 0, cs_k, tid);
+    build_table<VBITS>(tab, 128, cs_v, tid);
+    // q_rot[h][i] = sum_j q[h][j] * R[i][j] (and the JL projection P q) on tensor cores: rows =
+    // heads (the float16 query is exact), columns = 8 outputs per warp-step, R split into two
+    // float16 terms of 4096*R on the fly.  Matrix rows are read as 32-byte pieces by 4 lanes.
+    for (int nt = warp; nt < (D + M) / 8; nt += kDecWarps) {
+        const int i = nt * 8 + g;                                        // this lane's output column
+        const float* mrow = i < D ? p.rot + (size_t)i * D : p.jl + (size_t)(i - D) * D;
+        const __half* qrow = p.q + ((size_t)b * p.Hq + head0 + g) * D;   // row g = head g (if it exists)
+        const bool have = g < Gp;
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int ks = 0; ks < D / 16; ++ks) {
+            const float2 r0 = __ldg(reinterpret_cast<const float2*>(mrow + ks * 16 + 2 * t));
+            const float2 r1 = __ldg(reinterpret_cast<const float2*>(mrow + ks * 16 + 8 + 2 * t));
+            const uint32_t a0 = have ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t) : 0u;
+            const uint32_t a2 = have ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
+            const float x0 = r0.x * 4096.f, x1 = r0.y * 4096.f, x2 = r1.x * 4096.f, x3 = r1.y * 4096.f;
+            const __half2 h01 = __floats2half2_rn(x0, x1), h23 = __floats2half2_rn(x2, x3);
+            const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+            mma_16816(c, a0, 0u, a2, 0u, *reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+            mma_16816(c, a0, 0u, a2, 0u, pack_half2(x0 - f01.x, x1 - f01.y), pack_half2(x2 - f23.x, x3 - f23.y));
+        }
+        // C rows g = heads, columns 2t, 2t+1 = outputs nt*8 + 2t, +1
+        if (g < HPC) {
+            const int o0 = nt * 8 + 2 * t;
+            if (o0 < D) {
+                q_rot[g * D + o0] = c[0] * (p.scale_log2 / 4096.f);
+                q_rot[g * D + o0 + 1] = c[1] * (p.scale_log2 / 4096.f);
+            } else {
+                const float sj = QJL ? p.scale_log2 / (4096.f * (float)p.jl_dim) : 0.f;
+                q_jl[g * M + o0 - D] = c[0] * sj;
+                q_jl[g * M + o0 - D + 1] = c[1] * sj;
             }
         }
     }
@@ -340,8 +394,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
     __syncthreads();
 
     // this lane's private table copies (shared-memory byte addresses)
-    const uint32_t tabk_lane = smem_addr(tab) + (KBITS == 4 ? (lane & 15) * 8 : (lane & 7) * 16);
-    const uint32_t tabv_lane = smem_addr(tab) + 128 + (VBITS == 4 ? (lane & 15) * 8 : (lane & 7) * 16);
+    const uint32_t kconst = kTabAddr | (KBITS == 4 ? (lane & 15) * 8 : (lane & 7) * 16);
+    const uint32_t vconst = kTabAddr | (128 + (VBITS == 4 ? (lane & 15) * 8 : (lane & 7) * 16));
     const uint32_t sign_lane = smem_addr(signtab) + (lane & 15) * 8;
     const uint32_t qjl_frag_lane = smem_addr(qjl_frag) + lane * 16;
     const uint32_t ring_addr = smem_addr(my_ring);
@@ -383,16 +437,14 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
                 float c[4] = {0.f, 0.f, 0.f, 0.f};
                 uint32_t ah[2][4], al[2][4];                        // [k-step][a0..a3]
                 if (KBITS == 4) {
-                    constexpr bool A4 = true;
                     const uint32_t off = blk * C::BBK + 2 + 4 * t;
                     const bool al4 = ((blk * C::BBK + 2) & 3) == 0; // tile base and token stride are 4-aligned
                     const uint32_t wa = al4 ? lds_word<true>(tok_a + off) : lds_word<false>(tok_a + off);
                     const uint32_t wb = al4 ? lds_word<true>(tok_b + off) : lds_word<false>(tok_b + off);
-                    (void)A4;
-                    const uint2 a0 = lds_v2(tabk_lane + row_of_byte<0>(wa)), a1 = lds_v2(tabk_lane + row_of_byte<1>(wa));
-                    const uint2 a2 = lds_v2(tabk_lane + row_of_byte<2>(wa)), a3 = lds_v2(tabk_lane + row_of_byte<3>(wa));
-                    const uint2 b0 = lds_v2(tabk_lane + row_of_byte<0>(wb)), b1 = lds_v2(tabk_lane + row_of_byte<1>(wb));
-                    const uint2 b2 = lds_v2(tabk_lane + row_of_byte<2>(wb)), b3 = lds_v2(tabk_lane + row_of_byte<3>(wb));
+                    const uint2 a0 = lds_v2(entry_addr<0>(wa, kconst)), a1 = lds_v2(entry_addr<1>(wa, kconst));
+                    const uint2 a2 = lds_v2(entry_addr<2>(wa, kconst)), a3 = lds_v2(entry_addr<3>(wa, kconst));
+                    const uint2 b0 = lds_v2(entry_addr<0>(wb, kconst)), b1 = lds_v2(entry_addr<1>(wb, kconst));
+                    const uint2 b2 = lds_v2(entry_addr<2>(wb, kconst)), b3 = lds_v2(entry_addr<3>(wb, kconst));
                     ah[0][0] = a0.x; ah[0][1] = b0.x; ah[0][2] = a1.x; ah[0][3] = b1.x;
                     al[0][0] = a0.y; al[0][1] = b0.y; al[0][2] = a1.y; al[0][3] = b1.y;
                     ah[1][0] = a2.x; ah[1][1] = b2.x; ah[1][2] = a3.x; ah[1][3] = b3.x;
@@ -400,8 +452,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
                 } else {
                     const uint32_t off = blk * C::BBK + 2 + 2 * t;
                     const uint32_t ha = lds_u16(tok_a + off), hb = lds_u16(tok_b + off);
-                    const uint4 a0 = lds_v4(tabk_lane + row_of_byte<0>(ha)), a1 = lds_v4(tabk_lane + row_of_byte<1>(ha));
-                    const uint4 b0 = lds_v4(tabk_lane + row_of_byte<0>(hb)), b1 = lds_v4(tabk_lane + row_of_byte<1>(hb));
+                    const uint4 a0 = lds_v4(entry_addr<0>(ha, kconst)), a1 = lds_v4(entry_addr<1>(ha, kconst));
+                    const uint4 b0 = lds_v4(entry_addr<0>(hb, kconst)), b1 = lds_v4(entry_addr<1>(hb, kconst));
                     ah[0][0] = a0.x; ah[0][1] = b0.x; ah[0][2] = a0.y; ah[0][3] = b0.y;
                     al[0][0] = a0.z; al[0][1] = b0.z; al[0][2] = a0.w; al[0][3] = b0.w;
                     ah[1][0] = a1.x; ah[1][1] = b1.x; ah[1][2] = a1.y; ah[1][3] = b1.y;
@@ -510,12 +562,9 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
                 const float y2 = __shfl_sync(0xffffffffu, pr[NH - 1][1], la), y3 = __shfl_sync(0xffffffffu, pr[NH - 1][1], lb);
                 if (g & 1) { x0 = y0; x1 = y1; x2 = y2; x3 = y3; }
             }
-            pv[0] = (2 * t < ntok) ? x0 : 0.f;
-            pv[1] = (2 * t + 1 < ntok) ? x1 : 0.f;
-            pv[2] = (2 * t + 8 < ntok) ? x2 : 0.f;
-            pv[3] = (2 * t + 9 < ntok) ? x3 : 0.f;
+            pv[0] = x0; pv[1] = x1; pv[2] = x2; pv[3] = x3;   // masked tokens: p == 0 and radius == 0
         }
-        const bool lo_col = NH == 1 && (g & 1);
+        const float lo_col = (NH == 1 && (g & 1)) ? 1.f : 0.f;     // odd columns carry the lo term
         const uint32_t vtok = vs_base + (2 * t) * C::TBV;            // tokens 2t, 2t+1, 2t+8, 2t+9
 #pragma unroll
         for (int blk = 0; blk < NBLK; ++blk) {
@@ -523,13 +572,15 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 const uint32_t a = vtok + ((k >> 1) * 8 + (k & 1)) * C::TBV + blk * C::BBV;
-                const float d = lds_half_as_float(a);
-                w[k] = pv[k] != 0.f ? pv[k] * d : 0.f;               // masked tokens may hold stale bytes
+                w[k] = pv[k] * lds_half_as_float(a);
             }
             uint32_t bh0, bh1, bl0 = 0u, bl1 = 0u;
             if (NH == 1) {
-                bh0 = pack_half2(term_of(w[0], lo_col), term_of(w[1], lo_col));
-                bh1 = pack_half2(term_of(w[2], lo_col), term_of(w[3], lo_col));
+                // even column: w itself (rounded to its hi term by the pack); odd column: w - hi
+                const float2 h01 = __half22float2(__floats2half2_rn(w[0], w[1]));
+                const float2 h23 = __half22float2(__floats2half2_rn(w[2], w[3]));
+                bh0 = pack_half2(fmaf(-lo_col, h01.x, w[0]), fmaf(-lo_col, h01.y, w[1]));
+                bh1 = pack_half2(fmaf(-lo_col, h23.x, w[2]), fmaf(-lo_col, h23.y, w[3]));
             } else {
                 bh0 = pack_half2(w[0], w[1]);
                 bh1 = pack_half2(w[2], w[3]);
@@ -546,8 +597,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
                     // byte k of m1: dims 0 / 2, byte k of m2: dims 1 / 3; low nibble token a, high token b
                     const uint32_t m1 = (ha & 0x0F0Fu) | ((hb << 4) & 0xF0F0u);
                     const uint32_t m2 = ((ha >> 4) & 0x0F0Fu) | (hb & 0xF0F0u);
-                    const uint2 e0 = lds_v2(tabv_lane + row_of_byte<0>(m1)), e1 = lds_v2(tabv_lane + row_of_byte<0>(m2));
-                    const uint2 e2 = lds_v2(tabv_lane + row_of_byte<1>(m1)), e3 = lds_v2(tabv_lane + row_of_byte<1>(m2));
+                    const uint2 e0 = lds_v2(entry_addr<0>(m1, vconst)), e1 = lds_v2(entry_addr<0>(m2, vconst));
+                    const uint2 e2 = lds_v2(entry_addr<1>(m1, vconst)), e3 = lds_v2(entry_addr<1>(m2, vconst));
                     ahi[0][pair * 2 + 0] = e0.x; ahi[0][pair * 2 + 1] = e1.x;
                     alo[0][pair * 2 + 0] = e0.y; alo[0][pair * 2 + 1] = e1.y;
                     ahi[1][pair * 2 + 0] = e2.x; ahi[1][pair * 2 + 1] = e3.x;
@@ -557,7 +608,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
                     const uint32_t m1 = (ba & 3u) | ((bb & 3u) << 2) | ((ba & 0xCu) << 2) | ((bb & 0xCu) << 4);
                     const uint32_t ua = ba >> 4, ub = bb >> 4;
                     const uint32_t m2 = (ua & 3u) | ((ub & 3u) << 2) | ((ua & 0xCu) << 2) | ((ub & 0xCu) << 4);
-                    const uint4 e0 = lds_v4(tabv_lane + (m1 << 8)), e1 = lds_v4(tabv_lane + (m2 << 8));
+                    const uint4 e0 = lds_v4(entry_addr<0>(m1, vconst)), e1 = lds_v4(entry_addr<0>(m2, vconst));
                     ahi[0][pair * 2 + 0] = e0.x; ahi[0][pair * 2 + 1] = e0.y;
                     alo[0][pair * 2 + 0] = e0.z; alo[0][pair * 2 + 1] = e0.w;
                     ahi[1][pair * 2 + 0] = e1.x; ahi[1][pair * 2 + 1] = e1.y;
