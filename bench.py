@@ -39,6 +39,7 @@ WORKLOAD = dict(name="llama3-8b-shaped PQ4 decode attention", batch=32, kv_heads
                 head_dim=128, context=8192, k_bits=4, v_bits=4)
 COMPRESS_VECS = 1 << 22        # vectors per compress launch in the secondary measurement
 FALLBACK_HBM_GBS = 6650.0      # used only when MEASURED_PEAKS.json is absent
+DECODE_TRAFFIC_BYTES = 308_857_600   # ncu: 302.39 MB read + 6.46 MB written per launch of the headline workload
 
 
 def algorithmic_bytes(w) -> int:
@@ -268,12 +269,17 @@ def run_ours(args):
         barrier()
         return ms
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()          # nvidia-smi takes a moment to start: begin before the warm-up
     for i in range(max(3, args.warmup)):
         step(i)
         step_e2e(i)
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    torch.cuda.synchronize()
+    t_busy = time.perf_counter()
+    while rank == 0 and time.perf_counter() - t_busy < 0.6:   # keep the GPU loaded until samples arrive
+        step(0)
+        torch.cuda.synchronize()
     ms_total = timed(step, args.steps)
     ms_e2e = timed(step_e2e, args.steps)
     clocks = sampler.stop() if rank == 0 else None
@@ -330,15 +336,9 @@ def run_ours(args):
     except Exception:
         blas_threads = 1
 
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "decode_attn_traffic.json")
-    if os.path.exists(tpath):
-        try:
-            with open(tpath) as f:
-                traffic = json.load(f).get("dram_bytes_per_launch_full_workload")
-        except Exception:
-            traffic = None
-
+    # DRAM bytes per launch from the ncu capture summarised in profiles/decode_attn_c1_ncu.md
+    # (dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload)
+    traffic = DECODE_TRAFFIC_BYTES if w["batch"] == 32 else None
     line = {
         "metric": "PQ4 decode-attn compressed-byte throughput", "value": round(value, 1), "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(ms_step, 5),

@@ -1,0 +1,161 @@
+"""CPU-side checks: the C-ABI library loads and exports every declared symbol; host logic
+(codebook, thresholds, operand splits, parameter validation, shard arithmetic)."""
+
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+from oracle import pq_oracle as O
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "polarquant_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(pq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from polarquant_kv import _ext
+    names = declared_symbols()
+    assert len(names) >= 10
+    handle = ctypes.CDLL(_ext.library_path())
+    for n in names:
+        assert hasattr(handle, n), f"{n} is declared in the header but not exported"
+        assert n in _ext.SIGNATURES, f"{n} has no ctypes signature"
+    lib = _ext.lib()
+    assert lib.pq_version() >= 100
+    assert lib.pq_strerror(0) == b"ok"
+    assert b"head_dim" in lib.pq_strerror(2)
+
+
+def test_argument_validation_without_gpu():
+    """Status codes for bad arguments are decided on the host before anything is launched."""
+    from polarquant_kv import _ext
+    lib = _ext.lib()
+    f = _ext.float_array([0.0] * 16)
+    assert lib.pq_compress(None, -1, 128, 4, None, f, f, None, None, 0, None, None, None) == 4
+    assert lib.pq_compress(None, 8, 96, 4, None, f, f, None, None, 0, None, None, None) == 2
+    assert lib.pq_compress(None, 8, 128, 3, None, f, f, None, None, 0, None, None, None) == 3
+    assert lib.pq_compress(None, 8, 128, 4, None, f, f, None, None, 0, None, None, None) == 1
+    assert lib.pq_compress(None, 0, 128, 4, None, f, f, None, None, 0, None, None, None) == 0
+    assert lib.pq_dequant(None, 4, 128, 5, f, None, None, 0, None) == 3
+    assert lib.pq_lse_merge(None, 0, 4, 128, None, None, 0, None) == 4
+    assert lib.pq_decode_attn_scratch_bytes(32, 32, 8, 8192, 128, 4) == 256 * 4 + 256 * 4 * 8 * 130 * 4
+    assert lib.pq_decode_attn_scratch_bytes(1, 7, 2, 10, 128, 1) == 0     # q heads not a multiple of kv heads
+
+
+def test_package_codebook_matches_oracle_and_reference(golden):
+    from polarquant_kv.codebook import block_codebook, build_lloyd_max_codebook
+    for bits in (2, 4):
+        c, b = build_lloyd_max_codebook(32, bits)
+        assert np.array_equal(c, golden[f"codebook_dim32_b{bits}"])
+        assert np.array_equal(b, golden[f"boundaries_dim32_b{bits}"])
+        assert np.array_equal(block_codebook(bits), c)
+
+
+@pytest.mark.parametrize("bits", [2, 4])
+def test_decision_thresholds_reproduce_argmin(golden, bits):
+    from polarquant_kv.codebook import decision_thresholds
+    c = golden[f"codebook_dim32_b{bits}"]
+    thr = decision_thresholds(c)
+    assert np.all(np.diff(thr) > 0)
+    rng = np.random.default_rng(0)
+    v = rng.uniform(-1, 1, 300000).astype(np.float32)
+    edge = []
+    for t in thr:
+        x = np.float32(t)
+        for _ in range(4):
+            edge.append(x)
+            x = np.nextafter(x, np.float32(np.inf))
+        x = np.float32(t)
+        for _ in range(4):
+            x = np.nextafter(x, np.float32(-np.inf))
+            edge.append(x)
+    tiny = np.float32(10.0) ** np.arange(-45, -5, 0.5)
+    v = np.concatenate([v, np.array(edge, np.float32), c, tiny.astype(np.float32), -tiny.astype(np.float32),
+                        np.array([0.0, -0.0, 1.0, -1.0], np.float32)])
+    want = O.nearest_centroid(v, c)
+    got = (v[:, None] > thr[None, :]).sum(-1).astype(np.uint8)
+    assert np.array_equal(want, got)
+
+
+def test_rotation_api_and_split_accuracy(golden):
+    from polarquant_kv.rotation import ROT_SCALE, generate_rotation_matrix, inverse_rotate, rotate, split_fp16
+    R = generate_rotation_matrix(128, 0)
+    assert np.array_equal(R, golden["R_d128_seed0"])           # same scipy call as the reference
+    assert np.allclose(R.T @ R, np.eye(128), atol=1e-6)
+    with pytest.raises(ValueError):
+        generate_rotation_matrix(0)
+    with pytest.raises(ValueError):
+        generate_rotation_matrix(1.5)
+    assert generate_rotation_matrix(1, 7).shape == (1, 1)
+    v = np.random.default_rng(1).standard_normal((5, 128)).astype(np.float32)
+    assert np.allclose(inverse_rotate(rotate(v, R), R), v, atol=1e-5)
+    s = split_fp16(R, ROT_SCALE).astype(np.float64)
+    back = (s[:, :128] + s[:, 128:]) / ROT_SCALE
+    assert np.abs(back - R).max() < 2.0 ** -22
+
+
+def test_parameter_validation_messages():
+    from polarquant_kv.quantizer import _validate_params
+    for bad in (dict(n_bits=1, group_size=32, d=128), dict(n_bits=9, group_size=32, d=128),
+                dict(n_bits=4, group_size=0, d=128), dict(n_bits=4, group_size=256, d=128),
+                dict(n_bits=3, group_size=32, d=128), dict(n_bits=4, group_size=16, d=128),
+                dict(n_bits=4, group_size=32, d=96)):
+        with pytest.raises(ValueError):
+            _validate_params(**bad)
+    _validate_params(4, 32, 128)
+    _validate_params(2, 32, 64)
+
+
+def test_utils_formulas():
+    from polarquant_kv import utils
+    assert utils.compute_compression_ratio(128, 4, 32, 0) == pytest.approx(128 * 16 / (16 + 512 + 128))
+    assert utils.block_pq4_bits_per_vector(128, 4) == 4 * 144
+    assert utils.block_pq4_compression_ratio(128, 4) == pytest.approx(2048 / 576)
+    assert utils.estimate_memory_bytes(32, 8, 8192, 128, 4) == 32 * 8 * 8192 * 72
+    assert utils.cosine_similarity(np.ones(4), np.ones(4)) == pytest.approx(1.0)
+    assert utils.cosine_similarity(np.zeros(4), np.ones(4)) == 0.0
+
+
+def test_jl_matrix_and_bit_packing(golden):
+    import torch
+    from polarquant_kv import qjl
+    assert np.array_equal(qjl.generate_jl_matrix(128, 128, 1), golden["P_m128_d128_seed1"])
+    with pytest.raises(ValueError):
+        qjl.generate_jl_matrix(0, 8)
+    signs = torch.from_numpy(np.random.default_rng(0).integers(0, 2, (3, 5, 40)).astype(bool))
+    packed = qjl.bit_pack(signs)
+    assert packed.shape == (3, 5, 5)
+    assert np.array_equal(packed.numpy(), O.pack_sign_bits(signs.numpy()))
+    assert torch.equal(qjl.bit_unpack(packed, 40), signs)
+
+
+def test_shard_arithmetic():
+    from polarquant_kv.distributed import batch_shard, sequence_shard
+    for n, w in ((32, 8), (33, 8), (5, 8), (0, 4)):
+        parts = [batch_shard(n, r, w) for r in range(w)]
+        assert parts[0][0] == 0 and parts[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(parts, parts[1:]))
+    for S, w in ((131072, 8), (1000, 3), (17, 4), (0, 2), (16, 8)):
+        parts = [sequence_shard(S, r, w) for r in range(w)]
+        assert parts[0][0] == 0 and parts[-1][1] == S
+        assert all(a[1] == b[0] for a, b in zip(parts, parts[1:]))
+        assert all(a[0] % 16 == 0 or a[0] == S for a in parts)
+    with pytest.raises(ValueError):
+        sequence_shard(10, 3, 2)
+
+
+def test_cuda_only_api_refuses_cpu_tensors():
+    import torch
+    from polarquant_kv import attention, quantizer
+    R = O.rotation_matrix(64, 0)
+    with pytest.raises(TypeError):
+        quantizer.compress(torch.zeros((1, 1, 2, 64), dtype=torch.float16), R)
+    with pytest.raises(TypeError):
+        attention.compressed_attention(torch.zeros((1, 2, 1, 64), dtype=torch.float16), None, None, R)
