@@ -23,11 +23,14 @@
 // per lane so lookups never bank-conflict; a byte is moved into address position with a
 // single byte-permute.
 //
-// Work split: grid = (n_splits, batch*kv_heads, head groups); 16 warps per CTA, one CTA per
-// SM; a warp owns 16-token tiles of its CTA's range, streamed through a private 3-stage
-// cp.async ring.  Each CTA reduces its warps' partials in shared memory and writes one
-// (m, l, o) record per query head; the last CTA of a (row, head group) to arrive (atomic
-// ticket, no spinning) merges all records, normalises, rotates back and resets the ticket.
+// Work split: persistent CTAs, one per SM, 16 warps each.  The 16-token tiles of all
+// (batch, kv head, head group) rows form one sequence that is cut into equal contiguous
+// ranges, one per CTA (n_splits == 0), or every row is cut into n_splits equal segments dealt
+// round-robin (n_splits > 0).  Inside a segment a warp owns every 16th tile, streamed through
+// a private 3-stage cp.async ring.  Per segment the CTA reduces its warps' partials in shared
+// memory and writes one (m, l, o) record per query head; the last segment of a row to
+// finish (atomic ticket, no spinning) merges the row's records, normalises, rotates back
+// and resets the ticket.
 #include "pq_common.cuh"
 
 namespace pq {
@@ -53,8 +56,8 @@ struct DecodeParams {
     float* records;            // scratch: [rows*HG][splits][8][D+2]
     unsigned int* tickets;     // scratch: [rows*HG]
     int64_t S, Scap;
-    int Hq, Hkv, G, HG;
-    int splits, tiles_per_split;
+    int Hq, Hkv, G, HG, n_rows;
+    int splits, tiles_per_split, max_segs;   // splits == 0: balanced contiguous partition
     int jl_dim;
     int out_is_fp16;
     float scale_log2;          // softmax scale * log2(e)
@@ -112,7 +115,7 @@ __device__ __forceinline__ uint32_t lds_word(uint32_t a) {
 
 // ------------------------------------------------------------------ centroid tables
 // Row r (256 B) belongs to byte value r.  4-bit: entry = {half2(c[r&15], c[r>>4]) hi, same lo},
-// 8 bytes, 16 lane copies.  2-bit: entry = {c[r&3], c[r>>2&3] | c[r>>4&3], c[r>>6] hi; same lo},
+// 8 bytes, 16 lane copies.  2-bit: entry = {hi(c[r&3], c[r>>2&3]), lo(same), hi(c[r>>4&3], c[r>>6]), lo(same)},
 // 16 bytes, 8 lane copies.  `half_off` is 0 for the K copies and 128 for the V copies.
 // `cs` holds the split centroids as bit patterns: cs[i] = hi16(64*c[i]) | lo16 << 16.
 template <int BITS>
@@ -129,8 +132,8 @@ __device__ __forceinline__ void build_table(uint8_t* tab, int half_off, const ui
             const int b = e >> 3, copy = e & 7;
             const uint32_t c0 = cs[b & 3], c1 = cs[(b >> 2) & 3], c2 = cs[(b >> 4) & 3], c3 = cs[b >> 6];
             *reinterpret_cast<uint4*>(tab + b * 256 + half_off + copy * 16) =
-                make_uint4(__byte_perm(c0, c1, 0x5410), __byte_perm(c2, c3, 0x5410),
-                           __byte_perm(c0, c1, 0x7632), __byte_perm(c2, c3, 0x7632));
+                make_uint4(__byte_perm(c0, c1, 0x5410), __byte_perm(c0, c1, 0x7632),
+                           __byte_perm(c2, c3, 0x5410), __byte_perm(c2, c3, 0x7632));
         }
     }
 }
@@ -180,8 +183,12 @@ struct DecodeCfg {
     //   [base, 64K)        query buffers, split codebooks, the rings of the first n_low warps
     //   [64K, 128K)        centroid table (its address is baked into the lookups)
     //   [128K, ...)        sign table, JL query fragments, the rings of the remaining warps
-    // After the main loop the merge area ([16 warps][8][D+2] floats) reuses [64K, ...).
-    __host__ __device__ static int ring_bytes(int jl_dim) { return kStages * stage_bytes_total(jl_dim); }
+    // At the end of a work item every warp parks its (m, l, o) record in its own ring.
+    // a warp's ring also holds its (m, l, o) record at the end of an item
+    __host__ __device__ static int ring_bytes(int jl_dim) {
+        const int r = kStages * stage_bytes_total(jl_dim), rec = HPC * (D + 2) * 4;
+        return ((r > rec ? r : rec) + 15) & ~15;
+    }
     __host__ __device__ static int low_fixed(int jl_dim) {
         return ((HPC * (3 * D + (QJL ? jl_dim : 0)) * 4 + 2 * 16 * 4) + 15) & ~15;
     }
@@ -192,8 +199,6 @@ struct DecodeCfg {
     }
     __host__ __device__ static size_t smem_bytes(int jl_dim) {
         size_t high = kSignTab + qjl_frag_bytes(jl_dim) + (size_t)(kDecWarps - n_low(jl_dim)) * ring_bytes(jl_dim);
-        size_t merge = (size_t)kDecWarps * kRecHeads * (D + 2) * 4;
-        if (kTabBytes + high < merge) high = merge - kTabBytes;
         return 2 * 65536 + high + 16;
     }
 };
@@ -222,26 +227,85 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
     uint8_t* signtab = tab + kTabBytes;
     uint8_t* qjl_frag = signtab + C::kSignTab;
     uint8_t* high_ring = qjl_frag + C::qjl_frag_bytes(QJL ? p.jl_dim : 0);
-    float* merge = reinterpret_cast<float*>(tab);                        // [16 warps][8][D+2]
     __shared__ unsigned int s_ticket;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int split = blockIdx.x, row = blockIdx.y, hg = blockIdx.z;
-    const int b = row / p.Hkv, hkv = row % p.Hkv;
-    const int Gp = min(HPC, p.G - hg * HPC);                             // query heads of this CTA
-    const int head0 = hkv * p.G + hg * HPC;                              // first query head
     const int M = QJL ? p.jl_dim : 0;
-
-    // ---- token range of this CTA and of this warp
-    const int64_t tiles_total = (p.S + kTileTok - 1) / kTileTok;
-    const int64_t tile_begin = (int64_t)split * p.tiles_per_split;
-    const int64_t tile_end = min(tiles_total, tile_begin + p.tiles_per_split);
     const int stage_sz = C::stage_bytes_total(M);
     const int n_low = C::n_low(M);
     if (smem_base + C::low_fixed(M) + n_low * C::ring_bytes(M) > kTabAddr) return;   // window starts too high
-    uint8_t* my_ring = warp < n_low ? low_ring + (size_t)warp * C::ring_bytes(M)
-                                    : high_ring + (size_t)(warp - n_low) * C::ring_bytes(M);
+    auto ring_of = [&](int w) -> uint8_t* {
+        return w < n_low ? low_ring + (size_t)w * C::ring_bytes(M) : high_ring + (size_t)(w - n_low) * C::ring_bytes(M);
+    };
+    uint8_t* my_ring = ring_of(warp);
+
+    // ---- once per CTA: the lookup tables (the CTA is persistent and walks over work items)
+    if (tid < 32) {
+        const float c = (tid < 16 ? p.cbk[tid] : p.cbv[tid - 16]) * kCbScale;
+        __half h, l;
+        split_half(c, h, l);
+        cs_k[tid] = (uint32_t)__half_as_ushort(h) | ((uint32_t)__half_as_ushort(l) << 16);   // cs_v = cs_k + 16
+    }
+    if (QJL) {
+        // sign table: nibble -> 4 halves of +-1; entry 8 bytes, 16 lane copies
+        for (int e = tid; e < 16 * 16; e += kDecThreads) {
+            const int nib = e >> 4;
+            __half2 a = __floats2half2_rn((nib & 1) ? 1.f : -1.f, (nib & 2) ? 1.f : -1.f);
+            __half2 c = __floats2half2_rn((nib & 4) ? 1.f : -1.f, (nib & 8) ? 1.f : -1.f);
+            reinterpret_cast<uint2*>(signtab)[e] =
+                make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&c));
+        }
+    }
+    __syncthreads();
+    build_table<KBITS>(tab, 0, cs_k, tid);
+    build_table<VBITS>(tab, 128, cs_v, tid);
+    // this lane's private table copies (shared-memory byte addresses)
+    const uint32_t kconst = kTabAddr | (KBITS == 4 ? (lane & 15) * 8 : (lane & 7) * 16);
+    const uint32_t vconst = kTabAddr | (128 + (VBITS == 4 ? (lane & 15) * 8 : (lane & 7) * 16));
+    const uint32_t sign_lane = smem_addr(signtab) + (lane & 15) * 8;
+    const uint32_t qjl_frag_lane = smem_addr(qjl_frag) + lane * 16;
+    const uint32_t ring_addr = smem_addr(my_ring);
+    const int64_t tiles_total = (p.S + kTileTok - 1) / kTileTok;
+
+    // ---- work distribution.  A "virtual row" is one (batch, kv head, head group); its tiles
+    // are numbered 0..tiles_total-1.  Balanced mode (p.splits == 0): the tiles of all virtual
+    // rows form one sequence that is cut into gridDim.x equal contiguous ranges, one per CTA;
+    // a CTA walks the segments (pieces of rows) inside its range.  Split mode: every row is
+    // cut into p.splits equal segments that are dealt round-robin to the CTAs.
+    const int64_t n_vrows = (int64_t)p.n_rows * p.HG;
+    const int64_t all_tiles = n_vrows * tiles_total;
+    const int64_t n_cta = gridDim.x;
+    int64_t cur = p.splits ? (int64_t)blockIdx.x : (int64_t)blockIdx.x * all_tiles / n_cta;
+    const int64_t cur_end = p.splits ? n_vrows * p.splits : ((int64_t)blockIdx.x + 1) * all_tiles / n_cta;
+    while (cur < cur_end) {
+    int64_t vrow, tile_begin, tile_end;
+    int seg_idx, n_segs;
+    if (p.splits) {
+        vrow = cur / p.splits;
+        seg_idx = (int)(cur % p.splits);
+        n_segs = p.splits;
+        tile_begin = (int64_t)seg_idx * p.tiles_per_split;
+        tile_end = min(tiles_total, tile_begin + p.tiles_per_split);
+        cur += n_cta;
+    } else {
+        vrow = cur / tiles_total;
+        const int64_t row_t0 = vrow * tiles_total, row_t1 = row_t0 + tiles_total;
+        const int64_t seg_end = min(cur_end, row_t1);
+        tile_begin = cur - row_t0;
+        tile_end = seg_end - row_t0;
+        // CTA that owns tile x: largest c with floor(c * all_tiles / n_cta) <= x
+        const int64_t c_first = ((row_t0 + 1) * n_cta + all_tiles - 1) / all_tiles - 1;
+        const int64_t c_last = (row_t1 * n_cta + all_tiles - 1) / all_tiles - 1;
+        seg_idx = (int)((int64_t)blockIdx.x - c_first);
+        n_segs = (int)(c_last - c_first + 1);
+        cur = seg_end;
+    }
+    const int row = (int)(vrow / p.HG), hg = (int)(vrow % p.HG);
+    const int b = row / p.Hkv, hkv = row % p.Hkv;
+    const int Gp = min(HPC, p.G - hg * HPC);                             // query heads of this segment
+    const int head0 = hkv * p.G + hg * HPC;                              // first query head
+
     const uint8_t* k_row = p.kb + (size_t)row * p.Scap * C::TBK;
     const uint8_t* v_row = p.vb + (size_t)row * p.Scap * C::TBV;
     const uint8_t* bits_row = QJL ? p.qjl_bits + (size_t)row * p.Scap * (M / 8) : nullptr;
@@ -292,26 +356,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
     issue_tile(tile_begin + warp, 0);
     issue_tile(tile_begin + warp + kDecWarps, 1);
 
-    // ---- prologue: tables, query rotation (and JL projection of the query)
-    if (tid < 32) {
-        const float c = (tid < 16 ? p.cbk[tid] : p.cbv[tid - 16]) * kCbScale;
-        __half h, l;
-        split_half(c, h, l);
-        cs_k[tid] = (uint32_t)__half_as_ushort(h) | ((uint32_t)__half_as_ushort(l) << 16);   // cs_v = cs_k + 16
-    }
-    if (QJL) {
-        // sign table: nibble -> 4 halves of +-1; entry 8 bytes, 16 lane copies
-        for (int e = tid; e < 16 * 16; e += kDecThreads) {
-            const int nib = e >> 4;
-            __half2 a = __floats2half2_rn((nib & 1) ? 1.f : -1.f, (nib & 2) ? 1.f : -1.f);
-            __half2 c = __floats2half2_rn((nib & 4) ? 1.f : -1.f, (nib & 8) ? 1.f : -1.f);
-            reinterpret_cast<uint2*>(signtab)[e] =
-                make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&c));
-        }
-    }
-    __syncthreads();
-    build_table<KBITS>(tab, 0, cs_k, tid);
-    build_table<VBITS>(tab, 128, cs_v, tid);
+    // ---- per item: query rotation (and JL projection of the query)
     // q_rot[h][i] = sum_j q[h][j] * R[i][j] (and the JL projection P q) on tensor cores: rows =
     // heads (the float16 query is exact), columns = 8 outputs per warp-step, R split into two
     // float16 terms of 4096*R on the fly.  Matrix rows are read as 32-byte pieces by 4 lanes.
@@ -393,25 +438,19 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
     }
     __syncthreads();
 
-    // this lane's private table copies (shared-memory byte addresses)
-    const uint32_t kconst = kTabAddr | (KBITS == 4 ? (lane & 15) * 8 : (lane & 7) * 16);
-    const uint32_t vconst = kTabAddr | (128 + (VBITS == 4 ? (lane & 15) * 8 : (lane & 7) * 16));
-    const uint32_t sign_lane = smem_addr(signtab) + (lane & 15) * 8;
-    const uint32_t qjl_frag_lane = smem_addr(qjl_frag) + lane * 16;
-    const uint32_t ring_addr = smem_addr(my_ring);
-
     // ---- running softmax state.  A lane holds scores of NH heads (NH == 1: head t;
     // NH == 2: heads 2t, 2t+1) for tokens g and g+8 of the tile.
     float m_run[NH], l_run[NH];
 #pragma unroll
     for (int h = 0; h < NH; ++h) { m_run[h] = -INFINITY; l_run[h] = 0.f; }
-    float o_acc[NBLK][2][4];
+    // output accumulators: o_main[block][j][h] = dim 32*block + 4g + j of head (NH == 1: t; else 2t + h)
+    float o_main[NBLK][4][NH];
 #pragma unroll
     for (int blk = 0; blk < NBLK; ++blk)
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt)
+        for (int j = 0; j < 4; ++j)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) o_acc[blk][mt][i] = 0.f;
+            for (int h = 0; h < NH; ++h) o_main[blk][j][h] = 0.f;
 
     int slot = 0;
     for (int64_t tile = tile_begin + warp; tile < tile_end; tile += kDecWarps) {
@@ -425,62 +464,52 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
         const uint32_t vs_base = st + C::kStageK +
                                  (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(v_row + tok0 * C::TBV)) & 15u);
 
-        // ================= scores: MMA rows = tokens (g, g+8), columns = query heads
-        float sc[NH][2];
+        // ================= scores.  One MMA covers 8 tokens: row g carries the hi term of token
+        // grp*8+g and row g+8 its lo term, so one 64-bit table entry {hi, lo} fills the register
+        // pair (a0, a1) or (a2, a3) as loaded.  Columns = query heads.
+        float sc[NH][2];                                            // [head][token group]
 #pragma unroll
         for (int h = 0; h < NH; ++h) { sc[h][0] = 0.f; sc[h][1] = 0.f; }
-        {
-            const uint32_t tok_a = ks_base + g * C::TBK;            // token g
-            const uint32_t tok_b = tok_a + 8 * C::TBK;              // token g + 8
+#pragma unroll
+        for (int grp = 0; grp < 2; ++grp) {
+            const uint32_t tok = ks_base + (grp * 8 + g) * C::TBK;
 #pragma unroll
             for (int blk = 0; blk < NBLK; ++blk) {
                 float c[4] = {0.f, 0.f, 0.f, 0.f};
-                uint32_t ah[2][4], al[2][4];                        // [k-step][a0..a3]
                 if (KBITS == 4) {
                     const uint32_t off = blk * C::BBK + 2 + 4 * t;
                     const bool al4 = ((blk * C::BBK + 2) & 3) == 0; // tile base and token stride are 4-aligned
-                    const uint32_t wa = al4 ? lds_word<true>(tok_a + off) : lds_word<false>(tok_a + off);
-                    const uint32_t wb = al4 ? lds_word<true>(tok_b + off) : lds_word<false>(tok_b + off);
-                    const uint2 a0 = lds_v2(entry_addr<0>(wa, kconst)), a1 = lds_v2(entry_addr<1>(wa, kconst));
-                    const uint2 a2 = lds_v2(entry_addr<2>(wa, kconst)), a3 = lds_v2(entry_addr<3>(wa, kconst));
-                    const uint2 b0 = lds_v2(entry_addr<0>(wb, kconst)), b1 = lds_v2(entry_addr<1>(wb, kconst));
-                    const uint2 b2 = lds_v2(entry_addr<2>(wb, kconst)), b3 = lds_v2(entry_addr<3>(wb, kconst));
-                    ah[0][0] = a0.x; ah[0][1] = b0.x; ah[0][2] = a1.x; ah[0][3] = b1.x;
-                    al[0][0] = a0.y; al[0][1] = b0.y; al[0][2] = a1.y; al[0][3] = b1.y;
-                    ah[1][0] = a2.x; ah[1][1] = b2.x; ah[1][2] = a3.x; ah[1][3] = b3.x;
-                    al[1][0] = a2.y; al[1][1] = b2.y; al[1][2] = a3.y; al[1][3] = b3.y;
+                    const uint32_t w = al4 ? lds_word<true>(tok + off) : lds_word<false>(tok + off);
+                    const uint2 e0 = lds_v2(entry_addr<0>(w, kconst)), e1 = lds_v2(entry_addr<1>(w, kconst));
+                    const uint2 e2 = lds_v2(entry_addr<2>(w, kconst)), e3 = lds_v2(entry_addr<3>(w, kconst));
+                    mma_16816(c, e0.x, e0.y, e1.x, e1.y, qb[blk][0][0], qb[blk][0][1]);
+                    mma_16816(c, e2.x, e2.y, e3.x, e3.y, qb[blk][1][0], qb[blk][1][1]);
+                    if (NH == 2) {
+                        mma_16816(c, e0.x, e0.y, e1.x, e1.y, qb[blk][0][2], qb[blk][0][3]);
+                        mma_16816(c, e2.x, e2.y, e3.x, e3.y, qb[blk][1][2], qb[blk][1][3]);
+                    }
                 } else {
-                    const uint32_t off = blk * C::BBK + 2 + 2 * t;
-                    const uint32_t ha = lds_u16(tok_a + off), hb = lds_u16(tok_b + off);
-                    const uint4 a0 = lds_v4(entry_addr<0>(ha, kconst)), a1 = lds_v4(entry_addr<1>(ha, kconst));
-                    const uint4 b0 = lds_v4(entry_addr<0>(hb, kconst)), b1 = lds_v4(entry_addr<1>(hb, kconst));
-                    ah[0][0] = a0.x; ah[0][1] = b0.x; ah[0][2] = a0.y; ah[0][3] = b0.y;
-                    al[0][0] = a0.z; al[0][1] = b0.z; al[0][2] = a0.w; al[0][3] = b0.w;
-                    ah[1][0] = a1.x; ah[1][1] = b1.x; ah[1][2] = a1.y; ah[1][3] = b1.y;
-                    al[1][0] = a1.z; al[1][1] = b1.z; al[1][2] = a1.w; al[1][3] = b1.w;
+                    const uint32_t h = lds_u16(tok + blk * C::BBK + 2 + 2 * t);
+                    const uint4 e0 = lds_v4(entry_addr<0>(h, kconst)), e1 = lds_v4(entry_addr<1>(h, kconst));
+                    mma_16816(c, e0.x, e0.y, e0.z, e0.w, qb[blk][0][0], qb[blk][0][1]);
+                    mma_16816(c, e1.x, e1.y, e1.z, e1.w, qb[blk][1][0], qb[blk][1][1]);
+                    if (NH == 2) {
+                        mma_16816(c, e0.x, e0.y, e0.z, e0.w, qb[blk][0][2], qb[blk][0][3]);
+                        mma_16816(c, e1.x, e1.y, e1.z, e1.w, qb[blk][1][2], qb[blk][1][3]);
+                    }
                 }
-#pragma unroll
-                for (int ks = 0; ks < 2; ++ks) {
-                    mma_16816(c, ah[ks][0], ah[ks][1], ah[ks][2], ah[ks][3], qb[blk][ks][0], qb[blk][ks][1]);
-                    mma_16816(c, al[ks][0], al[ks][1], al[ks][2], al[ks][3], qb[blk][ks][0], qb[blk][ks][1]);
-                    if (NH == 2)
-                        mma_16816(c, ah[ks][0], ah[ks][1], ah[ks][2], ah[ks][3], qb[blk][ks][2], qb[blk][ks][3]);
-                }
-                const float d0 = lds_half_as_float(tok_a + blk * C::BBK);
-                const float d1 = lds_half_as_float(tok_b + blk * C::BBK);
-                if (NH == 1) {      // columns 2t, 2t+1 = hi and lo term of head t
-                    sc[0][0] = fmaf(d0, c[0] + c[1], sc[0][0]);
-                    sc[0][1] = fmaf(d1, c[2] + c[3], sc[0][1]);
-                } else {            // columns 2t, 2t+1 = heads 2t, 2t+1
-                    sc[0][0] = fmaf(d0, c[0], sc[0][0]);
-                    sc[NH - 1][0] = fmaf(d0, c[1], sc[NH - 1][0]);
-                    sc[0][1] = fmaf(d1, c[2], sc[0][1]);
-                    sc[NH - 1][1] = fmaf(d1, c[3], sc[NH - 1][1]);
+                // rows g / g+8 = hi / lo term of the token; columns 2t, 2t+1
+                const float d = lds_half_as_float(tok + blk * C::BBK);
+                if (NH == 1) {      // columns = hi and lo term of head t
+                    sc[0][grp] = fmaf(d, (c[0] + c[1]) + (c[2] + c[3]), sc[0][grp]);
+                } else {            // columns = heads 2t, 2t+1
+                    sc[0][grp] = fmaf(d, c[0] + c[2], sc[0][grp]);
+                    sc[NH - 1][grp] = fmaf(d, c[1] + c[3], sc[NH - 1][grp]);
                 }
             }
-#pragma unroll
-            for (int h = 0; h < NH; ++h) { sc[h][0] *= (1.0f / kCbScale); sc[h][1] *= (1.0f / kCbScale); }
         }
+#pragma unroll
+        for (int h = 0; h < NH; ++h) { sc[h][0] *= (1.0f / kCbScale); sc[h][1] *= (1.0f / kCbScale); }
 
         if (QJL) {
             // corr[token][head] = sum_i (+-1) * qp[head][i] (qp already scaled by scale*log2e/M)
@@ -537,15 +566,14 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
             m_run[h] = m_new;
             rescale |= alpha[h] != 1.0f;
         }
-        // accumulator columns 2t, 2t+1 belong to this lane's own head(s)
+        // the accumulators belong to this lane's own head(s)
         if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
             for (int blk = 0; blk < NBLK; ++blk)
 #pragma unroll
-                for (int mt = 0; mt < 2; ++mt) {
-                    o_acc[blk][mt][0] *= alpha[0]; o_acc[blk][mt][1] *= alpha[NH - 1];
-                    o_acc[blk][mt][2] *= alpha[0]; o_acc[blk][mt][3] *= alpha[NH - 1];
-                }
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int h = 0; h < NH; ++h) o_main[blk][j][h] *= alpha[h];
         }
 
         // ================= values: O[dim][column] += V^T[dim][token] * (p*d)[token][column]
@@ -587,40 +615,61 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
                 bl0 = pack_half2(term_of(w[0], true), term_of(w[1], true));
                 bl1 = pack_half2(term_of(w[2], true), term_of(w[3], true));
             }
-            // A rows: g <-> dim 4g+2mt, g+8 <-> dim 4g+2mt+1 of the block; k slots = tokens
-            uint32_t ahi[2][4], alo[2][4];
+            float o_tmp[4][4];
 #pragma unroll
-            for (int pair = 0; pair < 2; ++pair) {
-                const uint32_t pa = vtok + pair * 8 * C::TBV + blk * C::BBV + 2;
-                if (VBITS == 4) {
+            for (int j = 0; j < 4; ++j) { o_tmp[j][0] = 0.f; o_tmp[j][1] = 0.f; o_tmp[j][2] = 0.f; o_tmp[j][3] = 0.f; }
+            // One MMA per dim j of this lane's 4 dims: row g carries the hi term of dim 4g+j,
+            // row g+8 its lo term; k slots = tokens (2t, 2t+1 | 8+2t, 9+2t).  A table entry
+            // {hi, lo} of a (token a, token b) nibble pair fills (a0, a1) / (a2, a3) as loaded.
+            if (VBITS == 4) {
+                uint32_t m1[2], m2[2];
+#pragma unroll
+                for (int pair = 0; pair < 2; ++pair) {
+                    const uint32_t pa = vtok + pair * 8 * C::TBV + blk * C::BBV + 2;
                     const uint32_t ha = lds_u16(pa + 2 * g), hb = lds_u16(pa + C::TBV + 2 * g);
-                    // byte k of m1: dims 0 / 2, byte k of m2: dims 1 / 3; low nibble token a, high token b
-                    const uint32_t m1 = (ha & 0x0F0Fu) | ((hb << 4) & 0xF0F0u);
-                    const uint32_t m2 = ((ha >> 4) & 0x0F0Fu) | (hb & 0xF0F0u);
-                    const uint2 e0 = lds_v2(entry_addr<0>(m1, vconst)), e1 = lds_v2(entry_addr<0>(m2, vconst));
-                    const uint2 e2 = lds_v2(entry_addr<1>(m1, vconst)), e3 = lds_v2(entry_addr<1>(m2, vconst));
-                    ahi[0][pair * 2 + 0] = e0.x; ahi[0][pair * 2 + 1] = e1.x;
-                    alo[0][pair * 2 + 0] = e0.y; alo[0][pair * 2 + 1] = e1.y;
-                    ahi[1][pair * 2 + 0] = e2.x; ahi[1][pair * 2 + 1] = e3.x;
-                    alo[1][pair * 2 + 0] = e2.y; alo[1][pair * 2 + 1] = e3.y;
-                } else {
+                    // byte k of m1: dims 0 / 2, of m2: dims 1 / 3; low nibble token a, high nibble token b
+                    m1[pair] = (ha & 0x0F0Fu) | ((hb << 4) & 0xF0F0u);
+                    m2[pair] = ((ha >> 4) & 0x0F0Fu) | (hb & 0xF0F0u);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t s0 = (j & 1) ? m2[0] : m1[0], s1 = (j & 1) ? m2[1] : m1[1];
+                    const uint2 e0 = (j >> 1) ? lds_v2(entry_addr<1>(s0, vconst)) : lds_v2(entry_addr<0>(s0, vconst));
+                    const uint2 e1 = (j >> 1) ? lds_v2(entry_addr<1>(s1, vconst)) : lds_v2(entry_addr<0>(s1, vconst));
+                    mma_16816(o_tmp[j], e0.x, e0.y, e1.x, e1.y, bh0, bh1);
+                    if (NH == 2) mma_16816(o_tmp[j], e0.x, e0.y, e1.x, e1.y, bl0, bl1);
+                }
+            } else {
+                uint4 e[2][2];      // [pair][dims 0,1 | dims 2,3] = {hi d, lo d, hi d+1, lo d+1}
+#pragma unroll
+                for (int pair = 0; pair < 2; ++pair) {
+                    const uint32_t pa = vtok + pair * 8 * C::TBV + blk * C::BBV + 2;
                     const uint32_t ba = lds_u8(pa + g), bb = lds_u8(pa + C::TBV + g);
                     const uint32_t m1 = (ba & 3u) | ((bb & 3u) << 2) | ((ba & 0xCu) << 2) | ((bb & 0xCu) << 4);
                     const uint32_t ua = ba >> 4, ub = bb >> 4;
                     const uint32_t m2 = (ua & 3u) | ((ub & 3u) << 2) | ((ua & 0xCu) << 2) | ((ub & 0xCu) << 4);
-                    const uint4 e0 = lds_v4(entry_addr<0>(m1, vconst)), e1 = lds_v4(entry_addr<0>(m2, vconst));
-                    ahi[0][pair * 2 + 0] = e0.x; ahi[0][pair * 2 + 1] = e0.y;
-                    alo[0][pair * 2 + 0] = e0.z; alo[0][pair * 2 + 1] = e0.w;
-                    ahi[1][pair * 2 + 0] = e1.x; ahi[1][pair * 2 + 1] = e1.y;
-                    alo[1][pair * 2 + 0] = e1.z; alo[1][pair * 2 + 1] = e1.w;
+                    e[pair][0] = lds_v4(entry_addr<0>(m1, vconst));
+                    e[pair][1] = lds_v4(entry_addr<0>(m2, vconst));
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint4 x = e[0][j >> 1], y = e[1][j >> 1];
+                    const uint32_t a0 = (j & 1) ? x.z : x.x, a1 = (j & 1) ? x.w : x.y;
+                    const uint32_t a2 = (j & 1) ? y.z : y.x, a3 = (j & 1) ? y.w : y.y;
+                    mma_16816(o_tmp[j], a0, a1, a2, a3, bh0, bh1);
+                    if (NH == 2) mma_16816(o_tmp[j], a0, a1, a2, a3, bl0, bl1);
                 }
             }
+            // fold: rows g / g+8 are the hi / lo term of the dim; columns 2t, 2t+1 are the hi / lo
+            // term of head t's weights (NH == 1) or heads 2t, 2t+1 (NH == 2)
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
-                mma_16816(o_acc[blk][mt], ahi[mt][0], ahi[mt][1], ahi[mt][2], ahi[mt][3], bh0, bh1);
-                mma_16816(o_acc[blk][mt], alo[mt][0], alo[mt][1], alo[mt][2], alo[mt][3], bh0, bh1);
-                if (NH == 2)
-                    mma_16816(o_acc[blk][mt], ahi[mt][0], ahi[mt][1], ahi[mt][2], ahi[mt][3], bl0, bl1);
+            for (int j = 0; j < 4; ++j) {
+                if (NH == 1) {
+                    o_main[blk][j][0] += (o_tmp[j][0] + o_tmp[j][1]) + (o_tmp[j][2] + o_tmp[j][3]);
+                } else {
+                    o_main[blk][j][0] += o_tmp[j][0] + o_tmp[j][2];
+                    o_main[blk][j][NH - 1] += o_tmp[j][1] + o_tmp[j][3];
+                }
             }
         }
         __syncwarp();
@@ -635,11 +684,11 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 8);
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 16);
     }
-    __syncthreads();   // tables and rings are dead: the merge area takes their place
+    __syncwarp();
 
-    // per-warp record: merge[warp][head][0] = m, [1] = l, [2 + dim] = o
+    // per-warp record in the warp's own (now idle) ring: [head][0] = m, [1] = l, [2 + dim] = o
     {
-        float* rec = merge + (size_t)warp * kRecHeads * (D + 2);
+        float* rec = reinterpret_cast<float*>(my_ring);
         if (g == 0) {
 #pragma unroll
             for (int h = 0; h < NH; ++h) {
@@ -651,40 +700,36 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
 #pragma unroll
         for (int blk = 0; blk < NBLK; ++blk)
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
-                const int dim = blk * 32 + 4 * g + 2 * mt;
-                const float* o = o_acc[blk][mt];
-                if (NH == 1) {     // columns 2t, 2t+1 are the hi and lo parts of head t
-                    rec[t * (D + 2) + 2 + dim] = (o[0] + o[1]) * (1.0f / kCbScale);
-                    rec[t * (D + 2) + 2 + dim + 1] = (o[2] + o[3]) * (1.0f / kCbScale);
+            for (int j = 0; j < 4; ++j) {
+                const int dim = blk * 32 + 4 * g + j;
+                if (NH == 1) {
+                    rec[t * (D + 2) + 2 + dim] = o_main[blk][j][0] * (1.0f / kCbScale);
                 } else {
-                    rec[(2 * t) * (D + 2) + 2 + dim] = o[0] * (1.0f / kCbScale);
-                    rec[(2 * t + 1) * (D + 2) + 2 + dim] = o[1] * (1.0f / kCbScale);
-                    rec[(2 * t) * (D + 2) + 2 + dim + 1] = o[2] * (1.0f / kCbScale);
-                    rec[(2 * t + 1) * (D + 2) + 2 + dim + 1] = o[3] * (1.0f / kCbScale);
+                    rec[(2 * t) * (D + 2) + 2 + dim] = o_main[blk][j][0] * (1.0f / kCbScale);
+                    rec[(2 * t + 1) * (D + 2) + 2 + dim] = o_main[blk][j][NH - 1] * (1.0f / kCbScale);
                 }
             }
     }
     __syncthreads();
 
-    // ---- CTA record = merge of the warp records
-    const size_t group = (size_t)row * p.HG + hg;
-    float* cta_rec = p.records + (group * p.splits + split) * kRecHeads * (D + 2);
+    // ---- item record = merge of the warp records
+    const size_t group = (size_t)vrow;
+    float* cta_rec = p.records + (group * p.max_segs + seg_idx) * kRecHeads * (D + 2);
     for (int e = tid; e < HPC * (D + 2); e += kDecThreads) {
         const int head = e / (D + 2), col = e % (D + 2);
         float mx = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < kDecWarps; ++w) mx = fmaxf(mx, merge[(w * kRecHeads + head) * (D + 2)]);
+        for (int w = 0; w < kDecWarps; ++w)
+            mx = fmaxf(mx, reinterpret_cast<const float*>(ring_of(w))[head * (D + 2)]);
         float val;
         if (col == 0) {
             val = mx;
         } else {
             val = 0.f;
-#pragma unroll
             for (int w = 0; w < kDecWarps; ++w) {
-                const float mw = merge[(w * kRecHeads + head) * (D + 2)];
+                const float* r = reinterpret_cast<const float*>(ring_of(w)) + head * (D + 2);
+                const float mw = r[0];
                 const float s = (mw == -INFINITY) ? 0.f : fast_exp2(mw - mx);
-                val = fmaf(s, merge[(w * kRecHeads + head) * (D + 2) + col], val);
+                val = fmaf(s, r[col], val);
             }
         }
         __stcg(cta_rec + e, val);
@@ -693,47 +738,52 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
     __syncthreads();
     if (tid == 0) s_ticket = atomicAdd(p.tickets + group, 1u);
     __syncthreads();
-    if (s_ticket != (unsigned)(p.splits - 1)) return;
-    __threadfence();
-
-    // ---- last CTA of this (row, head group): merge the split records
-    const float* recs = p.records + group * p.splits * kRecHeads * (D + 2);
-    for (int e = tid; e < HPC * D; e += kDecThreads) {
-        const int head = e / D, dim = e % D;
-        float mx = -INFINITY;
-        for (int s = 0; s < p.splits; ++s) mx = fmaxf(mx, __ldcg(recs + (s * kRecHeads + head) * (D + 2)));
-        float l = 0.f, o = 0.f;
-        for (int s = 0; s < p.splits; ++s) {
-            const float* r = recs + (s * kRecHeads + head) * (D + 2);
-            const float ms = __ldcg(r);
-            const float sc = (ms == -INFINITY) ? 0.f : fast_exp2(ms - mx);
-            l = fmaf(sc, __ldcg(r + 1), l);
-            o = fmaf(sc, __ldcg(r + 2 + dim), o);
-        }
-        if (p.partial_out) {
-            if (head < Gp) {
-                float* dst = p.partial_out + ((size_t)b * p.Hq + head0 + head) * (D + 2);
-                dst[2 + dim] = o;
-                if (dim == 0) { dst[0] = mx; dst[1] = l; }
+    if (s_ticket == (unsigned)(n_segs - 1)) {
+        // ---- last segment of this virtual row to finish: merge the segment records
+        __threadfence();
+        const float* recs = p.records + group * p.max_segs * kRecHeads * (D + 2);
+        for (int e = tid; e < HPC * D; e += kDecThreads) {
+            const int head = e / D, dim = e % D;
+            float mx = -INFINITY;
+            for (int s = 0; s < n_segs; ++s) mx = fmaxf(mx, __ldcg(recs + (s * kRecHeads + head) * (D + 2)));
+            float l = 0.f, o = 0.f;
+            for (int s = 0; s < n_segs; ++s) {
+                const float* r = recs + (s * kRecHeads + head) * (D + 2);
+                const float ms = __ldcg(r);
+                const float sc = (ms == -INFINITY) ? 0.f : fast_exp2(ms - mx);
+                l = fmaf(sc, __ldcg(r + 1), l);
+                o = fmaf(sc, __ldcg(r + 2 + dim), o);
             }
-        } else {
-            o_fin[e] = l > 0.f ? o / l : 0.f;
+            if (p.partial_out) {
+                if (head < Gp) {
+                    float* dst = p.partial_out + ((size_t)b * p.Hq + head0 + head) * (D + 2);
+                    dst[2 + dim] = o;
+                    if (dim == 0) { dst[0] = mx; dst[1] = l; }
+                }
+            } else {
+                o_fin[e] = l > 0.f ? o / l : 0.f;
+            }
+        }
+        if (tid == 0) p.tickets[group] = 0;   // ready for the next call on this stream
+        if (!p.partial_out) {
+            __syncthreads();
+            // out[head][i] = sum_j o_fin[head][j] * R[j][i]
+            for (int e = tid; e < HPC * D; e += kDecThreads) {
+                const int head = e / D, i = e % D;
+                if (head >= Gp) continue;
+                float acc = 0.f;
+#pragma unroll 8
+                for (int j = 0; j < D; ++j) acc = fmaf(o_fin[head * D + j], __ldg(p.rot + (size_t)j * D + i), acc);
+                const size_t off = ((size_t)b * p.Hq + head0 + head) * D + i;
+                if (p.out_is_fp16)
+                    static_cast<__half*>(p.out)[off] = __float2half_rn(fminf(fmaxf(acc, -65504.f), 65504.f));
+                else
+                    static_cast<float*>(p.out)[off] = acc;
+            }
         }
     }
-    if (tid == 0) p.tickets[group] = 0;   // ready for the next call on this stream
-    if (p.partial_out) return;
-    __syncthreads();
-    // out[head][i] = sum_j o_fin[head][j] * R[j][i]
-    for (int e = tid; e < HPC * D; e += kDecThreads) {
-        const int head = e / D, i = e % D;
-        if (head >= Gp) continue;
-        float acc = 0.f;
-#pragma unroll 8
-        for (int j = 0; j < D; ++j) acc = fmaf(o_fin[head * D + j], __ldg(p.rot + (size_t)j * D + i), acc);
-        const size_t off = ((size_t)b * p.Hq + head0 + head) * D + i;
-        if (p.out_is_fp16) static_cast<__half*>(p.out)[off] = __float2half_rn(fminf(fmaxf(acc, -65504.f), 65504.f));
-        else static_cast<float*>(p.out)[off] = acc;
-    }
+    __syncthreads();   // the next segment reuses the rings and the query buffers
+    }   // segments
 }
 
 // ------------------------------------------------------------------ host side
@@ -749,8 +799,19 @@ static int heads_per_cta(int G) { return G <= 4 ? 4 : 8; }
 
 static int head_groups(int G) { const int h = heads_per_cta(G); return (G + h - 1) / h; }
 
-// One CTA per SM: pick the split count whose CTA total fills whole waves best, with at
-// least two tiles per warp and no more than 64 splits.
+// Balanced mode: number of persistent CTAs and the largest number of segments a row can have.
+static void balanced_plan(int64_t n_vrows, int64_t tiles_per_row, int sms, int* n_cta, int* max_segs) {
+    if (sms <= 0) sms = 148;
+    const int64_t all_tiles = n_vrows * tiles_per_row;
+    int64_t n = all_tiles < sms ? all_tiles : sms;
+    if (n < 1) n = 1;
+    const int64_t per = all_tiles / n > 0 ? all_tiles / n : 1;
+    *n_cta = (int)n;
+    *max_segs = (int)(tiles_per_row / per + 2);
+}
+
+// Split count offered to callers that want the static scheme: enough segments to fill the
+// SMs in whole waves, at least two tiles per warp, at most 64.
 static int choose_splits(int batch, int q_heads, int kv_heads, int64_t seq_len, int sms) {
     if (sms <= 0) sms = 148;
     const int G = q_heads / kv_heads;
@@ -777,7 +838,16 @@ static int launch_decode(const DecodeParams& p, int rows, cudaStream_t st) {
     auto kern = pq_decode_attn_kernel<D, KBITS, VBITS, NH, QJL>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return PQ_ERR_CUDA;
-    dim3 grid(p.splits, rows, p.HG);
+    int sms = device_sms();
+    if (sms <= 0) sms = 148;
+    int grid;
+    if (p.splits) {
+        const int64_t n_items = (int64_t)p.splits * rows * p.HG;
+        grid = (int)(n_items < sms ? n_items : sms);             // persistent: one CTA per SM
+    } else {
+        int ms = 0;
+        balanced_plan((int64_t)rows * p.HG, (p.S + kTileTok - 1) / kTileTok, sms, &grid, &ms);
+    }
     kern<<<grid, kDecThreads, smem, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? PQ_OK : PQ_ERR_CUDA;
 }
@@ -793,11 +863,15 @@ extern "C" int pq_decode_attn_default_splits(int batch, int q_heads, int kv_head
 extern "C" size_t pq_decode_attn_scratch_bytes(int batch, int q_heads, int kv_heads, int64_t seq_len,
                                                int head_dim, int n_splits) {
     if (batch <= 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads) return 0;
-    if (n_splits <= 0) n_splits = pq::choose_splits(batch, q_heads, kv_heads, seq_len, pq::device_sms());
     const int G = q_heads / kv_heads;
     const size_t groups = (size_t)batch * kv_heads * pq::head_groups(G);
+    int segs = n_splits;
+    if (n_splits <= 0) {
+        int n_cta = 0;
+        pq::balanced_plan((int64_t)groups, (seq_len + pq::kTileTok - 1) / pq::kTileTok, pq::device_sms(), &n_cta, &segs);
+    }
     const size_t tickets = (groups * sizeof(unsigned int) + 255) & ~size_t(255);
-    return tickets + groups * n_splits * pq::kRecHeads * (head_dim + 2) * sizeof(float);
+    return tickets + groups * segs * pq::kRecHeads * (head_dim + 2) * sizeof(float);
 }
 
 extern "C" int pq_decode_attn(const void* q, const void* k_blocks, const void* v_blocks,
@@ -838,12 +912,11 @@ extern "C" int pq_decode_attn(const void* q, const void* k_blocks, const void* v
         (reinterpret_cast<uintptr_t>(scratch) & 255) || (reinterpret_cast<uintptr_t>(rot) & 15))
         return PQ_ERR_MISALIGNED;
     const int64_t tiles = (seq_len + kTileTok - 1) / kTileTok;
-    if (n_splits <= 0) n_splits = choose_splits(batch, q_heads, kv_heads, seq_len, device_sms());
+    if (n_splits < 0) n_splits = 0;
     if (n_splits > tiles) n_splits = (int)tiles;
     if (scratch_bytes < pq_decode_attn_scratch_bytes(batch, q_heads, kv_heads, seq_len, head_dim, n_splits))
         return PQ_ERR_SCRATCH_TOO_SMALL;
     const int rows = batch * kv_heads;
-    if (rows > 65535) return PQ_ERR_TOO_LARGE;
 
     DecodeParams p{};
     p.q = static_cast<const __half*>(q);
@@ -859,10 +932,17 @@ extern "C" int pq_decode_attn(const void* q, const void* k_blocks, const void* v
     p.Scap = seq_capacity;
     p.Hq = q_heads;
     p.Hkv = kv_heads;
+    p.n_rows = rows;
     p.G = q_heads / kv_heads;
     p.HG = head_groups(p.G);
     p.splits = n_splits;
-    p.tiles_per_split = (int)((tiles + n_splits - 1) / n_splits);
+    p.tiles_per_split = n_splits ? (int)((tiles + n_splits - 1) / n_splits) : 0;
+    if (n_splits) {
+        p.max_segs = n_splits;
+    } else {
+        int n_cta = 0;
+        balanced_plan((int64_t)rows * p.HG, tiles, device_sms(), &n_cta, &p.max_segs);
+    }
     p.jl_dim = qjl ? jl_dim : 0;
     p.out_is_fp16 = out_is_fp16;
     p.scale_log2 = scale * 1.4426950408889634f;
@@ -940,8 +1020,8 @@ extern "C" int pq_decode_attn_static(const void* q, const void* k_blocks, const 
     if (batch == 0) return PQ_OK;
     // Fix the split count here so the size check below and the launch agree.
     const int64_t tiles = (seq_len + kTileTok - 1) / kTileTok;
-    if (n_splits <= 0) n_splits = choose_splits(batch, q_heads, kv_heads, seq_len, device_sms());
-    if (n_splits > tiles) n_splits = tiles > 0 ? (int)tiles : 1;
+    if (n_splits < 0) n_splits = 0;
+    if (n_splits > tiles) n_splits = (int)tiles;
     const size_t need = pq_decode_attn_scratch_bytes(batch, q_heads, kv_heads, seq_len, head_dim, n_splits);
     if (need > kStaticScratchBytes) return PQ_ERR_STATIC_SCRATCH_EXCEEDED;
     void* scratch = static_scratch_for_current_device();

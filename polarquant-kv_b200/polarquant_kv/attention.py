@@ -80,8 +80,7 @@ def decode_attention(query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, pl
     use_qjl = bool(enable_qjl and plan.jl is not None and bits_t is not None)
     q = query.to(torch.float16).contiguous()
     lib = _ext.lib()
-    if n_splits <= 0:
-        n_splits = lib.pq_decode_attn_default_splits(B, Hq, Hkv, S, D)
+    n_splits = max(0, int(n_splits))     # 0: the library balances the work itself
     need = lib.pq_decode_attn_scratch_bytes(B, Hq, Hkv, S, D, n_splits)
     scratch = _scratch(dev, need)
     if partial:
