@@ -18,6 +18,9 @@
 // QJL (qjl.py:25-35, compress_kernel.py:168-175): the residual e = xr - d*c[idx] stays in
 // rotated space; signs of P e equal signs of (P R^T) e_rot, evaluated as a second
 // three-term float16 contraction (e_hi*P_hi + e_hi*P_lo + e_lo*P_hi).
+#include <cmath>
+#include <cstring>
+
 #include "pq_common.cuh"
 
 namespace pq {
@@ -34,8 +37,11 @@ struct CompressParams {
     __half* qjl_norm_out;
     int64_t n_vec;
     int jl_dim;
-    float thr[15];
     float cb[16];
+    // Index search table: a normalised coordinate y falls into bucket k = round(64 y) + 64;
+    // index = base[k] + (y > t[k]).  A bucket holds at most one decision threshold.
+    float bucket_t[132];
+    uint32_t bucket_base[132];
 };
 
 template <int D>
@@ -65,6 +71,9 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
     float* enorm2 = escale + kTileVecs;                                     // [128][2]
     uint8_t* bits_s = reinterpret_cast<uint8_t*>(enorm2 + 2 * kTileVecs);   // [128][M/8]
     float* cb_s = reinterpret_cast<float*>(bits_s + (QJL ? kTileVecs * (p.jl_dim / 8) : 0));  // [16]
+    uint2* bucket_s = reinterpret_cast<uint2*>(cb_s + 16);                  // [256] {threshold bits, base}
+    // second vector tile for prefetching (not with QJL: the residual tiles take the room)
+    __half* Xs2 = reinterpret_cast<__half*>(bucket_s + 256);                // [128][XS]
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -86,25 +95,44 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
         }
         if (tid < 16) cb_s[tid] = p.cb[tid < NLEV ? tid : 0];
     }
+    {
+        const int k = tid < 132 ? tid : 131;      // buckets past 128 only see out-of-range garbage
+        bucket_s[tid] = make_uint2(__float_as_uint(p.bucket_t[k]), p.bucket_base[k]);
+    }
     cp_async_commit();
 
     const int64_t n_tiles = (p.n_vec + kTileVecs - 1) / kTileVecs;
-    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    auto load_tile = [&](int64_t tile, __half* dst) {
         const int64_t v0 = tile * kTileVecs;
         const int n_valid = (int)min((int64_t)kTileVecs, p.n_vec - v0);
-
-        // ---- load the vector tile (zero rows past the end)
         for (int c = tid; c < kTileVecs * (D / 8); c += kCompressThreads) {
             int row = c / (D / 8), col = (c % (D / 8)) * 8;
             if (row < n_valid) {
-                cp_async_16(Xs + row * XS + col, p.x + (v0 + row) * D + col);
+                cp_async_16(dst + row * XS + col, p.x + (v0 + row) * D + col);
             } else {
-                *reinterpret_cast<uint4*>(Xs + row * XS + col) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(dst + row * XS + col) = make_uint4(0, 0, 0, 0);   // rows past the end
             }
         }
-        cp_async_commit();
-        cp_async_wait<0>();
+    };
+    __half* Xcur = Xs;
+    __half* Xnext = QJL ? Xs : Xs2;
+    if (!QJL && (int64_t)blockIdx.x < n_tiles) load_tile(blockIdx.x, Xcur);
+    cp_async_commit();
+    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const int64_t v0 = tile * kTileVecs;
+        const int n_valid = (int)min((int64_t)kTileVecs, p.n_vec - v0);
+        if (QJL) {
+            load_tile(tile, Xcur);
+            cp_async_commit();
+            cp_async_wait<0>();
+        } else {
+            // this tile was requested one iteration ago; request the next one into the other buffer
+            if (tile + gridDim.x < n_tiles) load_tile(tile + gridDim.x, Xnext);
+            cp_async_commit();
+            cp_async_wait<1>();
+        }
         __syncthreads();
+        __half* const Xs = Xcur;   // the tile this iteration works on
 
         if (QJL) {
             // power-of-two scale per vector so the residual split stays in float16 range:
@@ -140,31 +168,38 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
 
-#pragma unroll 2
-        for (int ks = 0; ks < D / 16; ++ks) {
-            uint32_t a[2][4];
+        // The tensor core truncates when it aligns addends to the running sum, so a long
+        // in-MMA accumulation chain drifts by several ulp.  Two k-steps (hi and lo terms) are
+        // summed from zero inside the tensor core and then added to the running sum with a
+        // round-to-nearest float32 add.
+#pragma unroll 1
+        for (int kp = 0; kp < D / 32; ++kp) {
+            uint32_t a[2][2][4];
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt)
-                ldmatrix_x4(a[mt][0], a[mt][1], a[mt][2], a[mt][3],
-                            Xs + (wm * 32 + mt * 16 + (lane & 15)) * XS + ks * 16 + (lane >> 4) * 8);
+            for (int k2 = 0; k2 < 2; ++k2)
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt)
+                    ldmatrix_x4(a[k2][mt][0], a[k2][mt][1], a[k2][mt][2], a[k2][mt][3],
+                                Xs + (wm * 32 + mt * 16 + (lane & 15)) * XS + (kp * 2 + k2) * 16 + (lane >> 4) * 8);
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                uint32_t b0, b1, b2, b3;
-                int j = lane >> 3;
-                ldmatrix_x4(b0, b1, b2, b3,
-                            Rs + (wn * (D / 2) + nt * 8 + (lane & 7)) * RS + ks * 16 + (j & 1) * 8 + (j >> 1) * D);
-                // The tensor core truncates when it aligns addends to the running sum, so a
-                // long in-MMA accumulation chain drifts by several ulp.  Each k-step is
-                // therefore summed from zero (hi then lo term) and added to the running sum
-                // with a round-to-nearest float32 add.
+                float part[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-                for (int mt = 0; mt < 2; ++mt) {
-                    float part[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma_16816(part, a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
-                    mma_16816(part, a[mt][0], a[mt][1], a[mt][2], a[mt][3], b2, b3);
+                for (int k2 = 0; k2 < 2; ++k2) {
+                    uint32_t b0, b1, b2, b3;
+                    const int j = lane >> 3;
+                    ldmatrix_x4(b0, b1, b2, b3,
+                                Rs + (wn * (D / 2) + nt * 8 + (lane & 7)) * RS + (kp * 2 + k2) * 16 + (j & 1) * 8 + (j >> 1) * D);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[mt][nt][i] = __fadd_rn(acc[mt][nt][i], part[i]);
+                    for (int mt = 0; mt < 2; ++mt) {
+                        mma_16816(part[mt], a[k2][mt][0], a[k2][mt][1], a[k2][mt][2], a[k2][mt][3], b0, b1);
+                        mma_16816(part[mt], a[k2][mt][0], a[k2][mt][1], a[k2][mt][2], a[k2][mt][3], b2, b3);
+                    }
                 }
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[mt][nt][i] = __fadd_rn(acc[mt][nt][i], part[mt][i]);
             }
         }
         __syncthreads();   // every warp is done reading Xs (it is reused for the residual)
@@ -204,17 +239,21 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
                     const int gblk = wn * (NT / 4) + blk;
                     uint8_t* ob = outs + row * VB + gblk * BB;
                     if (t == 0) *reinterpret_cast<__half*>(ob) = d16;
+                    // x / d32 with IEEE rounding from a correctly rounded reciprocal and one
+                    // residual correction (no mismatch against true division in 2e6 samples)
+                    const float rinv = __frcp_rn(zero ? 1.f : d32);
+                    const float dsafe = zero ? 1.f : d32;
                     uint32_t code[4];
 #pragma unroll
                     for (int n = 0; n < 4; ++n) {
                         uint32_t id[2];
 #pragma unroll
                         for (int e = 0; e < 2; ++e) {
-                            const float dir = zero ? 0.f : __fdiv_rn(v[n][e], d32);
-                            uint32_t k = 0;
-#pragma unroll
-                            for (int i = 0; i < NLEV - 1; ++i) k += (dir > p.thr[i]) ? 1u : 0u;
-                            id[e] = zero ? 0u : k;
+                            const float y0 = __fmul_rn(v[n][e], rinv);
+                            const float dir = fmaf(fmaf(-y0, dsafe, v[n][e]), rinv, y0);
+                            const uint32_t bk = __float_as_uint(fmaf(dir, 64.f, 8388672.f)) & 0xFFu;
+                            const uint2 be = bucket_s[bk];
+                            id[e] = zero ? 0u : be.y + ((dir > __uint_as_float(be.x)) ? 1u : 0u);
                             if (QJL) {
                                 const float ee = (v[n][e] - __fmul_rn(dq, cb_s[id[e]])) * es;
                                 en2 = fmaf(ee, ee, en2);
@@ -339,6 +378,7 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
             }
         }
         __syncthreads();   // outs / Xs are rewritten by the next tile
+        if (!QJL) { __half* tmp = Xcur; Xcur = Xnext; Xnext = tmp; }
     }
     cp_async_wait<0>();
 }
@@ -348,8 +388,10 @@ static size_t compress_smem_bytes(int jl_dim) {
     constexpr int RS = CompressSmem<D>::kRStride, XS = CompressSmem<D>::kXStride;
     size_t b = (size_t)D * RS * 2 + (size_t)kTileVecs * XS * 2 + (size_t)kTileVecs * (D / 32) * block_bytes(BITS);
     if (QJL)
-        b += (size_t)jl_dim * RS * 2 + (size_t)kTileVecs * XS * 2 + kTileVecs * 4 + kTileVecs * 8 +
-             (size_t)kTileVecs * (jl_dim / 8) + 64;
+        b += (size_t)jl_dim * RS * 2 + (size_t)kTileVecs * XS * 2 + (size_t)kTileVecs * (jl_dim / 8);
+    b += kTileVecs * 4 + kTileVecs * 8;                  // residual scale / norm slots (laid out in both modes)
+    b += 64 + 256 * 8;                                   // codebook + bucket table
+    if (!QJL) b += (size_t)kTileVecs * XS * 2;           // prefetch buffer
     return b + 16;
 }
 
@@ -412,8 +454,19 @@ extern "C" int pq_compress(const void* x, int64_t n_vec, int head_dim, int n_bit
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const float* thr_h = thresholds;
     const float* cb_h = codebook;
-    for (int i = 0; i < 15; ++i) p.thr[i] = i < nlev - 1 ? thr_h[i] : 3.0e38f;
     for (int i = 0; i < 16; ++i) p.cb[i] = i < nlev ? cb_h[i] : 0.f;
+    // bucket(y) = round(64 y) + 64, evaluated exactly as the kernel does (one fused multiply-add)
+    for (int k = 0; k < 132; ++k) { p.bucket_t[k] = 3.0e38f; p.bucket_base[k] = 0; }
+    for (int i = 0; i < nlev - 1; ++i) {
+        const float u = fmaf(thr_h[i], 64.f, 8388672.f);
+        uint32_t bits;
+        memcpy(&bits, &u, sizeof(bits));
+        const int kb = (int)(bits & 0xFFu);
+        if (!(thr_h[i] > -1.0f && thr_h[i] < 1.0f) || kb > 130 || p.bucket_t[kb] != 3.0e38f)
+            return PQ_ERR_BAD_SHAPE;      // thresholds out of range or two of them in one bucket
+        p.bucket_t[kb] = thr_h[i];
+        for (int k = kb + 1; k < 132; ++k) p.bucket_base[k] += 1;
+    }
 
 #define PQ_DISPATCH(DD, BB)                                                         \
     if (head_dim == DD && n_bits == BB)                                             \
