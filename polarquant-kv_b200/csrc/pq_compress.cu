@@ -1,7 +1,7 @@
 // pq_compress: fused rotate -> per-32 radius -> nearest Lloyd-Max centroid -> pack
 // [-> QJL 1-bit residual sketch], for block_pq4 storage.
 //
-// One CTA (8 warps) owns a tile of 128 vectors.  The rotation  xr = x @ R^T  is a dense
+// One CTA (4 x D/32 warps) owns a tile of 128 vectors; a warp owns 32 vectors x one 32-element block.  The rotation  xr = x @ R^T  is a dense
 // contraction on tensor cores.  x is float16 (exact); R is pre-split on the host into two
 // float16 terms  4096*R = hi + lo  so that, with float32 accumulation, xr carries about
 // 22 mantissa bits of R and matches the float64-then-float32 rotation of the numpy
@@ -26,7 +26,8 @@
 namespace pq {
 
 constexpr int kTileVecs = 128;
-constexpr int kCompressThreads = 256;
+// warps: 4 along the vectors (32 each) x D/32 along the outputs (one 32-element block each)
+__host__ __device__ constexpr int compress_threads(int D) { return 32 * 4 * (D / 32); }
 
 struct CompressParams {
     const __half* x;
@@ -51,13 +52,16 @@ struct CompressSmem {
 };
 
 template <int D, int BITS, bool QJL>
-__global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const CompressParams p) {
+__global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(const CompressParams p) {
+    constexpr int kCompressThreads = compress_threads(D);
+    constexpr int WN = D / 32;                    // warps along the output dims
     constexpr int NBLK = D / 32;
     constexpr int BB = block_bytes(BITS);
     constexpr int VB = NBLK * BB;                 // bytes per stored vector
     constexpr int RS = CompressSmem<D>::kRStride;
     constexpr int XS = CompressSmem<D>::kXStride;
-    constexpr int NT = D / 16;                    // n-tiles (8 outputs) per warp: half of D
+    constexpr int NT = 4;                         // n-tiles (8 outputs) per warp: one 32-element block
+    constexpr int BREP = QJL ? 1 : 16;            // lane copies of the index-search table
     constexpr int NLEV = 1 << BITS;
 
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -68,20 +72,20 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
     __half* Ps = reinterpret_cast<__half*>(outs + kTileVecs * VB);          // [M][RS]
     __half* Elo = Ps + (QJL ? p.jl_dim : 0) * RS;                           // [128][XS]
     float* escale = reinterpret_cast<float*>(Elo + (QJL ? kTileVecs * XS : 0));  // [128]
-    float* enorm2 = escale + kTileVecs;                                     // [128][2]
-    uint8_t* bits_s = reinterpret_cast<uint8_t*>(enorm2 + 2 * kTileVecs);   // [128][M/8]
+    float* enorm2 = escale + kTileVecs;                                     // [128][4]
+    uint8_t* bits_s = reinterpret_cast<uint8_t*>(enorm2 + 4 * kTileVecs);   // [128][M/8]
     float* cb_s = reinterpret_cast<float*>(bits_s + (QJL ? kTileVecs * (p.jl_dim / 8) : 0));  // [16]
-    uint2* bucket_s = reinterpret_cast<uint2*>(cb_s + 16);                  // [256] {threshold bits, base}
+    uint2* bucket_s = reinterpret_cast<uint2*>(cb_s + 16);                  // [256][BREP] {threshold bits, base}
     // second vector tile for prefetching (not with QJL: the residual tiles take the room)
-    __half* Xs2 = reinterpret_cast<__half*>(bucket_s + 256);                // [128][XS]
+    __half* Xs2 = reinterpret_cast<__half*>(bucket_s + 256 * BREP);         // [128][XS]
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
     const int g = lane >> 2;
     const int t = lane & 3;
-    const int wm = warp >> 1;   // 32-vector group
-    const int wn = warp & 1;    // half of the output dims
+    const int wm = warp / WN;   // 32-vector group
+    const int wn = warp % WN;   // block of 32 output dims
 
     // ---- split rotation (and JL) matrices: resident for the CTA's lifetime
     for (int c = tid; c < D * (2 * D / 8); c += kCompressThreads) {
@@ -95,10 +99,12 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
         }
         if (tid < 16) cb_s[tid] = p.cb[tid < NLEV ? tid : 0];
     }
-    {
-        const int k = tid < 132 ? tid : 131;      // buckets past 128 only see out-of-range garbage
-        bucket_s[tid] = make_uint2(__float_as_uint(p.bucket_t[k]), p.bucket_base[k]);
+    for (int e = tid; e < 256 * BREP; e += kCompressThreads) {
+        const int b = e / BREP;
+        const int k = b < 132 ? b : 131;          // buckets past 128 only see out-of-range garbage
+        bucket_s[e] = make_uint2(__float_as_uint(p.bucket_t[k]), p.bucket_base[k]);
     }
+    const uint2* bucket_lane = bucket_s + (lane % BREP);
     cp_async_commit();
 
     const int64_t n_tiles = (p.n_vec + kTileVecs - 1) / kTileVecs;
@@ -137,11 +143,12 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
         if (QJL) {
             // power-of-two scale per vector so the residual split stays in float16 range:
             // |e_j| < 32 * max|x_j|, scaled to below 2^15.
-            int row = tid >> 1, hf = tid & 1;
-            const uint4* src = reinterpret_cast<const uint4*>(Xs + row * XS + hf * (D / 2));
+            constexpr int PARTS = kCompressThreads / kTileVecs;      // threads per row (2 or 4)
+            const int row = tid / PARTS, part = tid % PARTS;
+            const uint4* src = reinterpret_cast<const uint4*>(Xs + row * XS + part * (D / PARTS));
             float vmax = 0.f;
 #pragma unroll
-            for (int i = 0; i < D / 16; ++i) {
+            for (int i = 0; i < D / PARTS / 8; ++i) {
                 uint4 u = src[i];
                 const __half2* h = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
@@ -150,13 +157,13 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
                     vmax = fmaxf(vmax, fmaxf(f.x, f.y));
                 }
             }
-            vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, 1));
-            if (hf == 0) {
+#pragma unroll
+            for (int o = 1; o < PARTS; o <<= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+            if (part == 0) {
                 uint32_t be = __float_as_uint(vmax) >> 23;
                 escale[row] = (vmax > 0.f) ? __uint_as_float((263u - be) << 23) : 1.0f;
-                enorm2[2 * row] = 0.f;
-                enorm2[2 * row + 1] = 0.f;
             }
+            for (int e = tid; e < kTileVecs * WN; e += kCompressThreads) enorm2[e] = 0.f;
         }
 
         // ---- rotation: acc[mt][nt] (16 vectors x 8 dims each), K = D with hi and lo terms
@@ -189,7 +196,7 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
                     uint32_t b0, b1, b2, b3;
                     const int j = lane >> 3;
                     ldmatrix_x4(b0, b1, b2, b3,
-                                Rs + (wn * (D / 2) + nt * 8 + (lane & 7)) * RS + (kp * 2 + k2) * 16 + (j & 1) * 8 + (j >> 1) * D);
+                                Rs + (wn * 32 + nt * 8 + (lane & 7)) * RS + (kp * 2 + k2) * 16 + (j & 1) * 8 + (j >> 1) * D);
 #pragma unroll
                     for (int mt = 0; mt < 2; ++mt) {
                         mma_16816(part[mt], a[k2][mt][0], a[k2][mt][1], a[k2][mt][2], a[k2][mt][3], b0, b1);
@@ -252,14 +259,14 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
                             const float y0 = __fmul_rn(v[n][e], rinv);
                             const float dir = fmaf(fmaf(-y0, dsafe, v[n][e]), rinv, y0);
                             const uint32_t bk = __float_as_uint(fmaf(dir, 64.f, 8388672.f)) & 0xFFu;
-                            const uint2 be = bucket_s[bk];
+                            const uint2 be = bucket_lane[bk * BREP];
                             id[e] = zero ? 0u : be.y + ((dir > __uint_as_float(be.x)) ? 1u : 0u);
                             if (QJL) {
                                 const float ee = (v[n][e] - __fmul_rn(dq, cb_s[id[e]])) * es;
                                 en2 = fmaf(ee, ee, en2);
                                 __half eh, el;
                                 split_half(ee, eh, el);
-                                const int col = wn * (D / 2) + (blk * 4 + n) * 8 + 2 * t + e;
+                                const int col = wn * 32 + (blk * 4 + n) * 8 + 2 * t + e;
                                 Xs[row * XS + col] = eh;
                                 Elo[row * XS + col] = el;
                             }
@@ -281,7 +288,7 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
                 if (QJL) {
                     en2 += __shfl_xor_sync(0xffffffffu, en2, 1);
                     en2 += __shfl_xor_sync(0xffffffffu, en2, 2);
-                    if (t == 0) enorm2[2 * row + wn] = en2;
+                    if (t == 0) enorm2[WN * row + wn] = en2;
                 }
             }
         }
@@ -291,7 +298,7 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
             // ---- sign sketch: proj[vec][i] = sum_j e[vec][j] * P'[i][j]; this warp owns
             // 32 vectors x (M/2) projections, in chunks of 8 n-tiles to bound registers.
             const int M = p.jl_dim;
-            const int nt_per_warp = M / 16;
+            const int nt_per_warp = (M / 8 + WN - 1) / WN;       // bytes of the sketch per warp
             for (int nt0 = 0; nt0 < nt_per_warp; nt0 += 4) {
                 float pc[2][4][4];
 #pragma unroll
@@ -311,11 +318,11 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
                     }
 #pragma unroll
                     for (int n = 0; n < 4; ++n) {
-                        if (nt0 + n < nt_per_warp) {
+                        if (nt0 + n < nt_per_warp && wn * nt_per_warp + nt0 + n < M / 8) {
                             uint32_t b0, b1, b2, b3;
                             int j = lane >> 3;
                             ldmatrix_x4(b0, b1, b2, b3,
-                                        Ps + (wn * (M / 2) + (nt0 + n) * 8 + (lane & 7)) * RS + ks * 16 +
+                                        Ps + ((wn * nt_per_warp + nt0 + n) * 8 + (lane & 7)) * RS + ks * 16 +
                                             (j & 1) * 8 + (j >> 1) * D);
 #pragma unroll
                             for (int mt = 0; mt < 2; ++mt) {
@@ -341,10 +348,10 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
                         w |= __shfl_xor_sync(0xffffffffu, w, 2);
                         const int row = wm * 32 + mt * 16 + hh * 8 + g;
                         if (t == 0) {
-                            uint8_t* dst = bits_s + row * (M / 8) + wn * (M / 16) + nt0;
+                            uint8_t* dst = bits_s + row * (M / 8) + wn * nt_per_warp + nt0;
 #pragma unroll
                             for (int n = 0; n < 4; ++n)
-                                if (nt0 + n < nt_per_warp) dst[n] = (uint8_t)(w >> (8 * n));
+                                if (nt0 + n < nt_per_warp && wn * nt_per_warp + nt0 + n < M / 8) dst[n] = (uint8_t)(w >> (8 * n));
                         }
                     }
             }
@@ -372,7 +379,9 @@ __global__ void __launch_bounds__(kCompressThreads, 1) pq_compress_kernel(const 
                     for (int c = tid; c < nb; c += kCompressThreads) bd[c] = bits_s[c];
                 }
                 for (int r = tid; r < n_valid; r += kCompressThreads) {
-                    const float n2 = enorm2[2 * r] + enorm2[2 * r + 1];
+                    float n2 = 0.f;
+#pragma unroll
+                    for (int k = 0; k < WN; ++k) n2 += enorm2[WN * r + k];
                     p.qjl_norm_out[v0 + r] = __float2half_rn(fminf(sqrtf(n2) / escale[r], 65504.0f));
                 }
             }
@@ -389,8 +398,8 @@ static size_t compress_smem_bytes(int jl_dim) {
     size_t b = (size_t)D * RS * 2 + (size_t)kTileVecs * XS * 2 + (size_t)kTileVecs * (D / 32) * block_bytes(BITS);
     if (QJL)
         b += (size_t)jl_dim * RS * 2 + (size_t)kTileVecs * XS * 2 + (size_t)kTileVecs * (jl_dim / 8);
-    b += kTileVecs * 4 + kTileVecs * 8;                  // residual scale / norm slots (laid out in both modes)
-    b += 64 + 256 * 8;                                   // codebook + bucket table
+    b += kTileVecs * 4 + kTileVecs * 16;                 // residual scale / norm slots (laid out in both modes)
+    b += 64 + 256 * 8 * (QJL ? 1 : 16);                  // codebook + index-search table copies
     if (!QJL) b += (size_t)kTileVecs * XS * 2;           // prefetch buffer
     return b + 16;
 }
@@ -407,12 +416,12 @@ static int launch_compress(const CompressParams& p, cudaStream_t stream) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return PQ_ERR_CUDA;
     int per_sm = 1;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kCompressThreads, smem) != cudaSuccess || per_sm < 1)
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, compress_threads(D), smem) != cudaSuccess || per_sm < 1)
         return PQ_ERR_CUDA;
     const int64_t n_tiles = (p.n_vec + kTileVecs - 1) / kTileVecs;
     const int64_t cap = (int64_t)sm_count * per_sm;
     const int grid = (int)(n_tiles < cap ? n_tiles : cap);
-    kern<<<grid, kCompressThreads, smem, stream>>>(p);
+    kern<<<grid, compress_threads(D), smem, stream>>>(p);
     return cudaGetLastError() == cudaSuccess ? PQ_OK : PQ_ERR_CUDA;
 }
 
