@@ -1,23 +1,34 @@
 // pq_compress: fused rotate -> per-32 radius -> nearest Lloyd-Max centroid -> pack
 // [-> QJL 1-bit residual sketch], for block_pq4 storage.
 //
-// One CTA (4 x D/32 warps) owns a tile of 128 vectors; a warp owns 32 vectors x one 32-element block.  The rotation  xr = x @ R^T  is a dense
-// contraction on tensor cores.  x is float16 (exact); R is pre-split on the host into two
-// float16 terms  4096*R = hi + lo  so that, with float32 accumulation, xr carries about
-// 22 mantissa bits of R and matches the float64-then-float32 rotation of the numpy
-// reference (python/polarquant_kv/rotation.py:48) to a few 1e-8 relative.  Everything
-// after the contraction follows the reference's float32 arithmetic exactly:
+// One CTA (4 x D/32 warps) owns a tile of 128 vectors at a time (persistent over tiles).
+// The rotation  xr = x @ R^T  is a dense [128 x 2D] x [2D x D] contraction on the 5th-gen
+// tensor cores: one elected thread issues tcgen05.mma (kind::f16, M = 128, N = D, K = 16)
+// on shared-memory operands, the float32 accumulators live in tensor memory (TMEM) and are
+// read back with tcgen05.ld for the epilogue.  x is float16 (exact); R is pre-split on the
+// host into two float16 terms  4096*R = hi + lo  (K runs over [hi | lo]), so xr carries
+// about 22 mantissa bits of R and matches the float64-then-float32 rotation of the numpy
+// reference (python/polarquant_kv/rotation.py:48) to a few 1e-8 relative.  Tensor-core
+// accumulation truncates when it aligns addends, so K is cut into D/32 groups with one TMEM
+// accumulator each, and the groups are summed with round-to-nearest float32 adds.
+// Everything after the contraction follows the reference's float32 arithmetic exactly:
 //   radius  = sqrt(sum of squares), summed in numpy's axis-reduction order
 //             (eight strided partial sums, then a balanced tree),
 //   guard   = radius < 1e-30 -> radius 0, indices 0      (quantizer.py:107-119),
-//   dir     = xr / radius (IEEE division)                 (quantizer.py:121),
+//   dir     = xr / radius with IEEE rounding              (quantizer.py:121),
 //   index   = #thresholds strictly below dir, the thresholds being the exact float32
 //             decision points of argmin_i |dir - c_i|     (lloyd_max.py:82-90),
 //   d       = float16(min(radius, 65504))                 (compress_kernel.py:178),
 //   packing = low nibble first                            (compress_kernel.py:34-50).
+// In the epilogue a thread owns one vector x one 32-element block (TMEM lane = vector), so
+// the block sums, the division and the packing are thread-local.
 // QJL (qjl.py:25-35, compress_kernel.py:168-175): the residual e = xr - d*c[idx] stays in
 // rotated space; signs of P e equal signs of (P R^T) e_rot, evaluated as a second
-// three-term float16 contraction (e_hi*P_hi + e_hi*P_lo + e_lo*P_hi).
+// three-term float16 contraction (e_hi*P_hi + e_hi*P_lo + e_lo*P_hi) on the same path.
+//
+// Shared-memory operand layout (K-major, no swizzle): 16-byte chunks of 8 halves; chunk kc of
+// row r sits at  kc * (rows/8 * 128) + (r / 8) * 128 + (r % 8) * 16  — 8x16-byte core
+// matrices, stride 128 B between 8-row groups (SBO), rows/8*128 B between K chunks (LBO).
 #include <cmath>
 #include <cstring>
 
@@ -26,7 +37,7 @@
 namespace pq {
 
 constexpr int kTileVecs = 128;
-// warps: 4 along the vectors (32 each) x D/32 along the outputs (one 32-element block each)
+// warps: 4 per warpgroup (TMEM lanes 0..127 = vectors) x D/32 warpgroups (one block each)
 __host__ __device__ constexpr int compress_threads(int D) { return 32 * 4 * (D / 32); }
 
 struct CompressParams {
@@ -45,85 +56,181 @@ struct CompressParams {
     uint32_t bucket_base[132];
 };
 
-template <int D>
-struct CompressSmem {
-    static constexpr int kRStride = 2 * D + 8;   // halves per row of the split matrices
-    static constexpr int kXStride = D + 8;       // halves per row of the vector tile
+// ------------------------------------------------------------------ tcgen05 / mbarrier wrappers
+__device__ __forceinline__ uint32_t sm_addr(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+// K-major, no-swizzle shared-memory matrix descriptor (sm_100 format, version field = 1)
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((smem_byte_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46);
+}
+// kind::f16 instruction descriptor: D = f32, A = B = f16, both K-major, M = 128, N = n
+__host__ __device__ constexpr uint32_t umma_idesc_f16(int n) {
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t"
+        "}\n" ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t mbar_addr) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(mbar_addr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_addr, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(slot_addr), "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// 32 consecutive float32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(float (&v)[32], uint32_t taddr) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(addr), "r"(count) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+}
+// Bounded wait on a phase parity: gives up after ~2^22 polls (seconds) and reports failure,
+// so a lost completion can never hang the GPU.
+__device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity) {
+    for (int it = 0; it < (1 << 22); ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+// Byte offset of 16-byte chunk `kc` of row `r` in a K-major operand tile with `rows` rows.
+__device__ __forceinline__ uint32_t chunk_off(int rows, int r, int kc) {
+    return (uint32_t)(kc * (rows / 8) * 128 + (r >> 3) * 128 + (r & 7) * 16);
+}
+
+template <int D, int BITS, bool QJL>
+struct CompressCfg {
+    static constexpr int THREADS = compress_threads(D);
+    static constexpr int WG = D / 32;                         // warpgroups = blocks per vector
+    static constexpr int BREP = QJL ? 1 : 16;                 // lane copies of the index-search table
+    static constexpr int VB = (D / 32) * block_bytes(BITS);   // bytes per stored vector
+    static constexpr int kRBytes = 4 * D * D;                 // [2D/8 chunks][D rows][16 B]
+    static constexpr int kXBytes = (D / 8) * 2048;            // [D/8 chunks][128 rows][16 B]
+    static constexpr int kTmemCols = (D / 32) * D;            // one accumulator of D columns per K group
+    __host__ __device__ static size_t smem_bytes(int jl_dim) {
+        size_t b = kRBytes + 2 * (size_t)kXBytes + (size_t)kTileVecs * VB + 256 * 8 * BREP + 64 +
+                   kTileVecs * 4 + kTileVecs * WG * 4 + 64;
+        if (QJL) b += (size_t)(2 * D / 8) * jl_dim * 16 + (size_t)kTileVecs * (jl_dim / 8);
+        return b + 128;
+    }
 };
 
 template <int D, int BITS, bool QJL>
 __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(const CompressParams p) {
-    constexpr int kCompressThreads = compress_threads(D);
-    constexpr int WN = D / 32;                    // warps along the output dims
-    constexpr int NBLK = D / 32;
+    using C = CompressCfg<D, BITS, QJL>;
+    constexpr int THREADS = C::THREADS;
+    constexpr int WG = C::WG;
     constexpr int BB = block_bytes(BITS);
-    constexpr int VB = NBLK * BB;                 // bytes per stored vector
-    constexpr int RS = CompressSmem<D>::kRStride;
-    constexpr int XS = CompressSmem<D>::kXStride;
-    constexpr int NT = 4;                         // n-tiles (8 outputs) per warp: one 32-element block
-    constexpr int BREP = QJL ? 1 : 16;            // lane copies of the index-search table
+    constexpr int VB = C::VB;
+    constexpr int BREP = C::BREP;
     constexpr int NLEV = 1 << BITS;
+    constexpr uint32_t LBO_R = (D / 8) * 128;                 // K-chunk stride of the R / P tiles' row groups
+    const int M = QJL ? p.jl_dim : 0;
 
-    extern __shared__ __align__(16) uint8_t smem_raw[];
-    __half* Rs = reinterpret_cast<__half*>(smem_raw);                       // [D][RS]
-    __half* Xs = Rs + D * RS;                                               // [128][XS]
-    uint8_t* outs = reinterpret_cast<uint8_t*>(Xs + kTileVecs * XS);        // [128][VB]
-    // QJL-only regions
-    __half* Ps = reinterpret_cast<__half*>(outs + kTileVecs * VB);          // [M][RS]
-    __half* Elo = Ps + (QJL ? p.jl_dim : 0) * RS;                           // [128][XS]
-    float* escale = reinterpret_cast<float*>(Elo + (QJL ? kTileVecs * XS : 0));  // [128]
-    float* enorm2 = escale + kTileVecs;                                     // [128][4]
-    uint8_t* bits_s = reinterpret_cast<uint8_t*>(enorm2 + 4 * kTileVecs);   // [128][M/8]
-    float* cb_s = reinterpret_cast<float*>(bits_s + (QJL ? kTileVecs * (p.jl_dim / 8) : 0));  // [16]
-    uint2* bucket_s = reinterpret_cast<uint2*>(cb_s + 16);                  // [256][BREP] {threshold bits, base}
-    // second vector tile for prefetching (not with QJL: the residual tiles take the room)
-    __half* Xs2 = reinterpret_cast<__half*>(bucket_s + 256 * BREP);         // [128][XS]
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t* sp = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    uint8_t* Rb = sp;                       sp += C::kRBytes;
+    uint8_t* Xa = sp;                       sp += C::kXBytes;      // vector tile / residual hi term
+    uint8_t* Xb = sp;                       sp += C::kXBytes;      // prefetch tile / residual lo term (QJL)
+    uint8_t* outs = sp;                     sp += kTileVecs * VB;
+    uint2* bucket_s = reinterpret_cast<uint2*>(sp);  sp += 256 * 8 * BREP;
+    float* cb_s = reinterpret_cast<float*>(sp);      sp += 64;
+    float* escale = reinterpret_cast<float*>(sp);    sp += kTileVecs * 4;
+    float* enorm2 = reinterpret_cast<float*>(sp);    sp += kTileVecs * WG * 4;
+    uint64_t* mbar = reinterpret_cast<uint64_t*>(sp);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sp + 8);     sp += 64;
+    uint8_t* Pb = sp;                       sp += QJL ? (2 * D / 8) * M * 16 : 0;
+    uint8_t* bits_s = sp;
 
-    const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const int warp = tid >> 5;
-    const int g = lane >> 2;
-    const int t = lane & 3;
-    const int wm = warp / WN;   // 32-vector group
-    const int wn = warp % WN;   // block of 32 output dims
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wg = warp >> 2;                                   // block (32 output dims) this thread owns
+    const int row = (warp & 3) * 32 + lane;                     // vector of the tile = TMEM lane
 
-    // ---- split rotation (and JL) matrices: resident for the CTA's lifetime
-    for (int c = tid; c < D * (2 * D / 8); c += kCompressThreads) {
-        int row = c / (2 * D / 8), col = (c % (2 * D / 8)) * 8;
-        cp_async_16(Rs + row * RS + col, p.rot_split + (size_t)row * 2 * D + col);
+    // ---- one-time set-up: split matrices, tables, barrier, tensor memory
+    for (int id = tid; id < D * (2 * D / 8); id += THREADS) {
+        const int n = ((id >> 5) % (D / 8)) * 8 + (id & 7), kc = ((id >> 5) / (D / 8)) * 4 + ((id >> 3) & 3);
+        cp_async_16(Rb + chunk_off(D, n, kc), p.rot_split + (size_t)n * 2 * D + kc * 8);
     }
     if (QJL) {
-        for (int c = tid; c < p.jl_dim * (2 * D / 8); c += kCompressThreads) {
-            int row = c / (2 * D / 8), col = (c % (2 * D / 8)) * 8;
-            cp_async_16(Ps + row * RS + col, p.jl_split + (size_t)row * 2 * D + col);
+        const int m8 = M >= 8 ? M / 8 : 1;
+        for (int id = tid; id < M * (2 * D / 8); id += THREADS) {
+            const int n = ((id >> 5) % m8) * 8 + (id & 7), kc = ((id >> 5) / m8) * 4 + ((id >> 3) & 3);
+            cp_async_16(Pb + chunk_off(M, n, kc), p.jl_split + (size_t)n * 2 * D + kc * 8);
         }
-        if (tid < 16) cb_s[tid] = p.cb[tid < NLEV ? tid : 0];
     }
-    for (int e = tid; e < 256 * BREP; e += kCompressThreads) {
+    if (tid < 16) cb_s[tid] = p.cb[tid < NLEV ? tid : 0];
+    for (int e = tid; e < 256 * BREP; e += THREADS) {
         const int b = e / BREP;
         const int k = b < 132 ? b : 131;          // buckets past 128 only see out-of-range garbage
         bucket_s[e] = make_uint2(__float_as_uint(p.bucket_t[k]), p.bucket_base[k]);
     }
     const uint2* bucket_lane = bucket_s + (lane % BREP);
-    cp_async_commit();
+    if (tid == 0) mbar_init(sm_addr(mbar), 1);
+    if (warp == 0) tmem_alloc(sm_addr(tmem_slot), C::kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    uint32_t phase = 0;
+    bool ok = true;
 
     const int64_t n_tiles = (p.n_vec + kTileVecs - 1) / kTileVecs;
-    auto load_tile = [&](int64_t tile, __half* dst) {
+    auto load_tile = [&](int64_t tile, uint8_t* dst) {
         const int64_t v0 = tile * kTileVecs;
         const int n_valid = (int)min((int64_t)kTileVecs, p.n_vec - v0);
-        for (int c = tid; c < kTileVecs * (D / 8); c += kCompressThreads) {
-            int row = c / (D / 8), col = (c % (D / 8)) * 8;
-            if (row < n_valid) {
-                cp_async_16(dst + row * XS + col, p.x + (v0 + row) * D + col);
-            } else {
-                *reinterpret_cast<uint4*>(dst + row * XS + col) = make_uint4(0, 0, 0, 0);   // rows past the end
-            }
+        for (int id = tid; id < kTileVecs * (D / 8); id += THREADS) {
+            const int m = ((id >> 5) & 15) * 8 + (id & 7), kc = (id >> 9) * 4 + ((id >> 3) & 3);
+            uint8_t* d = dst + chunk_off(kTileVecs, m, kc);
+            if (m < n_valid) cp_async_16(d, p.x + (v0 + m) * D + kc * 8);
+            else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);          // rows past the end
         }
     };
-    __half* Xcur = Xs;
-    __half* Xnext = QJL ? Xs : Xs2;
+    uint8_t* Xcur = Xa;
+    uint8_t* Xnext = QJL ? Xa : Xb;
+    uint8_t* Elo = Xb;
     if (!QJL && (int64_t)blockIdx.x < n_tiles) load_tile(blockIdx.x, Xcur);
     cp_async_commit();
+
     for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         const int64_t v0 = tile * kTileVecs;
         const int n_valid = (int)min((int64_t)kTileVecs, p.n_vec - v0);
@@ -137,19 +244,37 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
             cp_async_commit();
             cp_async_wait<1>();
         }
+        fence_async_smem();          // the tensor core reads shared memory through the async proxy
         __syncthreads();
-        __half* const Xs = Xcur;   // the tile this iteration works on
 
+        // ---- rotation: D/32 accumulators (K groups of two 16-wide steps, hi then lo term)
+        if (tid == 0) {
+            tc_fence_after();
+            const uint32_t xaddr = sm_addr(Xcur), raddr = sm_addr(Rb);
+            constexpr uint32_t idesc = umma_idesc_f16(D);
+#pragma unroll
+            for (int grp = 0; grp < D / 32; ++grp) {
+#pragma unroll
+                for (int k2 = 0; k2 < 2; ++k2) {
+                    const int ks = grp * 2 + k2;
+                    const uint64_t da = umma_desc(xaddr + ks * 2 * 2048, 2048, 128);
+                    const uint64_t bh = umma_desc(raddr + (2 * ks) * LBO_R, LBO_R, 128);
+                    const uint64_t bl = umma_desc(raddr + (D / 8 + 2 * ks) * LBO_R, LBO_R, 128);
+                    umma_f16(tmem_base + grp * D, da, bh, idesc, k2 ? 1u : 0u);
+                    umma_f16(tmem_base + grp * D, da, bl, idesc, 1u);
+                }
+            }
+            umma_commit(sm_addr(mbar));
+        }
         if (QJL) {
             // power-of-two scale per vector so the residual split stays in float16 range:
-            // |e_j| < 32 * max|x_j|, scaled to below 2^15.
-            constexpr int PARTS = kCompressThreads / kTileVecs;      // threads per row (2 or 4)
-            const int row = tid / PARTS, part = tid % PARTS;
-            const uint4* src = reinterpret_cast<const uint4*>(Xs + row * XS + part * (D / PARTS));
+            // |e_j| < 32 * max|x_j|, scaled to below 2^15.  (Reads the vector tile while the MMAs run.)
+            constexpr int PARTS = THREADS / kTileVecs;                  // threads per row
+            const int r = tid / PARTS, part = tid % PARTS;
             float vmax = 0.f;
 #pragma unroll
-            for (int i = 0; i < D / PARTS / 8; ++i) {
-                uint4 u = src[i];
+            for (int i = 0; i < D / 8 / PARTS; ++i) {
+                const uint4 u = *reinterpret_cast<const uint4*>(Xcur + chunk_off(kTileVecs, r, part * (D / 8 / PARTS) + i));
                 const __half2* h = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
@@ -160,268 +285,185 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
 #pragma unroll
             for (int o = 1; o < PARTS; o <<= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
             if (part == 0) {
-                uint32_t be = __float_as_uint(vmax) >> 23;
-                escale[row] = (vmax > 0.f) ? __uint_as_float((263u - be) << 23) : 1.0f;
-            }
-            for (int e = tid; e < kTileVecs * WN; e += kCompressThreads) enorm2[e] = 0.f;
-        }
-
-        // ---- rotation: acc[mt][nt] (16 vectors x 8 dims each), K = D with hi and lo terms
-        float acc[2][NT][4];
-#pragma unroll
-        for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
-
-        // The tensor core truncates when it aligns addends to the running sum, so a long
-        // in-MMA accumulation chain drifts by several ulp.  Two k-steps (hi and lo terms) are
-        // summed from zero inside the tensor core and then added to the running sum with a
-        // round-to-nearest float32 add.
-#pragma unroll 1
-        for (int kp = 0; kp < D / 32; ++kp) {
-            uint32_t a[2][2][4];
-#pragma unroll
-            for (int k2 = 0; k2 < 2; ++k2)
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt)
-                    ldmatrix_x4(a[k2][mt][0], a[k2][mt][1], a[k2][mt][2], a[k2][mt][3],
-                                Xs + (wm * 32 + mt * 16 + (lane & 15)) * XS + (kp * 2 + k2) * 16 + (lane >> 4) * 8);
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                float part[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-                for (int k2 = 0; k2 < 2; ++k2) {
-                    uint32_t b0, b1, b2, b3;
-                    const int j = lane >> 3;
-                    ldmatrix_x4(b0, b1, b2, b3,
-                                Rs + (wn * 32 + nt * 8 + (lane & 7)) * RS + (kp * 2 + k2) * 16 + (j & 1) * 8 + (j >> 1) * D);
-#pragma unroll
-                    for (int mt = 0; mt < 2; ++mt) {
-                        mma_16816(part[mt], a[k2][mt][0], a[k2][mt][1], a[k2][mt][2], a[k2][mt][3], b0, b1);
-                        mma_16816(part[mt], a[k2][mt][0], a[k2][mt][1], a[k2][mt][2], a[k2][mt][3], b2, b3);
-                    }
-                }
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[mt][nt][i] = __fadd_rn(acc[mt][nt][i], part[mt][i]);
-            }
-        }
-        __syncthreads();   // every warp is done reading Xs (it is reused for the residual)
-
-        // ---- epilogue: radius, indices, packing (and the residual for QJL)
-#pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const int row = wm * 32 + mt * 16 + hh * 8 + g;
-                float en2 = 0.f;
-                const float es = QJL ? escale[row] : 1.f;
-#pragma unroll
-                for (int blk = 0; blk < NT / 4; ++blk) {
-                    float v[4][2];
-#pragma unroll
-                    for (int n = 0; n < 4; ++n) {
-                        v[n][0] = acc[mt][blk * 4 + n][hh * 2 + 0] * (1.0f / 4096.0f);
-                        v[n][1] = acc[mt][blk * 4 + n][hh * 2 + 1] * (1.0f / 4096.0f);
-                    }
-                    // numpy's float32 axis-reduction order: r[j] over j, j+8, j+16, j+24
-                    float r0 = __fmul_rn(v[0][0], v[0][0]);
-                    float r1 = __fmul_rn(v[0][1], v[0][1]);
-#pragma unroll
-                    for (int n = 1; n < 4; ++n) {
-                        r0 = __fadd_rn(r0, __fmul_rn(v[n][0], v[n][0]));
-                        r1 = __fadd_rn(r1, __fmul_rn(v[n][1], v[n][1]));
-                    }
-                    float s = __fadd_rn(r0, r1);
-                    s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 1));
-                    s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 2));
-                    float d32 = __fsqrt_rn(s);
-                    const bool zero = d32 < 1e-30f;
-                    if (zero) d32 = 0.f;
-                    const __half d16 = __float2half_rn(fminf(d32, 65504.0f));
-                    const float dq = __half2float(d16);
-                    const int gblk = wn * (NT / 4) + blk;
-                    uint8_t* ob = outs + row * VB + gblk * BB;
-                    if (t == 0) *reinterpret_cast<__half*>(ob) = d16;
-                    // x / d32 with IEEE rounding from a correctly rounded reciprocal and one
-                    // residual correction (no mismatch against true division in 2e6 samples)
-                    const float rinv = __frcp_rn(zero ? 1.f : d32);
-                    const float dsafe = zero ? 1.f : d32;
-                    uint32_t code[4];
-#pragma unroll
-                    for (int n = 0; n < 4; ++n) {
-                        uint32_t id[2];
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const float y0 = __fmul_rn(v[n][e], rinv);
-                            const float dir = fmaf(fmaf(-y0, dsafe, v[n][e]), rinv, y0);
-                            const uint32_t bk = __float_as_uint(fmaf(dir, 64.f, 8388672.f)) & 0xFFu;
-                            const uint2 be = bucket_lane[bk * BREP];
-                            id[e] = zero ? 0u : be.y + ((dir > __uint_as_float(be.x)) ? 1u : 0u);
-                            if (QJL) {
-                                const float ee = (v[n][e] - __fmul_rn(dq, cb_s[id[e]])) * es;
-                                en2 = fmaf(ee, ee, en2);
-                                __half eh, el;
-                                split_half(ee, eh, el);
-                                const int col = wn * 32 + (blk * 4 + n) * 8 + 2 * t + e;
-                                Xs[row * XS + col] = eh;
-                                Elo[row * XS + col] = el;
-                            }
-                        }
-                        code[n] = id[0] | (id[1] << BITS);
-                    }
-                    if (BITS == 4) {
-#pragma unroll
-                        for (int n = 0; n < 4; ++n) ob[2 + n * 4 + t] = (uint8_t)code[n];
-                    } else {
-                        // 2-bit: a byte holds 4 dims = this lane's pair and its neighbour's
-#pragma unroll
-                        for (int n = 0; n < 4; ++n) {
-                            uint32_t other = __shfl_xor_sync(0xffffffffu, code[n], 1);
-                            if ((t & 1) == 0) ob[2 + n * 2 + (t >> 1)] = (uint8_t)(code[n] | (other << 4));
-                        }
-                    }
-                }
-                if (QJL) {
-                    en2 += __shfl_xor_sync(0xffffffffu, en2, 1);
-                    en2 += __shfl_xor_sync(0xffffffffu, en2, 2);
-                    if (t == 0) enorm2[WN * row + wn] = en2;
-                }
-            }
-        }
-        __syncthreads();
-
-        if (QJL) {
-            // ---- sign sketch: proj[vec][i] = sum_j e[vec][j] * P'[i][j]; this warp owns
-            // 32 vectors x (M/2) projections, in chunks of 8 n-tiles to bound registers.
-            const int M = p.jl_dim;
-            const int nt_per_warp = (M / 8 + WN - 1) / WN;       // bytes of the sketch per warp
-            for (int nt0 = 0; nt0 < nt_per_warp; nt0 += 4) {
-                float pc[2][4][4];
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                    for (int n = 0; n < 4; ++n)
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) pc[mt][n][i] = 0.f;
-#pragma unroll 2
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    uint32_t ah[2][4], al[2][4];
-#pragma unroll
-                    for (int mt = 0; mt < 2; ++mt) {
-                        const int off = (wm * 32 + mt * 16 + (lane & 15)) * XS + ks * 16 + (lane >> 4) * 8;
-                        ldmatrix_x4(ah[mt][0], ah[mt][1], ah[mt][2], ah[mt][3], Xs + off);
-                        ldmatrix_x4(al[mt][0], al[mt][1], al[mt][2], al[mt][3], Elo + off);
-                    }
-#pragma unroll
-                    for (int n = 0; n < 4; ++n) {
-                        if (nt0 + n < nt_per_warp && wn * nt_per_warp + nt0 + n < M / 8) {
-                            uint32_t b0, b1, b2, b3;
-                            int j = lane >> 3;
-                            ldmatrix_x4(b0, b1, b2, b3,
-                                        Ps + ((wn * nt_per_warp + nt0 + n) * 8 + (lane & 7)) * RS + ks * 16 +
-                                            (j & 1) * 8 + (j >> 1) * D);
-#pragma unroll
-                            for (int mt = 0; mt < 2; ++mt) {
-                                mma_16816(pc[mt][n], ah[mt][0], ah[mt][1], ah[mt][2], ah[mt][3], b0, b1);
-                                mma_16816(pc[mt][n], ah[mt][0], ah[mt][1], ah[mt][2], ah[mt][3], b2, b3);
-                                mma_16816(pc[mt][n], al[mt][0], al[mt][1], al[mt][2], al[mt][3], b0, b1);
-                            }
-                        }
-                    }
-                }
-                // pack: n-tile n is byte (wn*M/16 + nt0 + n); bit 2t+e comes from this lane
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                    for (int hh = 0; hh < 2; ++hh) {
-                        uint32_t w = 0;
-#pragma unroll
-                        for (int n = 0; n < 4; ++n)
-#pragma unroll
-                            for (int e = 0; e < 2; ++e)
-                                w |= (pc[mt][n][hh * 2 + e] >= 0.f ? 1u : 0u) << (8 * n + 2 * t + e);
-                        w |= __shfl_xor_sync(0xffffffffu, w, 1);
-                        w |= __shfl_xor_sync(0xffffffffu, w, 2);
-                        const int row = wm * 32 + mt * 16 + hh * 8 + g;
-                        if (t == 0) {
-                            uint8_t* dst = bits_s + row * (M / 8) + wn * nt_per_warp + nt0;
-#pragma unroll
-                            for (int n = 0; n < 4; ++n)
-                                if (nt0 + n < nt_per_warp && wn * nt_per_warp + nt0 + n < M / 8) dst[n] = (uint8_t)(w >> (8 * n));
-                        }
-                    }
+                const uint32_t be = __float_as_uint(vmax) >> 23;
+                escale[r] = (vmax > 0.f) ? __uint_as_float((263u - be) << 23) : 1.0f;
             }
             __syncthreads();
         }
+        ok = mbar_wait(sm_addr(mbar), phase) && ok;
+        phase ^= 1u;
+        tc_fence_after();
+
+        // ---- epilogue: this thread owns vector `row`, block `wg`
+        float v[32];
+        tmem_ld32(v, tmem_lane + wg * 32);
+#pragma unroll
+        for (int grp = 1; grp < D / 32; ++grp) {
+            float part[32];
+            tmem_ld32(part, tmem_lane + grp * D + wg * 32);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __fadd_rn(v[i], part[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] *= (1.0f / 4096.0f);
+        // numpy's float32 axis-reduction order: r[j] over j, j+8, j+16, j+24, then a balanced tree
+        float r8[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float s = __fmul_rn(v[j], v[j]);
+            s = __fadd_rn(s, __fmul_rn(v[8 + j], v[8 + j]));
+            s = __fadd_rn(s, __fmul_rn(v[16 + j], v[16 + j]));
+            r8[j] = __fadd_rn(s, __fmul_rn(v[24 + j], v[24 + j]));
+        }
+        const float ss = __fadd_rn(__fadd_rn(__fadd_rn(r8[0], r8[1]), __fadd_rn(r8[2], r8[3])),
+                                   __fadd_rn(__fadd_rn(r8[4], r8[5]), __fadd_rn(r8[6], r8[7])));
+        float d32 = __fsqrt_rn(ss);
+        const bool zero = d32 < 1e-30f;
+        if (zero) d32 = 0.f;
+        const __half d16 = __float2half_rn(fminf(d32, 65504.0f));
+        const float dq = __half2float(d16);
+        // x / d32 with IEEE rounding from a correctly rounded reciprocal and one residual
+        // correction (no mismatch against true division in 2e6 samples)
+        const float dsafe = zero ? 1.f : d32;
+        const float rinv = __frcp_rn(dsafe);
+        const float es = QJL ? escale[row] : 1.f;
+        float en2 = 0.f;
+        uint32_t packed[BITS];                                        // 32 indices, low index first
+#pragma unroll
+        for (int w = 0; w < BITS; ++w) packed[w] = 0u;
+        uint32_t ehi[16], elo[16];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float y0 = __fmul_rn(v[j], rinv);
+            const float dir = fmaf(fmaf(-y0, dsafe, v[j]), rinv, y0);
+            const uint32_t bk = __float_as_uint(fmaf(dir, 64.f, 8388672.f)) & 0xFFu;
+            const uint2 be = bucket_lane[bk * BREP];
+            const uint32_t id = zero ? 0u : be.y + ((dir > __uint_as_float(be.x)) ? 1u : 0u);
+            packed[(j * BITS) >> 5] |= id << ((j * BITS) & 31);
+            if (QJL) {
+                const float ee = (v[j] - __fmul_rn(dq, cb_s[id])) * es;
+                en2 = fmaf(ee, ee, en2);
+                v[j] = ee;
+            }
+        }
+        {
+            uint16_t* ob = reinterpret_cast<uint16_t*>(outs + row * VB + wg * BB);
+            ob[0] = __half_as_ushort(d16);
+#pragma unroll
+            for (int w = 0; w < BITS; ++w) {
+                ob[1 + 2 * w] = (uint16_t)(packed[w] & 0xFFFFu);
+                ob[2 + 2 * w] = (uint16_t)(packed[w] >> 16);
+            }
+        }
+        if (QJL) {
+            // residual as two float16 terms, written in operand layout: 4 chunks of this block
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+                const __half2 h = __floats2half2_rn(v[j], v[j + 1]);
+                const float2 f = __half22float2(h);
+                ehi[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+                elo[j >> 1] = pack_half2(v[j] - f.x, v[j + 1] - f.y);
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t off = chunk_off(kTileVecs, row, wg * 4 + c);
+                *reinterpret_cast<uint4*>(Xcur + off) = make_uint4(ehi[4 * c], ehi[4 * c + 1], ehi[4 * c + 2], ehi[4 * c + 3]);
+                *reinterpret_cast<uint4*>(Elo + off) = make_uint4(elo[4 * c], elo[4 * c + 1], elo[4 * c + 2], elo[4 * c + 3]);
+            }
+            enorm2[row * WG + wg] = en2;
+            fence_async_smem();
+            tc_fence_before();
+            __syncthreads();
+            // ---- sign sketch: proj[vec][i] = sum_j e[vec][j] * P'[i][j], three float16 product terms
+            if (tid == 0) {
+                tc_fence_after();
+                const uint32_t ah = sm_addr(Xcur), al = sm_addr(Elo), pa = sm_addr(Pb);
+                const uint32_t lbo_p = (uint32_t)(M / 8) * 128;
+                const uint32_t idesc = umma_idesc_f16(M);
+#pragma unroll 1
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint64_t dah = umma_desc(ah + ks * 2 * 2048, 2048, 128);
+                    const uint64_t dal = umma_desc(al + ks * 2 * 2048, 2048, 128);
+                    const uint64_t bh = umma_desc(pa + (2 * ks) * lbo_p, lbo_p, 128);
+                    const uint64_t bl = umma_desc(pa + (D / 8 + 2 * ks) * lbo_p, lbo_p, 128);
+                    umma_f16(tmem_base, dah, bh, idesc, ks ? 1u : 0u);
+                    umma_f16(tmem_base, dah, bl, idesc, 1u);
+                    umma_f16(tmem_base, dal, bh, idesc, 1u);
+                }
+                umma_commit(sm_addr(mbar));
+            }
+            ok = mbar_wait(sm_addr(mbar), phase) && ok;
+            phase ^= 1u;
+            tc_fence_after();
+            if (wg * 32 < M) {
+                float pr[32];
+                tmem_ld32(pr, tmem_lane + wg * 32);
+                uint32_t w = 0;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) w |= (pr[j] >= 0.f ? 1u : 0u) << j;
+                uint8_t* dst = bits_s + row * (M / 8) + wg * 4;
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (wg * 32 + k * 8 < M) dst[k] = (uint8_t)(w >> (8 * k));
+            }
+        }
+        tc_fence_before();
+        __syncthreads();
 
         // ---- coalesced copy-out of the tile
         {
             const int n_bytes = n_valid * VB;                       // multiple of 4
             uint8_t* dst = p.blocks_out + v0 * VB;                  // 16-byte aligned (v0 % 128 == 0)
             const int n16 = n_bytes / 16;
-            for (int c = tid; c < n16; c += kCompressThreads)
+            for (int c = tid; c < n16; c += THREADS)
                 reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(outs)[c];
             const int rest4 = (n_bytes & 15) >> 2;                  // ragged end in 4-byte words
             if (tid < rest4)
                 reinterpret_cast<uint32_t*>(dst)[n16 * 4 + tid] = reinterpret_cast<const uint32_t*>(outs)[n16 * 4 + tid];
             if (QJL) {
-                const int M8 = p.jl_dim / 8;
+                const int M8 = M / 8;
                 uint8_t* bd = p.qjl_bits_out + v0 * M8;
                 const int nb = n_valid * M8;
                 if ((M8 & 3) == 0) {
-                    for (int c = tid; c < nb / 4; c += kCompressThreads)
+                    for (int c = tid; c < nb / 4; c += THREADS)
                         reinterpret_cast<uint32_t*>(bd)[c] = reinterpret_cast<const uint32_t*>(bits_s)[c];
                 } else {
-                    for (int c = tid; c < nb; c += kCompressThreads) bd[c] = bits_s[c];
+                    for (int c = tid; c < nb; c += THREADS) bd[c] = bits_s[c];
                 }
-                for (int r = tid; r < n_valid; r += kCompressThreads) {
+                for (int r = tid; r < n_valid; r += THREADS) {
                     float n2 = 0.f;
 #pragma unroll
-                    for (int k = 0; k < WN; ++k) n2 += enorm2[WN * r + k];
+                    for (int k = 0; k < WG; ++k) n2 += enorm2[r * WG + k];
                     p.qjl_norm_out[v0 + r] = __float2half_rn(fminf(sqrtf(n2) / escale[r], 65504.0f));
                 }
             }
         }
-        __syncthreads();   // outs / Xs are rewritten by the next tile
-        if (!QJL) { __half* tmp = Xcur; Xcur = Xnext; Xnext = tmp; }
+        __syncthreads();   // outs and the tiles are rewritten by the next iteration
+        if (!QJL) { uint8_t* tmp = Xcur; Xcur = Xnext; Xnext = tmp; }
     }
     cp_async_wait<0>();
-}
-
-template <int D, int BITS, bool QJL>
-static size_t compress_smem_bytes(int jl_dim) {
-    constexpr int RS = CompressSmem<D>::kRStride, XS = CompressSmem<D>::kXStride;
-    size_t b = (size_t)D * RS * 2 + (size_t)kTileVecs * XS * 2 + (size_t)kTileVecs * (D / 32) * block_bytes(BITS);
-    if (QJL)
-        b += (size_t)jl_dim * RS * 2 + (size_t)kTileVecs * XS * 2 + (size_t)kTileVecs * (jl_dim / 8);
-    b += kTileVecs * 4 + kTileVecs * 16;                 // residual scale / norm slots (laid out in both modes)
-    b += 64 + 256 * 8 * (QJL ? 1 : 16);                  // codebook + index-search table copies
-    if (!QJL) b += (size_t)kTileVecs * XS * 2;           // prefetch buffer
-    return b + 16;
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, C::kTmemCols);
+    (void)ok;
 }
 
 template <int D, int BITS, bool QJL>
 static int launch_compress(const CompressParams& p, cudaStream_t stream) {
+    using C = CompressCfg<D, BITS, QJL>;
     static int sm_count = 0;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return PQ_ERR_CUDA;
     if (sm_count == 0 && cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
         return PQ_ERR_CUDA;
-    const size_t smem = compress_smem_bytes<D, BITS, QJL>(p.jl_dim);
+    const size_t smem = C::smem_bytes(p.jl_dim);
     auto kern = pq_compress_kernel<D, BITS, QJL>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return PQ_ERR_CUDA;
-    int per_sm = 1;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, compress_threads(D), smem) != cudaSuccess || per_sm < 1)
-        return PQ_ERR_CUDA;
     const int64_t n_tiles = (p.n_vec + kTileVecs - 1) / kTileVecs;
-    const int64_t cap = (int64_t)sm_count * per_sm;
-    const int grid = (int)(n_tiles < cap ? n_tiles : cap);
-    kern<<<grid, compress_threads(D), smem, stream>>>(p);
+    // one CTA per SM: a CTA holds up to all 512 tensor-memory columns of its SM
+    const int grid = (int)(n_tiles < sm_count ? n_tiles : sm_count);
+    kern<<<grid, C::THREADS, smem, stream>>>(p);
     return cudaGetLastError() == cudaSuccess ? PQ_OK : PQ_ERR_CUDA;
 }
 
