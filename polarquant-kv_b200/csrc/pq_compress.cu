@@ -34,6 +34,11 @@
 
 #include "pq_common.cuh"
 
+// 16-wide k-steps accumulated inside the tensor core before a round-to-nearest float32 add
+#ifndef PQ_COMPRESS_KSTEPS_PER_GROUP
+#define PQ_COMPRESS_KSTEPS_PER_GROUP 4
+#endif
+
 namespace pq {
 
 constexpr int kTileVecs = 128;
@@ -145,7 +150,12 @@ struct CompressCfg {
     static constexpr int VB = (D / 32) * block_bytes(BITS);   // bytes per stored vector
     static constexpr int kRBytes = 4 * D * D;                 // [2D/8 chunks][D rows][16 B]
     static constexpr int kXBytes = (D / 8) * 2048;            // [D/8 chunks][128 rows][16 B]
-    static constexpr int kTmemCols = (D / 32) * D;            // one accumulator of D columns per K group
+    static constexpr int KPG = PQ_COMPRESS_KSTEPS_PER_GROUP < D / 16 ? PQ_COMPRESS_KSTEPS_PER_GROUP : D / 16;
+    static constexpr int KG = (D / 16) / KPG;                 // K groups = TMEM accumulators per tile
+    // tensor-memory columns of one accumulator buffer (the sketch reuses it and needs jl_dim <= 128
+    // columns); without QJL two buffers alternate so the next tile's MMAs overlap this tile's epilogue
+    static constexpr int kBufCols = (KG * D < 128 && QJL) ? 128 : KG * D;
+    static constexpr int kTmemCols = QJL ? kBufCols : 2 * kBufCols;
     __host__ __device__ static size_t smem_bytes(int jl_dim) {
         size_t b = kRBytes + 2 * (size_t)kXBytes + (size_t)kTileVecs * VB + 256 * 8 * BREP + 64 +
                    kTileVecs * 4 + kTileVecs * WG * 4 + 64;
@@ -228,45 +238,50 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
     uint8_t* Xcur = Xa;
     uint8_t* Xnext = QJL ? Xa : Xb;
     uint8_t* Elo = Xb;
-    if (!QJL && (int64_t)blockIdx.x < n_tiles) load_tile(blockIdx.x, Xcur);
-    cp_async_commit();
+    // rotation of one tile: KG accumulators (KPG 16-wide k-steps each, hi then lo term)
+    auto issue_rotation = [&](const uint8_t* X, uint32_t tcol) {
+        tc_fence_after();
+        const uint32_t xaddr = sm_addr(X), raddr = sm_addr(Rb);
+        constexpr uint32_t idesc = umma_idesc_f16(D);
+        constexpr int KG = C::KG, KPG = C::KPG;
+#pragma unroll
+        for (int grp = 0; grp < KG; ++grp) {
+#pragma unroll
+            for (int k2 = 0; k2 < KPG; ++k2) {
+                const int ks = grp * KPG + k2;
+                const uint64_t da = umma_desc(xaddr + ks * 2 * 2048, 2048, 128);
+                const uint64_t bh = umma_desc(raddr + (2 * ks) * LBO_R, LBO_R, 128);
+                const uint64_t bl = umma_desc(raddr + (D / 8 + 2 * ks) * LBO_R, LBO_R, 128);
+                umma_f16(tmem_base + tcol + grp * D, da, bh, idesc, k2 ? 1u : 0u);
+                umma_f16(tmem_base + tcol + grp * D, da, bl, idesc, 1u);
+            }
+        }
+        umma_commit(sm_addr(mbar));
+    };
+    if (!QJL && (int64_t)blockIdx.x < n_tiles) {
+        // pipeline fill: first tile's MMAs issued, second tile's load in flight
+        load_tile(blockIdx.x, Xcur);
+        cp_async_commit();
+        cp_async_wait<0>();
+        fence_async_smem();
+        __syncthreads();
+        if (tid == 0) issue_rotation(Xcur, 0u);
+        if ((int64_t)blockIdx.x + gridDim.x < n_tiles) load_tile(blockIdx.x + gridDim.x, Xnext);
+        cp_async_commit();
+    }
 
-    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    uint32_t it = 0;
+    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
         const int64_t v0 = tile * kTileVecs;
         const int n_valid = (int)min((int64_t)kTileVecs, p.n_vec - v0);
+        const uint32_t tcol = QJL ? 0u : (it & 1u) * C::kBufCols;     // this tile's accumulator buffer
         if (QJL) {
             load_tile(tile, Xcur);
             cp_async_commit();
             cp_async_wait<0>();
-        } else {
-            // this tile was requested one iteration ago; request the next one into the other buffer
-            if (tile + gridDim.x < n_tiles) load_tile(tile + gridDim.x, Xnext);
-            cp_async_commit();
-            cp_async_wait<1>();
-        }
-        fence_async_smem();          // the tensor core reads shared memory through the async proxy
-        __syncthreads();
-
-        // ---- rotation: D/32 accumulators (K groups of two 16-wide steps, hi then lo term)
-        if (tid == 0) {
-            tc_fence_after();
-            const uint32_t xaddr = sm_addr(Xcur), raddr = sm_addr(Rb);
-            constexpr uint32_t idesc = umma_idesc_f16(D);
-#pragma unroll
-            for (int grp = 0; grp < D / 32; ++grp) {
-#pragma unroll
-                for (int k2 = 0; k2 < 2; ++k2) {
-                    const int ks = grp * 2 + k2;
-                    const uint64_t da = umma_desc(xaddr + ks * 2 * 2048, 2048, 128);
-                    const uint64_t bh = umma_desc(raddr + (2 * ks) * LBO_R, LBO_R, 128);
-                    const uint64_t bl = umma_desc(raddr + (D / 8 + 2 * ks) * LBO_R, LBO_R, 128);
-                    umma_f16(tmem_base + grp * D, da, bh, idesc, k2 ? 1u : 0u);
-                    umma_f16(tmem_base + grp * D, da, bl, idesc, 1u);
-                }
-            }
-            umma_commit(sm_addr(mbar));
-        }
-        if (QJL) {
+            fence_async_smem();      // the tensor core reads shared memory through the async proxy
+            __syncthreads();
+            if (tid == 0) issue_rotation(Xcur, 0u);
             // power-of-two scale per vector so the residual split stays in float16 range:
             // |e_j| < 32 * max|x_j|, scaled to below 2^15.  (Reads the vector tile while the MMAs run.)
             constexpr int PARTS = THREADS / kTileVecs;                  // threads per row
@@ -289,23 +304,36 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
                 escale[r] = (vmax > 0.f) ? __uint_as_float((263u - be) << 23) : 1.0f;
             }
             __syncthreads();
+            ok = mbar_wait(sm_addr(mbar), phase) && ok;
+            phase ^= 1u;
+            tc_fence_after();
+        } else {
+            // This tile's MMAs were issued one iteration ago; the next tile's vectors are landing in
+            // Xnext.  Wait for both, start the next tile's MMAs into the other accumulator buffer and
+            // refill the vector buffer this tile just released - all of it overlaps the epilogue.
+            cp_async_wait<0>();
+            fence_async_smem();
+            __syncthreads();
+            ok = mbar_wait(sm_addr(mbar), phase) && ok;
+            phase ^= 1u;
+            tc_fence_after();
+            const int64_t next = tile + gridDim.x, next2 = next + gridDim.x;
+            if (next < n_tiles && tid == 0) issue_rotation(Xnext, ((it + 1u) & 1u) * C::kBufCols);
+            if (next2 < n_tiles) load_tile(next2, Xcur);
+            cp_async_commit();
         }
-        ok = mbar_wait(sm_addr(mbar), phase) && ok;
-        phase ^= 1u;
-        tc_fence_after();
+        const uint32_t tmem_tile = tmem_lane + tcol;
 
         // ---- epilogue: this thread owns vector `row`, block `wg`
-        float v[32];
-        tmem_ld32(v, tmem_lane + wg * 32);
+        float v[32];                    // 4096 * rotated coordinates (the scale is a power of two:
+        tmem_ld32(v, tmem_tile + wg * 32);   // every rounding below commutes with it)
 #pragma unroll
-        for (int grp = 1; grp < D / 32; ++grp) {
+        for (int grp = 1; grp < C::KG; ++grp) {
             float part[32];
-            tmem_ld32(part, tmem_lane + grp * D + wg * 32);
+            tmem_ld32(part, tmem_tile + grp * D + wg * 32);
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = __fadd_rn(v[i], part[i]);
         }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] *= (1.0f / 4096.0f);
         // numpy's float32 axis-reduction order: r[j] over j, j+8, j+16, j+24, then a balanced tree
         float r8[8];
 #pragma unroll
@@ -317,16 +345,16 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
         }
         const float ss = __fadd_rn(__fadd_rn(__fadd_rn(r8[0], r8[1]), __fadd_rn(r8[2], r8[3])),
                                    __fadd_rn(__fadd_rn(r8[4], r8[5]), __fadd_rn(r8[6], r8[7])));
-        float d32 = __fsqrt_rn(ss);
-        const bool zero = d32 < 1e-30f;
-        if (zero) d32 = 0.f;
+        const float d_raw = __fsqrt_rn(ss);                          // 4096 * radius
+        const bool zero = d_raw < 4096.0f * 1e-30f;
+        const float d32 = zero ? 0.f : d_raw * (1.0f / 4096.0f);
         const __half d16 = __float2half_rn(fminf(d32, 65504.0f));
-        const float dq = __half2float(d16);
-        // x / d32 with IEEE rounding from a correctly rounded reciprocal and one residual
+        const float dq = __half2float(d16) * 4096.0f;
+        // x / d with IEEE rounding from a correctly rounded reciprocal and one residual
         // correction (no mismatch against true division in 2e6 samples)
-        const float dsafe = zero ? 1.f : d32;
+        const float dsafe = zero ? 1.f : d_raw;
         const float rinv = __frcp_rn(dsafe);
-        const float es = QJL ? escale[row] : 1.f;
+        const float es = QJL ? escale[row] * (1.0f / 4096.0f) : 1.f;
         float en2 = 0.f;
         uint32_t packed[BITS];                                        // 32 indices, low index first
 #pragma unroll
@@ -386,9 +414,9 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
                     const uint64_t dal = umma_desc(al + ks * 2 * 2048, 2048, 128);
                     const uint64_t bh = umma_desc(pa + (2 * ks) * lbo_p, lbo_p, 128);
                     const uint64_t bl = umma_desc(pa + (D / 8 + 2 * ks) * lbo_p, lbo_p, 128);
-                    umma_f16(tmem_base, dah, bh, idesc, ks ? 1u : 0u);
-                    umma_f16(tmem_base, dah, bl, idesc, 1u);
-                    umma_f16(tmem_base, dal, bh, idesc, 1u);
+                    umma_f16(tmem_base + tcol, dah, bh, idesc, ks ? 1u : 0u);
+                    umma_f16(tmem_base + tcol, dah, bl, idesc, 1u);
+                    umma_f16(tmem_base + tcol, dal, bh, idesc, 1u);
                 }
                 umma_commit(sm_addr(mbar));
             }
@@ -397,7 +425,7 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
             tc_fence_after();
             if (wg * 32 < M) {
                 float pr[32];
-                tmem_ld32(pr, tmem_lane + wg * 32);
+                tmem_ld32(pr, tmem_tile + wg * 32);
                 uint32_t w = 0;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) w |= (pr[j] >= 0.f ? 1u : 0u) << j;

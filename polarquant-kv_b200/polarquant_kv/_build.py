@@ -49,6 +49,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
               "-Xcompiler", "-fPIC", "-I", INCLUDE, "-I", CSRC]
     if verbose:
         common += ["-Xptxas", "-v"]
+    common += os.environ.get("PQ_NVCC_FLAGS", "").split()     # extra flags for experiments
     procs = []
     for src in SOURCES:
         path = os.path.join(CSRC, src)
