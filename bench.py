@@ -226,6 +226,9 @@ def run_ours(args):
 
     w = WORKLOAD
     B, Hq, D = w["batch"], w["q_heads"], w["head_dim"]
+    if args.only_compress:
+        w = dict(w, batch=1, context=256)        # a token-sized decode set-up; only compress is measured
+        B = 1
     alg_bytes = algorithmic_bytes(w)
     # two independent caches, alternated between steps, so no step finds its data in L2
     sets = [build_cache(w, dev, 1000 * rank + i) for i in range(2)]
@@ -287,7 +290,7 @@ def run_ours(args):
     # ---- secondary: bulk compress throughput (4-bit, with and without the QJL sketch)
     from polarquant_kv.qjl import generate_jl_matrix
     from polarquant_kv.rotation import device_plan, generate_rotation_matrix
-    n = 1024 if args.only_decode else COMPRESS_VECS
+    n = 1024 if args.only_decode else args.compress_vecs
     x = (torch.randn((n, D), generator=gen, device=dev) * torch.exp(torch.randn(D, generator=gen, device=dev))).to(torch.float16)
     x2 = x.flip(0).contiguous()
     Rm = generate_rotation_matrix(D, 0)
@@ -315,6 +318,14 @@ def run_ours(args):
         return
 
     peak, peak_kind = measured_peak()
+    if args.only_compress:
+        for c in comp.values():
+            c["frac_of_hbm_peak"] = round(c["achieved_gbs"] / peak, 4)
+        print(json.dumps({"metric": "block_pq4 compress throughput", "unit": "Mvec/s", "n_gpus": world,
+                          "compress": comp, "peak_gbs": peak, "peak_kind": f"of {peak_kind}"}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     ms_step = ms_total / args.steps
     achieved = alg_bytes / (ms_step * 1e-3) / 1e9            # per GPU: one launch per step per GPU
     value = achieved * world
@@ -349,7 +360,7 @@ def run_ours(args):
                    "l2": "two 302 MB caches alternated between steps (each larger than the 126 MB L2)"},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "traffic": traffic, "peak_kind": f"of {peak_kind}",
-                     "kernel": "pq_decode_attn_kernel<128,4,4,false>", "algorithmic_bytes_per_launch": alg_bytes},
+                     "kernel": "pq_decode_attn_kernel<128,4,4,1,false>", "algorithmic_bytes_per_launch": alg_bytes},
         "e2e": {"value": round(e2e_val, 1), "unit": "GB/s", "h2d_bytes_per_step": q_host.numel() * 2,
                 "d2h_bytes_per_step": out_host.numel() * 4, "ms_per_step": round(ms_e2e / args.steps, 5)},
         "gpu_launches": args.steps,
@@ -374,6 +385,9 @@ def main():
     ap.add_argument("--only-decode", action="store_true",
                     help="skip the compress and CPU-baseline measurements (profiler captures)")
     ap.add_argument("--splits", type=int, default=0, help="sequence splits per (batch, kv head); 0 = library default")
+    ap.add_argument("--only-compress", action="store_true",
+                    help="run only the bulk-compress measurement and print its JSON (profiler captures)")
+    ap.add_argument("--compress-vecs", type=int, default=COMPRESS_VECS, help="vectors per compress launch")
     args = ap.parse_args()
     WORKLOAD["batch"] = args.batch
     if args.impl == "reference":
