@@ -113,6 +113,9 @@ __device__ __forceinline__ void tmem_ld32(float (&v)[32], uint32_t taddr) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_ld32(float2 (&v)[16], uint32_t taddr) {
+    tmem_ld32(*reinterpret_cast<float(*)[32]>(&v[0]), taddr);
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
@@ -135,6 +138,30 @@ __device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity) {
         if (done) return true;
     }
     return false;
+}
+
+// Packed float32x2 arithmetic (sm_100): two IEEE round-to-nearest operations per instruction.
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;\n"
+        : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+    return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 d;
+    asm("add.rn.f32x2 %0, %1, %2;\n"
+        : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+    return d;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n"
+        : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+          "l"(*reinterpret_cast<unsigned long long*>(&c)));
+    return d;
 }
 
 // Byte offset of 16-byte chunk `kc` of row `r` in a K-major operand tile with `rows` rows.
@@ -225,14 +252,24 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
     bool ok = true;
 
     const int64_t n_tiles = (p.n_vec + kTileVecs - 1) / kTileVecs;
+    // every tile is copied with the same per-thread chunk pattern: keep the offsets in registers
+    constexpr int NCH = kTileVecs * (D / 8) / THREADS;               // 16-byte chunks per thread
+    uint32_t ch_soff[NCH], ch_goff[NCH];
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+        const int id = tid + i * THREADS;
+        const int m = ((id >> 5) & 15) * 8 + (id & 7), kc = (id >> 9) * 4 + ((id >> 3) & 3);
+        ch_soff[i] = chunk_off(kTileVecs, m, kc);
+        ch_goff[i] = (uint32_t)(m * D + kc * 8);                     // in halves; row = goff / D
+    }
     auto load_tile = [&](int64_t tile, uint8_t* dst) {
         const int64_t v0 = tile * kTileVecs;
-        const int n_valid = (int)min((int64_t)kTileVecs, p.n_vec - v0);
-        for (int id = tid; id < kTileVecs * (D / 8); id += THREADS) {
-            const int m = ((id >> 5) & 15) * 8 + (id & 7), kc = (id >> 9) * 4 + ((id >> 3) & 3);
-            uint8_t* d = dst + chunk_off(kTileVecs, m, kc);
-            if (m < n_valid) cp_async_16(d, p.x + (v0 + m) * D + kc * 8);
-            else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);          // rows past the end
+        const uint32_t valid_halves = (uint32_t)min((int64_t)kTileVecs, p.n_vec - v0) * D;
+        const __half* src = p.x + v0 * D;
+#pragma unroll
+        for (int i = 0; i < NCH; ++i) {
+            if (ch_goff[i] < valid_halves) cp_async_16(dst + ch_soff[i], src + ch_goff[i]);
+            else *reinterpret_cast<uint4*>(dst + ch_soff[i]) = make_uint4(0, 0, 0, 0);   // rows past the end
         }
     };
     uint8_t* Xcur = Xa;
@@ -325,26 +362,27 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
         const uint32_t tmem_tile = tmem_lane + tcol;
 
         // ---- epilogue: this thread owns vector `row`, block `wg`
-        float v[32];                    // 4096 * rotated coordinates (the scale is a power of two:
-        tmem_ld32(v, tmem_tile + wg * 32);   // every rounding below commutes with it)
+        float2 v2[16];                  // 4096 * rotated coordinates, pairs (2k, 2k+1); the scale is a
+        tmem_ld32(v2, tmem_tile + wg * 32);  // power of two: every rounding below commutes with it
 #pragma unroll
         for (int grp = 1; grp < C::KG; ++grp) {
-            float part[32];
+            float2 part[16];
             tmem_ld32(part, tmem_tile + grp * D + wg * 32);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __fadd_rn(v[i], part[i]);
+            for (int k = 0; k < 16; ++k) v2[k] = add2(v2[k], part[k]);
         }
-        // numpy's float32 axis-reduction order: r[j] over j, j+8, j+16, j+24, then a balanced tree
-        float r8[8];
+        // numpy's float32 axis-reduction order: r[j] over j, j+8, j+16, j+24 (products rounded
+        // separately), then a balanced tree
+        float2 r2[4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            float s = __fmul_rn(v[j], v[j]);
-            s = __fadd_rn(s, __fmul_rn(v[8 + j], v[8 + j]));
-            s = __fadd_rn(s, __fmul_rn(v[16 + j], v[16 + j]));
-            r8[j] = __fadd_rn(s, __fmul_rn(v[24 + j], v[24 + j]));
+        for (int q = 0; q < 4; ++q) {
+            float2 a = mul2(v2[q], v2[q]);
+            a = add2(a, mul2(v2[4 + q], v2[4 + q]));
+            a = add2(a, mul2(v2[8 + q], v2[8 + q]));
+            r2[q] = add2(a, mul2(v2[12 + q], v2[12 + q]));
         }
-        const float ss = __fadd_rn(__fadd_rn(__fadd_rn(r8[0], r8[1]), __fadd_rn(r8[2], r8[3])),
-                                   __fadd_rn(__fadd_rn(r8[4], r8[5]), __fadd_rn(r8[6], r8[7])));
+        const float ss = __fadd_rn(__fadd_rn(__fadd_rn(r2[0].x, r2[0].y), __fadd_rn(r2[1].x, r2[1].y)),
+                                   __fadd_rn(__fadd_rn(r2[2].x, r2[2].y), __fadd_rn(r2[3].x, r2[3].y)));
         const float d_raw = __fsqrt_rn(ss);                          // 4096 * radius
         const bool zero = d_raw < 4096.0f * 1e-30f;
         const float d32 = zero ? 0.f : d_raw * (1.0f / 4096.0f);
@@ -354,25 +392,38 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
         // correction (no mismatch against true division in 2e6 samples)
         const float dsafe = zero ? 1.f : d_raw;
         const float rinv = __frcp_rn(dsafe);
+        const float2 rinv2 = make_float2(rinv, rinv), negd2 = make_float2(-dsafe, -dsafe);
+        const float2 c64 = make_float2(64.f, 64.f), cmagic = make_float2(8388672.f, 8388672.f);
         const float es = QJL ? escale[row] * (1.0f / 4096.0f) : 1.f;
         float en2 = 0.f;
         uint32_t packed[BITS];                                        // 32 indices, low index first
 #pragma unroll
         for (int w = 0; w < BITS; ++w) packed[w] = 0u;
         uint32_t ehi[16], elo[16];
+        float* v = reinterpret_cast<float*>(&v2[0]);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            const float y0 = __fmul_rn(v[j], rinv);
-            const float dir = fmaf(fmaf(-y0, dsafe, v[j]), rinv, y0);
-            const uint32_t bk = __float_as_uint(fmaf(dir, 64.f, 8388672.f)) & 0xFFu;
-            const uint2 be = bucket_lane[bk * BREP];
-            const uint32_t id = zero ? 0u : be.y + ((dir > __uint_as_float(be.x)) ? 1u : 0u);
-            packed[(j * BITS) >> 5] |= id << ((j * BITS) & 31);
-            if (QJL) {
-                const float ee = (v[j] - __fmul_rn(dq, cb_s[id])) * es;
-                en2 = fmaf(ee, ee, en2);
-                v[j] = ee;
+        for (int k = 0; k < 16; ++k) {
+            const float2 y0 = mul2(v2[k], rinv2);
+            const float2 dir = fma2(fma2(y0, negd2, v2[k]), rinv2, y0);
+            const float2 u = fma2(dir, c64, cmagic);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = 2 * k + e;
+                const float dj = e ? dir.y : dir.x;
+                const uint32_t bk = __float_as_uint(e ? u.y : u.x) & 0xFFu;
+                const uint2 be = bucket_lane[bk * BREP];
+                const uint32_t id = be.y + ((dj > __uint_as_float(be.x)) ? 1u : 0u);
+                packed[(j * BITS) >> 5] |= id << ((j * BITS) & 31);
+                if (QJL) {
+                    const float ee = (v[j] - __fmul_rn(dq, cb_s[zero ? 0u : id])) * es;
+                    en2 = fmaf(ee, ee, en2);
+                    v[j] = ee;
+                }
             }
+        }
+        if (zero) {                                                   // all-zero block: indices 0
+#pragma unroll
+            for (int w = 0; w < BITS; ++w) packed[w] = 0u;
         }
         {
             uint16_t* ob = reinterpret_cast<uint16_t*>(outs + row * VB + wg * BB);
