@@ -296,20 +296,34 @@ def run_ours(args):
     Rm = generate_rotation_matrix(D, 0)
     plan_q = device_plan(Rm, dev, generate_jl_matrix(D, D, 1))
     comp = {}
-    for label, pl, jl in (() if args.only_decode else (("4bit", plan, None), ("4bit_qjl", plan_q, True))):
-        outs = [quantizer.allocate_cache(1, 1, n, D, 4, D if jl else 0, dev) for _ in range(2)]
+    # variants: (label, [(bits, share of the vectors)], with QJL sketch); "mixed" = first half of the
+    # vectors (heads) at 4-bit, the rest at 2-bit, as two launches
+    variants = (("4bit", [(4, 1.0)], False), ("2bit", [(2, 1.0)], False),
+                ("mixed_4bit_2bit", [(4, 0.5), (2, 0.5)], False), ("4bit_qjl", [(4, 1.0)], True))
+    for label, parts, jl in (() if args.only_decode else variants):
+        pl = plan_q if jl else plan
+        jobs = []
+        lo = 0
+        for bits, share in parts:
+            cnt = int(n * share)
+            jobs.append((bits, lo, cnt, [quantizer.allocate_cache(1, 1, cnt, D, bits, D if jl else 0, dev)
+                                          for _ in range(2)]))
+            lo += cnt
         xs = [x.view(1, 1, n, D), x2.view(1, 1, n, D)]
 
-        def cstep(i, pl=pl, jl=jl, outs=outs, xs=xs):
-            quantizer.compress(xs[i & 1], pl, 4, 32, pl.jl if jl else None, out=outs[i & 1], position=0)
+        def cstep(i, pl=pl, jl=jl, jobs=jobs, xs=xs):
+            for bits, lo, cnt, outs in jobs:
+                quantizer.compress(xs[i & 1][:, :, lo:lo + cnt], pl, bits, 32, pl.jl if jl else None,
+                                   out=outs[i & 1], position=0)
 
         for i in range(3):
             cstep(i)
-        cms = timed(cstep, max(4, min(args.steps, 20)))
-        per_launch = cms / max(4, min(args.steps, 20))
-        bytes_per_vec = 2 * D + (D // 32) * 18 + ((D // 8 + 2) if jl else 0)
-        comp[label] = {"mvec_per_s": round(n * world / per_launch / 1e3, 1), "ms_per_launch": round(per_launch, 4),
-                       "vectors_per_launch": n, "bytes_per_vector": bytes_per_vec,
+        k = max(4, min(args.steps, 20))
+        per_launch = timed(cstep, k) / k
+        out_bytes = sum(share * (D // 32) * (2 + 4 * bits) for bits, share in parts)
+        bytes_per_vec = 2 * D + out_bytes + ((D // 8 + 2) if jl else 0)
+        comp[label] = {"mvec_per_s": round(n * world / per_launch / 1e3, 1), "ms_per_step": round(per_launch, 4),
+                       "vectors_per_step": n, "launches_per_step": len(jobs), "bytes_per_vector": bytes_per_vec,
                        "achieved_gbs": round(n * bytes_per_vec / per_launch / 1e6, 1)}
 
     if rank != 0:

@@ -86,6 +86,13 @@ int pq_compress(const void* x, int64_t n_vec, int head_dim, int n_bits,
                 const void* jl_split, int jl_dim, void* qjl_bits_out, void* qjl_norm_out,
                 void* stream);
 
+/* pq_poll_device_errors — HOST-synchronising check for device-side failures of earlier launches on
+ * the current device.  The compress kernel waits for its tensor-core work through a barrier with
+ * an iteration limit (so that a lost completion can never hang the GPU); if a wait ever gives up,
+ * bit 0 of *flags_out is set and the output of that launch must be discarded.  The flags are
+ * cleared by the call.  No counterpart in the reference (its kernels report nothing). */
+int pq_poll_device_errors(unsigned int* flags_out);
+
 /* ---------------------------------------------------------------------------------
  * pq_dequant — blocks -> centroid * d -> inverse rotation (v @ R).
  *

@@ -41,6 +41,10 @@
 
 namespace pq {
 
+// Set (bit 0) when a bounded wait on a tensor-core completion barrier gave up; read and cleared
+// by pq_poll_device_errors().  A set bit means the results of that launch are not valid.
+static __device__ unsigned int g_compress_error = 0;
+
 constexpr int kTileVecs = 128;
 // warps: 4 per warpgroup (TMEM lanes 0..127 = vectors) x D/32 warpgroups (one block each)
 __host__ __device__ constexpr int compress_threads(int D) { return 32 * 4 * (D / 32); }
@@ -524,7 +528,7 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_base, C::kTmemCols);
-    (void)ok;
+    if (!ok && lane == 0) atomicOr(&g_compress_error, 1u);
 }
 
 template <int D, int BITS, bool QJL>
@@ -547,6 +551,15 @@ static int launch_compress(const CompressParams& p, cudaStream_t stream) {
 }
 
 }  // namespace pq
+
+extern "C" int pq_poll_device_errors(unsigned int* flags_out) {
+    if (!flags_out) return PQ_ERR_NULL_POINTER;
+    unsigned int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, pq::g_compress_error, sizeof(v)) != cudaSuccess) return PQ_ERR_CUDA;
+    if (v && cudaMemcpyToSymbol(pq::g_compress_error, &zero, sizeof(zero)) != cudaSuccess) return PQ_ERR_CUDA;
+    *flags_out = v;
+    return PQ_OK;
+}
 
 extern "C" int pq_compress(const void* x, int64_t n_vec, int head_dim, int n_bits,
                            const void* rot_split, const float* thresholds, const float* codebook,

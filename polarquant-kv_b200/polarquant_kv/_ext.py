@@ -21,6 +21,7 @@ c_float_p = ctypes.POINTER(ctypes.c_float)
 SIGNATURES = {
     "pq_version": (c_int, []),
     "pq_strerror": (ctypes.c_char_p, [c_int]),
+    "pq_poll_device_errors": (c_int, [ctypes.POINTER(ctypes.c_uint)]),
     "pq_compress": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_float_p, c_float_p, c_void_p,
                             c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "pq_dequant": (c_int, [c_void_p, c_int64, c_int, c_int, c_float_p, c_void_p, c_void_p, c_int, c_void_p]),
@@ -77,6 +78,16 @@ def lib() -> ctypes.CDLL:
 def check(status: int, where: str) -> None:
     if status != 0:
         raise PQError(status, where)
+
+
+def poll_device_errors() -> int:
+    """Synchronising check of the device-side error flags (0 = none); raises on a set flag."""
+    flags = ctypes.c_uint(0)
+    check(lib().pq_poll_device_errors(ctypes.byref(flags)), "pq_poll_device_errors")
+    if flags.value:
+        raise RuntimeError(f"device-side error flags {flags.value:#x}: a bounded tensor-core wait gave up; "
+                           "results of the affected launch are invalid")
+    return flags.value
 
 
 def float_array(values) -> ctypes.Array:
