@@ -326,6 +326,28 @@ def run_ours(args):
                        "vectors_per_step": n, "launches_per_step": len(jobs), "bytes_per_vector": bytes_per_vec,
                        "achieved_gbs": round(n * bytes_per_vec / per_launch / 1e6, 1)}
 
+    # ---- secondary: prefill-shape attention over the compressed cache (tensor-core bound)
+    prefill = None
+    if not args.only_decode and not args.only_compress:
+        Sq, Sp, Bp = 512, 4096, 2
+        _, ck0, cv0 = sets[0]
+        ckp = type(ck0)(ck0.blocks[:Bp, :, :Sp].contiguous(), None, None, 4, 32, D, Sp, Sp)
+        cvp = type(cv0)(cv0.blocks[:Bp, :, :Sp].contiguous(), None, None, 4, 32, D, Sp, Sp)
+        qp = torch.randn((Bp, Hq, Sq, D), generator=gen, device=dev).to(torch.float16)
+
+        def pstep(i):
+            attention.prefill_attention(qp, ckp, cvp, plan)
+
+        for i in range(2):
+            pstep(i)
+        kp = max(3, min(args.steps, 10))
+        pms = timed(pstep, kp) / kp
+        useful = 4.0 * Bp * Hq * Sq * Sp * D                       # QK^T and PV multiply-adds x2
+        prefill = {"shape": {"batch": Bp, "q_heads": Hq, "kv_heads": w["kv_heads"], "seq_q": Sq, "seq_kv": Sp,
+                             "head_dim": D}, "ms": round(pms, 4),
+                   "useful_tflops": round(useful / pms / 1e9, 1),
+                   "issued_tflops_3_term_fp16": round(3 * useful / pms / 1e9, 1)}
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -379,6 +401,7 @@ def run_ours(args):
                 "d2h_bytes_per_step": out_host.numel() * 4, "ms_per_step": round(ms_e2e / args.steps, 5)},
         "gpu_launches": args.steps,
         "compress": comp,
+        "prefill": prefill,
         "cpu_baseline": {"value": round(cpu_gbs, 4), "unit": "GB/s", "cores": blas_threads, "kind": "port",
                          "sample": f"{rows} (batch, kv-head) rows of the workload in {cpu_dt:.1f} s, numpy oracle, one process"},
         "clocks": clocks,

@@ -74,7 +74,7 @@ const char* pq_strerror(int status);
  *   thresholds  HOST float32 [2^n_bits - 1]: index = number of thresholds strictly below the
  *               normalised coordinate; exact decision points of argmin|v - c_i| in float32
  *   codebook    HOST float32 [2^n_bits] centroids (used for the QJL residual only)
- *   blocks_out  uint8 [n_vec, head_dim/32, block_bytes], 16-byte aligned
+ *   blocks_out  uint8 [n_vec, head_dim/32, block_bytes], 4-byte aligned (16-byte aligned is faster)
  *   jl_split    float16 [jl_dim, 2*head_dim] split of 1024*(P @ R^T), or NULL for no sketch;
  *               jl_dim a multiple of 16 in [16, 128]
  *   qjl_bits_out  uint8 [n_vec, jl_dim/8]      (required when jl_split != NULL)

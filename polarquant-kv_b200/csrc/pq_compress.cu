@@ -496,13 +496,18 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
         // ---- coalesced copy-out of the tile
         {
             const int n_bytes = n_valid * VB;                       // multiple of 4
-            uint8_t* dst = p.blocks_out + v0 * VB;                  // 16-byte aligned (v0 % 128 == 0)
-            const int n16 = n_bytes / 16;
-            for (int c = tid; c < n16; c += THREADS)
-                reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(outs)[c];
-            const int rest4 = (n_bytes & 15) >> 2;                  // ragged end in 4-byte words
-            if (tid < rest4)
-                reinterpret_cast<uint32_t*>(dst)[n16 * 4 + tid] = reinterpret_cast<const uint32_t*>(outs)[n16 * 4 + tid];
+            uint8_t* dst = p.blocks_out + v0 * VB;
+            if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                const int n16 = n_bytes / 16;
+                for (int c = tid; c < n16; c += THREADS)
+                    reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(outs)[c];
+                const int rest4 = (n_bytes & 15) >> 2;              // ragged end in 4-byte words
+                if (tid < rest4)
+                    reinterpret_cast<uint32_t*>(dst)[n16 * 4 + tid] = reinterpret_cast<const uint32_t*>(outs)[n16 * 4 + tid];
+            } else {                                                // appended at an odd token offset
+                for (int c = tid; c < n_bytes / 4; c += THREADS)
+                    reinterpret_cast<uint32_t*>(dst)[c] = reinterpret_cast<const uint32_t*>(outs)[c];
+            }
             if (QJL) {
                 const int M8 = M / 8;
                 uint8_t* bd = p.qjl_bits_out + v0 * M8;
@@ -580,7 +585,7 @@ extern "C" int pq_compress(const void* x, int64_t n_vec, int head_dim, int n_bit
         if (((jl_dim / 8) % 4 == 0) && (reinterpret_cast<uintptr_t>(qjl_bits_out) & 3)) return PQ_ERR_MISALIGNED;
     }
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(rot_split) & 15) ||
-        (reinterpret_cast<uintptr_t>(blocks_out) & 15))
+        (reinterpret_cast<uintptr_t>(blocks_out) & 3))
         return PQ_ERR_MISALIGNED;
 
     CompressParams p{};
