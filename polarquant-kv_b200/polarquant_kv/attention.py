@@ -100,6 +100,49 @@ def decode_attention(query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, pl
     return out
 
 
+class PreparedDecode:
+    """A decode-attention call with every argument resolved once (pointers, tables, scratch,
+    output buffer), for serving loops where the Python-side set-up of ``decode_attention``
+    would sit on the critical path of every token.  The cache objects and the query buffer
+    are captured by reference: update ``ck.seq_len`` / the cache contents / the query buffer in
+    place and call the object again.  Returns the (reused) output tensor."""
+
+    def __init__(self, query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, plan,
+                 scale: float | None = None, out_dtype: torch.dtype = torch.float32, n_splits: int = 0):
+        _require_cuda(query, "query")
+        if query.dtype != torch.float16 or not query.is_contiguous():
+            raise ValueError("the query buffer must be a contiguous float16 tensor [B, Hq, D]")
+        if not ck.blocks.is_contiguous() or not cv.blocks.is_contiguous():
+            raise ValueError("cache tensors must be contiguous")
+        self.query, self.ck, self.cv, self.plan = query, ck, cv, plan
+        B, Hq, D = query.shape
+        Hkv = ck.blocks.shape[1]
+        self.dev = query.device
+        self.out = torch.empty((B, Hq, D), dtype=out_dtype, device=self.dev)
+        lib = _ext.lib()
+        self._fn = lib.pq_decode_attn
+        need = lib.pq_decode_attn_scratch_bytes(B, Hq, Hkv, ck.max_seq_len, D, max(0, n_splits))
+        self.scratch = torch.zeros(max(need, 256), dtype=torch.uint8, device=self.dev)   # private: no sharing
+        cbk, cbv = tables(ck.n_bits)[0], tables(cv.n_bits)[0]
+        self._head = (query.data_ptr(), ck.blocks.data_ptr(), cv.blocks.data_ptr(), B, Hq, Hkv)
+        self._tail = (ck.max_seq_len, D, ck.n_bits, cv.n_bits, cbk, cbv, plan.rot.data_ptr(),
+                      ctypes.c_float(scale if scale is not None else 1.0 / math.sqrt(D)),
+                      None, 0, None, None, self.out.data_ptr(), 1 if out_dtype == torch.float16 else 0, None,
+                      max(0, n_splits), self.scratch.data_ptr(), self.scratch.numel())
+        self._stream = torch.cuda.current_stream(self.dev)
+
+    def __call__(self) -> torch.Tensor:
+        st = self._fn(*self._head, self.ck.seq_len, *self._tail, self._stream.cuda_stream)
+        if st:
+            _ext.check(st, "pq_decode_attn")
+        return self.out
+
+
+def prepare_decode(query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, plan, **kw) -> PreparedDecode:
+    """See PreparedDecode."""
+    return PreparedDecode(query, ck, cv, plan, **kw)
+
+
 def prefill_attention(query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, plan,
                       scale: float | None = None, causal: bool = False,
                       out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
