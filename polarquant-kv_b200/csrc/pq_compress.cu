@@ -29,8 +29,14 @@
 // Shared-memory operand layout (K-major, no swizzle): 16-byte chunks of 8 halves; chunk kc of
 // row r sits at  kc * (rows/8 * 128) + (r / 8) * 128 + (r % 8) * 16  — 8x16-byte core
 // matrices, stride 128 B between 8-row groups (SBO), rows/8*128 B between K chunks (LBO).
+// Without the sketch the vector tiles instead arrive by TMA (cp.async.bulk.tensor, one thread
+// issues, an mbarrier counts the bytes) in the 128-byte-swizzled K-major layout: boxes of
+// 128 vectors x 64 halves, rows 128 B apart, 8-row groups 1024 B apart; the packed tile
+// leaves by one bulk store.  A tile then costs one CTA-wide barrier.
 #include <cmath>
 #include <cstring>
+
+#include <cuda.h>   // CUtensorMap and its enums only; the encoder is looked up at run time
 
 #include "pq_common.cuh"
 
@@ -74,6 +80,30 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr, uint32_t 
     return (uint64_t)((smem_byte_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
            ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46);
 }
+// K-major operand in the 128-byte swizzle: rows 128 B apart, 8-row groups `sbo_bytes` apart
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_byte_addr, uint32_t sbo_bytes) {
+    return (uint64_t)((smem_byte_addr >> 4) & 0x3FFFu) | (1ull << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar_addr, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbar_addr), "r"(bytes) : "memory");
+}
+// One box of a 2-D tensor map into shared memory; x (halves) must be a multiple of 8.
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t mbar_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::
+            "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(mbar_addr)
+        : "memory");
+}
+// Contiguous shared -> global copy; both addresses and the size are multiples of 16.
+__device__ __forceinline__ void bulk_store(void* gdst, uint32_t smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(gdst), "r"(smem_src), "r"(bytes)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
 // kind::f16 instruction descriptor: D = f32, A = B = f16, both K-major, M = 128, N = n
 __host__ __device__ constexpr uint32_t umma_idesc_f16(int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
@@ -127,9 +157,10 @@ __device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(addr), "r"(count) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
 }
-// Bounded wait on a phase parity: gives up after ~2^22 polls (seconds) and reports failure,
-// so a lost completion can never hang the GPU.
+// Bounded wait on a phase parity: gives up after about a second (2^31 clock ticks, and never
+// more than 2^22 polls) and reports failure, so a lost completion can never hang the GPU.
 __device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity) {
+    long long t0 = 0;
     for (int it = 0; it < (1 << 22); ++it) {
         uint32_t done;
         asm volatile(
@@ -140,6 +171,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity) {
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
+        if ((it & 255) == 255) {
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > (1ll << 31)) return false;
+        }
     }
     return false;
 }
@@ -187,16 +223,18 @@ struct CompressCfg {
     // columns); without QJL two buffers alternate so the next tile's MMAs overlap this tile's epilogue
     static constexpr int kBufCols = (KG * D < 128 && QJL) ? 128 : KG * D;
     static constexpr int kTmemCols = QJL ? kBufCols : 2 * kBufCols;
+    static constexpr int kOutBufs = QJL ? 1 : 2;              // packed-tile staging buffers
     __host__ __device__ static size_t smem_bytes(int jl_dim) {
-        size_t b = kRBytes + 2 * (size_t)kXBytes + (size_t)kTileVecs * VB + 256 * 8 * BREP + 64 +
+        size_t b = kRBytes + 2 * (size_t)kXBytes + (size_t)kOutBufs * kTileVecs * VB + 256 * 8 * BREP + 64 +
                    kTileVecs * 4 + kTileVecs * WG * 4 + 64;
         if (QJL) b += (size_t)(2 * D / 8) * jl_dim * 16 + (size_t)kTileVecs * (jl_dim / 8);
-        return b + 128;
+        return b + 1024;                                      // the swizzled tiles sit on 1024-byte boundaries
     }
 };
 
 template <int D, int BITS, bool QJL>
-__global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(const CompressParams p) {
+__global__ void __launch_bounds__(compress_threads(D), 1)
+pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x_map) {
     using C = CompressCfg<D, BITS, QJL>;
     constexpr int THREADS = C::THREADS;
     constexpr int WG = C::WG;
@@ -208,17 +246,18 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
     const int M = QJL ? p.jl_dim : 0;
 
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    uint8_t* sp = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    uint8_t* sp = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* Rb = sp;                       sp += C::kRBytes;
     uint8_t* Xa = sp;                       sp += C::kXBytes;      // vector tile / residual hi term
     uint8_t* Xb = sp;                       sp += C::kXBytes;      // prefetch tile / residual lo term (QJL)
-    uint8_t* outs = sp;                     sp += kTileVecs * VB;
+    uint8_t* outs0 = sp;                    sp += C::kOutBufs * kTileVecs * VB;
     uint2* bucket_s = reinterpret_cast<uint2*>(sp);  sp += 256 * 8 * BREP;
     float* cb_s = reinterpret_cast<float*>(sp);      sp += 64;
     float* escale = reinterpret_cast<float*>(sp);    sp += kTileVecs * 4;
     float* enorm2 = reinterpret_cast<float*>(sp);    sp += kTileVecs * WG * 4;
     uint64_t* mbar = reinterpret_cast<uint64_t*>(sp);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sp + 8);     sp += 64;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sp + 32);
+    volatile uint32_t* abort_s = reinterpret_cast<volatile uint32_t*>(sp + 40);    sp += 64;
     uint8_t* Pb = sp;                       sp += QJL ? (2 * D / 8) * M * 16 : 0;
     uint8_t* bits_s = sp;
 
@@ -245,7 +284,10 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
         bucket_s[e] = make_uint2(__float_as_uint(p.bucket_t[k]), p.bucket_base[k]);
     }
     const uint2* bucket_lane = bucket_s + (lane % BREP);
-    if (tid == 0) mbar_init(sm_addr(mbar), 1);
+    if (tid == 0) {       // [0], [1]: MMAs of accumulator buffer 0 / 1 done; [2], [3]: vector buffer 0 / 1 landed
+        for (int i = 0; i < 4; ++i) mbar_init(sm_addr(mbar + i), 1);
+        *abort_s = 0u;
+    }
     if (warp == 0) tmem_alloc(sm_addr(tmem_slot), C::kTmemCols);
     tc_fence_before();
     __syncthreads();
@@ -276,11 +318,10 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
             else *reinterpret_cast<uint4*>(dst + ch_soff[i]) = make_uint4(0, 0, 0, 0);   // rows past the end
         }
     };
-    uint8_t* Xcur = Xa;
-    uint8_t* Xnext = QJL ? Xa : Xb;
+    uint8_t* const Xcur = Xa;      // (sketch flow) vector tile, then residual hi term
     uint8_t* Elo = Xb;
     // rotation of one tile: KG accumulators (KPG 16-wide k-steps each, hi then lo term)
-    auto issue_rotation = [&](const uint8_t* X, uint32_t tcol) {
+    auto issue_rotation = [&](const uint8_t* X, uint32_t tcol, uint64_t* done_bar) {
         tc_fence_after();
         const uint32_t xaddr = sm_addr(X), raddr = sm_addr(Rb);
         constexpr uint32_t idesc = umma_idesc_f16(D);
@@ -290,25 +331,30 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
 #pragma unroll
             for (int k2 = 0; k2 < KPG; ++k2) {
                 const int ks = grp * KPG + k2;
-                const uint64_t da = umma_desc(xaddr + ks * 2 * 2048, 2048, 128);
+                // TMA tiles: 64-half boxes of 16 KB, a k-step is 32 B further inside the swizzled row
+                const uint64_t da = QJL ? umma_desc(xaddr + ks * 2 * 2048, 2048, 128)
+                                        : umma_desc_sw128(xaddr + (ks >> 2) * 16384 + (ks & 3) * 32, 1024);
                 const uint64_t bh = umma_desc(raddr + (2 * ks) * LBO_R, LBO_R, 128);
                 const uint64_t bl = umma_desc(raddr + (D / 8 + 2 * ks) * LBO_R, LBO_R, 128);
                 umma_f16(tmem_base + tcol + grp * D, da, bh, idesc, k2 ? 1u : 0u);
                 umma_f16(tmem_base + tcol + grp * D, da, bl, idesc, 1u);
             }
         }
-        umma_commit(sm_addr(mbar));
+        umma_commit(sm_addr(done_bar));
     };
-    if (!QJL && (int64_t)blockIdx.x < n_tiles) {
-        // pipeline fill: first tile's MMAs issued, second tile's load in flight
-        load_tile(blockIdx.x, Xcur);
-        cp_async_commit();
-        cp_async_wait<0>();
-        fence_async_smem();
-        __syncthreads();
-        if (tid == 0) issue_rotation(Xcur, 0u);
-        if ((int64_t)blockIdx.x + gridDim.x < n_tiles) load_tile(blockIdx.x + gridDim.x, Xnext);
-        cp_async_commit();
+    // TMA fetch of one tile into vector buffer `buf` (rows past the end of x arrive as zeros)
+    auto fetch_tile = [&](int64_t tile, int buf) {
+        const uint32_t bar = sm_addr(mbar + 2 + buf), dst = sm_addr(buf ? Xb : Xa);
+        mbar_expect_tx(bar, (uint32_t)C::kXBytes);
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) tma_load_2d(dst + h * 16384, &x_map, h * 64, (int)(tile * kTileVecs), bar);
+    };
+    if (!QJL && tid == 0 && (int64_t)blockIdx.x < n_tiles) {
+        // pipeline fill: two tiles in flight, the first tile's MMAs issued
+        fetch_tile(blockIdx.x, 0);
+        if ((int64_t)blockIdx.x + gridDim.x < n_tiles) fetch_tile((int64_t)blockIdx.x + gridDim.x, 1);
+        ok = mbar_wait(sm_addr(mbar + 2), 0u) && ok;
+        issue_rotation(Xa, 0u, mbar);
     }
 
     uint32_t it = 0;
@@ -322,7 +368,7 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
             cp_async_wait<0>();
             fence_async_smem();      // the tensor core reads shared memory through the async proxy
             __syncthreads();
-            if (tid == 0) issue_rotation(Xcur, 0u);
+            if (tid == 0) issue_rotation(Xcur, 0u, mbar);
             // power-of-two scale per vector so the residual split stays in float16 range:
             // |e_j| < 32 * max|x_j|, scaled to below 2^15.  (Reads the vector tile while the MMAs run.)
             constexpr int PARTS = THREADS / kTileVecs;                  // threads per row
@@ -349,20 +395,24 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
             phase ^= 1u;
             tc_fence_after();
         } else {
-            // This tile's MMAs were issued one iteration ago; the next tile's vectors are landing in
-            // Xnext.  Wait for both, start the next tile's MMAs into the other accumulator buffer and
-            // refill the vector buffer this tile just released - all of it overlaps the epilogue.
-            cp_async_wait<0>();
-            fence_async_smem();
-            __syncthreads();
-            ok = mbar_wait(sm_addr(mbar), phase) && ok;
-            phase ^= 1u;
+            // This tile's MMAs were issued one iteration ago into accumulator buffer b; buffers are
+            // used every other iteration, so their barriers flip parity every second use.
+            const uint32_t b = it & 1u, par = (it >> 1) & 1u;
+            ok = mbar_wait(sm_addr(mbar + b), par) && ok;
             tc_fence_after();
-            const int64_t next = tile + gridDim.x, next2 = next + gridDim.x;
-            if (next < n_tiles && tid == 0) issue_rotation(Xnext, ((it + 1u) & 1u) * C::kBufCols);
-            if (next2 < n_tiles) load_tile(next2, Xcur);
-            cp_async_commit();
+            if (tid == 0) {
+                // The other accumulator buffer was drained before the previous iteration's barrier:
+                // start the next tile's MMAs into it, then refill the vector buffer this tile's MMAs
+                // have finished reading.  All of it overlaps the epilogue below.
+                const int64_t next = tile + gridDim.x, next2 = next + gridDim.x;
+                if (next < n_tiles) {
+                    ok = mbar_wait(sm_addr(mbar + 2 + (b ^ 1u)), ((it + 1u) >> 1) & 1u) && ok;
+                    issue_rotation(b ? Xa : Xb, (b ^ 1u) * C::kBufCols, mbar + (b ^ 1u));
+                }
+                if (next2 < n_tiles) fetch_tile(next2, (int)b);
+            }
         }
+        uint8_t* outs = outs0 + (QJL ? 0u : (it & 1u) * (uint32_t)(kTileVecs * VB));
         const uint32_t tmem_tile = tmem_lane + tcol;
 
         // ---- epilogue: this thread owns vector `row`, block `wg`
@@ -490,14 +540,22 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
                     if (wg * 32 + k * 8 < M) dst[k] = (uint8_t)(w >> (8 * k));
             }
         }
+        if (!QJL) {
+            fence_async_smem();                  // the bulk store reads `outs` through the async proxy
+            if (tid == 0) bulk_wait_read();      // the store that last read the other staging buffer is done
+        }
+        if (!ok) *abort_s = 1u;                  // a wait gave up: the whole CTA stops after this barrier
         tc_fence_before();
         __syncthreads();
+        if (*abort_s) break;
 
         // ---- coalesced copy-out of the tile
         {
             const int n_bytes = n_valid * VB;                       // multiple of 4
             uint8_t* dst = p.blocks_out + v0 * VB;
-            if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            if (!QJL && n_valid == kTileVecs && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                if (tid == 0) bulk_store(dst, sm_addr(outs), (uint32_t)(kTileVecs * VB));
+            } else if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
                 const int n16 = n_bytes / 16;
                 for (int c = tid; c < n16; c += THREADS)
                     reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(outs)[c];
@@ -526,14 +584,45 @@ __global__ void __launch_bounds__(compress_threads(D), 1) pq_compress_kernel(con
                 }
             }
         }
-        __syncthreads();   // outs and the tiles are rewritten by the next iteration
-        if (!QJL) { uint8_t* tmp = Xcur; Xcur = Xnext; Xnext = tmp; }
+        if (QJL) __syncthreads();   // outs and the tiles are rewritten by the next iteration
     }
     cp_async_wait<0>();
+    if (!QJL && tid == 0) {
+        bulk_wait_all();
+        if (*abort_s) {                          // give tile copies still in flight time to land
+            const long long t0 = clock64();
+            while (clock64() - t0 < (1ll << 20)) {}
+        }
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_base, C::kTmemCols);
     if (!ok && lane == 0) atomicOr(&g_compress_error, 1u);
+}
+
+// Tensor map of x as a [n_vec][D] float16 matrix, boxes of 128 vectors x 64 halves, 128-byte swizzle.
+// The encoder is a driver entry point, fetched through the runtime so the library links to cudart only.
+static int make_x_map(const CompressParams& p, int D, CUtensorMap* map) {
+    typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static encode_fn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess || !fn)
+            return PQ_ERR_CUDA;
+        encode = reinterpret_cast<encode_fn>(fn);
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)p.n_vec};
+    const cuuint64_t strides[1] = {(cuuint64_t)D * sizeof(__half)};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)kTileVecs};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(p.x), dims, strides, box,
+                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? PQ_OK : PQ_ERR_CUDA;
 }
 
 template <int D, int BITS, bool QJL>
@@ -551,7 +640,13 @@ static int launch_compress(const CompressParams& p, cudaStream_t stream) {
     const int64_t n_tiles = (p.n_vec + kTileVecs - 1) / kTileVecs;
     // one CTA per SM: a CTA holds up to all 512 tensor-memory columns of its SM
     const int grid = (int)(n_tiles < sm_count ? n_tiles : sm_count);
-    kern<<<grid, C::THREADS, smem, stream>>>(p);
+    CUtensorMap x_map;
+    memset(&x_map, 0, sizeof(x_map));
+    if (!QJL) {
+        const int st = make_x_map(p, D, &x_map);
+        if (st != PQ_OK) return st;
+    }
+    kern<<<grid, C::THREADS, smem, stream>>>(p, x_map);
     return cudaGetLastError() == cudaSuccess ? PQ_OK : PQ_ERR_CUDA;
 }
 
@@ -573,6 +668,7 @@ extern "C" int pq_compress(const void* x, int64_t n_vec, int head_dim, int n_bit
                            void* stream) {
     using namespace pq;
     if (n_vec < 0) return PQ_ERR_BAD_SHAPE;
+    if (n_vec > (int64_t)0x7FFFFF00) return PQ_ERR_TOO_LARGE;   // tile coordinates are 32-bit
     if (head_dim != 64 && head_dim != 128) return PQ_ERR_BAD_HEAD_DIM;
     if (n_bits != 2 && n_bits != 4) return PQ_ERR_BAD_BITS;
     if (n_vec == 0) return PQ_OK;
