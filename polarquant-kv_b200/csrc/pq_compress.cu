@@ -54,6 +54,8 @@ static __device__ unsigned int g_compress_error = 0;
 constexpr int kTileVecs = 128;
 // warps: 4 per warpgroup (TMEM lanes 0..127 = vectors) x D/32 warpgroups (one block each)
 __host__ __device__ constexpr int compress_threads(int D) { return 32 * 4 * (D / 32); }
+// Without the sketch one more warp runs beside them: its first lane issues the tile copies and the MMAs.
+__host__ __device__ constexpr int compress_launch_threads(int D, bool qjl) { return compress_threads(D) + (qjl ? 0 : 32); }
 
 struct CompressParams {
     const __half* x;
@@ -101,6 +103,22 @@ __device__ __forceinline__ void bulk_store(void* gdst, uint32_t smem_src, uint32
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(gdst), "r"(smem_src), "r"(bytes)
                  : "memory");
     asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t mbar_addr) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(mbar_addr) : "memory");
+}
+// Named barrier over `count` threads that also ORs a flag across them (same result in every thread).
+__device__ __forceinline__ bool group_barrier_any(uint32_t id, uint32_t count, bool flag) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "barrier.cta.red.or.pred p, %2, %3, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(r)
+        : "r"((uint32_t)flag), "r"(id), "r"(count)
+        : "memory");
+    return r != 0u;
 }
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
@@ -159,7 +177,7 @@ __device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
 }
 // Bounded wait on a phase parity: gives up after about a second (2^31 clock ticks, and never
 // more than 2^22 polls) and reports failure, so a lost completion can never hang the GPU.
-__device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity, const volatile uint32_t* abort = nullptr) {
     long long t0 = 0;
     for (int it = 0; it < (1 << 22); ++it) {
         uint32_t done;
@@ -172,6 +190,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity) {
             : "memory");
         if (done) return true;
         if ((it & 255) == 255) {
+            if (abort && *abort) return false;       // another thread of the CTA already gave up
             const long long now = clock64();
             if (t0 == 0) t0 = now;
             else if (now - t0 > (1ll << 31)) return false;
@@ -233,7 +252,7 @@ struct CompressCfg {
 };
 
 template <int D, int BITS, bool QJL>
-__global__ void __launch_bounds__(compress_threads(D), 1)
+__global__ void __launch_bounds__(compress_launch_threads(D, QJL), 1)
 pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x_map) {
     using C = CompressCfg<D, BITS, QJL>;
     constexpr int THREADS = C::THREADS;
@@ -256,8 +275,8 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
     float* escale = reinterpret_cast<float*>(sp);    sp += kTileVecs * 4;
     float* enorm2 = reinterpret_cast<float*>(sp);    sp += kTileVecs * WG * 4;
     uint64_t* mbar = reinterpret_cast<uint64_t*>(sp);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sp + 32);
-    volatile uint32_t* abort_s = reinterpret_cast<volatile uint32_t*>(sp + 40);    sp += 64;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sp + 48);
+    volatile uint32_t* abort_s = reinterpret_cast<volatile uint32_t*>(sp + 56);    sp += 64;
     uint8_t* Pb = sp;                       sp += QJL ? (2 * D / 8) * M * 16 : 0;
     uint8_t* bits_s = sp;
 
@@ -266,7 +285,7 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
     const int row = (warp & 3) * 32 + lane;                     // vector of the tile = TMEM lane
 
     // ---- one-time set-up: split matrices, tables, barrier, tensor memory
-    for (int id = tid; id < D * (2 * D / 8); id += THREADS) {
+    for (int id = tid; id < D * (2 * D / 8); id += blockDim.x) {
         const int n = ((id >> 5) % (D / 8)) * 8 + (id & 7), kc = ((id >> 5) / (D / 8)) * 4 + ((id >> 3) & 3);
         cp_async_16(Rb + chunk_off(D, n, kc), p.rot_split + (size_t)n * 2 * D + kc * 8);
     }
@@ -278,17 +297,23 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
         }
     }
     if (tid < 16) cb_s[tid] = p.cb[tid < NLEV ? tid : 0];
-    for (int e = tid; e < 256 * BREP; e += THREADS) {
+    for (int e = tid; e < 256 * BREP; e += blockDim.x) {
         const int b = e / BREP;
         const int k = b < 132 ? b : 131;          // buckets past 128 only see out-of-range garbage
         bucket_s[e] = make_uint2(__float_as_uint(p.bucket_t[k]), p.bucket_base[k]);
     }
     const uint2* bucket_lane = bucket_s + (lane % BREP);
-    if (tid == 0) {       // [0], [1]: MMAs of accumulator buffer 0 / 1 done; [2], [3]: vector buffer 0 / 1 landed
+    if (tid == 0) {
+        // [0], [1]: MMAs of accumulator buffer 0 / 1 done; [2], [3]: vector buffer 0 / 1 landed;
+        // [4], [5]: accumulator buffer 0 / 1 read out by every epilogue thread
         for (int i = 0; i < 4; ++i) mbar_init(sm_addr(mbar + i), 1);
+        for (int i = 4; i < 6; ++i) mbar_init(sm_addr(mbar + i), THREADS);
         *abort_s = 0u;
     }
     if (warp == 0) tmem_alloc(sm_addr(tmem_slot), C::kTmemCols);
+    cp_async_commit();
+    cp_async_wait<0>();          // the split matrices are in place ...
+    fence_async_smem();          // ... and visible to the tensor core's (async proxy) reads
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -349,13 +374,29 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) tma_load_2d(dst + h * 16384, &x_map, h * 64, (int)(tile * kTileVecs), bar);
     };
-    if (!QJL && tid == 0 && (int64_t)blockIdx.x < n_tiles) {
-        // pipeline fill: two tiles in flight, the first tile's MMAs issued
-        fetch_tile(blockIdx.x, 0);
-        if ((int64_t)blockIdx.x + gridDim.x < n_tiles) fetch_tile((int64_t)blockIdx.x + gridDim.x, 1);
-        ok = mbar_wait(sm_addr(mbar + 2), 0u) && ok;
-        issue_rotation(Xa, 0u, mbar);
-    }
+    if (!QJL && warp == THREADS / 32) {
+        // ---- issuing warp (one lane): tile copies two ahead, a tile's MMAs as soon as its vectors have
+        // landed and the accumulator buffer they go to has been read out
+        if (lane == 0) {
+            const int64_t n_my = (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+            auto tile_of = [&](int64_t i) { return (int64_t)blockIdx.x + i * gridDim.x; };
+            if (n_my > 0) fetch_tile(tile_of(0), 0);
+            if (n_my > 1) fetch_tile(tile_of(1), 1);
+            for (int64_t i = 0; i < n_my && ok && !*abort_s; ++i) {
+                const uint32_t b = (uint32_t)i & 1u, use = (uint32_t)(i >> 1);
+                ok = mbar_wait(sm_addr(mbar + 2 + b), use & 1u, abort_s) && ok;
+                if (i >= 2) ok = mbar_wait(sm_addr(mbar + 4 + b), (use - 1u) & 1u, abort_s) && ok;
+                if (!ok) break;
+                issue_rotation(b ? Xb : Xa, b * C::kBufCols, mbar + b);
+                if (i >= 1 && i + 1 < n_my) {
+                    // the previous tile's MMAs have finished reading the other vector buffer: refill it
+                    ok = mbar_wait(sm_addr(mbar + (b ^ 1u)), (uint32_t)((i - 1) >> 1) & 1u, abort_s) && ok;
+                    if (ok) fetch_tile(tile_of(i + 1), (int)(b ^ 1u));
+                }
+            }
+            if (!ok) { *abort_s = 1u; atomicOr(&g_compress_error, 1u); }
+        }
+    } else {
 
     uint32_t it = 0;
     for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
@@ -395,22 +436,10 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
             phase ^= 1u;
             tc_fence_after();
         } else {
-            // This tile's MMAs were issued one iteration ago into accumulator buffer b; buffers are
-            // used every other iteration, so their barriers flip parity every second use.
-            const uint32_t b = it & 1u, par = (it >> 1) & 1u;
-            ok = mbar_wait(sm_addr(mbar + b), par) && ok;
+            // The issuing warp runs ahead; accumulator buffers alternate, so their barriers flip parity
+            // every second tile.
+            ok = mbar_wait(sm_addr(mbar + (it & 1u)), (it >> 1) & 1u, abort_s) && ok;
             tc_fence_after();
-            if (tid == 0) {
-                // The other accumulator buffer was drained before the previous iteration's barrier:
-                // start the next tile's MMAs into it, then refill the vector buffer this tile's MMAs
-                // have finished reading.  All of it overlaps the epilogue below.
-                const int64_t next = tile + gridDim.x, next2 = next + gridDim.x;
-                if (next < n_tiles) {
-                    ok = mbar_wait(sm_addr(mbar + 2 + (b ^ 1u)), ((it + 1u) >> 1) & 1u) && ok;
-                    issue_rotation(b ? Xa : Xb, (b ^ 1u) * C::kBufCols, mbar + (b ^ 1u));
-                }
-                if (next2 < n_tiles) fetch_tile(next2, (int)b);
-            }
         }
         uint8_t* outs = outs0 + (QJL ? 0u : (it & 1u) * (uint32_t)(kTileVecs * VB));
         const uint32_t tmem_tile = tmem_lane + tcol;
@@ -424,6 +453,10 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
             tmem_ld32(part, tmem_tile + grp * D + wg * 32);
 #pragma unroll
             for (int k = 0; k < 16; ++k) v2[k] = add2(v2[k], part[k]);
+        }
+        if (!QJL) {                      // this thread's part of the accumulator buffer is in registers
+            tc_fence_before();
+            mbar_arrive(sm_addr(mbar + 4 + (it & 1u)));
         }
         // numpy's float32 axis-reduction order: r[j] over j, j+8, j+16, j+24 (products rounded
         // separately), then a balanced tree
@@ -541,8 +574,29 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
             }
         }
         if (!QJL) {
+            // ---- the warps that share 32 vectors (one per block) meet at their own barrier; its first
+            // lane then sends the 32 packed vectors off with one bulk store.  No CTA-wide barrier.
+            const int q = warp & 3;                                  // row group = TMEM lane quarter
+            const bool leader = wg == 0 && lane == 0;
             fence_async_smem();                  // the bulk store reads `outs` through the async proxy
-            if (tid == 0) bulk_wait_read();      // the store that last read the other staging buffer is done
+            if (leader) bulk_wait_read();        // the store that last read the other staging buffer is done
+            // the barrier also votes: a wait that gave up anywhere in the CTA stops every group
+            if (group_barrier_any(1u + q, 32u * WG, !ok || *abort_s != 0u)) {
+                *abort_s = 1u;
+                break;
+            }
+            const int rows = min(32, n_valid - 32 * q);
+            if (rows > 0) {
+                uint8_t* dst = p.blocks_out + (v0 + 32 * q) * VB;
+                const uint8_t* src = outs + 32 * q * VB;
+                if (rows == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                    if (leader) bulk_store(dst, sm_addr(src), 32u * VB);
+                } else {                                             // ragged end or odd token offset
+                    for (int c = wg * 32 + lane; c < rows * VB / 4; c += 32 * WG)
+                        reinterpret_cast<uint32_t*>(dst)[c] = reinterpret_cast<const uint32_t*>(src)[c];
+                }
+            }
+            continue;
         }
         if (!ok) *abort_s = 1u;                  // a wait gave up: the whole CTA stops after this barrier
         tc_fence_before();
@@ -553,9 +607,7 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
         {
             const int n_bytes = n_valid * VB;                       // multiple of 4
             uint8_t* dst = p.blocks_out + v0 * VB;
-            if (!QJL && n_valid == kTileVecs && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-                if (tid == 0) bulk_store(dst, sm_addr(outs), (uint32_t)(kTileVecs * VB));
-            } else if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
                 const int n16 = n_bytes / 16;
                 for (int c = tid; c < n16; c += THREADS)
                     reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(outs)[c];
@@ -584,20 +636,19 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
                 }
             }
         }
-        if (QJL) __syncthreads();   // outs and the tiles are rewritten by the next iteration
+        __syncthreads();   // outs and the tiles are rewritten by the next iteration
     }
     cp_async_wait<0>();
-    if (!QJL && tid == 0) {
-        bulk_wait_all();
-        if (*abort_s) {                          // give tile copies still in flight time to land
-            const long long t0 = clock64();
-            while (clock64() - t0 < (1ll << 20)) {}
-        }
+    if (!QJL && wg == 0 && lane == 0) bulk_wait_all();
+    if (!ok && lane == 0) atomicOr(&g_compress_error, 1u);
+    }   // epilogue warps
+    if (!QJL && *abort_s && tid == 0) {          // give tile copies still in flight time to land
+        const long long t0 = clock64();
+        while (clock64() - t0 < (1ll << 20)) {}
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_base, C::kTmemCols);
-    if (!ok && lane == 0) atomicOr(&g_compress_error, 1u);
 }
 
 // Tensor map of x as a [n_vec][D] float16 matrix, boxes of 128 vectors x 64 halves, 128-byte swizzle.
@@ -646,7 +697,7 @@ static int launch_compress(const CompressParams& p, cudaStream_t stream) {
         const int st = make_x_map(p, D, &x_map);
         if (st != PQ_OK) return st;
     }
-    kern<<<grid, C::THREADS, smem, stream>>>(p, x_map);
+    kern<<<grid, compress_launch_threads(D, QJL), smem, stream>>>(p, x_map);
     return cudaGetLastError() == cudaSuccess ? PQ_OK : PQ_ERR_CUDA;
 }
 
