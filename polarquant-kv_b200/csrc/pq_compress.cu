@@ -71,6 +71,7 @@ struct CompressParams {
     // index = base[k] + (y > t[k]).  A bucket holds at most one decision threshold.
     float bucket_t[132];
     uint32_t bucket_base[132];
+    int floor_buckets;         // 1: k = floor(64 y + 64) (fixed-address table, no sketch); 0: k = round(64 y) + 128
 };
 
 // ------------------------------------------------------------------ tcgen05 / mbarrier wrappers
@@ -243,7 +244,14 @@ struct CompressCfg {
     static constexpr int kBufCols = (KG * D < 128 && QJL) ? 128 : KG * D;
     static constexpr int kTmemCols = QJL ? kBufCols : 2 * kBufCols;
     static constexpr int kOutBufs = QJL ? 1 : 2;              // packed-tile staging buffers
+    // Without the sketch the layout is pinned to absolute shared-memory addresses so that a bucket's
+    // address is a single AND-OR of the fused-multiply-add result: the index table sits on a 32 KB
+    // boundary, small buffers below it, the operand tiles above.
+    static constexpr uint32_t kTabAddr = 0x8000u;              // 129 buckets x 16 lane copies x 8 B
+    static constexpr uint32_t kRAddr = 0x10000u;
+    static constexpr uint32_t kLowBytes = kOutBufs * kTileVecs * VB + 64 + 64;
     __host__ __device__ static size_t smem_bytes(int jl_dim) {
+        if (!QJL) return (size_t)kRAddr + kRBytes + 2 * (size_t)kXBytes;
         size_t b = kRBytes + 2 * (size_t)kXBytes + (size_t)kOutBufs * kTileVecs * VB + 256 * 8 * BREP + 64 +
                    kTileVecs * 4 + kTileVecs * WG * 4 + 64;
         if (QJL) b += (size_t)(2 * D / 8) * jl_dim * 16 + (size_t)kTileVecs * (jl_dim / 8);
@@ -265,20 +273,42 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
     const int M = QJL ? p.jl_dim : 0;
 
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    uint8_t* sp = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* Rb = sp;                       sp += C::kRBytes;
-    uint8_t* Xa = sp;                       sp += C::kXBytes;      // vector tile / residual hi term
-    uint8_t* Xb = sp;                       sp += C::kXBytes;      // prefetch tile / residual lo term (QJL)
-    uint8_t* outs0 = sp;                    sp += C::kOutBufs * kTileVecs * VB;
-    uint2* bucket_s = reinterpret_cast<uint2*>(sp);  sp += 256 * 8 * BREP;
-    float* cb_s = reinterpret_cast<float*>(sp);      sp += 64;
-    float* escale = reinterpret_cast<float*>(sp);    sp += kTileVecs * 4;
-    float* enorm2 = reinterpret_cast<float*>(sp);    sp += kTileVecs * WG * 4;
-    uint64_t* mbar = reinterpret_cast<uint64_t*>(sp);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sp + 48);
-    volatile uint32_t* abort_s = reinterpret_cast<volatile uint32_t*>(sp + 56);    sp += 64;
-    uint8_t* Pb = sp;                       sp += QJL ? (2 * D / 8) * M * 16 : 0;
-    uint8_t* bits_s = sp;
+    uint8_t *Rb, *Xa, *Xb, *outs0, *Pb = nullptr, *bits_s = nullptr;
+    uint2* bucket_s;
+    float *cb_s, *escale = nullptr, *enorm2 = nullptr;
+    uint64_t* mbar;
+    if (QJL) {
+        uint8_t* sp = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+        Rb = sp;                            sp += C::kRBytes;
+        Xa = sp;                            sp += C::kXBytes;      // vector tile, then residual hi term
+        Xb = sp;                            sp += C::kXBytes;      // residual lo term
+        outs0 = sp;                         sp += C::kOutBufs * kTileVecs * VB;
+        bucket_s = reinterpret_cast<uint2*>(sp);  sp += 256 * 8 * BREP;
+        cb_s = reinterpret_cast<float*>(sp);      sp += 64;
+        escale = reinterpret_cast<float*>(sp);    sp += kTileVecs * 4;
+        enorm2 = reinterpret_cast<float*>(sp);    sp += kTileVecs * WG * 4;
+        mbar = reinterpret_cast<uint64_t*>(sp);   sp += 64;
+        Pb = sp;                            sp += (2 * D / 8) * M * 16;
+        bits_s = sp;
+    } else {
+        const uint32_t base = sm_addr(smem_raw);
+        uint8_t* sp = smem_raw + ((128u - (base & 127u)) & 127u);
+        // the dynamic window must start low enough for the small buffers to end below the table
+        if (sm_addr(sp) + C::kLowBytes > C::kTabAddr) {
+            if (threadIdx.x == 0) atomicOr(&g_compress_error, 2u);
+            return;
+        }
+        outs0 = sp;                         sp += C::kOutBufs * kTileVecs * VB;
+        cb_s = reinterpret_cast<float*>(sp);      sp += 64;
+        mbar = reinterpret_cast<uint64_t*>(sp);
+        uint8_t* zero = smem_raw - base;           // generic address of shared address 0
+        bucket_s = reinterpret_cast<uint2*>(zero + C::kTabAddr);
+        Rb = zero + C::kRAddr;
+        Xa = Rb + C::kRBytes;
+        Xb = Xa + C::kXBytes;
+    }
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(mbar) + 48);
+    volatile uint32_t* abort_s = reinterpret_cast<volatile uint32_t*>(reinterpret_cast<uint8_t*>(mbar) + 56);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wg = warp >> 2;                                   // block (32 output dims) this thread owns
@@ -297,12 +327,13 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
         }
     }
     if (tid < 16) cb_s[tid] = p.cb[tid < NLEV ? tid : 0];
-    for (int e = tid; e < 256 * BREP; e += blockDim.x) {
+    for (int e = tid; e < (QJL ? 256 : 129) * BREP; e += blockDim.x) {
         const int b = e / BREP;
         const int k = b < 132 ? b : 131;          // buckets past 128 only see out-of-range garbage
         bucket_s[e] = make_uint2(__float_as_uint(p.bucket_t[k]), p.bucket_base[k]);
     }
     const uint2* bucket_lane = bucket_s + (lane % BREP);
+    const uint32_t tab_lane = C::kTabAddr | ((uint32_t)(lane & 15) << 3);     // this lane's copy
     if (tid == 0) {
         // [0], [1]: MMAs of accumulator buffer 0 / 1 done; [2], [3]: vector buffer 0 / 1 landed;
         // [4], [5]: accumulator buffer 0 / 1 read out by every epilogue thread
@@ -480,7 +511,10 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
         const float dsafe = zero ? 1.f : d_raw;
         const float rinv = __frcp_rn(dsafe);
         const float2 rinv2 = make_float2(rinv, rinv), negd2 = make_float2(-dsafe, -dsafe);
-        const float2 c64 = make_float2(64.f, 64.f), cmagic = make_float2(8388672.f, 8388672.f);
+        // bucket key in the low mantissa bits of 64 y + magic: with the sketch  round(64 y) + 128  in bits
+        // 0..7; without it the unit in the last place is 2^-7 and bits 7..14 hold  floor(64 y + 64)
+        const float magic = QJL ? 8388672.f : 98368.f;
+        const float2 c64 = make_float2(64.f, 64.f), cmagic = make_float2(magic, magic);
         const float es = QJL ? escale[row] * (1.0f / 4096.0f) : 1.f;
         float en2 = 0.f;
         uint32_t packed[BITS];                                        // 32 indices, low index first
@@ -497,10 +531,16 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
             for (int e = 0; e < 2; ++e) {
                 const int j = 2 * k + e;
                 const float dj = e ? dir.y : dir.x;
-                const uint32_t bk = __float_as_uint(e ? u.y : u.x) & 0xFFu;
-                const uint2 be = bucket_lane[bk * BREP];
+                uint2 be;
+                if (QJL) {
+                    const uint32_t bk = __float_as_uint(e ? u.y : u.x) & 0xFFu;
+                    be = bucket_lane[bk * BREP];
+                } else {
+                    const uint32_t a = (__float_as_uint(e ? u.y : u.x) & 0x7F80u) | tab_lane;
+                    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];\n" : "=r"(be.x), "=r"(be.y) : "r"(a));
+                }
                 const uint32_t id = be.y + ((dj > __uint_as_float(be.x)) ? 1u : 0u);
-                packed[(j * BITS) >> 5] |= id << ((j * BITS) & 31);
+                packed[(j * BITS) >> 5] += id << ((j * BITS) & 31);   // fields do not overlap
                 if (QJL) {
                     const float ee = (v[j] - __fmul_rn(dq, cb_s[zero ? 0u : id])) * es;
                     en2 = fmaf(ee, ee, en2);
@@ -513,12 +553,19 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
             for (int w = 0; w < BITS; ++w) packed[w] = 0u;
         }
         {
-            uint16_t* ob = reinterpret_cast<uint16_t*>(outs + row * VB + wg * BB);
-            ob[0] = __half_as_ushort(d16);
+            // 2 + 4*BITS bytes at a 2-byte aligned offset: whole words where the alignment allows
+            uint8_t* ob = outs + row * VB + wg * BB;
+            const uint32_t dbits = __half_as_ushort(d16);
+            if ((wg * BB) & 2) {                    // warp-uniform
+                *reinterpret_cast<uint16_t*>(ob) = (uint16_t)dbits;
 #pragma unroll
-            for (int w = 0; w < BITS; ++w) {
-                ob[1 + 2 * w] = (uint16_t)(packed[w] & 0xFFFFu);
-                ob[2 + 2 * w] = (uint16_t)(packed[w] >> 16);
+                for (int w = 0; w < BITS; ++w) *reinterpret_cast<uint32_t*>(ob + 2 + 4 * w) = packed[w];
+            } else {
+                *reinterpret_cast<uint32_t*>(ob) = dbits | (packed[0] << 16);
+#pragma unroll
+                for (int w = 1; w < BITS; ++w)
+                    *reinterpret_cast<uint32_t*>(ob + 4 * w) = __funnelshift_r(packed[w - 1], packed[w], 16);
+                *reinterpret_cast<uint16_t*>(ob + 4 * BITS) = (uint16_t)(packed[BITS - 1] >> 16);
             }
         }
         if (QJL) {
@@ -750,13 +797,15 @@ extern "C" int pq_compress(const void* x, int64_t n_vec, int head_dim, int n_bit
     const float* thr_h = thresholds;
     const float* cb_h = codebook;
     for (int i = 0; i < 16; ++i) p.cb[i] = i < nlev ? cb_h[i] : 0.f;
-    // bucket(y) = round(64 y) + 64, evaluated exactly as the kernel does (one fused multiply-add)
+    // bucket(y), evaluated exactly as the kernel does (one fused multiply-add, then mantissa bits):
+    // round(64 y) + 64 with the sketch, floor(64 y + 64) (after rounding to 1/128) without it
+    p.floor_buckets = qjl ? 0 : 1;
     for (int k = 0; k < 132; ++k) { p.bucket_t[k] = 3.0e38f; p.bucket_base[k] = 0; }
     for (int i = 0; i < nlev - 1; ++i) {
-        const float u = fmaf(thr_h[i], 64.f, 8388672.f);
+        const float u = fmaf(thr_h[i], 64.f, qjl ? 8388672.f : 98368.f);
         uint32_t bits;
         memcpy(&bits, &u, sizeof(bits));
-        const int kb = (int)(bits & 0xFFu);
+        const int kb = qjl ? (int)(bits & 0xFFu) : (int)((bits >> 7) & 0xFFu);
         if (!(thr_h[i] > -1.0f && thr_h[i] < 1.0f) || kb > 130 || p.bucket_t[kb] != 3.0e38f)
             return PQ_ERR_BAD_SHAPE;      // thresholds out of range or two of them in one bucket
         p.bucket_t[kb] = thr_h[i];
