@@ -45,6 +45,44 @@
 #define PQ_COMPRESS_KSTEPS_PER_GROUP 4
 #endif
 
+// Which of the epilogue's float32 steps use packed f32x2 instructions (1) or scalar pairs (0)
+#ifndef PQ_X2_ADD
+#define PQ_X2_ADD 1
+#endif
+#ifndef PQ_X2_SQ
+#define PQ_X2_SQ 1
+#endif
+#ifndef PQ_X2_DIR
+#define PQ_X2_DIR 1
+#endif
+#ifndef PQ_X2_KEY
+#define PQ_X2_KEY 1
+#endif
+#if PQ_X2_ADD
+#define PQ_ADD_OP add2
+#else
+#define PQ_ADD_OP add2s
+#endif
+#if PQ_X2_SQ
+#define PQ_SQ_MUL mul2
+#define PQ_SQ_ADD add2
+#else
+#define PQ_SQ_MUL mul2s
+#define PQ_SQ_ADD add2s
+#endif
+#if PQ_X2_DIR
+#define PQ_DIR_MUL mul2
+#define PQ_DIR_FMA fma2
+#else
+#define PQ_DIR_MUL mul2s
+#define PQ_DIR_FMA fma2s
+#endif
+#if PQ_X2_KEY
+#define PQ_KEY_FMA fma2
+#else
+#define PQ_KEY_FMA fma2s
+#endif
+
 namespace pq {
 
 // Set (bit 0) when a bounded wait on a tensor-core completion barrier gave up; read and cleared
@@ -184,7 +222,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity, const 
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 100000;\n\t"   // suspend up to 100 us per poll
             "selp.u32 %0, 1, 0, p;\n\t}\n"
             : "=r"(done)
             : "r"(addr), "r"(parity)
@@ -224,6 +262,13 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
     return d;
 }
 
+// The same operations as two scalar instructions (these can use either half of the FMA pipe).
+__device__ __forceinline__ float2 mul2s(float2 a, float2 b) { return make_float2(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y)); }
+__device__ __forceinline__ float2 add2s(float2 a, float2 b) { return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y)); }
+__device__ __forceinline__ float2 fma2s(float2 a, float2 b, float2 c) {
+    return make_float2(__fmaf_rn(a.x, b.x, c.x), __fmaf_rn(a.y, b.y, c.y));
+}
+
 // Byte offset of 16-byte chunk `kc` of row `r` in a K-major operand tile with `rows` rows.
 __device__ __forceinline__ uint32_t chunk_off(int rows, int r, int kc) {
     return (uint32_t)(kc * (rows / 8) * 128 + (r >> 3) * 128 + (r & 7) * 16);
@@ -249,9 +294,10 @@ struct CompressCfg {
     // boundary, small buffers below it, the operand tiles above.
     static constexpr uint32_t kTabAddr = 0x8000u;              // 129 buckets x 16 lane copies x 8 B
     static constexpr uint32_t kRAddr = 0x10000u;
+    static constexpr int kXBufs = 3;                           // vector tiles in flight or in use
     static constexpr uint32_t kLowBytes = kOutBufs * kTileVecs * VB + 64 + 64;
     __host__ __device__ static size_t smem_bytes(int jl_dim) {
-        if (!QJL) return (size_t)kRAddr + kRBytes + 2 * (size_t)kXBytes;
+        if (!QJL) return (size_t)kRAddr + kRBytes + kXBufs * (size_t)kXBytes;
         size_t b = kRBytes + 2 * (size_t)kXBytes + (size_t)kOutBufs * kTileVecs * VB + 256 * 8 * BREP + 64 +
                    kTileVecs * 4 + kTileVecs * WG * 4 + 64;
         if (QJL) b += (size_t)(2 * D / 8) * jl_dim * 16 + (size_t)kTileVecs * (jl_dim / 8);
@@ -307,8 +353,8 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
         Xa = Rb + C::kRBytes;
         Xb = Xa + C::kXBytes;
     }
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(mbar) + 48);
-    volatile uint32_t* abort_s = reinterpret_cast<volatile uint32_t*>(reinterpret_cast<uint8_t*>(mbar) + 56);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(mbar) + 56);
+    volatile uint32_t* abort_s = reinterpret_cast<volatile uint32_t*>(reinterpret_cast<uint8_t*>(mbar) + 60);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wg = warp >> 2;                                   // block (32 output dims) this thread owns
@@ -330,15 +376,18 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
     for (int e = tid; e < (QJL ? 256 : 129) * BREP; e += blockDim.x) {
         const int b = e / BREP;
         const int k = b < 132 ? b : 131;          // buckets past 128 only see out-of-range garbage
-        bucket_s[e] = make_uint2(__float_as_uint(p.bucket_t[k]), p.bucket_base[k]);
+        // without the sketch the count is replicated into every index field of the word, so packing
+        // a coordinate is one AND-OR with that field's mask
+        const uint32_t rep = QJL ? 1u : (BITS == 4 ? 0x11111111u : 0x55555555u);
+        bucket_s[e] = make_uint2(__float_as_uint(p.bucket_t[k]), p.bucket_base[k] * rep);
     }
     const uint2* bucket_lane = bucket_s + (lane % BREP);
     const uint32_t tab_lane = C::kTabAddr | ((uint32_t)(lane & 15) << 3);     // this lane's copy
     if (tid == 0) {
-        // [0], [1]: MMAs of accumulator buffer 0 / 1 done; [2], [3]: vector buffer 0 / 1 landed;
-        // [4], [5]: accumulator buffer 0 / 1 read out by every epilogue thread
-        for (int i = 0; i < 4; ++i) mbar_init(sm_addr(mbar + i), 1);
-        for (int i = 4; i < 6; ++i) mbar_init(sm_addr(mbar + i), THREADS);
+        // [0], [1]: MMAs of accumulator buffer 0 / 1 done; [2..4]: vector buffer 0 / 1 / 2 landed;
+        // [5], [6]: accumulator buffer 0 / 1 read out by every epilogue thread
+        for (int i = 0; i < 5; ++i) mbar_init(sm_addr(mbar + i), 1);
+        for (int i = 5; i < 7; ++i) mbar_init(sm_addr(mbar + i), THREADS);
         *abort_s = 0u;
     }
     if (warp == 0) tmem_alloc(sm_addr(tmem_slot), C::kTmemCols);
@@ -400,7 +449,7 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
     };
     // TMA fetch of one tile into vector buffer `buf` (rows past the end of x arrive as zeros)
     auto fetch_tile = [&](int64_t tile, int buf) {
-        const uint32_t bar = sm_addr(mbar + 2 + buf), dst = sm_addr(buf ? Xb : Xa);
+        const uint32_t bar = sm_addr(mbar + 2 + buf), dst = sm_addr(Xa) + (uint32_t)buf * C::kXBytes;
         mbar_expect_tx(bar, (uint32_t)C::kXBytes);
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) tma_load_2d(dst + h * 16384, &x_map, h * 64, (int)(tile * kTileVecs), bar);
@@ -411,24 +460,29 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
         if (lane == 0) {
             const int64_t n_my = (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
             auto tile_of = [&](int64_t i) { return (int64_t)blockIdx.x + i * gridDim.x; };
-            if (n_my > 0) fetch_tile(tile_of(0), 0);
-            if (n_my > 1) fetch_tile(tile_of(1), 1);
+            // Enough bytes must be in flight per SM to cover the memory latency: three tiles.
+            for (int i = 0; i < C::kXBufs && i < n_my; ++i) fetch_tile(tile_of(i), i);
+            uint32_t xb = 0, xuse = 0;                      // vector buffer of tile i and how often it was used
             for (int64_t i = 0; i < n_my && ok && !*abort_s; ++i) {
                 const uint32_t b = (uint32_t)i & 1u, use = (uint32_t)(i >> 1);
-                ok = mbar_wait(sm_addr(mbar + 2 + b), use & 1u, abort_s) && ok;
-                if (i >= 2) ok = mbar_wait(sm_addr(mbar + 4 + b), (use - 1u) & 1u, abort_s) && ok;
+                ok = mbar_wait(sm_addr(mbar + 2 + xb), xuse & 1u, abort_s) && ok;
+                if (i >= 2) ok = mbar_wait(sm_addr(mbar + 5 + b), (use - 1u) & 1u, abort_s) && ok;
                 if (!ok) break;
-                issue_rotation(b ? Xb : Xa, b * C::kBufCols, mbar + b);
-                if (i >= 1 && i + 1 < n_my) {
-                    // the previous tile's MMAs have finished reading the other vector buffer: refill it
+                issue_rotation(Xa + xb * C::kXBytes, b * C::kBufCols, mbar + b);
+                if (i >= 1 && i + 2 < n_my) {
+                    // the previous tile's MMAs have finished reading their vector buffer: refill it
                     ok = mbar_wait(sm_addr(mbar + (b ^ 1u)), (uint32_t)((i - 1) >> 1) & 1u, abort_s) && ok;
-                    if (ok) fetch_tile(tile_of(i + 1), (int)(b ^ 1u));
+                    if (ok) fetch_tile(tile_of(i + 2), (int)(xb == 0 ? C::kXBufs - 1 : xb - 1));
                 }
+                if (++xb == C::kXBufs) { xb = 0; ++xuse; }
             }
             if (!ok) { *abort_s = 1u; atomicOr(&g_compress_error, 1u); }
         }
     } else {
 
+#ifdef PQ_EXPERIMENT_STAGGER
+    { const long long t0 = clock64(); while (clock64() - t0 < (long long)wg * PQ_EXPERIMENT_STAGGER) {} }
+#endif
     uint32_t it = 0;
     for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
         const int64_t v0 = tile * kTileVecs;
@@ -483,21 +537,21 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
             float2 part[16];
             tmem_ld32(part, tmem_tile + grp * D + wg * 32);
 #pragma unroll
-            for (int k = 0; k < 16; ++k) v2[k] = add2(v2[k], part[k]);
+            for (int k = 0; k < 16; ++k) v2[k] = PQ_ADD_OP(v2[k], part[k]);
         }
         if (!QJL) {                      // this thread's part of the accumulator buffer is in registers
             tc_fence_before();
-            mbar_arrive(sm_addr(mbar + 4 + (it & 1u)));
+            mbar_arrive(sm_addr(mbar + 5 + (it & 1u)));
         }
         // numpy's float32 axis-reduction order: r[j] over j, j+8, j+16, j+24 (products rounded
         // separately), then a balanced tree
         float2 r2[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            float2 a = mul2(v2[q], v2[q]);
-            a = add2(a, mul2(v2[4 + q], v2[4 + q]));
-            a = add2(a, mul2(v2[8 + q], v2[8 + q]));
-            r2[q] = add2(a, mul2(v2[12 + q], v2[12 + q]));
+            float2 a = PQ_SQ_MUL(v2[q], v2[q]);
+            a = PQ_SQ_ADD(a, PQ_SQ_MUL(v2[4 + q], v2[4 + q]));
+            a = PQ_SQ_ADD(a, PQ_SQ_MUL(v2[8 + q], v2[8 + q]));
+            r2[q] = PQ_SQ_ADD(a, PQ_SQ_MUL(v2[12 + q], v2[12 + q]));
         }
         const float ss = __fadd_rn(__fadd_rn(__fadd_rn(r2[0].x, r2[0].y), __fadd_rn(r2[1].x, r2[1].y)),
                                    __fadd_rn(__fadd_rn(r2[2].x, r2[2].y), __fadd_rn(r2[3].x, r2[3].y)));
@@ -524,23 +578,32 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
         float* v = reinterpret_cast<float*>(&v2[0]);
 #pragma unroll
         for (int k = 0; k < 16; ++k) {
-            const float2 y0 = mul2(v2[k], rinv2);
-            const float2 dir = fma2(fma2(y0, negd2, v2[k]), rinv2, y0);
-            const float2 u = fma2(dir, c64, cmagic);
+            const float2 y0 = PQ_DIR_MUL(v2[k], rinv2);
+            const float2 dir = PQ_DIR_FMA(PQ_DIR_FMA(y0, negd2, v2[k]), rinv2, y0);
+            const float2 u = PQ_KEY_FMA(dir, c64, cmagic);
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int j = 2 * k + e;
                 const float dj = e ? dir.y : dir.x;
                 uint2 be;
-                if (QJL) {
-                    const uint32_t bk = __float_as_uint(e ? u.y : u.x) & 0xFFu;
-                    be = bucket_lane[bk * BREP];
-                } else {
+                if (!QJL) {
                     const uint32_t a = (__float_as_uint(e ? u.y : u.x) & 0x7F80u) | tab_lane;
                     asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];\n" : "=r"(be.x), "=r"(be.y) : "r"(a));
+                    // field = count of thresholds in lower buckets, plus one if y is above this bucket's
+                    const uint32_t sh = (j * BITS) & 31;
+                    uint32_t& pw = packed[(j * BITS) >> 5];
+                    pw |= be.y & (((1u << BITS) - 1u) << sh);
+                    asm("{\n\t.reg .pred p;\n\t"
+                        "setp.gt.f32 p, %1, %2;\n\t"
+                        "@p add.u32 %0, %0, %3;\n\t}\n"
+                        : "+r"(pw)
+                        : "f"(dj), "f"(__uint_as_float(be.x)), "r"(1u << sh));
+                    continue;
                 }
+                const uint32_t bk = __float_as_uint(e ? u.y : u.x) & 0xFFu;
+                be = bucket_lane[bk * BREP];
                 const uint32_t id = be.y + ((dj > __uint_as_float(be.x)) ? 1u : 0u);
-                packed[(j * BITS) >> 5] += id << ((j * BITS) & 31);   // fields do not overlap
+                packed[(j * BITS) >> 5] |= id << ((j * BITS) & 31);
                 if (QJL) {
                     const float ee = (v[j] - __fmul_rn(dq, cb_s[zero ? 0u : id])) * es;
                     en2 = fmaf(ee, ee, en2);
@@ -628,7 +691,11 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
             fence_async_smem();                  // the bulk store reads `outs` through the async proxy
             if (leader) bulk_wait_read();        // the store that last read the other staging buffer is done
             // the barrier also votes: a wait that gave up anywhere in the CTA stops every group
+#ifdef PQ_EXPERIMENT_NO_GROUP_BARRIER
+            if (false) {
+#else
             if (group_barrier_any(1u + q, 32u * WG, !ok || *abort_s != 0u)) {
+#endif
                 *abort_s = 1u;
                 break;
             }
