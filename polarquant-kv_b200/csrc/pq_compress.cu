@@ -1,16 +1,26 @@
 // pq_compress: fused rotate -> per-32 radius -> nearest Lloyd-Max centroid -> pack
 // [-> QJL 1-bit residual sketch], for block_pq4 storage.
 //
-// One CTA (4 x D/32 warps) owns a tile of 128 vectors at a time (persistent over tiles).
-// The rotation  xr = x @ R^T  is a dense [128 x 2D] x [2D x D] contraction on the 5th-gen
-// tensor cores: one elected thread issues tcgen05.mma (kind::f16, M = 128, N = D, K = 16)
-// on shared-memory operands, the float32 accumulators live in tensor memory (TMEM) and are
-// read back with tcgen05.ld for the epilogue.  x is float16 (exact); R is pre-split on the
-// host into two float16 terms  4096*R = hi + lo  (K runs over [hi | lo]), so xr carries
-// about 22 mantissa bits of R and matches the float64-then-float32 rotation of the numpy
-// reference (python/polarquant_kv/rotation.py:48) to a few 1e-8 relative.  Tensor-core
-// accumulation truncates when it aligns addends, so K is cut into D/32 groups with one TMEM
-// accumulator each, and the groups are summed with round-to-nearest float32 adds.
+// One CTA (4 x D/32 epilogue warps) owns a tile of 128 vectors at a time (persistent over tiles).
+// The rotation  xr = x @ R^T  runs on the 5th-gen tensor cores: tcgen05.mma (kind::f16, M = 128,
+// K = 16) on shared-memory operands, float32 accumulators in tensor memory (TMEM), read back
+// with tcgen05.ld for the epilogue.  x is float16 (exact); R is pre-split on the host into two
+// float16 terms  4096*R = hi + lo, so xr carries about 22 mantissa bits of R and matches the
+// float64-then-float32 rotation of the numpy reference (python/polarquant_kv/rotation.py:48) to a
+// few 1e-8 relative.  Tensor-core accumulation truncates when it aligns addends, so the hi and
+// lo products go to separate accumulators that are summed with a round-to-nearest float32 add.
+//
+// Without the QJL sketch the kernel is a three-role pipeline with no CTA-wide barrier per tile:
+//   copy warp   - keeps three vector tiles in flight or in use (TMA, cp.async.bulk.tensor, into the
+//                 128-byte-swizzled K-major layout; an mbarrier counts the bytes);
+//   MMA warp    - one MMA per k-step with N = 2D ([R_hi ; R_lo] stacked along N) into one of two
+//                 TMEM accumulator buffers, as soon as the tile has landed and the buffer has been
+//                 read out; tcgen05.commit signals the epilogue and frees the vector buffer;
+//   epilogue    - a thread owns one vector x one 32-element block (TMEM lane = vector).  The warps
+//                 that share 32 vectors meet at a named barrier and one lane sends those vectors'
+//                 packed bytes off with a bulk store.
+// With the sketch (a second contraction per tile) the older serial flow is kept: cp.async tile
+// loads, K groups with one accumulator each, CTA-wide barriers.
 // Everything after the contraction follows the reference's float32 arithmetic exactly:
 //   radius  = sqrt(sum of squares), summed in numpy's axis-reduction order
 //             (eight strided partial sums, then a balanced tree),
@@ -45,55 +55,18 @@
 #define PQ_COMPRESS_KSTEPS_PER_GROUP 4
 #endif
 
-// Which of the epilogue's float32 steps use packed f32x2 instructions (1) or scalar pairs (0)
-#ifndef PQ_X2_ADD
-#define PQ_X2_ADD 1
-#endif
-#ifndef PQ_X2_SQ
-#define PQ_X2_SQ 1
-#endif
-#ifndef PQ_X2_DIR
-#define PQ_X2_DIR 1
-#endif
-#ifndef PQ_X2_KEY
-#define PQ_X2_KEY 1
-#endif
-#if PQ_X2_ADD
-#define PQ_ADD_OP add2
-#else
-#define PQ_ADD_OP add2s
-#endif
-#if PQ_X2_SQ
-#define PQ_SQ_MUL mul2
-#define PQ_SQ_ADD add2
-#else
-#define PQ_SQ_MUL mul2s
-#define PQ_SQ_ADD add2s
-#endif
-#if PQ_X2_DIR
-#define PQ_DIR_MUL mul2
-#define PQ_DIR_FMA fma2
-#else
-#define PQ_DIR_MUL mul2s
-#define PQ_DIR_FMA fma2s
-#endif
-#if PQ_X2_KEY
-#define PQ_KEY_FMA fma2
-#else
-#define PQ_KEY_FMA fma2s
-#endif
-
 namespace pq {
 
-// Set (bit 0) when a bounded wait on a tensor-core completion barrier gave up; read and cleared
-// by pq_poll_device_errors().  A set bit means the results of that launch are not valid.
+// Bit 0: a bounded wait on a completion barrier gave up; bit 1: the dynamic shared-memory window
+// started too high for the fixed-address layout.  Read and cleared by pq_poll_device_errors().
+// A set bit means the results of that launch are not valid.
 static __device__ unsigned int g_compress_error = 0;
 
 constexpr int kTileVecs = 128;
 // warps: 4 per warpgroup (TMEM lanes 0..127 = vectors) x D/32 warpgroups (one block each)
 __host__ __device__ constexpr int compress_threads(int D) { return 32 * 4 * (D / 32); }
-// Without the sketch one more warp runs beside them: its first lane issues the tile copies and the MMAs.
-__host__ __device__ constexpr int compress_launch_threads(int D, bool qjl) { return compress_threads(D) + (qjl ? 0 : 32); }
+// Without the sketch two more warps run beside them: one issues the MMAs, one the tile copies.
+__host__ __device__ constexpr int compress_launch_threads(int D, bool qjl) { return compress_threads(D) + (qjl ? 0 : 64); }
 
 struct CompressParams {
     const __half* x;
@@ -120,11 +93,6 @@ __device__ __forceinline__ uint32_t sm_addr(const void* p) {
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     return (uint64_t)((smem_byte_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
            ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46);
-}
-// K-major operand in the 128-byte swizzle: rows 128 B apart, 8-row groups `sbo_bytes` apart
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_byte_addr, uint32_t sbo_bytes) {
-    return (uint64_t)((smem_byte_addr >> 4) & 0x3FFFu) | (1ull << 16) |
-           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t mbar_addr, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbar_addr), "r"(bytes) : "memory");
@@ -165,6 +133,7 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 __host__ __device__ constexpr uint32_t umma_idesc_f16(int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
+static_assert((256 >> 3) < 64, "N field of the instruction descriptor is 6 bits");
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                          uint32_t accumulate) {
     asm volatile(
@@ -173,6 +142,21 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint6
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t"
         "}\n" ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+// Same, descriptors given as (low, high) 32-bit halves: the high halves are constants and the low
+// halves differ from a base by compile-time offsets, which keeps the issuing lane's work per MMA small.
+__device__ __forceinline__ void umma_f16_split(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                               uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+        "}\n" ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t mbar_addr) {
@@ -214,21 +198,25 @@ __device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(addr), "r"(count) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
 }
-// Bounded wait on a phase parity: gives up after about a second (2^31 clock ticks, and never
-// more than 2^22 polls) and reports failure, so a lost completion can never hang the GPU.
-__device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity, const volatile uint32_t* abort = nullptr) {
+// Bounded wait on a phase parity: gives up after about a second (2^31 clock ticks) and reports
+// failure, so a lost completion can never hang the GPU.  `sleep_ns` > 0 backs off between polls
+// (for the issuing lane, whose waits are long and whose polling would steal issue slots from the
+// epilogue warps on its scheduler).
+__device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity, const volatile uint32_t* abort = nullptr,
+                                          unsigned sleep_ns = 0) {
     long long t0 = 0;
-    for (int it = 0; it < (1 << 22); ++it) {
+    for (int it = 0; it < (1 << 24); ++it) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 100000;\n\t"   // suspend up to 100 us per poll
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}\n"
             : "=r"(done)
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
-        if ((it & 255) == 255) {
+        if (sleep_ns) __nanosleep(sleep_ns);
+        if ((it & 63) == 63) {
             if (abort && *abort) return false;       // another thread of the CTA already gave up
             const long long now = clock64();
             if (t0 == 0) t0 = now;
@@ -262,13 +250,6 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
     return d;
 }
 
-// The same operations as two scalar instructions (these can use either half of the FMA pipe).
-__device__ __forceinline__ float2 mul2s(float2 a, float2 b) { return make_float2(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y)); }
-__device__ __forceinline__ float2 add2s(float2 a, float2 b) { return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y)); }
-__device__ __forceinline__ float2 fma2s(float2 a, float2 b, float2 c) {
-    return make_float2(__fmaf_rn(a.x, b.x, c.x), __fmaf_rn(a.y, b.y, c.y));
-}
-
 // Byte offset of 16-byte chunk `kc` of row `r` in a K-major operand tile with `rows` rows.
 __device__ __forceinline__ uint32_t chunk_off(int rows, int r, int kc) {
     return (uint32_t)(kc * (rows / 8) * 128 + (r >> 3) * 128 + (r & 7) * 16);
@@ -282,8 +263,10 @@ struct CompressCfg {
     static constexpr int VB = (D / 32) * block_bytes(BITS);   // bytes per stored vector
     static constexpr int kRBytes = 4 * D * D;                 // [2D/8 chunks][D rows][16 B]
     static constexpr int kXBytes = (D / 8) * 2048;            // [D/8 chunks][128 rows][16 B]
+    // With the sketch: K groups of KPG k-steps, one TMEM accumulator each.  Without: one MMA per k-step
+    // with N = 2D ([R_hi ; R_lo] stacked), i.e. two accumulators (hi and lo products) per tile.
     static constexpr int KPG = PQ_COMPRESS_KSTEPS_PER_GROUP < D / 16 ? PQ_COMPRESS_KSTEPS_PER_GROUP : D / 16;
-    static constexpr int KG = (D / 16) / KPG;                 // K groups = TMEM accumulators per tile
+    static constexpr int KG = QJL ? (D / 16) / KPG : 2;
     // tensor-memory columns of one accumulator buffer (the sketch reuses it and needs jl_dim <= 128
     // columns); without QJL two buffers alternate so the next tile's MMAs overlap this tile's epilogue
     static constexpr int kBufCols = (KG * D < 128 && QJL) ? 128 : KG * D;
@@ -295,11 +278,11 @@ struct CompressCfg {
     static constexpr uint32_t kTabAddr = 0x8000u;              // 129 buckets x 16 lane copies x 8 B
     static constexpr uint32_t kRAddr = 0x10000u;
     static constexpr int kXBufs = 3;                           // vector tiles in flight or in use
-    static constexpr uint32_t kLowBytes = kOutBufs * kTileVecs * VB + 64 + 64;
+    static constexpr uint32_t kLowBytes = kOutBufs * kTileVecs * VB + 64 + 128;
     __host__ __device__ static size_t smem_bytes(int jl_dim) {
         if (!QJL) return (size_t)kRAddr + kRBytes + kXBufs * (size_t)kXBytes;
         size_t b = kRBytes + 2 * (size_t)kXBytes + (size_t)kOutBufs * kTileVecs * VB + 256 * 8 * BREP + 64 +
-                   kTileVecs * 4 + kTileVecs * WG * 4 + 64;
+                   kTileVecs * 4 + kTileVecs * WG * 4 + 128;
         if (QJL) b += (size_t)(2 * D / 8) * jl_dim * 16 + (size_t)kTileVecs * (jl_dim / 8);
         return b + 1024;                                      // the swizzled tiles sit on 1024-byte boundaries
     }
@@ -333,7 +316,7 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
         cb_s = reinterpret_cast<float*>(sp);      sp += 64;
         escale = reinterpret_cast<float*>(sp);    sp += kTileVecs * 4;
         enorm2 = reinterpret_cast<float*>(sp);    sp += kTileVecs * WG * 4;
-        mbar = reinterpret_cast<uint64_t*>(sp);   sp += 64;
+        mbar = reinterpret_cast<uint64_t*>(sp);   sp += 128;
         Pb = sp;                            sp += (2 * D / 8) * M * 16;
         bits_s = sp;
     } else {
@@ -353,8 +336,8 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
         Xa = Rb + C::kRBytes;
         Xb = Xa + C::kXBytes;
     }
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(mbar) + 56);
-    volatile uint32_t* abort_s = reinterpret_cast<volatile uint32_t*>(reinterpret_cast<uint8_t*>(mbar) + 60);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(mbar) + 96);
+    volatile uint32_t* abort_s = reinterpret_cast<volatile uint32_t*>(reinterpret_cast<uint8_t*>(mbar) + 100);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wg = warp >> 2;                                   // block (32 output dims) this thread owns
@@ -363,7 +346,12 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
     // ---- one-time set-up: split matrices, tables, barrier, tensor memory
     for (int id = tid; id < D * (2 * D / 8); id += blockDim.x) {
         const int n = ((id >> 5) % (D / 8)) * 8 + (id & 7), kc = ((id >> 5) / (D / 8)) * 4 + ((id >> 3) & 3);
-        cp_async_16(Rb + chunk_off(D, n, kc), p.rot_split + (size_t)n * 2 * D + kc * 8);
+        if (QJL) {      // B tile [D rows][K = 2D]: the lo term follows the hi term along K
+            cp_async_16(Rb + chunk_off(D, n, kc), p.rot_split + (size_t)n * 2 * D + kc * 8);
+        } else {        // B tile [2D rows][K = D]: the lo term's rows follow the hi term's (N = 2D)
+            const int half = kc / (D / 8), kk = kc % (D / 8);
+            cp_async_16(Rb + chunk_off(2 * D, half * D + n, kk), p.rot_split + (size_t)n * 2 * D + kc * 8);
+        }
     }
     if (QJL) {
         const int m8 = M >= 8 ? M / 8 : 1;
@@ -385,9 +373,11 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
     const uint32_t tab_lane = C::kTabAddr | ((uint32_t)(lane & 15) << 3);     // this lane's copy
     if (tid == 0) {
         // [0], [1]: MMAs of accumulator buffer 0 / 1 done; [2..4]: vector buffer 0 / 1 / 2 landed;
-        // [5], [6]: accumulator buffer 0 / 1 read out by every epilogue thread
+        // [5], [6]: accumulator buffer 0 / 1 read out by every epilogue thread; [7..9]: vector buffer
+        // 0 / 1 / 2 consumed by its MMAs
         for (int i = 0; i < 5; ++i) mbar_init(sm_addr(mbar + i), 1);
         for (int i = 5; i < 7; ++i) mbar_init(sm_addr(mbar + i), THREADS);
+        for (int i = 7; i < 10; ++i) mbar_init(sm_addr(mbar + i), 1);
         *abort_s = 0u;
     }
     if (warp == 0) tmem_alloc(sm_addr(tmem_slot), C::kTmemCols);
@@ -436,9 +426,7 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
 #pragma unroll
             for (int k2 = 0; k2 < KPG; ++k2) {
                 const int ks = grp * KPG + k2;
-                // TMA tiles: 64-half boxes of 16 KB, a k-step is 32 B further inside the swizzled row
-                const uint64_t da = QJL ? umma_desc(xaddr + ks * 2 * 2048, 2048, 128)
-                                        : umma_desc_sw128(xaddr + (ks >> 2) * 16384 + (ks & 3) * 32, 1024);
+                const uint64_t da = umma_desc(xaddr + ks * 2 * 2048, 2048, 128);
                 const uint64_t bh = umma_desc(raddr + (2 * ks) * LBO_R, LBO_R, 128);
                 const uint64_t bl = umma_desc(raddr + (D / 8 + 2 * ks) * LBO_R, LBO_R, 128);
                 umma_f16(tmem_base + tcol + grp * D, da, bh, idesc, k2 ? 1u : 0u);
@@ -454,35 +442,55 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
 #pragma unroll
         for (int h = 0; h < D / 64; ++h) tma_load_2d(dst + h * 16384, &x_map, h * 64, (int)(tile * kTileVecs), bar);
     };
+    const int64_t n_my = (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;      // tiles of this CTA
     if (!QJL && warp == THREADS / 32) {
-        // ---- issuing warp (one lane): tile copies two ahead, a tile's MMAs as soon as its vectors have
-        // landed and the accumulator buffer they go to has been read out
-        if (lane == 0) {
-            const int64_t n_my = (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
-            auto tile_of = [&](int64_t i) { return (int64_t)blockIdx.x + i * gridDim.x; };
-            // Enough bytes must be in flight per SM to cover the memory latency: three tiles.
-            for (int i = 0; i < C::kXBufs && i < n_my; ++i) fetch_tile(tile_of(i), i);
-            uint32_t xb = 0, xuse = 0;                      // vector buffer of tile i and how often it was used
-            for (int64_t i = 0; i < n_my && ok && !*abort_s; ++i) {
-                const uint32_t b = (uint32_t)i & 1u, use = (uint32_t)(i >> 1);
-                ok = mbar_wait(sm_addr(mbar + 2 + xb), xuse & 1u, abort_s) && ok;
-                if (i >= 2) ok = mbar_wait(sm_addr(mbar + 5 + b), (use - 1u) & 1u, abort_s) && ok;
-                if (!ok) break;
-                issue_rotation(Xa + xb * C::kXBytes, b * C::kBufCols, mbar + b);
-                if (i >= 1 && i + 2 < n_my) {
-                    // the previous tile's MMAs have finished reading their vector buffer: refill it
-                    ok = mbar_wait(sm_addr(mbar + (b ^ 1u)), (uint32_t)((i - 1) >> 1) & 1u, abort_s) && ok;
-                    if (ok) fetch_tile(tile_of(i + 2), (int)(xb == 0 ? C::kXBufs - 1 : xb - 1));
+        // ---- MMA warp: a tile's MMAs go out as soon as its vectors have landed and the accumulator
+        // buffer they write has been read out.  One MMA per k-step, N = 2D: columns [0, D) receive the
+        // products with R's hi term, [D, 2D) those with its lo term.  Every lane runs the loop (so the
+        // waits and the descriptor arithmetic stay warp-uniform); lane 0 issues.
+        constexpr uint32_t idesc = umma_idesc_f16(2 * D);
+        constexpr uint32_t kLboB = (2 * D / 8) * 128;                     // K-chunk stride of the stacked R tile
+        constexpr uint32_t a_hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // 8-row groups 1024 B apart, 128-B swizzle
+        constexpr uint32_t b_hi = (128u >> 4) | (1u << 14);                // 8-row groups 128 B apart, no swizzle
+        const uint32_t a_lo0 = ((sm_addr(Xa) >> 4) & 0x3FFFu) | (1u << 16);
+        const uint32_t b_lo0 = ((sm_addr(Rb) >> 4) & 0x3FFFu) | ((kLboB >> 4) << 16);
+        uint32_t xb = 0, xuse = 0;                          // vector buffer of tile i and how often it was used
+        for (int64_t i = 0; i < n_my && ok; ++i) {
+            const uint32_t b = (uint32_t)i & 1u, use = (uint32_t)(i >> 1);
+            ok = mbar_wait(sm_addr(mbar + 2 + xb), xuse & 1u, abort_s, 32) && ok;
+            if (i >= 2) ok = mbar_wait(sm_addr(mbar + 5 + b), (use - 1u) & 1u, abort_s, 32) && ok;
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t a_lo = a_lo0 + xb * (uint32_t)(C::kXBytes >> 4);
+                const uint32_t acc = tmem_base + b * C::kBufCols;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    // a k-step is 32 B further inside the swizzled 128-byte row, 64 halves fill a 16 KB box
+                    umma_f16_split(acc, a_lo + (uint32_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), a_hi,
+                                   b_lo0 + (uint32_t)((2 * ks * kLboB) >> 4), b_hi, idesc, ks ? 1u : 0u);
                 }
-                if (++xb == C::kXBufs) { xb = 0; ++xuse; }
+                umma_commit(sm_addr(mbar + b));             // accumulators ready for the epilogue
+                umma_commit(sm_addr(mbar + 7 + xb));        // vector buffer free for the next copy
             }
-            if (!ok) { *abort_s = 1u; atomicOr(&g_compress_error, 1u); }
+            __syncwarp();
+            if (++xb == C::kXBufs) { xb = 0; ++xuse; }
         }
+        if (!ok && lane == 0) { *abort_s = 1u; atomicOr(&g_compress_error, 1u); }
+    } else if (!QJL && warp == THREADS / 32 + 1) {
+        // ---- copy warp: keeps kXBufs tiles in flight or in use; a buffer is refilled as soon as the
+        // MMAs that read it have completed
+        uint32_t xb = 0, xuse = 0;
+        for (int64_t i = 0; i < n_my && ok; ++i) {
+            if (i >= C::kXBufs) ok = mbar_wait(sm_addr(mbar + 7 + xb), (xuse - 1u) & 1u, abort_s, 64) && ok;
+            if (!ok) break;
+            if (lane == 0) fetch_tile((int64_t)blockIdx.x + i * gridDim.x, (int)xb);
+            __syncwarp();
+            if (++xb == C::kXBufs) { xb = 0; ++xuse; }
+        }
+        if (!ok && lane == 0) { *abort_s = 1u; atomicOr(&g_compress_error, 1u); }
     } else {
 
-#ifdef PQ_EXPERIMENT_STAGGER
-    { const long long t0 = clock64(); while (clock64() - t0 < (long long)wg * PQ_EXPERIMENT_STAGGER) {} }
-#endif
     uint32_t it = 0;
     for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
         const int64_t v0 = tile * kTileVecs;
@@ -537,7 +545,7 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
             float2 part[16];
             tmem_ld32(part, tmem_tile + grp * D + wg * 32);
 #pragma unroll
-            for (int k = 0; k < 16; ++k) v2[k] = PQ_ADD_OP(v2[k], part[k]);
+            for (int k = 0; k < 16; ++k) v2[k] = add2(v2[k], part[k]);
         }
         if (!QJL) {                      // this thread's part of the accumulator buffer is in registers
             tc_fence_before();
@@ -548,10 +556,10 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
         float2 r2[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            float2 a = PQ_SQ_MUL(v2[q], v2[q]);
-            a = PQ_SQ_ADD(a, PQ_SQ_MUL(v2[4 + q], v2[4 + q]));
-            a = PQ_SQ_ADD(a, PQ_SQ_MUL(v2[8 + q], v2[8 + q]));
-            r2[q] = PQ_SQ_ADD(a, PQ_SQ_MUL(v2[12 + q], v2[12 + q]));
+            float2 a = mul2(v2[q], v2[q]);
+            a = add2(a, mul2(v2[4 + q], v2[4 + q]));
+            a = add2(a, mul2(v2[8 + q], v2[8 + q]));
+            r2[q] = add2(a, mul2(v2[12 + q], v2[12 + q]));
         }
         const float ss = __fadd_rn(__fadd_rn(__fadd_rn(r2[0].x, r2[0].y), __fadd_rn(r2[1].x, r2[1].y)),
                                    __fadd_rn(__fadd_rn(r2[2].x, r2[2].y), __fadd_rn(r2[3].x, r2[3].y)));
@@ -578,9 +586,9 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
         float* v = reinterpret_cast<float*>(&v2[0]);
 #pragma unroll
         for (int k = 0; k < 16; ++k) {
-            const float2 y0 = PQ_DIR_MUL(v2[k], rinv2);
-            const float2 dir = PQ_DIR_FMA(PQ_DIR_FMA(y0, negd2, v2[k]), rinv2, y0);
-            const float2 u = PQ_KEY_FMA(dir, c64, cmagic);
+            const float2 y0 = mul2(v2[k], rinv2);
+            const float2 dir = fma2(fma2(y0, negd2, v2[k]), rinv2, y0);
+            const float2 u = fma2(dir, c64, cmagic);
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int j = 2 * k + e;
@@ -691,11 +699,7 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
             fence_async_smem();                  // the bulk store reads `outs` through the async proxy
             if (leader) bulk_wait_read();        // the store that last read the other staging buffer is done
             // the barrier also votes: a wait that gave up anywhere in the CTA stops every group
-#ifdef PQ_EXPERIMENT_NO_GROUP_BARRIER
-            if (false) {
-#else
             if (group_barrier_any(1u + q, 32u * WG, !ok || *abort_s != 0u)) {
-#endif
                 *abort_s = 1u;
                 break;
             }
@@ -816,6 +820,7 @@ static int launch_compress(const CompressParams& p, cudaStream_t stream) {
 }
 
 }  // namespace pq
+
 
 extern "C" int pq_poll_device_errors(unsigned int* flags_out) {
     if (!flags_out) return PQ_ERR_NULL_POINTER;
