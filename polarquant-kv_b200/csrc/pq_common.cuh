@@ -69,4 +69,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// Device error flags of the prefill kernel, read and cleared (defined in pq_prefill_attn.cu).
+int prefill_error_flags(unsigned int* flags);
+
 }  // namespace pq

@@ -1,25 +1,41 @@
-// pq_prefill_attn: seq_q >= 1 query tokens per head against a block_pq4 cache.
+// pq_prefill_attn: seq_q >= 1 query tokens per head against a block_pq4 cache, on the 5th-gen
+// tensor cores (tcgen05.mma, accumulators in tensor memory).
 //
 // Same rotated-space arithmetic as the decode kernel (softmax(q K^T * scale) V evaluated on
 // centroid * radius values, python/polarquant_kv/attention.py:111-163), organised for many
-// query rows: a CTA owns 128 query rows of one KV head (rows = (query head, position)
-// pairs of the GQA group, 16 per warp) and walks the sequence in tiles of 32 tokens.
-// Each tile of K and V is dequantised ONCE per CTA into shared memory as two float16 terms
-// (value = hi + lo, about 22 bits) and both contractions run on tensor cores
-// (mma.sync.m16n8k16, float32 accumulate) as three-term products hi*hi + hi*lo + lo*hi,
-// which keeps float32-level accuracy.  Online softmax in registers; the result is
-// normalised and rotated back (o @ R) through shared memory.
+// query rows: a CTA owns 128 query rows of one KV head (rows = (query head, position) pairs of
+// the GQA group; TMEM lane = row) and walks the sequence in tiles of 64 tokens.  Every operand
+// is a pair of float16 terms (value = hi + lo, about 22 bits) and every contraction a
+// three-term product hi*hi + hi*lo + lo*hi with float32 accumulation, which keeps float32-level
+// accuracy.  Radii: a token's largest block radius dmax is applied in float32 (to the score
+// column / to the probability before its split); the tiles hold (d / dmax) * centroid * 1024.
+//
+// Roles (no CTA-wide barrier inside the loop; all waits are bounded mbarrier waits):
+//   8 dequant warps - expand tile i of K, then of V, into shared memory in the 128-byte-swizzled
+//                     layout the tensor core reads ([half of 64 dims][token][128 B]);
+//   1 MMA warp      - S(i+1) = Q K(i+1)^T into one of two TMEM buffers (64 columns each) while
+//                     the softmax of tile i runs, then O += P(i) V(i) (V as an MN-major operand);
+//   4 softmax warps - thread = query row: read S from TMEM, scale, mask, online softmax with a
+//                     lazy rescale of O (only when a row's maximum grew by more than 2^8), write
+//                     P * dmax_v as float16 hi/lo into shared memory for the second contraction.
+// The query rotation q @ R^T and the final o @ R run before and after the loop.
 //
 // causal == 0 reproduces the reference (no mask, src/polarquant_kv_cuda/attention_kernel.py:
 // 92-113); causal == 1 lets query position i see tokens [0, seq_len - seq_q + i].
-#include "pq_common.cuh"
+#include "pq_tcgen05.cuh"
 
 namespace pq {
 
-constexpr int kPfWarps = 8;
-constexpr int kPfThreads = kPfWarps * 32;
-constexpr int kPfRows = kPfWarps * 16;   // query rows per CTA
-constexpr int kPfTok = 32;               // tokens per KV tile
+// Bit 2 of the device error flags: a bounded wait in the prefill kernel gave up.
+static __device__ unsigned int g_prefill_error = 0;
+
+constexpr int kPfRows = 128;                 // query rows per CTA = TMEM lanes
+constexpr int kPfTok = 64;                   // tokens per KV tile
+constexpr int kPfSoftWarps = 4, kPfDeqWarps = 8;
+constexpr int kPfDeqThreads = kPfDeqWarps * 32;
+constexpr int kPfThreads = (kPfSoftWarps + kPfDeqWarps + 1) * 32;
+constexpr float kPfValScale = 1024.0f;       // tiles hold 1024 * (d / dmax) * centroid
+constexpr float kPfRescaleGap = 8.0f;        // log2 units a row maximum may grow before O is rescaled
 
 struct PrefillParams {
     const __half* q;       // [B, Hq, Sq, D]
@@ -34,120 +50,143 @@ struct PrefillParams {
     float cbk[16], cbv[16];
 };
 
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3,
-                                                  const void* smem_row) {
-    uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr));
+enum { PF_K_FULL = 0, PF_V_FULL = 1, PF_P_FULL = 2, PF_S_FULL = 3, PF_S_FREE = 5, PF_PV_DONE = 7, PF_NBAR = 8 };
+
+// Byte offset of element (row r, column col) of a [rows][64*h columns] float16 tile stored as
+// 64-column halves of `rows` 128-byte rows, 16-byte chunks XOR-swizzled with the row (SWIZZLE_128B).
+__device__ __forceinline__ uint32_t sw128_off(int rows, int r, int col) {
+    return (uint32_t)((col >> 6) * rows * 128 + (r >> 3) * 1024 + (r & 7) * 128 + ((((col & 63) >> 3) ^ (r & 7)) << 4) +
+                      (col & 7) * 2);
 }
 
-// Expand `ntok` tokens of one operand into hi/lo float16 centroid tiles [kPfTok][LD] and the
-// float32 radii [kPfTok][NBLK].  `tab` maps a byte of packed indices to its centroids:
-// 4-bit: uint2 {half2 hi, half2 lo}; 2-bit: uint4 {hi01, hi23, lo01, lo23}.
-template <int D, int BITS, int LD>
-__device__ __forceinline__ void dequant_tile(const uint8_t* __restrict__ src, int ntok, const uint8_t* tab,
-                                             __half* hi, __half* lo, float* dd, int tid) {
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+        "%30,%31,%32};\n" ::"r"(taddr),
+        "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])),
+        "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
+        "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+        "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
+        "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+
+// Expand `ntok` tokens of one operand into the hi / lo tiles and the per-token largest radius.
+// Work item: 8 consecutive elements of one (token, block).  `cb` holds 1024 * centroid.
+template <int D, int BITS>
+__device__ __forceinline__ void dequant_tile(const uint8_t* __restrict__ src, int ntok, const float* cb,
+                                             uint8_t* hi, uint8_t* lo, float* dmax_out, int dt) {
     constexpr int NBLK = D / 32, BB = block_bytes(BITS), TB = NBLK * BB;
-    if (BITS == 4) {
-        // work item: 32 bits of indices = 8 elements
-        for (int w = tid; w < kPfTok * NBLK * 4; w += kPfThreads) {
-            const int tok = w / (NBLK * 4), rem = w % (NBLK * 4), blk = rem >> 2, qw = rem & 3;
-            uint4 vh = make_uint4(0, 0, 0, 0), vl = make_uint4(0, 0, 0, 0);
-            if (tok < ntok) {
-                const uint8_t* b = src + (size_t)tok * TB + blk * BB;
-                const uint16_t* p16 = reinterpret_cast<const uint16_t*>(b + 2 + qw * 4);
-                const uint32_t bits = (uint32_t)p16[0] | ((uint32_t)p16[1] << 16);
-                const uint2 e0 = reinterpret_cast<const uint2*>(tab)[bits & 0xFF];
-                const uint2 e1 = reinterpret_cast<const uint2*>(tab)[(bits >> 8) & 0xFF];
-                const uint2 e2 = reinterpret_cast<const uint2*>(tab)[(bits >> 16) & 0xFF];
-                const uint2 e3 = reinterpret_cast<const uint2*>(tab)[bits >> 24];
-                vh = make_uint4(e0.x, e1.x, e2.x, e3.x);
-                vl = make_uint4(e0.y, e1.y, e2.y, e3.y);
-                if (qw == 0) dd[tok * NBLK + blk] = __half2float(*reinterpret_cast<const __half*>(b));
-            } else if (qw == 0) {
-                dd[tok * NBLK + blk] = 0.f;
+    constexpr int ITEMS = kPfTok * NBLK * 4;
+#pragma unroll
+    for (int w = dt; w < ITEMS; w += kPfDeqThreads) {
+        const int tok = w / (NBLK * 4), rem = w % (NBLK * 4), blk = rem >> 2, qw = rem & 3;
+        uint4 vh = make_uint4(0, 0, 0, 0), vl = make_uint4(0, 0, 0, 0);
+        float dmax = 0.f;
+        if (tok < ntok) {
+            const uint8_t* tb = src + (size_t)tok * TB;
+            float d = 0.f;
+#pragma unroll
+            for (int k = 0; k < NBLK; ++k) {
+                const float dk = __half2float(*reinterpret_cast<const __half*>(tb + k * BB));
+                dmax = fmaxf(dmax, dk);
+                if (k == blk) d = dk;
             }
-            *reinterpret_cast<uint4*>(hi + tok * LD + blk * 32 + qw * 8) = vh;
-            *reinterpret_cast<uint4*>(lo + tok * LD + blk * 32 + qw * 8) = vl;
-        }
-    } else {
-        // work item: 16 bits of indices = 8 elements
-        for (int w = tid; w < kPfTok * NBLK * 4; w += kPfThreads) {
-            const int tok = w / (NBLK * 4), rem = w % (NBLK * 4), blk = rem >> 2, qw = rem & 3;
-            uint4 vh = make_uint4(0, 0, 0, 0), vl = make_uint4(0, 0, 0, 0);
-            if (tok < ntok) {
-                const uint8_t* b = src + (size_t)tok * TB + blk * BB;
-                const uint32_t bits = *reinterpret_cast<const uint16_t*>(b + 2 + qw * 2);
-                const uint4 e0 = reinterpret_cast<const uint4*>(tab)[bits & 0xFF];
-                const uint4 e1 = reinterpret_cast<const uint4*>(tab)[bits >> 8];
-                vh = make_uint4(e0.x, e0.y, e1.x, e1.y);
-                vl = make_uint4(e0.z, e0.w, e1.z, e1.w);
-                if (qw == 0) dd[tok * NBLK + blk] = __half2float(*reinterpret_cast<const __half*>(b));
-            } else if (qw == 0) {
-                dd[tok * NBLK + blk] = 0.f;
+            const float r = dmax > 0.f ? d / dmax : 0.f;
+            uint32_t bits;
+            if (BITS == 4) {
+                const uint16_t* p16 = reinterpret_cast<const uint16_t*>(tb + blk * BB + 2 + qw * 4);
+                bits = (uint32_t)p16[0] | ((uint32_t)p16[1] << 16);
+            } else {
+                bits = *reinterpret_cast<const uint16_t*>(tb + blk * BB + 2 + qw * 2);
             }
-            *reinterpret_cast<uint4*>(hi + tok * LD + blk * 32 + qw * 8) = vh;
-            *reinterpret_cast<uint4*>(lo + tok * LD + blk * 32 + qw * 8) = vl;
+            uint32_t h[4], l[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float v0 = cb[(bits >> (2 * e * BITS)) & ((1u << BITS) - 1u)] * r;
+                const float v1 = cb[(bits >> ((2 * e + 1) * BITS)) & ((1u << BITS) - 1u)] * r;
+                const __half2 hh = __floats2half2_rn(v0, v1);
+                const float2 hf = __half22float2(hh);
+                h[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                l[e] = pack_half2(v0 - hf.x, v1 - hf.y);
+            }
+            vh = make_uint4(h[0], h[1], h[2], h[3]);
+            vl = make_uint4(l[0], l[1], l[2], l[3]);
         }
+        const uint32_t off = sw128_off(kPfTok, tok, blk * 32 + qw * 8);
+        *reinterpret_cast<uint4*>(hi + off) = vh;
+        *reinterpret_cast<uint4*>(lo + off) = vl;
+        if (rem == 0) dmax_out[tok] = dmax;
     }
 }
 
-// Byte -> centroid table (not replicated: the tile expansion is a small part of the work).
-template <int BITS>
-__device__ __forceinline__ void build_byte_table(uint8_t* tab, const float* cb, int tid) {
-    for (int b = tid; b < 256; b += kPfThreads) {
-        if (BITS == 4) {
-            __half h0, l0, h1, l1;
-            split_half(cb[b & 15] * 64.0f, h0, l0);
-            split_half(cb[b >> 4] * 64.0f, h1, l1);
-            __half2 hi = __halves2half2(h0, h1), lo = __halves2half2(l0, l1);
-            reinterpret_cast<uint2*>(tab)[b] =
-                make_uint2(*reinterpret_cast<uint32_t*>(&hi), *reinterpret_cast<uint32_t*>(&lo));
-        } else {
-            __half h[4], l[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) split_half(cb[(b >> (2 * k)) & 3] * 64.0f, h[k], l[k]);
-            __half2 h01 = __halves2half2(h[0], h[1]), h23 = __halves2half2(h[2], h[3]);
-            __half2 l01 = __halves2half2(l[0], l[1]), l23 = __halves2half2(l[2], l[3]);
-            reinterpret_cast<uint4*>(tab)[b] =
-                make_uint4(*reinterpret_cast<uint32_t*>(&h01), *reinterpret_cast<uint32_t*>(&h23),
-                           *reinterpret_cast<uint32_t*>(&l01), *reinterpret_cast<uint32_t*>(&l23));
-        }
+template <int D>
+struct PrefillCfg {
+    static constexpr uint32_t QB = kPfRows * D * 2;            // one term of the query tile
+    static constexpr uint32_t KB = kPfTok * D * 2;             // one term of a K or V tile
+    static constexpr uint32_t PB = kPfRows * kPfTok * 2;       // one term of the probability tile
+    static constexpr uint32_t kTiles = 2 * QB + 4 * KB + 2 * PB;
+    static constexpr uint32_t kSmall = 3 * kPfTok * 4 + 32 * 4 + PF_NBAR * 8 + 16;
+    static constexpr int SLD = D + 4;                          // float32 staging row for the output rotation
+    static constexpr size_t smem_bytes() {
+        const size_t stage = (size_t)kPfRows * SLD * 4;
+        return (kTiles > stage ? kTiles : stage) + kSmall + 1024;
     }
-}
+    static constexpr uint32_t kTmemCols = 256;                 // S0 | S1 | O (64 + 64 + D <= 256)
+};
 
 template <int D, int KBITS, int VBITS>
 __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const PrefillParams p) {
+    using C = PrefillCfg<D>;
     constexpr int NBLK = D / 32;
-    constexpr int LD = D + 8;                         // padded row (halves) of the K/V tiles
     constexpr int TBK = NBLK * block_bytes(KBITS), TBV = NBLK * block_bytes(VBITS);
-    constexpr int KSTEPS = D / 16;
-    constexpr int NT_O = D / 8;
 
-    extern __shared__ __align__(16) uint8_t smem[];
-    __half* Khi = reinterpret_cast<__half*>(smem);            // [32][LD]
-    __half* Klo = Khi + kPfTok * LD;
-    __half* Vhi = Klo + kPfTok * LD;
-    __half* Vlo = Vhi + kPfTok * LD;
-    __half* Qhi = Vlo + kPfTok * LD;                          // [128][LD]
-    __half* Qlo = Qhi + kPfRows * LD;
-    float* stage = reinterpret_cast<float*>(Qhi);             // [128][D+4] float, reuses Q tiles at the end
-    __shared__ float cbk_s[16], cbv_s[16];
-    __shared__ float dK[kPfTok * NBLK], dV[kPfTok * NBLK];
-    __shared__ __align__(16) uint8_t tabk[4096], tabv[4096];
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* Qh = base;
+    uint8_t* Ql = Qh + C::QB;
+    uint8_t* Kh = Ql + C::QB;
+    uint8_t* Kl = Kh + C::KB;
+    uint8_t* Vh = Kl + C::KB;
+    uint8_t* Vl = Vh + C::KB;
+    uint8_t* Ph = Vl + C::KB;
+    uint8_t* Pl = Ph + C::PB;
+    float* stage = reinterpret_cast<float*>(base);                        // [128][SLD], after the loop
+    uint8_t* small = base + (C::kTiles > kPfRows * C::SLD * 4 ? C::kTiles : kPfRows * C::SLD * 4);
+    float* dmaxK = reinterpret_cast<float*>(small);                       // [2][64]
+    float* dmaxV = dmaxK + 2 * kPfTok;                                    // [64]
+    float* cbk_s = dmaxV + kPfTok;
+    float* cbv_s = cbk_s + 16;
+    uint64_t* mbar = reinterpret_cast<uint64_t*>(cbv_s + 16);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + PF_NBAR);
+    volatile uint32_t* abort_s = tmem_slot + 1;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = lane >> 2, t = lane & 3;
     const int row_tile = blockIdx.x, kvrow = blockIdx.y;
     const int b = kvrow / p.Hkv, hkv = kvrow % p.Hkv;
     const int n_rows = p.G * p.Sq;                            // query rows sharing this KV head
     const int row0 = row_tile * kPfRows;
 
-    if (tid < 16) { cbk_s[tid] = p.cbk[tid]; cbv_s[tid] = p.cbv[tid]; }
-    __syncthreads();
-    build_byte_table<KBITS>(tabk, cbk_s, tid);
-    build_byte_table<VBITS>(tabv, cbv_s, tid);
+    if (tid < 16) { cbk_s[tid] = p.cbk[tid] * kPfValScale; cbv_s[tid] = p.cbv[tid] * kPfValScale; }
+    if (tid == 0) {
+        mbar_init(sm_addr(mbar + PF_K_FULL), kPfDeqThreads);
+        mbar_init(sm_addr(mbar + PF_V_FULL), kPfDeqThreads);
+        mbar_init(sm_addr(mbar + PF_P_FULL), kPfSoftWarps * 32);
+        mbar_init(sm_addr(mbar + PF_S_FULL), 1);
+        mbar_init(sm_addr(mbar + PF_S_FULL + 1), 1);
+        mbar_init(sm_addr(mbar + PF_S_FREE), kPfSoftWarps * 32);
+        mbar_init(sm_addr(mbar + PF_S_FREE + 1), kPfSoftWarps * 32);
+        mbar_init(sm_addr(mbar + PF_PV_DONE), 1);
+        *abort_s = 0u;
+    }
+    if (warp == 0) tmem_alloc(sm_addr(tmem_slot), C::kTmemCols);
 
     // ---- rotate the CTA's query rows: q_rot = q @ R^T, scaled by scale*log2(e), split hi/lo
     for (int e = tid; e < kPfRows * D; e += kPfThreads) {
@@ -169,199 +208,222 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
         }
         __half h, l;
         split_half(acc, h, l);
-        Qhi[r * LD + i] = h;
-        Qlo[r * LD + i] = l;
+        const uint32_t off = sw128_off(kPfRows, r, i);
+        *reinterpret_cast<__half*>(Qh + off) = h;
+        *reinterpret_cast<__half*>(Ql + off) = l;
     }
+    fence_async_smem();          // the tensor core reads the query tiles through the async proxy
+    tc_fence_before();
     __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
 
-    uint32_t qh[KSTEPS][4], ql[KSTEPS][4];
-#pragma unroll
-    for (int ks = 0; ks < KSTEPS; ++ks) {
-        const int off = (warp * 16 + (lane & 15)) * LD + ks * 16 + (lane >> 4) * 8;
-        ldmatrix_x4(qh[ks][0], qh[ks][1], qh[ks][2], qh[ks][3], Qhi + off);
-        ldmatrix_x4(ql[ks][0], ql[ks][1], ql[ks][2], ql[ks][3], Qlo + off);
-    }
-
-    // per-thread rows: g and g+8 of the warp's 16
-    int limit[2];
-#pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-        const int row = row0 + warp * 16 + hh * 8 + g;
-        const int sq = row % p.Sq;
-        limit[hh] = p.causal ? (int)(p.S - p.Sq + sq + 1) : (int)p.S;      // tokens [0, limit)
-        if (row >= n_rows) limit[hh] = 0;
-    }
-    // the CTA can stop after the largest limit among its rows
+    // tokens this CTA has to visit
     int64_t kv_end = p.S;
     if (p.causal) {
         const int last_row = min(row0 + kPfRows, n_rows) - 1;
         // rows are (head, position) pairs; a tile may span several heads, so take the max
-        int max_sq = 0;
-        if (row0 / p.Sq != last_row / p.Sq) max_sq = p.Sq - 1;
-        else max_sq = last_row % p.Sq;
+        const int max_sq = (row0 / p.Sq != last_row / p.Sq) ? p.Sq - 1 : last_row % p.Sq;
         kv_end = p.S - p.Sq + max_sq + 1;
         if (kv_end > p.S) kv_end = p.S;
         if (kv_end < 0) kv_end = 0;
     }
-
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-    float o[NT_O][4];
-#pragma unroll
-    for (int n = 0; n < NT_O; ++n)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
-
+    const int n_tiles = (int)((kv_end + kPfTok - 1) / kPfTok);
     const uint8_t* k_row = p.kb + (size_t)kvrow * p.Scap * TBK;
     const uint8_t* v_row = p.vb + (size_t)kvrow * p.Scap * TBV;
+    bool ok = true;
+    float inv_l = 0.f;                                                    // softmax threads: 1 / (1024 * row sum)
 
-    for (int64_t tok0 = 0; tok0 < kv_end; tok0 += kPfTok) {
-        const int ntok = (p.S - tok0) < kPfTok ? (int)(p.S - tok0) : kPfTok;
-        __syncthreads();   // previous tile fully consumed
-        dequant_tile<D, KBITS, LD>(k_row + tok0 * TBK, ntok, tabk, Khi, Klo, dK, tid);
-        dequant_tile<D, VBITS, LD>(v_row + tok0 * TBV, ntok, tabv, Vhi, Vlo, dV, tid);
-        __syncthreads();
-
-        // ---- S = Q K^T : 16 rows x 32 tokens per warp, one 32-dim block at a time so the
-        // block radius can scale the partial sums in float32
-        float s[4][4];
-#pragma unroll
-        for (int n = 0; n < 4; ++n)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) s[n][i] = 0.f;
-#pragma unroll
-        for (int blk = 0; blk < NBLK; ++blk) {
-            float c[4][4];
-#pragma unroll
-            for (int n = 0; n < 4; ++n)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) c[n][i] = 0.f;
-#pragma unroll
-            for (int k2 = 0; k2 < 2; ++k2) {
-                const int ks = blk * 2 + k2;
-#pragma unroll
-                for (int n = 0; n < 4; n += 2) {
-                    // two token n-tiles per ldmatrix: (tok n*8.., k 0-7), (.., k 8-15), (tok (n+1)*8.., ..)
-                    uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
-                    const int j = lane >> 3;
-                    const int off = ((n + (j >> 1)) * 8 + (lane & 7)) * LD + ks * 16 + (j & 1) * 8;
-                    ldmatrix_x4(h0, h1, h2, h3, Khi + off);
-                    ldmatrix_x4(l0, l1, l2, l3, Klo + off);
-                    mma_16816(c[n], qh[ks][0], qh[ks][1], qh[ks][2], qh[ks][3], h0, h1);
-                    mma_16816(c[n], qh[ks][0], qh[ks][1], qh[ks][2], qh[ks][3], l0, l1);
-                    mma_16816(c[n], ql[ks][0], ql[ks][1], ql[ks][2], ql[ks][3], h0, h1);
-                    mma_16816(c[n + 1], qh[ks][0], qh[ks][1], qh[ks][2], qh[ks][3], h2, h3);
-                    mma_16816(c[n + 1], qh[ks][0], qh[ks][1], qh[ks][2], qh[ks][3], l2, l3);
-                    mma_16816(c[n + 1], ql[ks][0], ql[ks][1], ql[ks][2], ql[ks][3], h2, h3);
-                }
-            }
-#pragma unroll
-            for (int n = 0; n < 4; ++n) {
-                const float d0 = dK[(n * 8 + 2 * t) * NBLK + blk] * (1.0f / 64.0f);
-                const float d1 = dK[(n * 8 + 2 * t + 1) * NBLK + blk] * (1.0f / 64.0f);
-                s[n][0] = fmaf(d0, c[n][0], s[n][0]);
-                s[n][1] = fmaf(d1, c[n][1], s[n][1]);
-                s[n][2] = fmaf(d0, c[n][2], s[n][2]);
-                s[n][3] = fmaf(d1, c[n][3], s[n][3]);
-            }
-        }
-        // ---- mask, online softmax (rows g and g+8)
-    #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
+    if (warp < kPfSoftWarps) {
+        // =================================================== softmax: thread = query row
+        const int r = tid;
+        const uint32_t tlane = tmem_base + ((uint32_t)(warp * 32) << 16);
+        const int row = row0 + r;
+        int limit = p.causal ? (int)(p.S - p.Sq + (row % p.Sq) + 1) : (int)p.S;        // tokens [0, limit)
+        if (limit > p.S) limit = (int)p.S;
+        if (row >= n_rows || limit < 0) limit = 0;
+        float m_run = -INFINITY, m_used = -INFINITY, l_run = 0.f;
+        const uint32_t prow = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+        for (int i = 0; i < n_tiles && ok; ++i) {
+            const int sb = i & 1;
+            // (S complete implies the tile's K expansion, and with it dmaxK[sb], is complete)
+            ok = mbar_wait(sm_addr(mbar + PF_S_FULL + sb), (i >> 1) & 1, abort_s) && ok;
+            tc_fence_after();
+            float s[kPfTok];
+            tmem_ld32(*reinterpret_cast<float(*)[32]>(&s[0]), tlane + sb * kPfTok);
+            tmem_ld32(*reinterpret_cast<float(*)[32]>(&s[32]), tlane + sb * kPfTok + 32);
+            const float* dk = dmaxK + sb * kPfTok;
+            const int tok0 = i * kPfTok;
             float mx = -INFINITY;
 #pragma unroll
-            for (int n = 0; n < 4; ++n)
+            for (int t = 0; t < kPfTok; ++t) {
+                const float v = s[t] * (dk[t] * (1.0f / kPfValScale));
+                s[t] = (tok0 + t < limit) ? v : -INFINITY;
+                mx = fmaxf(mx, s[t]);
+            }
+            tc_fence_before();
+            mbar_arrive(sm_addr(mbar + PF_S_FREE + sb));                // S buffer and dmaxK[sb] consumed
+            m_run = fmaxf(m_run, mx);
+            // the previous tile's P V must be complete before P is rewritten or O rescaled
+            if (i > 0) {
+                ok = mbar_wait(sm_addr(mbar + PF_PV_DONE), (i - 1) & 1, abort_s) && ok;
+                tc_fence_after();
+            }
+            const bool grow = m_run > m_used + kPfRescaleGap;           // also true on the first finite maximum
+            if (__any_sync(0xffffffffu, grow)) {
+                if (i > 0) {
+                    const float alpha = (m_run == -INFINITY) ? 1.f : fast_exp2(m_used - m_run);   // exp2(-inf) = 0
+#pragma unroll 1
+                    for (int c = 0; c < D / 32; ++c) {
+                        float o[32];
+                        tmem_ld32(o, tlane + 2 * kPfTok + c * 32);
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int tok = (int)tok0 + n * 8 + 2 * t + e;
-                    if (tok >= limit[hh]) s[n][hh * 2 + e] = -INFINITY;
-                    mx = fmaxf(mx, s[n][hh * 2 + e]);
+                        for (int k = 0; k < 32; ++k) o[k] *= alpha;
+                        tmem_st32(tlane + 2 * kPfTok + c * 32, o);
+                    }
+                    l_run *= alpha;
+                    tc_fence_before();
                 }
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float m_new = fmaxf(m_run[hh], mx);
-            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            const float alpha = fast_exp2(m_run[hh] - m_use);
+                m_used = m_run;
+            }
+            const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+            ok = mbar_wait(sm_addr(mbar + PF_V_FULL), i & 1, abort_s) && ok;        // dmaxV of this tile is visible
             float sum = 0.f;
 #pragma unroll
-            for (int n = 0; n < 4; ++n)
+            for (int c = 0; c < kPfTok / 8; ++c) {
+                uint32_t h[4], l[4];
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const float pv = fast_exp2(s[n][hh * 2 + e] - m_use);
-                    s[n][hh * 2 + e] = pv;
-                    sum += pv;
+                for (int e = 0; e < 4; ++e) {
+                    const int t = c * 8 + 2 * e;
+                    const float p0 = fast_exp2(s[t] - m_sub), p1 = fast_exp2(s[t + 1] - m_sub);
+                    sum += p0 + p1;
+                    const float w0 = p0 * dmaxV[t], w1 = p1 * dmaxV[t + 1];
+                    const __half2 hh = __floats2half2_rn(w0, w1);
+                    const float2 hf = __half22float2(hh);
+                    h[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                    l[e] = pack_half2(w0 - hf.x, w1 - hf.y);
                 }
-            l_run[hh] = l_run[hh] * alpha + sum;
-            m_run[hh] = m_new;
-#pragma unroll
-            for (int n = 0; n < NT_O; ++n) {
-                o[n][hh * 2 + 0] *= alpha;
-                o[n][hh * 2 + 1] *= alpha;
+                const uint32_t off = prow + (uint32_t)((c ^ (r & 7)) << 4);
+                *reinterpret_cast<uint4*>(Ph + off) = make_uint4(h[0], h[1], h[2], h[3]);
+                *reinterpret_cast<uint4*>(Pl + off) = make_uint4(l[0], l[1], l[2], l[3]);
             }
+            l_run += sum;
+            fence_async_smem();
+            mbar_arrive(sm_addr(mbar + PF_P_FULL));
         }
-        // ---- O += P V, one 32-dim block at a time: the value radius of (token, block) is
-        // folded into P before the float16 split.  C fragments of P map onto A fragments:
-        // k-step kk covers token n-tiles 2kk and 2kk+1.
+        if (n_tiles > 0) {
+            ok = mbar_wait(sm_addr(mbar + PF_PV_DONE), (n_tiles - 1) & 1, abort_s) && ok;
+            tc_fence_after();
+        }
+        inv_l = l_run > 0.f ? (1.0f / kPfValScale) / l_run : 0.f;
+        (void)m_run;
+    } else if (warp < kPfSoftWarps + kPfDeqWarps) {
+        // =================================================== dequantisation
+        const int dt = tid - kPfSoftWarps * 32;
+        for (int i = 0; i < n_tiles && ok; ++i) {
+            const int64_t tok0 = (int64_t)i * kPfTok;
+            const int ntok = (int)min((int64_t)kPfTok, p.S - tok0);
+            // K tile: free once S(i-1) has been computed; its dmaxK slot once softmax(i-2) has read it
+            if (i >= 1) ok = mbar_wait(sm_addr(mbar + PF_S_FULL + ((i - 1) & 1)), ((i - 1) >> 1) & 1, abort_s) && ok;
+            if (i >= 2) ok = mbar_wait(sm_addr(mbar + PF_S_FREE + (i & 1)), ((i >> 1) - 1) & 1, abort_s) && ok;
+            if (!ok) break;
+            dequant_tile<D, KBITS>(k_row + tok0 * TBK, ntok, cbk_s, Kh, Kl, dmaxK + (i & 1) * kPfTok, dt);
+            fence_async_smem();
+            mbar_arrive(sm_addr(mbar + PF_K_FULL));
+            // V tile: free once P(i-1) V(i-1) has completed
+            if (i >= 1) ok = mbar_wait(sm_addr(mbar + PF_PV_DONE), (i - 1) & 1, abort_s) && ok;
+            if (!ok) break;
+            dequant_tile<D, VBITS>(v_row + tok0 * TBV, ntok, cbv_s, Vh, Vl, dmaxV, dt);
+            fence_async_smem();
+            mbar_arrive(sm_addr(mbar + PF_V_FULL));
+        }
+    } else {
+        // =================================================== MMA issue (all lanes loop, lane 0 issues)
+        constexpr uint32_t idesc_s = umma_idesc_f16(kPfTok);                   // M 128, N 64, A and B K-major
+        constexpr uint32_t idesc_pv = umma_idesc_f16(D) | (1u << 16);          // M 128, N D, B MN-major
+        constexpr uint32_t d_hi = (1024u >> 4) | (1u << 14) | (2u << 29);      // 8-row groups 1024 B apart, SWIZZLE_128B
+        const uint32_t q_h = ((sm_addr(Qh) >> 4) & 0x3FFFu) | (1u << 16), q_l = ((sm_addr(Ql) >> 4) & 0x3FFFu) | (1u << 16);
+        const uint32_t k_h = ((sm_addr(Kh) >> 4) & 0x3FFFu) | (1u << 16), k_l = ((sm_addr(Kl) >> 4) & 0x3FFFu) | (1u << 16);
+        const uint32_t p_h = ((sm_addr(Ph) >> 4) & 0x3FFFu) | (1u << 16), p_l = ((sm_addr(Pl) >> 4) & 0x3FFFu) | (1u << 16);
+        // V: 64-dim atoms kPfTok*128 B apart (leading offset), 8-token groups 1024 B apart
+        constexpr uint32_t v_lbo = ((kPfTok * 128u) >> 4) << 16;
+        const uint32_t v_h = ((sm_addr(Vh) >> 4) & 0x3FFFu) | v_lbo, v_l = ((sm_addr(Vl) >> 4) & 0x3FFFu) | v_lbo;
+        auto issue_s = [&](int i) {
+            const int sb = i & 1;
+            ok = mbar_wait(sm_addr(mbar + PF_K_FULL), i & 1, abort_s, 32) && ok;
+            if (i >= 2) ok = mbar_wait(sm_addr(mbar + PF_S_FREE + sb), ((i >> 1) - 1) & 1, abort_s, 32) && ok;
+            if (!ok) return;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t acc = tmem_base + sb * kPfTok;
 #pragma unroll
-        for (int blk = 0; blk < NBLK; ++blk) {
-#pragma unroll
-            for (int kk = 0; kk < 2; ++kk) {
-                uint32_t pah[4], pal[4];
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    // r: 0 -> (row g, n-tile 2kk), 1 -> (row g+8, 2kk), 2 -> (row g, 2kk+1), 3 -> (row g+8, 2kk+1)
-                    const int n = 2 * kk + (r >> 1), hh = r & 1;
-                    const float d0 = dV[(n * 8 + 2 * t) * NBLK + blk];
-                    const float d1 = dV[(n * 8 + 2 * t + 1) * NBLK + blk];
-                    __half h0, l0, h1, l1;
-                    split_half(s[n][hh * 2 + 0] * d0, h0, l0);
-                    split_half(s[n][hh * 2 + 1] * d1, h1, l1);
-                    __half2 hv = __halves2half2(h0, h1), lv = __halves2half2(l0, l1);
-                    pah[r] = *reinterpret_cast<uint32_t*>(&hv);
-                    pal[r] = *reinterpret_cast<uint32_t*>(&lv);
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t qo = (uint32_t)(((ks >> 2) * (kPfRows * 128) + (ks & 3) * 32) >> 4);
+                    const uint32_t ko = (uint32_t)(((ks >> 2) * (kPfTok * 128) + (ks & 3) * 32) >> 4);
+                    umma_f16_split(acc, q_h + qo, d_hi, k_h + ko, d_hi, idesc_s, ks ? 1u : 0u);
+                    umma_f16_split(acc, q_h + qo, d_hi, k_l + ko, d_hi, idesc_s, 1u);
+                    umma_f16_split(acc, q_l + qo, d_hi, k_h + ko, d_hi, idesc_s, 1u);
                 }
-#pragma unroll
-                for (int nn = 0; nn < 4; nn += 2) {
-                    const int n = blk * 4 + nn;
-                    uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
-                    const int j = lane >> 3;
-                    const int off = (kk * 16 + (j & 1) * 8 + (lane & 7)) * LD + (n + (j >> 1)) * 8;
-                    ldmatrix_x4_trans(h0, h1, h2, h3, Vhi + off);
-                    ldmatrix_x4_trans(l0, l1, l2, l3, Vlo + off);
-                    mma_16816(o[n], pah[0], pah[1], pah[2], pah[3], h0, h1);
-                    mma_16816(o[n], pah[0], pah[1], pah[2], pah[3], l0, l1);
-                    mma_16816(o[n], pal[0], pal[1], pal[2], pal[3], h0, h1);
-                    mma_16816(o[n + 1], pah[0], pah[1], pah[2], pah[3], h2, h3);
-                    mma_16816(o[n + 1], pah[0], pah[1], pah[2], pah[3], l2, l3);
-                    mma_16816(o[n + 1], pal[0], pal[1], pal[2], pal[3], h2, h3);
-                }
+                umma_commit(sm_addr(mbar + PF_S_FULL + sb));
             }
+            __syncwarp();
+        };
+        if (n_tiles > 0) issue_s(0);
+        for (int i = 0; i < n_tiles && ok; ++i) {
+            if (i + 1 < n_tiles) issue_s(i + 1);
+            ok = mbar_wait(sm_addr(mbar + PF_P_FULL), i & 1, abort_s, 32) && ok;
+            ok = mbar_wait(sm_addr(mbar + PF_V_FULL), i & 1, abort_s, 32) && ok;
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t acc = tmem_base + 2 * kPfTok;
+#pragma unroll
+                for (int kt = 0; kt < kPfTok / 16; ++kt) {
+                    const uint32_t po = (uint32_t)((kt * 32) >> 4), vo = (uint32_t)((kt * 16 * 128) >> 4);
+                    umma_f16_split(acc, p_h + po, d_hi, v_h + vo, d_hi, idesc_pv, (i > 0 || kt > 0) ? 1u : 0u);
+                    umma_f16_split(acc, p_h + po, d_hi, v_l + vo, d_hi, idesc_pv, 1u);
+                    umma_f16_split(acc, p_l + po, d_hi, v_h + vo, d_hi, idesc_pv, 1u);
+                }
+                umma_commit(sm_addr(mbar + PF_PV_DONE));
+            }
+            __syncwarp();
         }
     }
+    if (!ok) {
+        *abort_s = 1u;
+        if (lane == 0) atomicOr(&g_prefill_error, 4u);
+    }
+    tc_fence_before();
+    __syncthreads();          // every tile buffer is dead: the staging rows may overwrite them
+    tc_fence_after();
 
     // ---- normalise, stage in shared memory, rotate back: out = o_rot @ R
+    if (warp < kPfSoftWarps) {
+        const uint32_t tlane = tmem_base + ((uint32_t)(warp * 32) << 16);
+        float* dst = stage + tid * C::SLD;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+            float o[32];
+            if (n_tiles > 0) {
+                tmem_ld32(o, tlane + 2 * kPfTok + c * 32);
+            } else {
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 1);
-        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 2);
-    }
-    __syncthreads();   // Q tiles are dead (fragments live in registers); reuse them as the stage
-    constexpr int SLD = D + 4;
+                for (int k = 0; k < 32; ++k) o[k] = 0.f;
+            }
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-        const float inv = l_run[hh] > 0.f ? (1.0f / 64.0f) / l_run[hh] : 0.f;
-        float* dst = stage + (warp * 16 + hh * 8 + g) * SLD;
-#pragma unroll
-        for (int n = 0; n < NT_O; ++n) {
-            dst[n * 8 + 2 * t + 0] = o[n][hh * 2 + 0] * inv;
-            dst[n * 8 + 2 * t + 1] = o[n][hh * 2 + 1] * inv;
+            for (int k = 0; k < 32; k += 4)
+                *reinterpret_cast<float4*>(dst + c * 32 + k) =
+                    make_float4(o[k] * inv_l, o[k + 1] * inv_l, o[k + 2] * inv_l, o[k + 3] * inv_l);
         }
     }
+    tc_fence_before();
     __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, C::kTmemCols);
     for (int e = tid; e < kPfRows * D; e += kPfThreads) {
         const int r = e / D, i = e % D;
         const int row = row0 + r;
         if (row >= n_rows) continue;
-        const float* src = stage + r * SLD;
+        const float* src = stage + r * C::SLD;
         float acc = 0.f;
 #pragma unroll 8
         for (int j = 0; j < D; ++j) acc = fmaf(src[j], __ldg(p.rot + (size_t)j * D + i), acc);
@@ -374,11 +436,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
 
 template <int D, int KBITS, int VBITS>
 static int launch_prefill(const PrefillParams& p, int rows, cudaStream_t st) {
-    constexpr int LD = D + 8;
-    const size_t tiles = (size_t)4 * kPfTok * LD * 2;
-    const size_t qtiles = (size_t)2 * kPfRows * LD * 2;
-    const size_t stage = (size_t)kPfRows * (D + 4) * 4;
-    const size_t smem = tiles + (qtiles > stage ? qtiles : stage) + 16;
+    const size_t smem = PrefillCfg<D>::smem_bytes();
     auto kern = pq_prefill_attn_kernel<D, KBITS, VBITS>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return PQ_ERR_CUDA;
@@ -386,6 +444,15 @@ static int launch_prefill(const PrefillParams& p, int rows, cudaStream_t st) {
     dim3 grid((n_rows + kPfRows - 1) / kPfRows, rows, 1);
     kern<<<grid, kPfThreads, smem, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? PQ_OK : PQ_ERR_CUDA;
+}
+
+// Read and clear this file's device error flag (for pq_poll_device_errors).
+int prefill_error_flags(unsigned int* flags) {
+    unsigned int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_prefill_error, sizeof(v)) != cudaSuccess) return PQ_ERR_CUDA;
+    if (v && cudaMemcpyToSymbol(g_prefill_error, &zero, sizeof(zero)) != cudaSuccess) return PQ_ERR_CUDA;
+    *flags = v;
+    return PQ_OK;
 }
 
 }  // namespace pq
