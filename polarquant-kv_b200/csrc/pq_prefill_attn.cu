@@ -50,7 +50,7 @@ struct PrefillParams {
     float cbk[16], cbv[16];
 };
 
-enum { PF_K_FULL = 0, PF_V_FULL = 1, PF_P_FULL = 2, PF_S_FULL = 3, PF_S_FREE = 5, PF_PV_DONE = 7, PF_NBAR = 8 };
+enum { PF_K_FULL = 0, PF_V_FULL = 1, PF_P_FULL = 2, PF_S_FULL = 3, PF_S_FREE = 5, PF_PV_DONE = 7, PF_AUX = 8, PF_NBAR = 9 };
 
 // Byte offset of element (row r, column col) of a [rows][64*h columns] float16 tile stored as
 // 64-column halves of `rows` 128-byte rows, 16-byte chunks XOR-swizzled with the row (SWIZZLE_128B).
@@ -133,12 +133,8 @@ struct PrefillCfg {
     static constexpr uint32_t KB = kPfTok * D * 2;             // one term of a K or V tile
     static constexpr uint32_t PB = kPfRows * kPfTok * 2;       // one term of the probability tile
     static constexpr uint32_t kTiles = 2 * QB + 4 * KB + 2 * PB;
-    static constexpr uint32_t kSmall = 3 * kPfTok * 4 + 32 * 4 + PF_NBAR * 8 + 16;
-    static constexpr int SLD = D + 4;                          // float32 staging row for the output rotation
-    static constexpr size_t smem_bytes() {
-        const size_t stage = (size_t)kPfRows * SLD * 4;
-        return (kTiles > stage ? kTiles : stage) + kSmall + 1024;
-    }
+    static constexpr uint32_t kSmall = 3 * kPfTok * 4 + 32 * 4 + PF_NBAR * 8 + 24;
+    static constexpr size_t smem_bytes() { return (size_t)kTiles + kSmall + 1024; }
     static constexpr uint32_t kTmemCols = 256;                 // S0 | S1 | O (64 + 64 + D <= 256)
 };
 
@@ -158,8 +154,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
     uint8_t* Vl = Vh + C::KB;
     uint8_t* Ph = Vl + C::KB;
     uint8_t* Pl = Ph + C::PB;
-    float* stage = reinterpret_cast<float*>(base);                        // [128][SLD], after the loop
-    uint8_t* small = base + (C::kTiles > kPfRows * C::SLD * 4 ? C::kTiles : kPfRows * C::SLD * 4);
+    uint8_t* small = base + C::kTiles;
     float* dmaxK = reinterpret_cast<float*>(small);                       // [2][64]
     float* dmaxV = dmaxK + 2 * kPfTok;                                    // [64]
     float* cbk_s = dmaxV + kPfTok;
@@ -184,38 +179,102 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
         mbar_init(sm_addr(mbar + PF_S_FREE), kPfSoftWarps * 32);
         mbar_init(sm_addr(mbar + PF_S_FREE + 1), kPfSoftWarps * 32);
         mbar_init(sm_addr(mbar + PF_PV_DONE), 1);
+        mbar_init(sm_addr(mbar + PF_AUX), 1);                 // the two rotations before and after the loop
         *abort_s = 0u;
     }
     if (warp == 0) tmem_alloc(sm_addr(tmem_slot), C::kTmemCols);
-
-    // ---- rotate the CTA's query rows: q_rot = q @ R^T, scaled by scale*log2(e), split hi/lo
-    for (int e = tid; e < kPfRows * D; e += kPfThreads) {
-        const int r = e / D, i = e % D;
-        const int row = row0 + r;
-        float acc = 0.f;
-        if (row < n_rows) {
-            const int head = hkv * p.G + row / p.Sq, sq = row % p.Sq;
-            const __half2* qv = reinterpret_cast<const __half2*>(p.q + (((size_t)b * p.Hq + head) * p.Sq + sq) * D);
-            const float2* rv = reinterpret_cast<const float2*>(p.rot + (size_t)i * D);
-#pragma unroll 8
-            for (int j = 0; j < D / 2; ++j) {
-                const float2 qq = __half22float2(qv[j]);
-                const float2 rr = __ldg(rv + j);
-                acc = fmaf(qq.x, rr.x, acc);
-                acc = fmaf(qq.y, rr.y, acc);
-            }
-            acc *= p.scale_log2;
-        }
-        __half h, l;
-        split_half(acc, h, l);
-        const uint32_t off = sw128_off(kPfRows, r, i);
-        *reinterpret_cast<__half*>(Qh + off) = h;
-        *reinterpret_cast<__half*>(Ql + off) = l;
-    }
-    fence_async_smem();          // the tensor core reads the query tiles through the async proxy
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+
+    // ---- rotate the CTA's query rows on the tensor core: q_rot = q @ R^T with R as two float16
+    // terms of 4096*R stacked along N ([R_hi ; R_lo], 2D rows), q exact in float16.  Operands are built
+    // in the (still unused) tile buffers: A = q tile in the P buffers, B in the K/V buffers.
+    {
+        uint8_t* Aq = Ph;                                                  // [128][D] float16, 2 * PB = 128 * D * 2 bytes
+        uint8_t* Bq = Kh;                                                  // [2D][D] float16, 4 * KB = 2D * D * 2 bytes
+        for (int w = tid; w < kPfRows * (D / 8); w += kPfThreads) {
+            const int r = w / (D / 8), c = w % (D / 8);
+            const int row = row0 + r;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (row < n_rows) {
+                const int head = hkv * p.G + row / p.Sq, sq = row % p.Sq;
+                v = __ldg(reinterpret_cast<const uint4*>(p.q + (((size_t)b * p.Hq + head) * p.Sq + sq) * D) + c);
+            }
+            *reinterpret_cast<uint4*>(Aq + sw128_off(kPfRows, r, c * 8)) = v;
+        }
+        for (int w = tid; w < D * (D / 8); w += kPfThreads) {
+            const int n = w / (D / 8), c = w % (D / 8);
+            const float4 a = __ldg(reinterpret_cast<const float4*>(p.rot + (size_t)n * D + c * 8));
+            const float4 bq = __ldg(reinterpret_cast<const float4*>(p.rot + (size_t)n * D + c * 8 + 4));
+            const float x[8] = {a.x * 4096.f, a.y * 4096.f, a.z * 4096.f, a.w * 4096.f,
+                                bq.x * 4096.f, bq.y * 4096.f, bq.z * 4096.f, bq.w * 4096.f};
+            uint32_t h[4], l[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const __half2 hh = __floats2half2_rn(x[2 * e], x[2 * e + 1]);
+                const float2 hf = __half22float2(hh);
+                h[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                l[e] = pack_half2(x[2 * e] - hf.x, x[2 * e + 1] - hf.y);
+            }
+            *reinterpret_cast<uint4*>(Bq + sw128_off(2 * D, n, c * 8)) = make_uint4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<uint4*>(Bq + sw128_off(2 * D, D + n, c * 8)) = make_uint4(l[0], l[1], l[2], l[3]);
+        }
+        fence_async_smem();          // the tensor core reads shared memory through the async proxy
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+        const uint32_t tmem_base0 = *tmem_slot;
+        if (warp == kPfSoftWarps + kPfDeqWarps) {
+            if (lane == 0) {
+                constexpr uint32_t idesc = umma_idesc_f16(2 * D);
+                constexpr uint32_t d_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+                const uint32_t a_lo = ((sm_addr(Aq) >> 4) & 0x3FFFu) | (1u << 16);
+                const uint32_t b_lo = ((sm_addr(Bq) >> 4) & 0x3FFFu) | (1u << 16);
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t ao = (uint32_t)(((ks >> 2) * (kPfRows * 128) + (ks & 3) * 32) >> 4);
+                    const uint32_t bo = (uint32_t)(((ks >> 2) * (2 * D * 128) + (ks & 3) * 32) >> 4);
+                    umma_f16_split(tmem_base0, a_lo + ao, d_hi, b_lo + bo, d_hi, idesc, ks ? 1u : 0u);
+                }
+                umma_commit(sm_addr(mbar + PF_AUX));
+            }
+            __syncwarp();
+        }
+        if (warp < kPfSoftWarps) {
+            bool okq = mbar_wait(sm_addr(mbar + PF_AUX), 0u, abort_s);
+            tc_fence_after();
+            const uint32_t tlane = tmem_base0 + ((uint32_t)(warp * 32) << 16);
+            const float sc = p.scale_log2 * (1.0f / 4096.0f);
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                float vh[32], vl[32];
+                tmem_ld32(vh, tlane + c * 32);
+                tmem_ld32(vl, tlane + D + c * 32);
+#pragma unroll
+                for (int g8 = 0; g8 < 4; ++g8) {
+                    uint32_t h[4], l[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int k = g8 * 8 + 2 * e;
+                        const float x0 = (vh[k] + vl[k]) * sc, x1 = (vh[k + 1] + vl[k + 1]) * sc;
+                        const __half2 hh = __floats2half2_rn(x0, x1);
+                        const float2 hf = __half22float2(hh);
+                        h[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                        l[e] = pack_half2(x0 - hf.x, x1 - hf.y);
+                    }
+                    const uint32_t off = sw128_off(kPfRows, tid, c * 32 + g8 * 8);
+                    *reinterpret_cast<uint4*>(Qh + off) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4*>(Ql + off) = make_uint4(l[0], l[1], l[2], l[3]);
+                }
+            }
+            if (!okq) { *abort_s = 1u; if (lane == 0) atomicOr(&g_prefill_error, 4u); }
+        }
+        fence_async_smem();
+        tc_fence_before();
+        __syncthreads();          // query tiles complete; operand buffers and TMEM free for the loop
+        tc_fence_after();
+    }
     const uint32_t tmem_base = *tmem_slot;
 
     // tokens this CTA has to visit
@@ -394,44 +453,123 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
         if (lane == 0) atomicOr(&g_prefill_error, 4u);
     }
     tc_fence_before();
-    __syncthreads();          // every tile buffer is dead: the staging rows may overwrite them
+    __syncthreads();          // every tile buffer is dead
     tc_fence_after();
 
-    // ---- normalise, stage in shared memory, rotate back: out = o_rot @ R
-    if (warp < kPfSoftWarps) {
-        const uint32_t tlane = tmem_base + ((uint32_t)(warp * 32) << 16);
-        float* dst = stage + tid * C::SLD;
+    // ---- normalise and rotate back on the tensor core: out = o_rot @ R as o_hi*Rt_hi + o_hi*Rt_lo +
+    // o_lo*Rt_hi with Rt = 4096 * R^T.  A = o as two float16 terms in the query buffers, B = [Rt_hi ; Rt_lo]
+    // stacked along N in the K/V buffers.
+    {
+        uint8_t* Bq = Kh;
+        if (warp < kPfSoftWarps) {
+            const uint32_t tlane = tmem_base + ((uint32_t)(warp * 32) << 16);
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-            float o[32];
-            if (n_tiles > 0) {
-                tmem_ld32(o, tlane + 2 * kPfTok + c * 32);
-            } else {
+            for (int c = 0; c < D / 32; ++c) {
+                float o[32];
+                if (n_tiles > 0) {
+                    tmem_ld32(o, tlane + 2 * kPfTok + c * 32);
+                } else {
 #pragma unroll
-                for (int k = 0; k < 32; ++k) o[k] = 0.f;
+                    for (int k = 0; k < 32; ++k) o[k] = 0.f;
+                }
+#pragma unroll
+                for (int g8 = 0; g8 < 4; ++g8) {
+                    uint32_t h[4], l[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int k = g8 * 8 + 2 * e;
+                        const float x0 = o[k] * inv_l, x1 = o[k + 1] * inv_l;
+                        const __half2 hh = __floats2half2_rn(x0, x1);
+                        const float2 hf = __half22float2(hh);
+                        h[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                        l[e] = pack_half2(x0 - hf.x, x1 - hf.y);
+                    }
+                    const uint32_t off = sw128_off(kPfRows, tid, c * 32 + g8 * 8);
+                    *reinterpret_cast<uint4*>(Qh + off) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4*>(Ql + off) = make_uint4(l[0], l[1], l[2], l[3]);
+                }
             }
+        }
+        // B[n][j] = 4096 * R[j][n]: lanes walk n, so the reads of R are contiguous
+        for (int w = tid; w < D * (D / 8); w += kPfThreads) {
+            const int c = w / D, n = w % D;
+            uint32_t h[4], l[4];
 #pragma unroll
-            for (int k = 0; k < 32; k += 4)
-                *reinterpret_cast<float4*>(dst + c * 32 + k) =
-                    make_float4(o[k] * inv_l, o[k + 1] * inv_l, o[k + 2] * inv_l, o[k + 3] * inv_l);
+            for (int e = 0; e < 4; ++e) {
+                const float x0 = __ldg(p.rot + (size_t)(c * 8 + 2 * e) * D + n) * 4096.f;
+                const float x1 = __ldg(p.rot + (size_t)(c * 8 + 2 * e + 1) * D + n) * 4096.f;
+                const __half2 hh = __floats2half2_rn(x0, x1);
+                const float2 hf = __half22float2(hh);
+                h[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                l[e] = pack_half2(x0 - hf.x, x1 - hf.y);
+            }
+            *reinterpret_cast<uint4*>(Bq + sw128_off(2 * D, n, c * 8)) = make_uint4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<uint4*>(Bq + sw128_off(2 * D, D + n, c * 8)) = make_uint4(l[0], l[1], l[2], l[3]);
+        }
+        fence_async_smem();
+        tc_fence_before();
+        __syncthreads();          // operands complete, every thread has read its part of O
+        tc_fence_after();
+        if (warp == kPfSoftWarps + kPfDeqWarps) {
+            if (lane == 0) {
+                constexpr uint32_t idesc2 = umma_idesc_f16(2 * D), idesc1 = umma_idesc_f16(D);
+                constexpr uint32_t d_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+                const uint32_t ah = ((sm_addr(Qh) >> 4) & 0x3FFFu) | (1u << 16), al = ((sm_addr(Ql) >> 4) & 0x3FFFu) | (1u << 16);
+                const uint32_t b_lo = ((sm_addr(Bq) >> 4) & 0x3FFFu) | (1u << 16);
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t ao = (uint32_t)(((ks >> 2) * (kPfRows * 128) + (ks & 3) * 32) >> 4);
+                    const uint32_t bo = (uint32_t)(((ks >> 2) * (2 * D * 128) + (ks & 3) * 32) >> 4);
+                    umma_f16_split(tmem_base, ah + ao, d_hi, b_lo + bo, d_hi, idesc2, ks ? 1u : 0u);
+                }
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {       // o_lo against the hi rows only (N = D)
+                    const uint32_t ao = (uint32_t)(((ks >> 2) * (kPfRows * 128) + (ks & 3) * 32) >> 4);
+                    const uint32_t bo = (uint32_t)(((ks >> 2) * (2 * D * 128) + (ks & 3) * 32) >> 4);
+                    umma_f16_split(tmem_base, al + ao, d_hi, b_lo + bo, d_hi, idesc1, 1u);
+                }
+                umma_commit(sm_addr(mbar + PF_AUX));
+            }
+            __syncwarp();
+        }
+        if (warp < kPfSoftWarps) {
+            const bool oko = mbar_wait(sm_addr(mbar + PF_AUX), 1u, abort_s);
+            tc_fence_after();
+            const uint32_t tlane = tmem_base + ((uint32_t)(warp * 32) << 16);
+            const int row = row0 + tid;
+            const int head = hkv * p.G + (row < n_rows ? row / p.Sq : 0), sq = row < n_rows ? row % p.Sq : 0;
+            const size_t off = (((size_t)b * p.Hq + head) * p.Sq + sq) * D;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                float va[32], vb[32];
+                tmem_ld32(va, tlane + c * 32);
+                tmem_ld32(vb, tlane + D + c * 32);
+                if (row < n_rows) {
+                    if (p.out_is_fp16) {
+                        __half* dst = static_cast<__half*>(p.out) + off + c * 32;
+#pragma unroll
+                        for (int k = 0; k < 32; k += 2) {
+                            const float x0 = (va[k] + vb[k]) * (1.0f / 4096.0f), x1 = (va[k + 1] + vb[k + 1]) * (1.0f / 4096.0f);
+                            *reinterpret_cast<__half2*>(dst + k) = __floats2half2_rn(fminf(fmaxf(x0, -65504.f), 65504.f),
+                                                                                      fminf(fmaxf(x1, -65504.f), 65504.f));
+                        }
+                    } else {
+                        float* dst = static_cast<float*>(p.out) + off + c * 32;
+#pragma unroll
+                        for (int k = 0; k < 32; k += 4)
+                            *reinterpret_cast<float4*>(dst + k) = make_float4((va[k] + vb[k]) * (1.0f / 4096.0f),
+                                                                              (va[k + 1] + vb[k + 1]) * (1.0f / 4096.0f),
+                                                                              (va[k + 2] + vb[k + 2]) * (1.0f / 4096.0f),
+                                                                              (va[k + 3] + vb[k + 3]) * (1.0f / 4096.0f));
+                    }
+                }
+            }
+            if (!oko) { *abort_s = 1u; if (lane == 0) atomicOr(&g_prefill_error, 4u); }
         }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_base, C::kTmemCols);
-    for (int e = tid; e < kPfRows * D; e += kPfThreads) {
-        const int r = e / D, i = e % D;
-        const int row = row0 + r;
-        if (row >= n_rows) continue;
-        const float* src = stage + r * C::SLD;
-        float acc = 0.f;
-#pragma unroll 8
-        for (int j = 0; j < D; ++j) acc = fmaf(src[j], __ldg(p.rot + (size_t)j * D + i), acc);
-        const int head = hkv * p.G + row / p.Sq, sq = row % p.Sq;
-        const size_t off = (((size_t)b * p.Hq + head) * p.Sq + sq) * D + i;
-        if (p.out_is_fp16) static_cast<__half*>(p.out)[off] = __float2half_rn(fminf(fmaxf(acc, -65504.f), 65504.f));
-        else static_cast<float*>(p.out)[off] = acc;
-    }
 }
 
 template <int D, int KBITS, int VBITS>
@@ -477,7 +615,8 @@ extern "C" int pq_prefill_attn(const void* q, const void* k_blocks, const void* 
     }
     if (!k_blocks || !v_blocks) return PQ_ERR_NULL_POINTER;
     if ((reinterpret_cast<uintptr_t>(k_blocks) & 3) || (reinterpret_cast<uintptr_t>(v_blocks) & 3) ||
-        (reinterpret_cast<uintptr_t>(q) & 3) || (reinterpret_cast<uintptr_t>(rot) & 15))
+        (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(rot) & 15) ||
+        (reinterpret_cast<uintptr_t>(out) & (out_is_fp16 ? 3 : 15)))
         return PQ_ERR_MISALIGNED;
     const int rows = batch * kv_heads;
     if (rows > 65535) return PQ_ERR_TOO_LARGE;
