@@ -31,7 +31,8 @@ static __device__ unsigned int g_prefill_error = 0;
 
 constexpr int kPfRows = 128;                 // query rows per CTA = TMEM lanes
 constexpr int kPfTok = 64;                   // tokens per KV tile
-constexpr int kPfSoftWarps = 4, kPfDeqWarps = 8;
+constexpr int kPfRowWarps = 4;               // warps that cover the 128 TMEM lanes once (rotation epilogues)
+constexpr int kPfSoftWarps = 8, kPfDeqWarps = 8;   // softmax: two threads per query row (32 tokens of a tile each)
 constexpr int kPfDeqThreads = kPfDeqWarps * 32;
 constexpr int kPfThreads = (kPfSoftWarps + kPfDeqWarps + 1) * 32;
 constexpr float kPfValScale = 1024.0f;       // tiles hold 1024 * (d / dmax) * centroid
@@ -50,7 +51,9 @@ struct PrefillParams {
     float cbk[16], cbv[16];
 };
 
-enum { PF_K_FULL = 0, PF_V_FULL = 1, PF_P_FULL = 2, PF_S_FULL = 3, PF_S_FREE = 5, PF_PV_DONE = 7, PF_AUX = 8, PF_NBAR = 9 };
+// Barriers that two roles wait on come in pairs, one per tile parity: a barrier's next phase can then
+// only complete after every waiter has seen the current one (a waiter never lags a whole phase).
+enum { PF_K_FULL = 0, PF_V_FULL = 2, PF_S_FULL = 4, PF_S_FREE = 6, PF_PV_DONE = 8, PF_P_FULL = 10, PF_AUX = 11, PF_NBAR = 12 };
 
 // Byte offset of element (row r, column col) of a [rows][64*h columns] float16 tile stored as
 // 64-column halves of `rows` 128-byte rows, 16-byte chunks XOR-swizzled with the row (SWIZZLE_128B).
@@ -78,62 +81,79 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
     asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 }
 
-// Expand `ntok` tokens of one operand into the hi / lo tiles and the per-token largest radius.
-// Work item: 8 consecutive elements of one (token, block).  `cb` holds 1024 * centroid.
+// One thread's share of a 64-token tile of one operand: work item = 8 consecutive elements of one
+// (token, block).  load() fetches the raw bytes (indices and the token's block radii) into registers,
+// expand() writes the hi / lo tiles (1024 * (d / dmax) * centroid) and the per-token largest radius.
+// Splitting the two lets the next tile's loads fly while this tile is expanded.
 template <int D, int BITS>
-__device__ __forceinline__ void dequant_tile(const uint8_t* __restrict__ src, int ntok, const float* cb,
-                                             uint8_t* hi, uint8_t* lo, float* dmax_out, int dt) {
-    constexpr int NBLK = D / 32, BB = block_bytes(BITS), TB = NBLK * BB;
-    constexpr int ITEMS = kPfTok * NBLK * 4;
+struct RawItems {
+    static constexpr int NBLK = D / 32, BB = block_bytes(BITS), TB = NBLK * BB;
+    static constexpr int N = kPfTok * NBLK * 4 / kPfDeqThreads;           // items per thread
+    uint32_t bits[N];
+    uint32_t rad[N][NBLK / 2];                                            // the token's radii, two per word
+
+    __device__ __forceinline__ void load(const uint8_t* __restrict__ src, int ntok, int dt) {
 #pragma unroll
-    for (int w = dt; w < ITEMS; w += kPfDeqThreads) {
-        const int tok = w / (NBLK * 4), rem = w % (NBLK * 4), blk = rem >> 2, qw = rem & 3;
-        uint4 vh = make_uint4(0, 0, 0, 0), vl = make_uint4(0, 0, 0, 0);
-        float dmax = 0.f;
-        if (tok < ntok) {
-            const uint8_t* tb = src + (size_t)tok * TB;
-            float d = 0.f;
+        for (int k = 0; k < N; ++k) {
+            const int w = dt + k * kPfDeqThreads;
+            const int tok = w / (NBLK * 4), rem = w % (NBLK * 4), blk = rem >> 2, qw = rem & 3;
+            bits[k] = 0u;
 #pragma unroll
-            for (int k = 0; k < NBLK; ++k) {
-                const float dk = __half2float(*reinterpret_cast<const __half*>(tb + k * BB));
-                dmax = fmaxf(dmax, dk);
-                if (k == blk) d = dk;
+            for (int j = 0; j < NBLK / 2; ++j) rad[k][j] = 0u;
+            if (tok < ntok) {
+                const uint8_t* tb = src + (size_t)tok * TB;
+#pragma unroll
+                for (int j = 0; j < NBLK / 2; ++j)
+                    rad[k][j] = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(tb + (2 * j) * BB)) |
+                                ((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(tb + (2 * j + 1) * BB)) << 16);
+                if (BITS == 4) {
+                    const uint16_t* p16 = reinterpret_cast<const uint16_t*>(tb + blk * BB + 2 + qw * 4);
+                    bits[k] = (uint32_t)__ldg(p16) | ((uint32_t)__ldg(p16 + 1) << 16);
+                } else {
+                    bits[k] = __ldg(reinterpret_cast<const uint16_t*>(tb + blk * BB + 2 + qw * 2));
+                }
             }
-            const float r = dmax > 0.f ? d / dmax : 0.f;
-            uint32_t bits;
-            if (BITS == 4) {
-                const uint16_t* p16 = reinterpret_cast<const uint16_t*>(tb + blk * BB + 2 + qw * 4);
-                bits = (uint32_t)p16[0] | ((uint32_t)p16[1] << 16);
-            } else {
-                bits = *reinterpret_cast<const uint16_t*>(tb + blk * BB + 2 + qw * 2);
+        }
+    }
+
+    __device__ __forceinline__ void expand(const float* cb, uint8_t* hi, uint8_t* lo, float* dmax_out, int dt) const {
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+            const int w = dt + k * kPfDeqThreads;
+            const int tok = w / (NBLK * 4), rem = w % (NBLK * 4), blk = rem >> 2, qw = rem & 3;
+            float dmax = 0.f, d = 0.f;
+#pragma unroll
+            for (int j = 0; j < NBLK; ++j) {
+                const float dj = __half2float(__ushort_as_half((unsigned short)(rad[k][j >> 1] >> (16 * (j & 1)))));
+                dmax = fmaxf(dmax, dj);
+                if (j == blk) d = dj;
             }
+            const float r = dmax > 0.f ? d / dmax : 0.f;                  // rows past the end: radii 0 -> zeros
             uint32_t h[4], l[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float v0 = cb[(bits >> (2 * e * BITS)) & ((1u << BITS) - 1u)] * r;
-                const float v1 = cb[(bits >> ((2 * e + 1) * BITS)) & ((1u << BITS) - 1u)] * r;
+                const float v0 = cb[(bits[k] >> (2 * e * BITS)) & ((1u << BITS) - 1u)] * r;
+                const float v1 = cb[(bits[k] >> ((2 * e + 1) * BITS)) & ((1u << BITS) - 1u)] * r;
                 const __half2 hh = __floats2half2_rn(v0, v1);
                 const float2 hf = __half22float2(hh);
                 h[e] = *reinterpret_cast<const uint32_t*>(&hh);
                 l[e] = pack_half2(v0 - hf.x, v1 - hf.y);
             }
-            vh = make_uint4(h[0], h[1], h[2], h[3]);
-            vl = make_uint4(l[0], l[1], l[2], l[3]);
+            const uint32_t off = sw128_off(kPfTok, tok, blk * 32 + qw * 8);
+            *reinterpret_cast<uint4*>(hi + off) = make_uint4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<uint4*>(lo + off) = make_uint4(l[0], l[1], l[2], l[3]);
+            if (rem == 0) dmax_out[tok] = dmax;
         }
-        const uint32_t off = sw128_off(kPfTok, tok, blk * 32 + qw * 8);
-        *reinterpret_cast<uint4*>(hi + off) = vh;
-        *reinterpret_cast<uint4*>(lo + off) = vl;
-        if (rem == 0) dmax_out[tok] = dmax;
     }
-}
+};
 
 template <int D>
 struct PrefillCfg {
     static constexpr uint32_t QB = kPfRows * D * 2;            // one term of the query tile
     static constexpr uint32_t KB = kPfTok * D * 2;             // one term of a K or V tile
     static constexpr uint32_t PB = kPfRows * kPfTok * 2;       // one term of the probability tile
-    static constexpr uint32_t kTiles = 2 * QB + 4 * KB + 2 * PB;
-    static constexpr uint32_t kSmall = 3 * kPfTok * 4 + 32 * 4 + PF_NBAR * 8 + 24;
+    static constexpr uint32_t kTiles = 2 * QB + 8 * KB + 2 * PB;       // K and V tiles are double-buffered
+    static constexpr uint32_t kSmall = 4 * kPfTok * 4 + 32 * 4 + PF_NBAR * 8 + 24;
     static constexpr size_t smem_bytes() { return (size_t)kTiles + kSmall + 1024; }
     static constexpr uint32_t kTmemCols = 256;                 // S0 | S1 | O (64 + 64 + D <= 256)
 };
@@ -148,16 +168,14 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* Qh = base;
     uint8_t* Ql = Qh + C::QB;
-    uint8_t* Kh = Ql + C::QB;
-    uint8_t* Kl = Kh + C::KB;
-    uint8_t* Vh = Kl + C::KB;
-    uint8_t* Vl = Vh + C::KB;
-    uint8_t* Ph = Vl + C::KB;
+    uint8_t* Kh = Ql + C::QB;                 // buffer b: hi at Kh + b * 2KB, lo one KB further
+    uint8_t* Vh = Kh + 4 * C::KB;             // same for V
+    uint8_t* Ph = Vh + 4 * C::KB;
     uint8_t* Pl = Ph + C::PB;
     uint8_t* small = base + C::kTiles;
     float* dmaxK = reinterpret_cast<float*>(small);                       // [2][64]
-    float* dmaxV = dmaxK + 2 * kPfTok;                                    // [64]
-    float* cbk_s = dmaxV + kPfTok;
+    float* dmaxV = dmaxK + 2 * kPfTok;                                    // [2][64]
+    float* cbk_s = dmaxV + 2 * kPfTok;
     float* cbv_s = cbk_s + 16;
     uint64_t* mbar = reinterpret_cast<uint64_t*>(cbv_s + 16);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + PF_NBAR);
@@ -171,14 +189,14 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
 
     if (tid < 16) { cbk_s[tid] = p.cbk[tid] * kPfValScale; cbv_s[tid] = p.cbv[tid] * kPfValScale; }
     if (tid == 0) {
-        mbar_init(sm_addr(mbar + PF_K_FULL), kPfDeqThreads);
-        mbar_init(sm_addr(mbar + PF_V_FULL), kPfDeqThreads);
+        for (int k = 0; k < 2; ++k) {
+            mbar_init(sm_addr(mbar + PF_K_FULL + k), kPfDeqThreads);
+            mbar_init(sm_addr(mbar + PF_V_FULL + k), kPfDeqThreads);
+            mbar_init(sm_addr(mbar + PF_S_FULL + k), 1);
+            mbar_init(sm_addr(mbar + PF_S_FREE + k), kPfSoftWarps * 32);
+            mbar_init(sm_addr(mbar + PF_PV_DONE + k), 1);
+        }
         mbar_init(sm_addr(mbar + PF_P_FULL), kPfSoftWarps * 32);
-        mbar_init(sm_addr(mbar + PF_S_FULL), 1);
-        mbar_init(sm_addr(mbar + PF_S_FULL + 1), 1);
-        mbar_init(sm_addr(mbar + PF_S_FREE), kPfSoftWarps * 32);
-        mbar_init(sm_addr(mbar + PF_S_FREE + 1), kPfSoftWarps * 32);
-        mbar_init(sm_addr(mbar + PF_PV_DONE), 1);
         mbar_init(sm_addr(mbar + PF_AUX), 1);                 // the two rotations before and after the loop
         *abort_s = 0u;
     }
@@ -241,7 +259,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
             }
             __syncwarp();
         }
-        if (warp < kPfSoftWarps) {
+        if (warp < kPfRowWarps) {
             bool okq = mbar_wait(sm_addr(mbar + PF_AUX), 0u, abort_s);
             tc_fence_after();
             const uint32_t tlane = tmem_base0 + ((uint32_t)(warp * 32) << 16);
@@ -291,54 +309,84 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
     const uint8_t* k_row = p.kb + (size_t)kvrow * p.Scap * TBK;
     const uint8_t* v_row = p.vb + (size_t)kvrow * p.Scap * TBV;
     bool ok = true;
-    float inv_l = 0.f;                                                    // softmax threads: 1 / (1024 * row sum)
+    float inv_l = 0.f;                                                    // row owners: 1 / (1024 * row sum)
 
     if (warp < kPfSoftWarps) {
-        // =================================================== softmax: thread = query row
-        const int r = tid;
-        const uint32_t tlane = tmem_base + ((uint32_t)(warp * 32) << 16);
+        // =================================================== softmax: two threads per query row
+        const int q = warp & 3, hf = warp >> 2;                           // TMEM lane quarter, token half of the tile
+        const int r = q * 32 + lane;
+        const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
         const int row = row0 + r;
         int limit = p.causal ? (int)(p.S - p.Sq + (row % p.Sq) + 1) : (int)p.S;        // tokens [0, limit)
         if (limit > p.S) limit = (int)p.S;
         if (row >= n_rows || limit < 0) limit = 0;
         float m_run = -INFINITY, m_used = -INFINITY, l_run = 0.f;
         const uint32_t prow = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+        constexpr int HT = kPfTok / 2;                                    // tokens per thread and tile
         for (int i = 0; i < n_tiles && ok; ++i) {
             const int sb = i & 1;
             // (S complete implies the tile's K expansion, and with it dmaxK[sb], is complete)
             ok = mbar_wait(sm_addr(mbar + PF_S_FULL + sb), (i >> 1) & 1, abort_s) && ok;
             tc_fence_after();
-            float s[kPfTok];
-            tmem_ld32(*reinterpret_cast<float(*)[32]>(&s[0]), tlane + sb * kPfTok);
-            tmem_ld32(*reinterpret_cast<float(*)[32]>(&s[32]), tlane + sb * kPfTok + 32);
-            const float* dk = dmaxK + sb * kPfTok;
-            const int tok0 = i * kPfTok;
+            float s[HT];
+            tmem_ld32(s, tlane + sb * kPfTok + hf * HT);
+            const float4* dk4 = reinterpret_cast<const float4*>(dmaxK + sb * kPfTok + hf * HT);
+            const int tok0 = i * kPfTok + hf * HT;
             float mx = -INFINITY;
 #pragma unroll
-            for (int t = 0; t < kPfTok; ++t) {
-                const float v = s[t] * (dk[t] * (1.0f / kPfValScale));
-                s[t] = (tok0 + t < limit) ? v : -INFINITY;
-                mx = fmaxf(mx, s[t]);
+            for (int t4 = 0; t4 < HT / 4; ++t4) {
+                const float4 d4 = dk4[t4];
+                s[4 * t4 + 0] *= d4.x * (1.0f / kPfValScale);
+                s[4 * t4 + 1] *= d4.y * (1.0f / kPfValScale);
+                s[4 * t4 + 2] *= d4.z * (1.0f / kPfValScale);
+                s[4 * t4 + 3] *= d4.w * (1.0f / kPfValScale);
+            }
+            if (tok0 + HT > limit) {                                      // only tiles that reach past the row's limit
+#pragma unroll
+                for (int t = 0; t < HT; ++t)
+                    if (tok0 + t >= limit) s[t] = -INFINITY;
+            }
+#pragma unroll
+            for (int t = 0; t < HT; ++t) mx = fmaxf(mx, s[t]);
+            {
+                // the row maximum needs the partner thread's half of the tile as well: read it too
+                float so[HT];
+                tmem_ld32(so, tlane + sb * kPfTok + (hf ^ 1) * HT);
+                const float4* do4 = reinterpret_cast<const float4*>(dmaxK + sb * kPfTok + (hf ^ 1) * HT);
+                const int toko = i * kPfTok + (hf ^ 1) * HT;
+#pragma unroll
+                for (int t4 = 0; t4 < HT / 4; ++t4) {
+                    const float4 d4 = do4[t4];
+                    const float x0 = so[4 * t4 + 0] * (d4.x * (1.0f / kPfValScale));
+                    const float x1 = so[4 * t4 + 1] * (d4.y * (1.0f / kPfValScale));
+                    const float x2 = so[4 * t4 + 2] * (d4.z * (1.0f / kPfValScale));
+                    const float x3 = so[4 * t4 + 3] * (d4.w * (1.0f / kPfValScale));
+                    if (toko + 4 * t4 + 0 < limit) mx = fmaxf(mx, x0);
+                    if (toko + 4 * t4 + 1 < limit) mx = fmaxf(mx, x1);
+                    if (toko + 4 * t4 + 2 < limit) mx = fmaxf(mx, x2);
+                    if (toko + 4 * t4 + 3 < limit) mx = fmaxf(mx, x3);
+                }
             }
             tc_fence_before();
             mbar_arrive(sm_addr(mbar + PF_S_FREE + sb));                // S buffer and dmaxK[sb] consumed
             m_run = fmaxf(m_run, mx);
             // the previous tile's P V must be complete before P is rewritten or O rescaled
             if (i > 0) {
-                ok = mbar_wait(sm_addr(mbar + PF_PV_DONE), (i - 1) & 1, abort_s) && ok;
+                ok = mbar_wait(sm_addr(mbar + PF_PV_DONE + ((i - 1) & 1)), ((i - 1) >> 1) & 1, abort_s) && ok;
                 tc_fence_after();
             }
             const bool grow = m_run > m_used + kPfRescaleGap;           // also true on the first finite maximum
-            if (__any_sync(0xffffffffu, grow)) {
+            if (__any_sync(0xffffffffu, grow)) {                        // same outcome in both warps of a row group
                 if (i > 0) {
                     const float alpha = (m_run == -INFINITY) ? 1.f : fast_exp2(m_used - m_run);   // exp2(-inf) = 0
 #pragma unroll 1
-                    for (int c = 0; c < D / 32; ++c) {
+                    for (int c = 0; c < D / 64; ++c) {                  // this thread's half of the O columns
                         float o[32];
-                        tmem_ld32(o, tlane + 2 * kPfTok + c * 32);
+                        const uint32_t col = 2 * kPfTok + hf * (D / 2) + c * 32;
+                        tmem_ld32(o, tlane + col);
 #pragma unroll
                         for (int k = 0; k < 32; ++k) o[k] *= alpha;
-                        tmem_st32(tlane + 2 * kPfTok + c * 32, o);
+                        tmem_st32(tlane + col, o);
                     }
                     l_run *= alpha;
                     tc_fence_before();
@@ -346,23 +394,26 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
                 m_used = m_run;
             }
             const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
-            ok = mbar_wait(sm_addr(mbar + PF_V_FULL), i & 1, abort_s) && ok;        // dmaxV of this tile is visible
+            ok = mbar_wait(sm_addr(mbar + PF_V_FULL + sb), (i >> 1) & 1, abort_s) && ok;   // dmaxV[sb] is visible
+            const float4* dv4 = reinterpret_cast<const float4*>(dmaxV + sb * kPfTok + hf * HT);
             float sum = 0.f;
 #pragma unroll
-            for (int c = 0; c < kPfTok / 8; ++c) {
+            for (int c = 0; c < HT / 8; ++c) {
+                const float4 da = dv4[2 * c], db = dv4[2 * c + 1];
+                const float dv[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
                 uint32_t h[4], l[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int t = c * 8 + 2 * e;
                     const float p0 = fast_exp2(s[t] - m_sub), p1 = fast_exp2(s[t + 1] - m_sub);
                     sum += p0 + p1;
-                    const float w0 = p0 * dmaxV[t], w1 = p1 * dmaxV[t + 1];
+                    const float w0 = p0 * dv[2 * e], w1 = p1 * dv[2 * e + 1];
                     const __half2 hh = __floats2half2_rn(w0, w1);
-                    const float2 hf = __half22float2(hh);
+                    const float2 hfl = __half22float2(hh);
                     h[e] = *reinterpret_cast<const uint32_t*>(&hh);
-                    l[e] = pack_half2(w0 - hf.x, w1 - hf.y);
+                    l[e] = pack_half2(w0 - hfl.x, w1 - hfl.y);
                 }
-                const uint32_t off = prow + (uint32_t)((c ^ (r & 7)) << 4);
+                const uint32_t off = prow + (uint32_t)(((hf * (HT / 8) + c) ^ (r & 7)) << 4);
                 *reinterpret_cast<uint4*>(Ph + off) = make_uint4(h[0], h[1], h[2], h[3]);
                 *reinterpret_cast<uint4*>(Pl + off) = make_uint4(l[0], l[1], l[2], l[3]);
             }
@@ -371,30 +422,53 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
             mbar_arrive(sm_addr(mbar + PF_P_FULL));
         }
         if (n_tiles > 0) {
-            ok = mbar_wait(sm_addr(mbar + PF_PV_DONE), (n_tiles - 1) & 1, abort_s) && ok;
+            ok = mbar_wait(sm_addr(mbar + PF_PV_DONE + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, abort_s) && ok;
             tc_fence_after();
         }
+        // row sum over both halves (both were kept relative to the same m_used), through the dead Ph tile
+        float* xchg = reinterpret_cast<float*>(Ph);
+        xchg[hf * kPfRows + r] = l_run;
+        asm volatile("bar.sync %0, 64;\n" ::"r"(1 + q) : "memory");
+        l_run += xchg[(hf ^ 1) * kPfRows + r];
         inv_l = l_run > 0.f ? (1.0f / kPfValScale) / l_run : 0.f;
-        (void)m_run;
     } else if (warp < kPfSoftWarps + kPfDeqWarps) {
-        // =================================================== dequantisation
+        // =================================================== dequantisation, one tile ahead of the MMAs
         const int dt = tid - kPfSoftWarps * 32;
+        RawItems<D, KBITS> rk;
+        RawItems<D, VBITS> rv;
+        if (n_tiles > 0) {
+            rk.load(k_row, (int)min((int64_t)kPfTok, p.S), dt);
+            rv.load(v_row, (int)min((int64_t)kPfTok, p.S), dt);
+        }
         for (int i = 0; i < n_tiles && ok; ++i) {
-            const int64_t tok0 = (int64_t)i * kPfTok;
-            const int ntok = (int)min((int64_t)kPfTok, p.S - tok0);
-            // K tile: free once S(i-1) has been computed; its dmaxK slot once softmax(i-2) has read it
-            if (i >= 1) ok = mbar_wait(sm_addr(mbar + PF_S_FULL + ((i - 1) & 1)), ((i - 1) >> 1) & 1, abort_s) && ok;
-            if (i >= 2) ok = mbar_wait(sm_addr(mbar + PF_S_FREE + (i & 1)), ((i >> 1) - 1) & 1, abort_s) && ok;
+            const int bb = i & 1;
+            const uint32_t par2 = (uint32_t)(((i >> 1) - 1) & 1);         // phase of tile i - 2 on a per-parity barrier
+            // this tile's raw bytes are in registers; start the next tile's loads before the arithmetic
+            RawItems<D, KBITS> nk;
+            RawItems<D, VBITS> nv;
+            if (i + 1 < n_tiles) {
+                const int64_t tok1 = (int64_t)(i + 1) * kPfTok;
+                const int ntok1 = (int)min((int64_t)kPfTok, p.S - tok1);
+                nk.load(k_row + tok1 * TBK, ntok1, dt);
+                nv.load(v_row + tok1 * TBV, ntok1, dt);
+            }
+            // K buffer bb: free once S(i-2) is complete; its dmaxK slot once the softmax of tile i-2 has read it
+            if (i >= 2) {
+                ok = mbar_wait(sm_addr(mbar + PF_S_FULL + bb), par2, abort_s) && ok;
+                ok = mbar_wait(sm_addr(mbar + PF_S_FREE + bb), par2, abort_s) && ok;
+            }
             if (!ok) break;
-            dequant_tile<D, KBITS>(k_row + tok0 * TBK, ntok, cbk_s, Kh, Kl, dmaxK + (i & 1) * kPfTok, dt);
+            rk.expand(cbk_s, Kh + bb * 2 * C::KB, Kh + bb * 2 * C::KB + C::KB, dmaxK + bb * kPfTok, dt);
             fence_async_smem();
-            mbar_arrive(sm_addr(mbar + PF_K_FULL));
-            // V tile: free once P(i-1) V(i-1) has completed
-            if (i >= 1) ok = mbar_wait(sm_addr(mbar + PF_PV_DONE), (i - 1) & 1, abort_s) && ok;
+            mbar_arrive(sm_addr(mbar + PF_K_FULL + bb));
+            // V buffer bb (and dmaxV[bb]): free once P(i-2) V(i-2) has completed
+            if (i >= 2) ok = mbar_wait(sm_addr(mbar + PF_PV_DONE + bb), par2, abort_s) && ok;
             if (!ok) break;
-            dequant_tile<D, VBITS>(v_row + tok0 * TBV, ntok, cbv_s, Vh, Vl, dmaxV, dt);
+            rv.expand(cbv_s, Vh + bb * 2 * C::KB, Vh + bb * 2 * C::KB + C::KB, dmaxV + bb * kPfTok, dt);
             fence_async_smem();
-            mbar_arrive(sm_addr(mbar + PF_V_FULL));
+            mbar_arrive(sm_addr(mbar + PF_V_FULL + bb));
+            rk = nk;
+            rv = nv;
         }
     } else {
         // =================================================== MMA issue (all lanes loop, lane 0 issues)
@@ -402,19 +476,20 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
         constexpr uint32_t idesc_pv = umma_idesc_f16(D) | (1u << 16);          // M 128, N D, B MN-major
         constexpr uint32_t d_hi = (1024u >> 4) | (1u << 14) | (2u << 29);      // 8-row groups 1024 B apart, SWIZZLE_128B
         const uint32_t q_h = ((sm_addr(Qh) >> 4) & 0x3FFFu) | (1u << 16), q_l = ((sm_addr(Ql) >> 4) & 0x3FFFu) | (1u << 16);
-        const uint32_t k_h = ((sm_addr(Kh) >> 4) & 0x3FFFu) | (1u << 16), k_l = ((sm_addr(Kl) >> 4) & 0x3FFFu) | (1u << 16);
+        const uint32_t k_h0 = ((sm_addr(Kh) >> 4) & 0x3FFFu) | (1u << 16);
         const uint32_t p_h = ((sm_addr(Ph) >> 4) & 0x3FFFu) | (1u << 16), p_l = ((sm_addr(Pl) >> 4) & 0x3FFFu) | (1u << 16);
         // V: 64-dim atoms kPfTok*128 B apart (leading offset), 8-token groups 1024 B apart
         constexpr uint32_t v_lbo = ((kPfTok * 128u) >> 4) << 16;
-        const uint32_t v_h = ((sm_addr(Vh) >> 4) & 0x3FFFu) | v_lbo, v_l = ((sm_addr(Vl) >> 4) & 0x3FFFu) | v_lbo;
+        const uint32_t v_h0 = ((sm_addr(Vh) >> 4) & 0x3FFFu) | v_lbo;
         auto issue_s = [&](int i) {
             const int sb = i & 1;
-            ok = mbar_wait(sm_addr(mbar + PF_K_FULL), i & 1, abort_s, 32) && ok;
+            ok = mbar_wait(sm_addr(mbar + PF_K_FULL + sb), (i >> 1) & 1, abort_s, 32) && ok;
             if (i >= 2) ok = mbar_wait(sm_addr(mbar + PF_S_FREE + sb), ((i >> 1) - 1) & 1, abort_s, 32) && ok;
             if (!ok) return;
             tc_fence_after();
             if (lane == 0) {
                 const uint32_t acc = tmem_base + sb * kPfTok;
+                const uint32_t k_h = k_h0 + (uint32_t)(sb * 2 * (C::KB >> 4)), k_l = k_h + (C::KB >> 4);
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t qo = (uint32_t)(((ks >> 2) * (kPfRows * 128) + (ks & 3) * 32) >> 4);
@@ -429,13 +504,15 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
         };
         if (n_tiles > 0) issue_s(0);
         for (int i = 0; i < n_tiles && ok; ++i) {
+            const int sb = i & 1;
             if (i + 1 < n_tiles) issue_s(i + 1);
             ok = mbar_wait(sm_addr(mbar + PF_P_FULL), i & 1, abort_s, 32) && ok;
-            ok = mbar_wait(sm_addr(mbar + PF_V_FULL), i & 1, abort_s, 32) && ok;
+            ok = mbar_wait(sm_addr(mbar + PF_V_FULL + sb), (i >> 1) & 1, abort_s, 32) && ok;
             if (!ok) break;
             tc_fence_after();
             if (lane == 0) {
                 const uint32_t acc = tmem_base + 2 * kPfTok;
+                const uint32_t v_h = v_h0 + (uint32_t)(sb * 2 * (C::KB >> 4)), v_l = v_h + (C::KB >> 4);
 #pragma unroll
                 for (int kt = 0; kt < kPfTok / 16; ++kt) {
                     const uint32_t po = (uint32_t)((kt * 32) >> 4), vo = (uint32_t)((kt * 16 * 128) >> 4);
@@ -443,7 +520,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
                     umma_f16_split(acc, p_h + po, d_hi, v_l + vo, d_hi, idesc_pv, 1u);
                     umma_f16_split(acc, p_l + po, d_hi, v_h + vo, d_hi, idesc_pv, 1u);
                 }
-                umma_commit(sm_addr(mbar + PF_PV_DONE));
+                umma_commit(sm_addr(mbar + PF_PV_DONE + sb));
             }
             __syncwarp();
         }
@@ -461,7 +538,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
     // stacked along N in the K/V buffers.
     {
         uint8_t* Bq = Kh;
-        if (warp < kPfSoftWarps) {
+        if (warp < kPfRowWarps) {
             const uint32_t tlane = tmem_base + ((uint32_t)(warp * 32) << 16);
 #pragma unroll 1
             for (int c = 0; c < D / 32; ++c) {
@@ -532,7 +609,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
             }
             __syncwarp();
         }
-        if (warp < kPfSoftWarps) {
+        if (warp < kPfRowWarps) {
             const bool oko = mbar_wait(sm_addr(mbar + PF_AUX), 1u, abort_s);
             tc_fence_after();
             const uint32_t tlane = tmem_base + ((uint32_t)(warp * 32) << 16);
