@@ -87,10 +87,11 @@ int pq_compress(const void* x, int64_t n_vec, int head_dim, int n_bits,
                 void* stream);
 
 /* pq_poll_device_errors — HOST-synchronising check for device-side failures of earlier launches on
- * the current device.  The compress kernel waits for its tensor-core work through a barrier with
- * an iteration limit (so that a lost completion can never hang the GPU); if a wait ever gives up,
- * bit 0 of *flags_out is set and the output of that launch must be discarded.  The flags are
- * cleared by the call.  No counterpart in the reference (its kernels report nothing). */
+ * the current device.  The tensor-core kernels wait for copies and MMAs through barriers with a time
+ * limit (so that a lost completion can never hang the GPU); if a wait ever gives up a bit of
+ * *flags_out is set and the output of that launch must be discarded: bit 0 compress (a wait gave
+ * up), bit 1 compress (shared-memory window unusable), bit 2 prefill attention (a wait gave up).
+ * The flags are cleared by the call.  No counterpart in the reference (its kernels report nothing). */
 int pq_poll_device_errors(unsigned int* flags_out);
 
 /* ---------------------------------------------------------------------------------
@@ -118,8 +119,8 @@ int pq_dequant(const void* blocks, int64_t n_vec, int head_dim, int n_bits,
  * (csrc/flash_turboquant.cu:27-105), rotate_query/inverse_rotate kernels
  * (csrc/polarquant_full.cu:25-40, 125-140) and polarquant_fused_attention_cuda_c.
  * Non-causal, as the reference.  The query is rotated once inside the kernel, only
- * packed blocks are read, the sequence is cut into `n_splits` ranges whose (m, l, o)
- * partials are merged by the last CTA to finish, and the result is rotated back.
+ * packed blocks are read, the work is cut into segments whose (m, l, o) partials are
+ * merged by the last CTA to finish a row, and the result is rotated back.
  *
  *   q          float16 [batch, q_heads, head_dim]
  *   k_blocks   uint8 [batch*kv_heads, seq_capacity, head_dim/32, block_bytes(k_bits)]
@@ -128,8 +129,8 @@ int pq_dequant(const void* blocks, int64_t n_vec, int head_dim, int n_bits,
  *   codebook_k/codebook_v  HOST float32 [2^bits]
  *   rot        float32 [head_dim, head_dim] row-major R
  *   scale      softmax scale (1/sqrt(head_dim) in the reference)
- *   jl_qproj   NULL, or float16 split of the JL matrix for the QJL score correction:
- *              float32 [jl_dim, head_dim] row-major P (scores += corr * scale,
+ *   jl_matrix  NULL, or the JL matrix for the QJL score correction: float32
+ *              [jl_dim, head_dim] row-major P (scores += corr * scale,
  *              attention.py:150-155); then qjl_bits [rows, seq_capacity, jl_dim/8] and
  *              qjl_norms float16 [rows, seq_capacity] are required
  *   out        [batch, q_heads, head_dim] float32 (out_is_fp16 == 0) or float16
@@ -137,7 +138,9 @@ int pq_dequant(const void* blocks, int64_t n_vec, int head_dim, int n_bits,
  *              skips the final normalisation and inverse rotation and writes
  *              (m, l, o_rotated[head_dim]) per query head instead of `out`
  *              (m in log2 units) — the per-GPU partial of a sequence-sharded decode
- *   n_splits   >= 1 sequence ranges per (batch, kv head); 0 lets the library choose
+ *   n_splits   0 (recommended): all 16-token tiles of all rows form one sequence that is
+ *              cut into one equal contiguous range per SM; >= 1: that many equal
+ *              sequence ranges per (batch, kv head, head group), dealt to the SMs
  *   scratch    device buffer of at least pq_decode_attn_scratch_bytes(...) bytes,
  *              256-byte aligned, ZERO-FILLED ONCE before its first use; the kernel
  *              leaves its counters at zero again, so it can be reused by later calls
@@ -208,15 +211,17 @@ int pq_lse_merge(const float* partials, int n_parts, int64_t n_rows, int head_di
 
 /* ---------------------------------------------------------------------------------
  * pq_prefill_attn — seq_q >= 1 query tokens per head against the compressed cache:
- * K/V tiles are dequantised into shared memory and contracted on tensor cores.
+ * K/V tiles are dequantised into shared memory and contracted on the tensor cores
+ * (tcgen05.mma, accumulators in tensor memory).  Its bounded waits report through bit 2
+ * of pq_poll_device_errors.
  *
  * Replaces attention.compressed_attention for seq_q > 1 and compressed_attention_gpu's
  * dequantise-everything path (src/polarquant_kv_cuda/attention_kernel.py:70-113).
  *
- *   q          float16 [batch, q_heads, seq_q, head_dim]
+ *   q          float16 [batch, q_heads, seq_q, head_dim], 16-byte aligned
  *   causal     0: every query sees all seq_len tokens (the reference's behaviour);
  *              1: query i sees tokens [0, seq_len - seq_q + i]
- *   out        [batch, q_heads, seq_q, head_dim] float32 or float16
+ *   out        [batch, q_heads, seq_q, head_dim] float32 (16-byte aligned) or float16
  */
 int pq_prefill_attn(const void* q, const void* k_blocks, const void* v_blocks,
                     int batch, int q_heads, int kv_heads, int seq_q, int64_t seq_len,

@@ -81,27 +81,44 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
     asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 }
 
+// Two 32-column loads of this thread's TMEM lane with one wait.
+__device__ __forceinline__ void tmem_ld32x2(float (&a)[32], float (&b)[32], uint32_t taddr_a, uint32_t taddr_b) {
+    uint32_t ra[32], rb[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%64];\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%65];\n\t"
+        "tcgen05.wait::ld.sync.aligned;\n"
+        : "=r"(ra[0]), "=r"(ra[1]), "=r"(ra[2]), "=r"(ra[3]), "=r"(ra[4]), "=r"(ra[5]), "=r"(ra[6]), "=r"(ra[7]), "=r"(ra[8]), "=r"(ra[9]), "=r"(ra[10]), "=r"(ra[11]), "=r"(ra[12]), "=r"(ra[13]), "=r"(ra[14]), "=r"(ra[15]), "=r"(ra[16]), "=r"(ra[17]), "=r"(ra[18]), "=r"(ra[19]), "=r"(ra[20]), "=r"(ra[21]), "=r"(ra[22]), "=r"(ra[23]), "=r"(ra[24]), "=r"(ra[25]), "=r"(ra[26]), "=r"(ra[27]), "=r"(ra[28]), "=r"(ra[29]), "=r"(ra[30]), "=r"(ra[31]), "=r"(rb[0]), "=r"(rb[1]), "=r"(rb[2]), "=r"(rb[3]), "=r"(rb[4]), "=r"(rb[5]), "=r"(rb[6]), "=r"(rb[7]), "=r"(rb[8]), "=r"(rb[9]), "=r"(rb[10]), "=r"(rb[11]), "=r"(rb[12]), "=r"(rb[13]), "=r"(rb[14]), "=r"(rb[15]), "=r"(rb[16]), "=r"(rb[17]), "=r"(rb[18]), "=r"(rb[19]), "=r"(rb[20]), "=r"(rb[21]), "=r"(rb[22]), "=r"(rb[23]), "=r"(rb[24]), "=r"(rb[25]), "=r"(rb[26]), "=r"(rb[27]), "=r"(rb[28]), "=r"(rb[29]), "=r"(rb[30]), "=r"(rb[31])
+        : "r"(taddr_a), "r"(taddr_b)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) { a[i] = __uint_as_float(ra[i]); b[i] = __uint_as_float(rb[i]); }
+}
+
 // One thread's share of a 64-token tile of one operand: work item = 8 consecutive elements of one
-// (token, block).  load() fetches the raw bytes (indices and the token's block radii) into registers,
-// expand() writes the hi / lo tiles (1024 * (d / dmax) * centroid) and the per-token largest radius.
-// Splitting the two lets the next tile's loads fly while this tile is expanded.
+// (token, block).  A thread's items k = 0..N-1 share block and position and sit 256 / (4 * NBLK) tokens
+// apart, so every address is one per-thread base plus compile-time offsets.  load() fetches the raw
+// bytes (indices and the token's block radii) into registers, expand() writes the hi / lo tiles
+// (1024 * (d / dmax) * centroid) and the per-token largest radius.  Splitting the two lets the next
+// tile's loads fly while this tile is expanded.
 template <int D, int BITS>
 struct RawItems {
     static constexpr int NBLK = D / 32, BB = block_bytes(BITS), TB = NBLK * BB;
     static constexpr int N = kPfTok * NBLK * 4 / kPfDeqThreads;           // items per thread
+    static constexpr int TSTEP = kPfDeqThreads / (NBLK * 4);              // tokens between a thread's items
     uint32_t bits[N];
     uint32_t rad[N][NBLK / 2];                                            // the token's radii, two per word
 
-    __device__ __forceinline__ void load(const uint8_t* __restrict__ src, int ntok, int dt) {
+    // src = first byte of the tile; tok0 / blk / qw = this thread's first item
+    __device__ __forceinline__ void load(const uint8_t* __restrict__ src, int ntok, int tok0, int blk, int qw) {
+        const uint8_t* tb0 = src + tok0 * TB;
 #pragma unroll
         for (int k = 0; k < N; ++k) {
-            const int w = dt + k * kPfDeqThreads;
-            const int tok = w / (NBLK * 4), rem = w % (NBLK * 4), blk = rem >> 2, qw = rem & 3;
             bits[k] = 0u;
 #pragma unroll
             for (int j = 0; j < NBLK / 2; ++j) rad[k][j] = 0u;
-            if (tok < ntok) {
-                const uint8_t* tb = src + (size_t)tok * TB;
+            if (tok0 + k * TSTEP < ntok) {
+                const uint8_t* tb = tb0 + k * TSTEP * TB;
 #pragma unroll
                 for (int j = 0; j < NBLK / 2; ++j)
                     rad[k][j] = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(tb + (2 * j) * BB)) |
@@ -116,11 +133,12 @@ struct RawItems {
         }
     }
 
-    __device__ __forceinline__ void expand(const float* cb, uint8_t* hi, uint8_t* lo, float* dmax_out, int dt) const {
+    // off0 = sw128 offset of the thread's first item; later items are whole 8-token groups further
+    __device__ __forceinline__ void expand(const float* cb, uint8_t* hi, uint8_t* lo, float* dmax_out, int tok0,
+                                           int blk, bool first, uint32_t off0) const {
+        static_assert(TSTEP % 8 == 0, "items of a thread must keep their row inside the 8-row swizzle group");
 #pragma unroll
         for (int k = 0; k < N; ++k) {
-            const int w = dt + k * kPfDeqThreads;
-            const int tok = w / (NBLK * 4), rem = w % (NBLK * 4), blk = rem >> 2, qw = rem & 3;
             float dmax = 0.f, d = 0.f;
 #pragma unroll
             for (int j = 0; j < NBLK; ++j) {
@@ -128,7 +146,7 @@ struct RawItems {
                 dmax = fmaxf(dmax, dj);
                 if (j == blk) d = dj;
             }
-            const float r = dmax > 0.f ? d / dmax : 0.f;                  // rows past the end: radii 0 -> zeros
+            const float r = dmax > 0.f ? __fdividef(d, dmax) : 0.f;        // rows past the end: radii 0 -> zeros
             uint32_t h[4], l[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -139,10 +157,10 @@ struct RawItems {
                 h[e] = *reinterpret_cast<const uint32_t*>(&hh);
                 l[e] = pack_half2(v0 - hf.x, v1 - hf.y);
             }
-            const uint32_t off = sw128_off(kPfTok, tok, blk * 32 + qw * 8);
+            const uint32_t off = off0 + (uint32_t)(k * (TSTEP / 8) * 1024);
             *reinterpret_cast<uint4*>(hi + off) = make_uint4(h[0], h[1], h[2], h[3]);
             *reinterpret_cast<uint4*>(lo + off) = make_uint4(l[0], l[1], l[2], l[3]);
-            if (rem == 0) dmax_out[tok] = dmax;
+            if (first) dmax_out[tok0 + k * TSTEP] = dmax;
         }
     }
 };
@@ -328,8 +346,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
             // (S complete implies the tile's K expansion, and with it dmaxK[sb], is complete)
             ok = mbar_wait(sm_addr(mbar + PF_S_FULL + sb), (i >> 1) & 1, abort_s) && ok;
             tc_fence_after();
-            float s[HT];
-            tmem_ld32(s, tlane + sb * kPfTok + hf * HT);
+            float s[HT], so[HT];                                         // own half, partner's half (for the maximum)
+            tmem_ld32x2(s, so, tlane + sb * kPfTok + hf * HT, tlane + sb * kPfTok + (hf ^ 1) * HT);
             const float4* dk4 = reinterpret_cast<const float4*>(dmaxK + sb * kPfTok + hf * HT);
             const int tok0 = i * kPfTok + hf * HT;
             float mx = -INFINITY;
@@ -350,8 +368,6 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
             for (int t = 0; t < HT; ++t) mx = fmaxf(mx, s[t]);
             {
                 // the row maximum needs the partner thread's half of the tile as well: read it too
-                float so[HT];
-                tmem_ld32(so, tlane + sb * kPfTok + (hf ^ 1) * HT);
                 const float4* do4 = reinterpret_cast<const float4*>(dmaxK + sb * kPfTok + (hf ^ 1) * HT);
                 const int toko = i * kPfTok + (hf ^ 1) * HT;
 #pragma unroll
@@ -434,11 +450,15 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
     } else if (warp < kPfSoftWarps + kPfDeqWarps) {
         // =================================================== dequantisation, one tile ahead of the MMAs
         const int dt = tid - kPfSoftWarps * 32;
+        // this thread's first work item: token, block, 8-element position; the same for every tile
+        const int it_tok = dt / (NBLK * 4), it_blk = (dt % (NBLK * 4)) >> 2, it_qw = dt & 3;
+        const bool it_first = (dt % (NBLK * 4)) == 0;
+        const uint32_t it_off = sw128_off(kPfTok, it_tok, it_blk * 32 + it_qw * 8);
         RawItems<D, KBITS> rk;
         RawItems<D, VBITS> rv;
         if (n_tiles > 0) {
-            rk.load(k_row, (int)min((int64_t)kPfTok, p.S), dt);
-            rv.load(v_row, (int)min((int64_t)kPfTok, p.S), dt);
+            rk.load(k_row, (int)min((int64_t)kPfTok, p.S), it_tok, it_blk, it_qw);
+            rv.load(v_row, (int)min((int64_t)kPfTok, p.S), it_tok, it_blk, it_qw);
         }
         for (int i = 0; i < n_tiles && ok; ++i) {
             const int bb = i & 1;
@@ -449,8 +469,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
             if (i + 1 < n_tiles) {
                 const int64_t tok1 = (int64_t)(i + 1) * kPfTok;
                 const int ntok1 = (int)min((int64_t)kPfTok, p.S - tok1);
-                nk.load(k_row + tok1 * TBK, ntok1, dt);
-                nv.load(v_row + tok1 * TBV, ntok1, dt);
+                nk.load(k_row + tok1 * TBK, ntok1, it_tok, it_blk, it_qw);
+                nv.load(v_row + tok1 * TBV, ntok1, it_tok, it_blk, it_qw);
             }
             // K buffer bb: free once S(i-2) is complete; its dmaxK slot once the softmax of tile i-2 has read it
             if (i >= 2) {
@@ -458,13 +478,15 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
                 ok = mbar_wait(sm_addr(mbar + PF_S_FREE + bb), par2, abort_s) && ok;
             }
             if (!ok) break;
-            rk.expand(cbk_s, Kh + bb * 2 * C::KB, Kh + bb * 2 * C::KB + C::KB, dmaxK + bb * kPfTok, dt);
+            rk.expand(cbk_s, Kh + bb * 2 * C::KB, Kh + bb * 2 * C::KB + C::KB, dmaxK + bb * kPfTok, it_tok, it_blk,
+                      it_first, it_off);
             fence_async_smem();
             mbar_arrive(sm_addr(mbar + PF_K_FULL + bb));
             // V buffer bb (and dmaxV[bb]): free once P(i-2) V(i-2) has completed
             if (i >= 2) ok = mbar_wait(sm_addr(mbar + PF_PV_DONE + bb), par2, abort_s) && ok;
             if (!ok) break;
-            rv.expand(cbv_s, Vh + bb * 2 * C::KB, Vh + bb * 2 * C::KB + C::KB, dmaxV + bb * kPfTok, dt);
+            rv.expand(cbv_s, Vh + bb * 2 * C::KB, Vh + bb * 2 * C::KB + C::KB, dmaxV + bb * kPfTok, it_tok, it_blk,
+                      it_first, it_off);
             fence_async_smem();
             mbar_arrive(sm_addr(mbar + PF_V_FULL + bb));
             rk = nk;
@@ -472,6 +494,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
         }
     } else {
         // =================================================== MMA issue (all lanes loop, lane 0 issues)
+        const uint32_t issue = lane == 0 ? 1u : 0u;
         constexpr uint32_t idesc_s = umma_idesc_f16(kPfTok);                   // M 128, N 64, A and B K-major
         constexpr uint32_t idesc_pv = umma_idesc_f16(D) | (1u << 16);          // M 128, N D, B MN-major
         constexpr uint32_t d_hi = (1024u >> 4) | (1u << 14) | (2u << 29);      // 8-row groups 1024 B apart, SWIZZLE_128B
@@ -487,18 +510,18 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
             if (i >= 2) ok = mbar_wait(sm_addr(mbar + PF_S_FREE + sb), ((i >> 1) - 1) & 1, abort_s, 32) && ok;
             if (!ok) return;
             tc_fence_after();
-            if (lane == 0) {
+            {
                 const uint32_t acc = tmem_base + sb * kPfTok;
                 const uint32_t k_h = k_h0 + (uint32_t)(sb * 2 * (C::KB >> 4)), k_l = k_h + (C::KB >> 4);
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t qo = (uint32_t)(((ks >> 2) * (kPfRows * 128) + (ks & 3) * 32) >> 4);
                     const uint32_t ko = (uint32_t)(((ks >> 2) * (kPfTok * 128) + (ks & 3) * 32) >> 4);
-                    umma_f16_split(acc, q_h + qo, d_hi, k_h + ko, d_hi, idesc_s, ks ? 1u : 0u);
-                    umma_f16_split(acc, q_h + qo, d_hi, k_l + ko, d_hi, idesc_s, 1u);
-                    umma_f16_split(acc, q_l + qo, d_hi, k_h + ko, d_hi, idesc_s, 1u);
+                    umma_f16_split_pred(acc, q_h + qo, d_hi, k_h + ko, d_hi, idesc_s, ks ? 1u : 0u, issue);
+                    umma_f16_split_pred(acc, q_h + qo, d_hi, k_l + ko, d_hi, idesc_s, 1u, issue);
+                    umma_f16_split_pred(acc, q_l + qo, d_hi, k_h + ko, d_hi, idesc_s, 1u, issue);
                 }
-                umma_commit(sm_addr(mbar + PF_S_FULL + sb));
+                umma_commit_pred(sm_addr(mbar + PF_S_FULL + sb), issue);
             }
             __syncwarp();
         };
@@ -510,17 +533,17 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
             ok = mbar_wait(sm_addr(mbar + PF_V_FULL + sb), (i >> 1) & 1, abort_s, 32) && ok;
             if (!ok) break;
             tc_fence_after();
-            if (lane == 0) {
+            {
                 const uint32_t acc = tmem_base + 2 * kPfTok;
                 const uint32_t v_h = v_h0 + (uint32_t)(sb * 2 * (C::KB >> 4)), v_l = v_h + (C::KB >> 4);
 #pragma unroll
                 for (int kt = 0; kt < kPfTok / 16; ++kt) {
                     const uint32_t po = (uint32_t)((kt * 32) >> 4), vo = (uint32_t)((kt * 16 * 128) >> 4);
-                    umma_f16_split(acc, p_h + po, d_hi, v_h + vo, d_hi, idesc_pv, (i > 0 || kt > 0) ? 1u : 0u);
-                    umma_f16_split(acc, p_h + po, d_hi, v_l + vo, d_hi, idesc_pv, 1u);
-                    umma_f16_split(acc, p_l + po, d_hi, v_h + vo, d_hi, idesc_pv, 1u);
+                    umma_f16_split_pred(acc, p_h + po, d_hi, v_h + vo, d_hi, idesc_pv, (i > 0 || kt > 0) ? 1u : 0u, issue);
+                    umma_f16_split_pred(acc, p_h + po, d_hi, v_l + vo, d_hi, idesc_pv, 1u, issue);
+                    umma_f16_split_pred(acc, p_l + po, d_hi, v_h + vo, d_hi, idesc_pv, 1u, issue);
                 }
-                umma_commit(sm_addr(mbar + PF_PV_DONE + sb));
+                umma_commit_pred(sm_addr(mbar + PF_PV_DONE + sb), issue);
             }
             __syncwarp();
         }

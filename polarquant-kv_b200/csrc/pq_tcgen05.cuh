@@ -80,6 +80,32 @@ __device__ __forceinline__ void umma_f16_split(uint32_t tmem_d, uint32_t a_lo, u
         "}\n" ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Warp-uniform form: every lane executes the call with identical operands, only lanes with
+// `issue` != 0 (exactly one) issue the MMA.  Keeping the control flow uniform lets the
+// descriptor arithmetic stay in uniform registers.
+__device__ __forceinline__ void umma_f16_split_pred(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                    uint32_t b_hi, uint32_t idesc, uint32_t accumulate,
+                                                    uint32_t issue) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, pi;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "setp.ne.b32 pi, %7, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+        "}\n" ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(issue)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_pred(uint32_t mbar_addr, uint32_t issue) {
+    asm volatile(
+        "{\n\t.reg .pred pi;\n\t"
+        "setp.ne.b32 pi, %1, 0;\n\t"
+        "@pi tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}\n" ::"r"(mbar_addr),
+        "r"(issue)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t mbar_addr) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(mbar_addr)
                  : "memory");
