@@ -222,12 +222,23 @@ int pq_lse_merge(const float* partials, int n_parts, int64_t n_rows, int head_di
  *   causal     0: every query sees all seq_len tokens (the reference's behaviour);
  *              1: query i sees tokens [0, seq_len - seq_q + i]
  *   out        [batch, q_heads, seq_q, head_dim] float32 (16-byte aligned) or float16
+ *   workspace  NULL, or a 16-byte aligned device buffer of at least
+ *              pq_prefill_attn_workspace_bytes(...) bytes (1 KB per token and KV head at
+ *              head_dim 128).  With a workspace every K/V tile is expanded once by a first
+ *              kernel and the attention kernel streams the expanded tiles (faster when
+ *              several 128-row query tiles share a KV head: seq_q * q_heads/kv_heads > 128);
+ *              without it the attention kernel dequantises the tiles itself.  Contents need
+ *              no initialisation and mean nothing after the call.
  */
 int pq_prefill_attn(const void* q, const void* k_blocks, const void* v_blocks,
                     int batch, int q_heads, int kv_heads, int seq_q, int64_t seq_len,
                     int64_t seq_capacity, int head_dim, int k_bits, int v_bits,
                     const float* codebook_k, const float* codebook_v, const float* rot,
-                    float scale, int causal, void* out, int out_is_fp16, void* stream);
+                    float scale, int causal, void* out, int out_is_fp16,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* Bytes of workspace pq_prefill_attn can use for this shape (0 for an empty shape). */
+size_t pq_prefill_attn_workspace_bytes(int batch, int kv_heads, int64_t seq_len, int head_dim);
 
 #ifdef __cplusplus
 }

@@ -49,6 +49,7 @@ struct PrefillParams {
     int causal, out_is_fp16;
     float scale_log2;
     float cbk[16], cbv[16];
+    const uint8_t* ws;     // expanded tiles (see PrefillCfg::kRec) or null
 };
 
 // Barriers that two roles wait on come in pairs, one per tile parity: a barrier's next phase can then
@@ -81,6 +82,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
     asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 }
 
+// 16-bit read-only global load that the compiler may not move: the dequant warps issue the next
+// tile's loads before they start on the current tile, and the loads must stay there.
+__device__ __forceinline__ uint32_t ldg_u16_pinned(const void* p) {
+    uint16_t v;
+    asm volatile("ld.global.nc.u16 %0, [%1];\n" : "=h"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // Two 32-column loads of this thread's TMEM lane with one wait.
 __device__ __forceinline__ void tmem_ld32x2(float (&a)[32], float (&b)[32], uint32_t taddr_a, uint32_t taddr_b) {
     uint32_t ra[32], rb[32];
@@ -109,28 +118,43 @@ struct RawItems {
     uint32_t bits[N];
     uint32_t rad[N][NBLK / 2];                                            // the token's radii, two per word
 
+    // Raw 16-bit loads of the next tile.  issue() only starts them (no result is touched, so all of
+    // them are in flight together); pack() combines them once they have landed.
+    struct Pending {
+        uint32_t r[N][NBLK];
+        uint32_t b[N][BITS == 4 ? 2 : 1];
+    };
     // src = first byte of the tile; tok0 / blk / qw = this thread's first item
-    __device__ __forceinline__ void load(const uint8_t* __restrict__ src, int ntok, int tok0, int blk, int qw) {
+    __device__ __forceinline__ static void issue(Pending& pd, const uint8_t* __restrict__ src, int ntok, int tok0,
+                                                 int blk, int qw) {
         const uint8_t* tb0 = src + tok0 * TB;
 #pragma unroll
         for (int k = 0; k < N; ++k) {
-            bits[k] = 0u;
+            // rows past the end re-read the tile's first token (always valid) and are zeroed in pack()
+            const uint8_t* tb = (tok0 + k * TSTEP < ntok) ? tb0 + k * TSTEP * TB : src;
 #pragma unroll
-            for (int j = 0; j < NBLK / 2; ++j) rad[k][j] = 0u;
-            if (tok0 + k * TSTEP < ntok) {
-                const uint8_t* tb = tb0 + k * TSTEP * TB;
-#pragma unroll
-                for (int j = 0; j < NBLK / 2; ++j)
-                    rad[k][j] = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(tb + (2 * j) * BB)) |
-                                ((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(tb + (2 * j + 1) * BB)) << 16);
-                if (BITS == 4) {
-                    const uint16_t* p16 = reinterpret_cast<const uint16_t*>(tb + blk * BB + 2 + qw * 4);
-                    bits[k] = (uint32_t)__ldg(p16) | ((uint32_t)__ldg(p16 + 1) << 16);
-                } else {
-                    bits[k] = __ldg(reinterpret_cast<const uint16_t*>(tb + blk * BB + 2 + qw * 2));
-                }
+            for (int j = 0; j < NBLK; ++j) pd.r[k][j] = ldg_u16_pinned(tb + j * BB);
+            if (BITS == 4) {
+                pd.b[k][0] = ldg_u16_pinned(tb + blk * BB + 2 + qw * 4);
+                pd.b[k][1] = ldg_u16_pinned(tb + blk * BB + 4 + qw * 4);
+            } else {
+                pd.b[k][0] = ldg_u16_pinned(tb + blk * BB + 2 + qw * 2);
             }
         }
+    }
+    __device__ __forceinline__ void pack(const Pending& pd, int ntok, int tok0) {
+#pragma unroll
+        for (int k = 0; k < N; ++k) {
+            const bool valid = tok0 + k * TSTEP < ntok;
+#pragma unroll
+            for (int j = 0; j < NBLK / 2; ++j) rad[k][j] = valid ? (pd.r[k][2 * j] | (pd.r[k][2 * j + 1] << 16)) : 0u;
+            bits[k] = BITS == 4 ? (pd.b[k][0] | (pd.b[k][BITS == 4 ? 1 : 0] << 16)) : pd.b[k][0];
+        }
+    }
+    __device__ __forceinline__ void load(const uint8_t* __restrict__ src, int ntok, int tok0, int blk, int qw) {
+        Pending pd;
+        issue(pd, src, ntok, tok0, blk, qw);
+        pack(pd, ntok, tok0);
     }
 
     // off0 = sw128 offset of the thread's first item; later items are whole 8-token groups further
@@ -173,10 +197,41 @@ struct PrefillCfg {
     static constexpr uint32_t kTiles = 2 * QB + 8 * KB + 2 * PB;       // K and V tiles are double-buffered
     static constexpr uint32_t kSmall = 4 * kPfTok * 4 + 32 * 4 + PF_NBAR * 8 + 24;
     static constexpr size_t smem_bytes() { return (size_t)kTiles + kSmall + 1024; }
+    // Workspace record of one (kv row, 64-token tile): K hi | K lo | V hi | V lo tiles exactly as they
+    // sit in shared memory, then the per-token largest radii of K and of V (64 floats each).
+    static constexpr uint32_t kRec = 4 * KB + 2 * kPfTok * 4;
     static constexpr uint32_t kTmemCols = 256;                 // S0 | S1 | O (64 + 64 + D <= 256)
 };
 
+// Expands one 64-token tile of K and of V per CTA into the workspace (grid: tiles x kv rows).
 template <int D, int KBITS, int VBITS>
+__global__ void __launch_bounds__(kPfDeqThreads) pq_prefill_expand_kernel(const PrefillParams p, uint8_t* ws,
+                                                                             int n_tiles) {
+    using C = PrefillCfg<D>;
+    constexpr int NBLK = D / 32;
+    constexpr int TBK = NBLK * block_bytes(KBITS), TBV = NBLK * block_bytes(VBITS);
+    __shared__ float cbk_s[16], cbv_s[16];
+    const int dt = threadIdx.x, tile = blockIdx.x, kvrow = blockIdx.y;
+    if (dt < 16) { cbk_s[dt] = p.cbk[dt] * kPfValScale; cbv_s[dt] = p.cbv[dt] * kPfValScale; }
+    __syncthreads();
+    const int it_tok = dt / (NBLK * 4), it_blk = (dt % (NBLK * 4)) >> 2, it_qw = dt & 3;
+    const bool it_first = (dt % (NBLK * 4)) == 0;
+    const uint32_t it_off = sw128_off(kPfTok, it_tok, it_blk * 32 + it_qw * 8);
+    const int64_t tok0 = (int64_t)tile * kPfTok;
+    const int ntok = (int)min((int64_t)kPfTok, p.S - tok0);
+    uint8_t* rec = ws + ((size_t)kvrow * n_tiles + tile) * C::kRec;
+    float* dmax = reinterpret_cast<float*>(rec + 4 * C::KB);
+    RawItems<D, KBITS> rk;
+    RawItems<D, VBITS> rv;
+    rk.load(p.kb + ((size_t)kvrow * p.Scap + tok0) * TBK, ntok, it_tok, it_blk, it_qw);
+    rv.load(p.vb + ((size_t)kvrow * p.Scap + tok0) * TBV, ntok, it_tok, it_blk, it_qw);
+    rk.expand(cbk_s, rec, rec + C::KB, dmax, it_tok, it_blk, it_first, it_off);
+    rv.expand(cbv_s, rec + 2 * C::KB, rec + 3 * C::KB, dmax + kPfTok, it_tok, it_blk, it_first, it_off);
+}
+
+// PRE: the tiles come expanded from the workspace (bulk copies by one warp) instead of being
+// dequantised by eight warps of this CTA.
+template <int D, int KBITS, int VBITS, bool PRE>
 __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const PrefillParams p) {
     using C = PrefillCfg<D>;
     constexpr int NBLK = D / 32;
@@ -208,8 +263,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
     if (tid < 16) { cbk_s[tid] = p.cbk[tid] * kPfValScale; cbv_s[tid] = p.cbv[tid] * kPfValScale; }
     if (tid == 0) {
         for (int k = 0; k < 2; ++k) {
-            mbar_init(sm_addr(mbar + PF_K_FULL + k), kPfDeqThreads);
-            mbar_init(sm_addr(mbar + PF_V_FULL + k), kPfDeqThreads);
+            mbar_init(sm_addr(mbar + PF_K_FULL + k), PRE ? 1 : kPfDeqThreads);
+            mbar_init(sm_addr(mbar + PF_V_FULL + k), PRE ? 1 : kPfDeqThreads);
             mbar_init(sm_addr(mbar + PF_S_FULL + k), 1);
             mbar_init(sm_addr(mbar + PF_S_FREE + k), kPfSoftWarps * 32);
             mbar_init(sm_addr(mbar + PF_PV_DONE + k), 1);
@@ -343,8 +398,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
         constexpr int HT = kPfTok / 2;                                    // tokens per thread and tile
         for (int i = 0; i < n_tiles && ok; ++i) {
             const int sb = i & 1;
-            // (S complete implies the tile's K expansion, and with it dmaxK[sb], is complete)
             ok = mbar_wait(sm_addr(mbar + PF_S_FULL + sb), (i >> 1) & 1, abort_s) && ok;
+            ok = mbar_wait(sm_addr(mbar + PF_K_FULL + sb), (i >> 1) & 1, abort_s) && ok;   // dmaxK[sb] is visible
             tc_fence_after();
             float s[HT], so[HT];                                         // own half, partner's half (for the maximum)
             tmem_ld32x2(s, so, tlane + sb * kPfTok + hf * HT, tlane + sb * kPfTok + (hf ^ 1) * HT);
@@ -447,6 +502,37 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
         asm volatile("bar.sync %0, 64;\n" ::"r"(1 + q) : "memory");
         l_run += xchg[(hf ^ 1) * kPfRows + r];
         inv_l = l_run > 0.f ? (1.0f / kPfValScale) / l_run : 0.f;
+    } else if (PRE && warp < kPfSoftWarps + kPfDeqWarps) {
+        // =================================================== copy warp: expanded tiles from the workspace
+        if (warp == kPfSoftWarps) {
+            const uint8_t* rec0 = p.ws + (size_t)kvrow * ((p.S + kPfTok - 1) / kPfTok) * C::kRec;
+            for (int i = 0; i < n_tiles && ok; ++i) {
+                const int bb = i & 1;
+                const uint32_t par2 = (uint32_t)(((i >> 1) - 1) & 1);
+                const uint8_t* rec = rec0 + (size_t)i * C::kRec;
+                if (i >= 2) {
+                    ok = mbar_wait(sm_addr(mbar + PF_S_FULL + bb), par2, abort_s, 64) && ok;
+                    ok = mbar_wait(sm_addr(mbar + PF_S_FREE + bb), par2, abort_s, 64) && ok;
+                }
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t bar = sm_addr(mbar + PF_K_FULL + bb);
+                    mbar_expect_tx(bar, 2 * C::KB + kPfTok * 4);
+                    bulk_load(sm_addr(Kh + bb * 2 * C::KB), rec, 2 * C::KB, bar);
+                    bulk_load(sm_addr(dmaxK + bb * kPfTok), rec + 4 * C::KB, kPfTok * 4, bar);
+                }
+                __syncwarp();
+                if (i >= 2) ok = mbar_wait(sm_addr(mbar + PF_PV_DONE + bb), par2, abort_s, 64) && ok;
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t bar = sm_addr(mbar + PF_V_FULL + bb);
+                    mbar_expect_tx(bar, 2 * C::KB + kPfTok * 4);
+                    bulk_load(sm_addr(Vh + bb * 2 * C::KB), rec + 2 * C::KB, 2 * C::KB, bar);
+                    bulk_load(sm_addr(dmaxV + bb * kPfTok), rec + 4 * C::KB + kPfTok * 4, kPfTok * 4, bar);
+                }
+                __syncwarp();
+            }
+        }
     } else if (warp < kPfSoftWarps + kPfDeqWarps) {
         // =================================================== dequantisation, one tile ahead of the MMAs
         const int dt = tid - kPfSoftWarps * 32;
@@ -466,12 +552,13 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
             // this tile's raw bytes are in registers; start the next tile's loads before the arithmetic
             RawItems<D, KBITS> nk;
             RawItems<D, VBITS> nv;
-            if (i + 1 < n_tiles) {
-                const int64_t tok1 = (int64_t)(i + 1) * kPfTok;
-                const int ntok1 = (int)min((int64_t)kPfTok, p.S - tok1);
-                nk.load(k_row + tok1 * TBK, ntok1, it_tok, it_blk, it_qw);
-                nv.load(v_row + tok1 * TBV, ntok1, it_tok, it_blk, it_qw);
-            }
+            typename RawItems<D, KBITS>::Pending pk;
+            typename RawItems<D, VBITS>::Pending pv;
+            const bool more = i + 1 < n_tiles;
+            const int64_t tok1 = more ? (int64_t)(i + 1) * kPfTok : 0;            // (the last tile re-reads tile 0)
+            const int ntok1 = (int)min((int64_t)kPfTok, p.S - tok1);
+            RawItems<D, KBITS>::issue(pk, k_row + tok1 * TBK, ntok1, it_tok, it_blk, it_qw);
+            RawItems<D, VBITS>::issue(pv, v_row + tok1 * TBV, ntok1, it_tok, it_blk, it_qw);
             // K buffer bb: free once S(i-2) is complete; its dmaxK slot once the softmax of tile i-2 has read it
             if (i >= 2) {
                 ok = mbar_wait(sm_addr(mbar + PF_S_FULL + bb), par2, abort_s) && ok;
@@ -482,6 +569,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
                       it_first, it_off);
             fence_async_smem();
             mbar_arrive(sm_addr(mbar + PF_K_FULL + bb));
+            nk.pack(pk, ntok1, it_tok);           // the loads issued at the top have landed by now
+            nv.pack(pv, ntok1, it_tok);
             // V buffer bb (and dmaxV[bb]): free once P(i-2) V(i-2) has completed
             if (i >= 2) ok = mbar_wait(sm_addr(mbar + PF_PV_DONE + bb), par2, abort_s) && ok;
             if (!ok) break;
@@ -673,14 +762,25 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
 }
 
 template <int D, int KBITS, int VBITS>
-static int launch_prefill(const PrefillParams& p, int rows, cudaStream_t st) {
+static int launch_prefill(const PrefillParams& p, int rows, uint8_t* ws, cudaStream_t st) {
     const size_t smem = PrefillCfg<D>::smem_bytes();
-    auto kern = pq_prefill_attn_kernel<D, KBITS, VBITS>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return PQ_ERR_CUDA;
     const int n_rows = p.G * p.Sq;
     dim3 grid((n_rows + kPfRows - 1) / kPfRows, rows, 1);
-    kern<<<grid, kPfThreads, smem, st>>>(p);
+    if (ws) {
+        // expand every tile once, then run the attention kernel on the expanded tiles
+        const int n_tiles = (int)((p.S + kPfTok - 1) / kPfTok);
+        pq_prefill_expand_kernel<D, KBITS, VBITS><<<dim3(n_tiles, rows, 1), kPfDeqThreads, 0, st>>>(p, ws, n_tiles);
+        if (cudaGetLastError() != cudaSuccess) return PQ_ERR_CUDA;
+        auto kern = pq_prefill_attn_kernel<D, 4, 4, true>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return PQ_ERR_CUDA;
+        kern<<<grid, kPfThreads, smem, st>>>(p);
+    } else {
+        auto kern = pq_prefill_attn_kernel<D, KBITS, VBITS, false>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return PQ_ERR_CUDA;
+        kern<<<grid, kPfThreads, smem, st>>>(p);
+    }
     return cudaGetLastError() == cudaSuccess ? PQ_OK : PQ_ERR_CUDA;
 }
 
@@ -695,11 +795,18 @@ int prefill_error_flags(unsigned int* flags) {
 
 }  // namespace pq
 
+extern "C" size_t pq_prefill_attn_workspace_bytes(int batch, int kv_heads, int64_t seq_len, int head_dim) {
+    if (batch <= 0 || kv_heads <= 0 || seq_len <= 0 || (head_dim != 64 && head_dim != 128)) return 0;
+    const size_t rec = head_dim == 64 ? pq::PrefillCfg<64>::kRec : pq::PrefillCfg<128>::kRec;
+    return (size_t)batch * kv_heads * (size_t)((seq_len + pq::kPfTok - 1) / pq::kPfTok) * rec;
+}
+
 extern "C" int pq_prefill_attn(const void* q, const void* k_blocks, const void* v_blocks,
                                int batch, int q_heads, int kv_heads, int seq_q, int64_t seq_len,
                                int64_t seq_capacity, int head_dim, int k_bits, int v_bits,
                                const float* codebook_k, const float* codebook_v, const float* rot,
-                               float scale, int causal, void* out, int out_is_fp16, void* stream) {
+                               float scale, int causal, void* out, int out_is_fp16, void* workspace,
+                               size_t workspace_bytes, void* stream) {
     using namespace pq;
     if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads || seq_q < 0 || seq_len < 0 ||
         seq_capacity < seq_len)
@@ -720,6 +827,11 @@ extern "C" int pq_prefill_attn(const void* q, const void* k_blocks, const void* 
         return PQ_ERR_MISALIGNED;
     const int rows = batch * kv_heads;
     if (rows > 65535) return PQ_ERR_TOO_LARGE;
+    if (workspace) {
+        if (reinterpret_cast<uintptr_t>(workspace) & 15) return PQ_ERR_MISALIGNED;
+        if (workspace_bytes < pq_prefill_attn_workspace_bytes(batch, kv_heads, seq_len, head_dim))
+            return PQ_ERR_SCRATCH_TOO_SMALL;
+    }
     PrefillParams p{};
     p.q = static_cast<const __half*>(q);
     p.kb = static_cast<const uint8_t*>(k_blocks);
@@ -735,12 +847,14 @@ extern "C" int pq_prefill_attn(const void* q, const void* k_blocks, const void* 
     p.causal = causal;
     p.out_is_fp16 = out_is_fp16;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.ws = static_cast<const uint8_t*>(workspace);
     for (int i = 0; i < 16; ++i) {
         p.cbk[i] = i < (1 << k_bits) ? codebook_k[i] : 0.f;
         p.cbv[i] = i < (1 << v_bits) ? codebook_v[i] : 0.f;
     }
 #define PQ_PF(DD, KB, VB) \
-    if (head_dim == DD && k_bits == KB && v_bits == VB) return launch_prefill<DD, KB, VB>(p, rows, st);
+    if (head_dim == DD && k_bits == KB && v_bits == VB) \
+        return launch_prefill<DD, KB, VB>(p, rows, static_cast<uint8_t*>(workspace), st);
     PQ_PF(64, 4, 4) PQ_PF(64, 4, 2) PQ_PF(64, 2, 4) PQ_PF(64, 2, 2)
     PQ_PF(128, 4, 4) PQ_PF(128, 4, 2) PQ_PF(128, 2, 4) PQ_PF(128, 2, 2)
 #undef PQ_PF

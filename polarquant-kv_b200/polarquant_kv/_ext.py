@@ -39,7 +39,8 @@ SIGNATURES = {
     "pq_lse_merge": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "pq_prefill_attn": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64,
                                 c_int, c_int, c_int, c_float_p, c_float_p, c_void_p, c_float, c_int,
-                                c_void_p, c_int, c_void_p]),
+                                c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
+    "pq_prefill_attn_workspace_bytes": (c_size_t, [c_int, c_int, c_int64, c_int]),
 }
 
 _lib = None

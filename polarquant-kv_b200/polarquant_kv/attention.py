@@ -143,11 +143,28 @@ def prepare_decode(query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, plan
     return PreparedDecode(query, ck, cv, plan, **kw)
 
 
+_PREFILL_WS: dict = {}
+PREFILL_WORKSPACE_LIMIT = 1 << 30      # bytes; larger shapes use the fused (dequantise-in-kernel) path
+
+
+def _prefill_workspace(dev: torch.device, need: int) -> torch.Tensor:
+    """Per-(device, stream) buffer for the expanded K/V tiles, grown on demand."""
+    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    buf = _PREFILL_WS.get(key)
+    if buf is None or buf.numel() < need:
+        buf = torch.empty(need, dtype=torch.uint8, device=dev)
+        _PREFILL_WS[key] = buf
+    return buf
+
+
 def prefill_attention(query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, plan,
                       scale: float | None = None, causal: bool = False,
-                      out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+                      out_dtype: torch.dtype = torch.float32, use_workspace: bool | None = None) -> torch.Tensor:
     """query [B, Hq, Sq, D] float16 -> [B, Hq, Sq, D]; K/V tiles are dequantised into shared
-    memory and contracted on tensor cores (pq_prefill_attn)."""
+    memory and contracted on tensor cores (pq_prefill_attn).  `use_workspace`: True expands every
+    K/V tile once into a device workspace first (1 KB per token and KV head at D = 128), False
+    dequantises inside the attention kernel; None picks the workspace when more than one 128-row
+    query tile shares a KV head and the workspace stays below PREFILL_WORKSPACE_LIMIT."""
     _require_cuda(query, "query")
     B, Hq, Sq, D = query.shape
     Hkv = ck.blocks.shape[1]
@@ -161,11 +178,17 @@ def prefill_attention(query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, p
     q = query.to(torch.float16).contiguous()
     cbk, _, _ = tables(ck.n_bits)
     cbv, _, _ = tables(cv.n_bits)
-    st = _ext.lib().pq_prefill_attn(
+    lib = _ext.lib()
+    need = lib.pq_prefill_attn_workspace_bytes(B, Hkv, ck.seq_len, D)
+    if use_workspace is None:
+        use_workspace = Sq * (Hq // Hkv) > 128 and 0 < need <= PREFILL_WORKSPACE_LIMIT
+    ws = _prefill_workspace(dev, need) if (use_workspace and need > 0) else None
+    st = lib.pq_prefill_attn(
         q.data_ptr(), kb.data_ptr(), vb.data_ptr(), B, Hq, Hkv, Sq, ck.seq_len, ck.max_seq_len, D,
         ck.n_bits, cv.n_bits, cbk, cbv, plan.rot.data_ptr(),
         ctypes.c_float(scale if scale is not None else 1.0 / math.sqrt(D)), 1 if causal else 0,
-        out.data_ptr(), 1 if out_dtype == torch.float16 else 0, _stream(dev))
+        out.data_ptr(), 1 if out_dtype == torch.float16 else 0,
+        ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, _stream(dev))
     _ext.check(st, "pq_prefill_attn")
     return out
 
