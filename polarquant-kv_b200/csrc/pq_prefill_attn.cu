@@ -32,9 +32,15 @@ static __device__ unsigned int g_prefill_error = 0;
 constexpr int kPfRows = 128;                 // query rows per CTA = TMEM lanes
 constexpr int kPfTok = 64;                   // tokens per KV tile
 constexpr int kPfRowWarps = 4;               // warps that cover the 128 TMEM lanes once (rotation epilogues)
-constexpr int kPfSoftWarps = 8, kPfDeqWarps = 8;   // softmax: two threads per query row (32 tokens of a tile each)
+constexpr int kPfDeqWarps = 8;
 constexpr int kPfDeqThreads = kPfDeqWarps * 32;
-constexpr int kPfThreads = (kPfSoftWarps + kPfDeqWarps + 1) * 32;
+// Warp roles.  Fused kernel: 8 softmax warps (two threads per query row), 8 dequant warps, 1 MMA warp.
+// Workspace kernel: 8 softmax warps, 1 copy warp, 1 MMA warp.  (Four threads per row measured slower:
+// every thread of a row scans all 64 scores for the row maximum.)
+__host__ __device__ constexpr int pf_split(bool) { return 2; }                           // softmax threads per row
+__host__ __device__ constexpr int pf_soft_warps(bool pre) { return 4 * pf_split(pre); }
+__host__ __device__ constexpr int pf_mma_warp(bool pre) { return pre ? pf_soft_warps(pre) + 1 : pf_soft_warps(pre) + kPfDeqWarps; }
+__host__ __device__ constexpr int pf_threads(bool pre) { return (pf_mma_warp(pre) + 1) * 32; }
 constexpr float kPfValScale = 1024.0f;       // tiles hold 1024 * (d / dmax) * centroid
 constexpr float kPfRescaleGap = 8.0f;        // log2 units a row maximum may grow before O is rescaled
 
@@ -88,6 +94,18 @@ __device__ __forceinline__ uint32_t ldg_u16_pinned(const void* p) {
     uint16_t v;
     asm volatile("ld.global.nc.u16 %0, [%1];\n" : "=h"(v) : "l"(p) : "memory");
     return v;
+}
+
+// 16 consecutive float32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld16(float (&v)[16], uint32_t taddr) {
+    uint32_t r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n\t"
+                 "tcgen05.wait::ld.sync.aligned;\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr)
+                 : "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
 // Two 32-column loads of this thread's TMEM lane with one wait.
@@ -232,7 +250,9 @@ __global__ void __launch_bounds__(kPfDeqThreads) pq_prefill_expand_kernel(const 
 // PRE: the tiles come expanded from the workspace (bulk copies by one warp) instead of being
 // dequantised by eight warps of this CTA.
 template <int D, int KBITS, int VBITS, bool PRE>
-__global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const PrefillParams p) {
+__global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(const PrefillParams p) {
+    constexpr int kPfSoftWarps = pf_soft_warps(PRE), NSPLIT = pf_split(PRE), kMmaWarp = pf_mma_warp(PRE);
+    const int kPfThreads = blockDim.x;
     using C = PrefillCfg<D>;
     constexpr int NBLK = D / 32;
     constexpr int TBK = NBLK * block_bytes(KBITS), TBV = NBLK * block_bytes(VBITS);
@@ -316,7 +336,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
         __syncthreads();
         tc_fence_after();
         const uint32_t tmem_base0 = *tmem_slot;
-        if (warp == kPfSoftWarps + kPfDeqWarps) {
+        if (warp == kMmaWarp) {
             if (lane == 0) {
                 constexpr uint32_t idesc = umma_idesc_f16(2 * D);
                 constexpr uint32_t d_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
@@ -385,8 +405,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
     float inv_l = 0.f;                                                    // row owners: 1 / (1024 * row sum)
 
     if (warp < kPfSoftWarps) {
-        // =================================================== softmax: two threads per query row
-        const int q = warp & 3, hf = warp >> 2;                           // TMEM lane quarter, token half of the tile
+        // =================================================== softmax: NSPLIT threads per query row
+        const int q = warp & 3, hf = warp >> 2;                           // TMEM lane quarter, token part of the tile
         const int r = q * 32 + lane;
         const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16);
         const int row = row0 + r;
@@ -395,47 +415,59 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
         if (row >= n_rows || limit < 0) limit = 0;
         float m_run = -INFINITY, m_used = -INFINITY, l_run = 0.f;
         const uint32_t prow = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
-        constexpr int HT = kPfTok / 2;                                    // tokens per thread and tile
+        constexpr int HT = kPfTok / NSPLIT;                               // tokens per thread and tile
         for (int i = 0; i < n_tiles && ok; ++i) {
             const int sb = i & 1;
             ok = mbar_wait(sm_addr(mbar + PF_S_FULL + sb), (i >> 1) & 1, abort_s) && ok;
             ok = mbar_wait(sm_addr(mbar + PF_K_FULL + sb), (i >> 1) & 1, abort_s) && ok;   // dmaxK[sb] is visible
             tc_fence_after();
-            float s[HT], so[HT];                                         // own half, partner's half (for the maximum)
-            tmem_ld32x2(s, so, tlane + sb * kPfTok + hf * HT, tlane + sb * kPfTok + (hf ^ 1) * HT);
-            const float4* dk4 = reinterpret_cast<const float4*>(dmaxK + sb * kPfTok + hf * HT);
-            const int tok0 = i * kPfTok + hf * HT;
+            // the row maximum needs all 64 scores of the row (every thread of the row computes the same
+            // value from the same numbers), the probabilities only this thread's HT tokens
             float mx = -INFINITY;
 #pragma unroll
-            for (int t4 = 0; t4 < HT / 4; ++t4) {
-                const float4 d4 = dk4[t4];
-                s[4 * t4 + 0] *= d4.x * (1.0f / kPfValScale);
-                s[4 * t4 + 1] *= d4.y * (1.0f / kPfValScale);
-                s[4 * t4 + 2] *= d4.z * (1.0f / kPfValScale);
-                s[4 * t4 + 3] *= d4.w * (1.0f / kPfValScale);
-            }
-            if (tok0 + HT > limit) {                                      // only tiles that reach past the row's limit
+            for (int half = 0; half < 2; ++half) {
+                float sa[32];
+                tmem_ld32(sa, tlane + sb * kPfTok + half * 32);
+                const float4* d4p = reinterpret_cast<const float4*>(dmaxK + sb * kPfTok + half * 32);
+                const int tk = i * kPfTok + half * 32;
+                if (tk + 32 <= limit) {
 #pragma unroll
-                for (int t = 0; t < HT; ++t)
-                    if (tok0 + t >= limit) s[t] = -INFINITY;
-            }
+                    for (int t4 = 0; t4 < 8; ++t4) {
+                        const float4 d4 = d4p[t4];
+                        mx = fmaxf(mx, fmaxf(fmaxf(sa[4 * t4 + 0] * (d4.x * (1.0f / kPfValScale)),
+                                                   sa[4 * t4 + 1] * (d4.y * (1.0f / kPfValScale))),
+                                             fmaxf(sa[4 * t4 + 2] * (d4.z * (1.0f / kPfValScale)),
+                                                   sa[4 * t4 + 3] * (d4.w * (1.0f / kPfValScale)))));
+                    }
+                } else {
 #pragma unroll
-            for (int t = 0; t < HT; ++t) mx = fmaxf(mx, s[t]);
+                    for (int t4 = 0; t4 < 8; ++t4) {
+                        const float4 d4 = d4p[t4];
+                        const float dd[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (tk + 4 * t4 + e < limit) mx = fmaxf(mx, sa[4 * t4 + e] * (dd[e] * (1.0f / kPfValScale)));
+                    }
+                }
+            }
+            float s[HT];
+            if (HT == 32) tmem_ld32(*reinterpret_cast<float(*)[32]>(&s[0]), tlane + sb * kPfTok + hf * HT);
+            else tmem_ld16(*reinterpret_cast<float(*)[16]>(&s[0]), tlane + sb * kPfTok + hf * HT);
             {
-                // the row maximum needs the partner thread's half of the tile as well: read it too
-                const float4* do4 = reinterpret_cast<const float4*>(dmaxK + sb * kPfTok + (hf ^ 1) * HT);
-                const int toko = i * kPfTok + (hf ^ 1) * HT;
+                const float4* dk4 = reinterpret_cast<const float4*>(dmaxK + sb * kPfTok + hf * HT);
+                const int tok0 = i * kPfTok + hf * HT;
 #pragma unroll
                 for (int t4 = 0; t4 < HT / 4; ++t4) {
-                    const float4 d4 = do4[t4];
-                    const float x0 = so[4 * t4 + 0] * (d4.x * (1.0f / kPfValScale));
-                    const float x1 = so[4 * t4 + 1] * (d4.y * (1.0f / kPfValScale));
-                    const float x2 = so[4 * t4 + 2] * (d4.z * (1.0f / kPfValScale));
-                    const float x3 = so[4 * t4 + 3] * (d4.w * (1.0f / kPfValScale));
-                    if (toko + 4 * t4 + 0 < limit) mx = fmaxf(mx, x0);
-                    if (toko + 4 * t4 + 1 < limit) mx = fmaxf(mx, x1);
-                    if (toko + 4 * t4 + 2 < limit) mx = fmaxf(mx, x2);
-                    if (toko + 4 * t4 + 3 < limit) mx = fmaxf(mx, x3);
+                    const float4 d4 = dk4[t4];
+                    s[4 * t4 + 0] *= d4.x * (1.0f / kPfValScale);
+                    s[4 * t4 + 1] *= d4.y * (1.0f / kPfValScale);
+                    s[4 * t4 + 2] *= d4.z * (1.0f / kPfValScale);
+                    s[4 * t4 + 3] *= d4.w * (1.0f / kPfValScale);
+                }
+                if (tok0 + HT > limit) {                                  // only tiles that reach past the row's limit
+#pragma unroll
+                    for (int t = 0; t < HT; ++t)
+                        if (tok0 + t >= limit) s[t] = -INFINITY;
                 }
             }
             tc_fence_before();
@@ -450,10 +482,11 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
             if (__any_sync(0xffffffffu, grow)) {                        // same outcome in both warps of a row group
                 if (i > 0) {
                     const float alpha = (m_run == -INFINITY) ? 1.f : fast_exp2(m_used - m_run);   // exp2(-inf) = 0
+                    // the row's O columns in 32-column chunks, dealt round-robin to the row's threads
 #pragma unroll 1
-                    for (int c = 0; c < D / 64; ++c) {                  // this thread's half of the O columns
+                    for (int c = hf; c < D / 32; c += NSPLIT) {
                         float o[32];
-                        const uint32_t col = 2 * kPfTok + hf * (D / 2) + c * 32;
+                        const uint32_t col = 2 * kPfTok + c * 32;
                         tmem_ld32(o, tlane + col);
 #pragma unroll
                         for (int k = 0; k < 32; ++k) o[k] *= alpha;
@@ -496,13 +529,15 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
             ok = mbar_wait(sm_addr(mbar + PF_PV_DONE + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, abort_s) && ok;
             tc_fence_after();
         }
-        // row sum over both halves (both were kept relative to the same m_used), through the dead Ph tile
+        // row sum over the row's threads (all kept relative to the same m_used), through the dead Ph tile
         float* xchg = reinterpret_cast<float*>(Ph);
         xchg[hf * kPfRows + r] = l_run;
-        asm volatile("bar.sync %0, 64;\n" ::"r"(1 + q) : "memory");
-        l_run += xchg[(hf ^ 1) * kPfRows + r];
+        asm volatile("bar.sync %0, %1;\n" ::"r"(1 + q), "r"(32 * NSPLIT) : "memory");
+        l_run = 0.f;
+#pragma unroll
+        for (int k = 0; k < NSPLIT; ++k) l_run += xchg[k * kPfRows + r];
         inv_l = l_run > 0.f ? (1.0f / kPfValScale) / l_run : 0.f;
-    } else if (PRE && warp < kPfSoftWarps + kPfDeqWarps) {
+    } else if (PRE && warp < kMmaWarp) {
         // =================================================== copy warp: expanded tiles from the workspace
         if (warp == kPfSoftWarps) {
             const uint8_t* rec0 = p.ws + (size_t)kvrow * ((p.S + kPfTok - 1) / kPfTok) * C::kRec;
@@ -533,7 +568,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
                 __syncwarp();
             }
         }
-    } else if (warp < kPfSoftWarps + kPfDeqWarps) {
+    } else if (warp < kMmaWarp) {
         // =================================================== dequantisation, one tile ahead of the MMAs
         const int dt = tid - kPfSoftWarps * 32;
         // this thread's first work item: token, block, 8-element position; the same for every tile
@@ -699,7 +734,7 @@ __global__ void __launch_bounds__(kPfThreads, 1) pq_prefill_attn_kernel(const Pr
         tc_fence_before();
         __syncthreads();          // operands complete, every thread has read its part of O
         tc_fence_after();
-        if (warp == kPfSoftWarps + kPfDeqWarps) {
+        if (warp == kMmaWarp) {
             if (lane == 0) {
                 constexpr uint32_t idesc2 = umma_idesc_f16(2 * D), idesc1 = umma_idesc_f16(D);
                 constexpr uint32_t d_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
@@ -774,12 +809,12 @@ static int launch_prefill(const PrefillParams& p, int rows, uint8_t* ws, cudaStr
         auto kern = pq_prefill_attn_kernel<D, 4, 4, true>;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return PQ_ERR_CUDA;
-        kern<<<grid, kPfThreads, smem, st>>>(p);
+        kern<<<grid, pf_threads(true), smem, st>>>(p);
     } else {
         auto kern = pq_prefill_attn_kernel<D, KBITS, VBITS, false>;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return PQ_ERR_CUDA;
-        kern<<<grid, kPfThreads, smem, st>>>(p);
+        kern<<<grid, pf_threads(false), smem, st>>>(p);
     }
     return cudaGetLastError() == cudaSuccess ? PQ_OK : PQ_ERR_CUDA;
 }
