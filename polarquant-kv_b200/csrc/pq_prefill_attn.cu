@@ -96,6 +96,12 @@ __device__ __forceinline__ uint32_t ldg_u16_pinned(const void* p) {
     return v;
 }
 
+__device__ __forceinline__ float4 lds_f4(uint32_t saddr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(saddr));
+    return v;
+}
+
 // 16 consecutive float32 columns of this thread's TMEM lane.
 __device__ __forceinline__ void tmem_ld16(float (&v)[16], uint32_t taddr) {
     uint32_t r[16];
@@ -176,8 +182,9 @@ struct RawItems {
     }
 
     // off0 = sw128 offset of the thread's first item; later items are whole 8-token groups further
-    __device__ __forceinline__ void expand(const float* cb, uint8_t* hi, uint8_t* lo, float* dmax_out, int tok0,
-                                           int blk, bool first, uint32_t off0) const {
+    // dmax_scale: factor stored with the per-token radius (the K side folds the tile scale 1/1024 in)
+    __device__ __forceinline__ void expand(const float* cb, uint8_t* hi, uint8_t* lo, float* dmax_out, float dmax_scale,
+                                           int tok0, int blk, bool first, uint32_t off0) const {
         static_assert(TSTEP % 8 == 0, "items of a thread must keep their row inside the 8-row swizzle group");
 #pragma unroll
         for (int k = 0; k < N; ++k) {
@@ -202,7 +209,7 @@ struct RawItems {
             const uint32_t off = off0 + (uint32_t)(k * (TSTEP / 8) * 1024);
             *reinterpret_cast<uint4*>(hi + off) = make_uint4(h[0], h[1], h[2], h[3]);
             *reinterpret_cast<uint4*>(lo + off) = make_uint4(l[0], l[1], l[2], l[3]);
-            if (first) dmax_out[tok0 + k * TSTEP] = dmax;
+            if (first) dmax_out[tok0 + k * TSTEP] = dmax * dmax_scale;
         }
     }
 };
@@ -243,8 +250,8 @@ __global__ void __launch_bounds__(kPfDeqThreads) pq_prefill_expand_kernel(const 
     RawItems<D, VBITS> rv;
     rk.load(p.kb + ((size_t)kvrow * p.Scap + tok0) * TBK, ntok, it_tok, it_blk, it_qw);
     rv.load(p.vb + ((size_t)kvrow * p.Scap + tok0) * TBV, ntok, it_tok, it_blk, it_qw);
-    rk.expand(cbk_s, rec, rec + C::KB, dmax, it_tok, it_blk, it_first, it_off);
-    rv.expand(cbv_s, rec + 2 * C::KB, rec + 3 * C::KB, dmax + kPfTok, it_tok, it_blk, it_first, it_off);
+    rk.expand(cbk_s, rec, rec + C::KB, dmax, 1.0f / kPfValScale, it_tok, it_blk, it_first, it_off);
+    rv.expand(cbv_s, rec + 2 * C::KB, rec + 3 * C::KB, dmax + kPfTok, 1.0f, it_tok, it_blk, it_first, it_off);
 }
 
 // PRE: the tiles come expanded from the workspace (bulk copies by one warp) instead of being
@@ -416,6 +423,7 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
         float m_run = -INFINITY, m_used = -INFINITY, l_run = 0.f;
         const uint32_t prow = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
         constexpr int HT = kPfTok / NSPLIT;                               // tokens per thread and tile
+        const uint32_t dk_addr = sm_addr(dmaxK), dv_addr = sm_addr(dmaxV);
         for (int i = 0; i < n_tiles && ok; ++i) {
             const int sb = i & 1;
             ok = mbar_wait(sm_addr(mbar + PF_S_FULL + sb), (i >> 1) & 1, abort_s) && ok;
@@ -428,25 +436,23 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             for (int half = 0; half < 2; ++half) {
                 float sa[32];
                 tmem_ld32(sa, tlane + sb * kPfTok + half * 32);
-                const float4* d4p = reinterpret_cast<const float4*>(dmaxK + sb * kPfTok + half * 32);
+                const uint32_t d4p = dk_addr + (uint32_t)((sb * kPfTok + half * 32) * 4);     // dmaxK holds dmax / 1024
                 const int tk = i * kPfTok + half * 32;
                 if (tk + 32 <= limit) {
 #pragma unroll
                     for (int t4 = 0; t4 < 8; ++t4) {
-                        const float4 d4 = d4p[t4];
-                        mx = fmaxf(mx, fmaxf(fmaxf(sa[4 * t4 + 0] * (d4.x * (1.0f / kPfValScale)),
-                                                   sa[4 * t4 + 1] * (d4.y * (1.0f / kPfValScale))),
-                                             fmaxf(sa[4 * t4 + 2] * (d4.z * (1.0f / kPfValScale)),
-                                                   sa[4 * t4 + 3] * (d4.w * (1.0f / kPfValScale)))));
+                        const float4 d4 = lds_f4(d4p + t4 * 16);
+                        mx = fmaxf(mx, fmaxf(fmaxf(sa[4 * t4 + 0] * d4.x, sa[4 * t4 + 1] * d4.y),
+                                             fmaxf(sa[4 * t4 + 2] * d4.z, sa[4 * t4 + 3] * d4.w)));
                     }
                 } else {
 #pragma unroll
                     for (int t4 = 0; t4 < 8; ++t4) {
-                        const float4 d4 = d4p[t4];
+                        const float4 d4 = lds_f4(d4p + t4 * 16);
                         const float dd[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
                         for (int e = 0; e < 4; ++e)
-                            if (tk + 4 * t4 + e < limit) mx = fmaxf(mx, sa[4 * t4 + e] * (dd[e] * (1.0f / kPfValScale)));
+                            if (tk + 4 * t4 + e < limit) mx = fmaxf(mx, sa[4 * t4 + e] * dd[e]);
                     }
                 }
             }
@@ -454,15 +460,15 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             if (HT == 32) tmem_ld32(*reinterpret_cast<float(*)[32]>(&s[0]), tlane + sb * kPfTok + hf * HT);
             else tmem_ld16(*reinterpret_cast<float(*)[16]>(&s[0]), tlane + sb * kPfTok + hf * HT);
             {
-                const float4* dk4 = reinterpret_cast<const float4*>(dmaxK + sb * kPfTok + hf * HT);
+                const uint32_t dk4 = dk_addr + (uint32_t)((sb * kPfTok + hf * HT) * 4);
                 const int tok0 = i * kPfTok + hf * HT;
 #pragma unroll
                 for (int t4 = 0; t4 < HT / 4; ++t4) {
-                    const float4 d4 = dk4[t4];
-                    s[4 * t4 + 0] *= d4.x * (1.0f / kPfValScale);
-                    s[4 * t4 + 1] *= d4.y * (1.0f / kPfValScale);
-                    s[4 * t4 + 2] *= d4.z * (1.0f / kPfValScale);
-                    s[4 * t4 + 3] *= d4.w * (1.0f / kPfValScale);
+                    const float4 d4 = lds_f4(dk4 + t4 * 16);
+                    s[4 * t4 + 0] *= d4.x;
+                    s[4 * t4 + 1] *= d4.y;
+                    s[4 * t4 + 2] *= d4.z;
+                    s[4 * t4 + 3] *= d4.w;
                 }
                 if (tok0 + HT > limit) {                                  // only tiles that reach past the row's limit
 #pragma unroll
@@ -499,11 +505,11 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             }
             const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
             ok = mbar_wait(sm_addr(mbar + PF_V_FULL + sb), (i >> 1) & 1, abort_s) && ok;   // dmaxV[sb] is visible
-            const float4* dv4 = reinterpret_cast<const float4*>(dmaxV + sb * kPfTok + hf * HT);
+            const uint32_t dv4 = dv_addr + (uint32_t)((sb * kPfTok + hf * HT) * 4);
             float sum = 0.f;
 #pragma unroll
             for (int c = 0; c < HT / 8; ++c) {
-                const float4 da = dv4[2 * c], db = dv4[2 * c + 1];
+                const float4 da = lds_f4(dv4 + c * 32), db = lds_f4(dv4 + c * 32 + 16);
                 const float dv[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
                 uint32_t h[4], l[4];
 #pragma unroll
@@ -600,8 +606,8 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
                 ok = mbar_wait(sm_addr(mbar + PF_S_FREE + bb), par2, abort_s) && ok;
             }
             if (!ok) break;
-            rk.expand(cbk_s, Kh + bb * 2 * C::KB, Kh + bb * 2 * C::KB + C::KB, dmaxK + bb * kPfTok, it_tok, it_blk,
-                      it_first, it_off);
+            rk.expand(cbk_s, Kh + bb * 2 * C::KB, Kh + bb * 2 * C::KB + C::KB, dmaxK + bb * kPfTok, 1.0f / kPfValScale,
+                      it_tok, it_blk, it_first, it_off);
             fence_async_smem();
             mbar_arrive(sm_addr(mbar + PF_K_FULL + bb));
             nk.pack(pk, ntok1, it_tok);           // the loads issued at the top have landed by now
@@ -609,7 +615,7 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             // V buffer bb (and dmaxV[bb]): free once P(i-2) V(i-2) has completed
             if (i >= 2) ok = mbar_wait(sm_addr(mbar + PF_PV_DONE + bb), par2, abort_s) && ok;
             if (!ok) break;
-            rv.expand(cbv_s, Vh + bb * 2 * C::KB, Vh + bb * 2 * C::KB + C::KB, dmaxV + bb * kPfTok, it_tok, it_blk,
+            rv.expand(cbv_s, Vh + bb * 2 * C::KB, Vh + bb * 2 * C::KB + C::KB, dmaxV + bb * kPfTok, 1.0f, it_tok, it_blk,
                       it_first, it_off);
             fence_async_smem();
             mbar_arrive(sm_addr(mbar + PF_V_FULL + bb));
