@@ -230,6 +230,10 @@ def compressed_attention(query: torch.Tensor, compressed_keys, compressed_values
         out = decode_attention(q4[:, :, 0], ck, cv, plan, enable_qjl, out_dtype=out_dtype).unsqueeze(2)
     else:
         if enable_qjl and jl_matrix is not None and ck.qjl_signs is not None:
-            raise ValueError("the QJL score correction is implemented for decode (seq_q == 1) only")
-        out = prefill_attention(q4, ck, cv, plan, out_dtype=out_dtype)
+            # the sketch correction lives in the decode kernel: one decode per query position
+            # (non-causal, as the reference: every position sees the whole cache)
+            out = torch.stack([decode_attention(q4[:, :, i].contiguous(), ck, cv, plan, True, out_dtype=out_dtype)
+                               for i in range(Sq)], dim=2)
+        else:
+            out = prefill_attention(q4, ck, cv, plan, out_dtype=out_dtype)
     return out[0] if squeeze else out
