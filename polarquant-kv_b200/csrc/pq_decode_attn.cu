@@ -366,7 +366,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
         const __half* qrow = p.q + ((size_t)b * p.Hq + head0 + g) * D;   // row g = head g (if it exists)
         const bool have = g < Gp;
         float c[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
+#pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
             const float2 r0 = __ldg(reinterpret_cast<const float2*>(mrow + ks * 16 + 2 * t));
             const float2 r1 = __ldg(reinterpret_cast<const float2*>(mrow + ks * 16 + 8 + 2 * t));
@@ -772,7 +772,9 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
                 const int head = e / D, i = e % D;
                 if (head >= Gp) continue;
                 float acc = 0.f;
-#pragma unroll 8
+                // 32 independent loads in flight per thread: the column of R comes from L2, and with a short
+                // unroll the D dependent round trips dominate the merge
+#pragma unroll 32
                 for (int j = 0; j < D; ++j) acc = fmaf(o_fin[head * D + j], __ldg(p.rot + (size_t)j * D + i), acc);
                 const size_t off = ((size_t)b * p.Hq + head0 + head) * D + i;
                 if (p.out_is_fp16)
