@@ -35,9 +35,9 @@ constexpr int kPfRowWarps = 4;               // warps that cover the 128 TMEM la
 constexpr int kPfDeqWarps = 8;
 constexpr int kPfDeqThreads = kPfDeqWarps * 32;
 // Warp roles.  Fused kernel: 8 softmax warps (two threads per query row), 8 dequant warps, 1 MMA warp.
-// Workspace kernel: 8 softmax warps, 1 copy warp, 1 MMA warp.  (Four threads per row measured slower:
-// every thread of a row scans all 64 scores for the row maximum.)
-__host__ __device__ constexpr int pf_split(bool) { return 2; }                           // softmax threads per row
+// Workspace kernel: 16 softmax warps (four threads per row, row maxima exchanged through spare
+// TMEM columns), 1 copy warp, 1 MMA warp.
+__host__ __device__ constexpr int pf_split(bool pre) { return pre ? 4 : 2; }             // softmax threads per row
 __host__ __device__ constexpr int pf_soft_warps(bool pre) { return 4 * pf_split(pre); }
 __host__ __device__ constexpr int pf_mma_warp(bool pre) { return pre ? pf_soft_warps(pre) + 1 : pf_soft_warps(pre) + kPfDeqWarps; }
 __host__ __device__ constexpr int pf_threads(bool pre) { return (pf_mma_warp(pre) + 1) * 32; }
@@ -100,6 +100,22 @@ __device__ __forceinline__ float4 lds_f4(uint32_t saddr) {
     float4 v;
     asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(saddr));
     return v;
+}
+
+// One float32 into / four out of this thread's TMEM lane (row-maximum exchange between the warps of a row group).
+__device__ __forceinline__ void tmem_st1(uint32_t taddr, float v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};\n\t"
+                 "tcgen05.wait::st.sync.aligned;\n" ::"r"(taddr), "r"(__float_as_uint(v))
+                 : "memory");
+}
+__device__ __forceinline__ float4 tmem_ld4(uint32_t taddr) {
+    uint32_t a, b, c, d;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];\n\t"
+                 "tcgen05.wait::ld.sync.aligned;\n"
+                 : "=r"(a), "=r"(b), "=r"(c), "=r"(d)
+                 : "r"(taddr)
+                 : "memory");
+    return make_float4(__uint_as_float(a), __uint_as_float(b), __uint_as_float(c), __uint_as_float(d));
 }
 
 // 16 consecutive float32 columns of this thread's TMEM lane.
@@ -225,7 +241,8 @@ struct PrefillCfg {
     // Workspace record of one (kv row, 64-token tile): K hi | K lo | V hi | V lo tiles exactly as they
     // sit in shared memory, then the per-token largest radii of K and of V (64 floats each).
     static constexpr uint32_t kRec = 4 * KB + 2 * kPfTok * 4;
-    static constexpr uint32_t kTmemCols = 256;                 // S0 | S1 | O (64 + 64 + D <= 256)
+    static constexpr uint32_t kTmemCols = 512;                 // S0 | S1 | O (64 + 64 + D <= 256) | exchange columns
+    static constexpr uint32_t kXchgCol = 256;                  // 2 parities x 4 partial row maxima
 };
 
 // Expands one 64-token tile of K and of V per CTA into the workspace (grid: tiles x kv rows).
@@ -429,9 +446,10 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             ok = mbar_wait(sm_addr(mbar + PF_S_FULL + sb), (i >> 1) & 1, abort_s) && ok;
             ok = mbar_wait(sm_addr(mbar + PF_K_FULL + sb), (i >> 1) & 1, abort_s) && ok;   // dmaxK[sb] is visible
             tc_fence_after();
+            float mx = -INFINITY;
+            if (NSPLIT == 2) {
             // the row maximum needs all 64 scores of the row (every thread of the row computes the same
             // value from the same numbers), the probabilities only this thread's HT tokens
-            float mx = -INFINITY;
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 float sa[32];
@@ -456,6 +474,7 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
                     }
                 }
             }
+            }
             float s[HT];
             if (HT == 32) tmem_ld32(*reinterpret_cast<float(*)[32]>(&s[0]), tlane + sb * kPfTok + hf * HT);
             else tmem_ld16(*reinterpret_cast<float(*)[16]>(&s[0]), tlane + sb * kPfTok + hf * HT);
@@ -475,6 +494,19 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
                     for (int t = 0; t < HT; ++t)
                         if (tok0 + t >= limit) s[t] = -INFINITY;
                 }
+            }
+            if (NSPLIT == 4) {
+                // partial maximum of this thread's 16 tokens; the four threads of a row swap partials through
+                // four spare TMEM columns of the row's lane (one set per tile parity), with the row group's
+                // named barrier between the stores and the loads
+#pragma unroll
+                for (int t = 0; t < HT; ++t) mx = fmaxf(mx, s[t]);
+                tmem_st1(tlane + C::kXchgCol + sb * 4 + hf, mx);
+                tc_fence_before();
+                asm volatile("bar.sync %0, %1;\n" ::"r"(1 + q), "r"(32 * NSPLIT) : "memory");
+                tc_fence_after();
+                const float4 pm = tmem_ld4(tlane + C::kXchgCol + sb * 4);
+                mx = fmaxf(fmaxf(pm.x, pm.y), fmaxf(pm.z, pm.w));
             }
             tc_fence_before();
             mbar_arrive(sm_addr(mbar + PF_S_FREE + sb));                // S buffer and dmaxK[sb] consumed
