@@ -241,8 +241,12 @@ struct PrefillCfg {
     // Workspace record of one (kv row, 64-token tile): K hi | K lo | V hi | V lo tiles exactly as they
     // sit in shared memory, then the per-token largest radii of K and of V (64 floats each).
     static constexpr uint32_t kRec = 4 * KB + 2 * kPfTok * 4;
-    static constexpr uint32_t kTmemCols = 512;                 // S0 | S1 | O (64 + 64 + D <= 256) | exchange columns
-    static constexpr uint32_t kXchgCol = 256;                  // 2 parities x 4 partial row maxima
+    // TMEM columns: S0 | S1 (128 each: q_hi*k_hi + q_lo*k_hi in the first 64, q_hi*k_lo in the second 64) | O (D) |
+    // 2 parities x 4 partial row maxima.  The rotations before and after the loop use columns [0, 2D).
+    static constexpr uint32_t kTmemCols = 512;
+    static constexpr uint32_t kSCols = 2 * kPfTok;
+    static constexpr uint32_t kOCol = 2 * kSCols;
+    static constexpr uint32_t kXchgCol = kOCol + D;
 };
 
 // Expands one 64-token tile of K and of V per CTA into the workspace (grid: tiles x kv rows).
@@ -259,6 +263,7 @@ __global__ void __launch_bounds__(kPfDeqThreads) pq_prefill_expand_kernel(const 
     const int it_tok = dt / (NBLK * 4), it_blk = (dt % (NBLK * 4)) >> 2, it_qw = dt & 3;
     const bool it_first = (dt % (NBLK * 4)) == 0;
     const uint32_t it_off = sw128_off(kPfTok, it_tok, it_blk * 32 + it_qw * 8);
+    const uint32_t it_offk = sw128_off(2 * kPfTok, it_tok, it_blk * 32 + it_qw * 8);   // K: hi and lo rows stacked
     const int64_t tok0 = (int64_t)tile * kPfTok;
     const int ntok = (int)min((int64_t)kPfTok, p.S - tok0);
     uint8_t* rec = ws + ((size_t)kvrow * n_tiles + tile) * C::kRec;
@@ -267,7 +272,7 @@ __global__ void __launch_bounds__(kPfDeqThreads) pq_prefill_expand_kernel(const 
     RawItems<D, VBITS> rv;
     rk.load(p.kb + ((size_t)kvrow * p.Scap + tok0) * TBK, ntok, it_tok, it_blk, it_qw);
     rv.load(p.vb + ((size_t)kvrow * p.Scap + tok0) * TBV, ntok, it_tok, it_blk, it_qw);
-    rk.expand(cbk_s, rec, rec + C::KB, dmax, 1.0f / kPfValScale, it_tok, it_blk, it_first, it_off);
+    rk.expand(cbk_s, rec, rec + kPfTok * 128, dmax, 1.0f / kPfValScale, it_tok, it_blk, it_first, it_offk);
     rv.expand(cbv_s, rec + 2 * C::KB, rec + 3 * C::KB, dmax + kPfTok, 1.0f, it_tok, it_blk, it_first, it_off);
 }
 
@@ -452,8 +457,10 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             // value from the same numbers), the probabilities only this thread's HT tokens
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
-                float sa[32];
-                tmem_ld32(sa, tlane + sb * kPfTok + half * 32);
+                float sa[32], sl[32];
+                tmem_ld32x2(sa, sl, tlane + sb * C::kSCols + half * 32, tlane + sb * C::kSCols + kPfTok + half * 32);
+#pragma unroll
+                for (int t = 0; t < 32; ++t) sa[t] += sl[t];
                 const uint32_t d4p = dk_addr + (uint32_t)((sb * kPfTok + half * 32) * 4);     // dmaxK holds dmax / 1024
                 const int tk = i * kPfTok + half * 32;
                 if (tk + 32 <= limit) {
@@ -476,8 +483,18 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             }
             }
             float s[HT];
-            if (HT == 32) tmem_ld32(*reinterpret_cast<float(*)[32]>(&s[0]), tlane + sb * kPfTok + hf * HT);
-            else tmem_ld16(*reinterpret_cast<float(*)[16]>(&s[0]), tlane + sb * kPfTok + hf * HT);
+            {
+                float sl[HT];                                            // the q_hi * k_lo part of the same scores
+                if (HT == 32) {
+                    tmem_ld32x2(*reinterpret_cast<float(*)[32]>(&s[0]), *reinterpret_cast<float(*)[32]>(&sl[0]),
+                                tlane + sb * C::kSCols + hf * HT, tlane + sb * C::kSCols + kPfTok + hf * HT);
+                } else {
+                    tmem_ld16(*reinterpret_cast<float(*)[16]>(&s[0]), tlane + sb * C::kSCols + hf * HT);
+                    tmem_ld16(*reinterpret_cast<float(*)[16]>(&sl[0]), tlane + sb * C::kSCols + kPfTok + hf * HT);
+                }
+#pragma unroll
+                for (int t = 0; t < HT; ++t) s[t] += sl[t];
+            }
             {
                 const uint32_t dk4 = dk_addr + (uint32_t)((sb * kPfTok + hf * HT) * 4);
                 const int tok0 = i * kPfTok + hf * HT;
@@ -524,7 +541,7 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
 #pragma unroll 1
                     for (int c = hf; c < D / 32; c += NSPLIT) {
                         float o[32];
-                        const uint32_t col = 2 * kPfTok + c * 32;
+                        const uint32_t col = C::kOCol + c * 32;
                         tmem_ld32(o, tlane + col);
 #pragma unroll
                         for (int k = 0; k < 32; ++k) o[k] *= alpha;
@@ -613,6 +630,7 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
         const int it_tok = dt / (NBLK * 4), it_blk = (dt % (NBLK * 4)) >> 2, it_qw = dt & 3;
         const bool it_first = (dt % (NBLK * 4)) == 0;
         const uint32_t it_off = sw128_off(kPfTok, it_tok, it_blk * 32 + it_qw * 8);
+        const uint32_t it_offk = sw128_off(2 * kPfTok, it_tok, it_blk * 32 + it_qw * 8);
         RawItems<D, KBITS> rk;
         RawItems<D, VBITS> rv;
         if (n_tiles > 0) {
@@ -638,8 +656,8 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
                 ok = mbar_wait(sm_addr(mbar + PF_S_FREE + bb), par2, abort_s) && ok;
             }
             if (!ok) break;
-            rk.expand(cbk_s, Kh + bb * 2 * C::KB, Kh + bb * 2 * C::KB + C::KB, dmaxK + bb * kPfTok, 1.0f / kPfValScale,
-                      it_tok, it_blk, it_first, it_off);
+            rk.expand(cbk_s, Kh + bb * 2 * C::KB, Kh + bb * 2 * C::KB + kPfTok * 128, dmaxK + bb * kPfTok,
+                      1.0f / kPfValScale, it_tok, it_blk, it_first, it_offk);
             fence_async_smem();
             mbar_arrive(sm_addr(mbar + PF_K_FULL + bb));
             nk.pack(pk, ntok1, it_tok);           // the loads issued at the top have landed by now
@@ -658,6 +676,7 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
         // =================================================== MMA issue (all lanes loop, lane 0 issues)
         const uint32_t issue = lane == 0 ? 1u : 0u;
         constexpr uint32_t idesc_s = umma_idesc_f16(kPfTok);                   // M 128, N 64, A and B K-major
+        constexpr uint32_t idesc_s2 = umma_idesc_f16(2 * kPfTok);              // N 128: hi and lo rows of K at once
         constexpr uint32_t idesc_pv = umma_idesc_f16(D) | (1u << 16);          // M 128, N D, B MN-major
         constexpr uint32_t d_hi = (1024u >> 4) | (1u << 14) | (2u << 29);      // 8-row groups 1024 B apart, SWIZZLE_128B
         const uint32_t q_h = ((sm_addr(Qh) >> 4) & 0x3FFFu) | (1u << 16), q_l = ((sm_addr(Ql) >> 4) & 0x3FFFu) | (1u << 16);
@@ -673,15 +692,16 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             if (!ok) return;
             tc_fence_after();
             {
-                const uint32_t acc = tmem_base + sb * kPfTok;
-                const uint32_t k_h = k_h0 + (uint32_t)(sb * 2 * (C::KB >> 4)), k_l = k_h + (C::KB >> 4);
+                // K tile: per 64-dim half 128 rows (64 hi tokens, then 64 lo).  q_hi against all 128 rows
+                // (one MMA, N = 128: columns [0, 64) hi products, [64, 128) lo products), q_lo against the hi rows.
+                const uint32_t acc = tmem_base + sb * C::kSCols;
+                const uint32_t k_b = k_h0 + (uint32_t)(sb * 2 * (C::KB >> 4));
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t qo = (uint32_t)(((ks >> 2) * (kPfRows * 128) + (ks & 3) * 32) >> 4);
-                    const uint32_t ko = (uint32_t)(((ks >> 2) * (kPfTok * 128) + (ks & 3) * 32) >> 4);
-                    umma_f16_split_pred(acc, q_h + qo, d_hi, k_h + ko, d_hi, idesc_s, ks ? 1u : 0u, issue);
-                    umma_f16_split_pred(acc, q_h + qo, d_hi, k_l + ko, d_hi, idesc_s, 1u, issue);
-                    umma_f16_split_pred(acc, q_l + qo, d_hi, k_h + ko, d_hi, idesc_s, 1u, issue);
+                    const uint32_t ko = (uint32_t)(((ks >> 2) * (2 * kPfTok * 128) + (ks & 3) * 32) >> 4);
+                    umma_f16_split_pred(acc, q_h + qo, d_hi, k_b + ko, d_hi, idesc_s2, ks ? 1u : 0u, issue);
+                    umma_f16_split_pred(acc, q_l + qo, d_hi, k_b + ko, d_hi, idesc_s, 1u, issue);
                 }
                 umma_commit_pred(sm_addr(mbar + PF_S_FULL + sb), issue);
             }
@@ -696,7 +716,7 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             if (!ok) break;
             tc_fence_after();
             {
-                const uint32_t acc = tmem_base + 2 * kPfTok;
+                const uint32_t acc = tmem_base + C::kOCol;
                 const uint32_t v_h = v_h0 + (uint32_t)(sb * 2 * (C::KB >> 4)), v_l = v_h + (C::KB >> 4);
 #pragma unroll
                 for (int kt = 0; kt < kPfTok / 16; ++kt) {
@@ -729,7 +749,7 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             for (int c = 0; c < D / 32; ++c) {
                 float o[32];
                 if (n_tiles > 0) {
-                    tmem_ld32(o, tlane + 2 * kPfTok + c * 32);
+                    tmem_ld32(o, tlane + C::kOCol + c * 32);
                 } else {
 #pragma unroll
                     for (int k = 0; k < 32; ++k) o[k] = 0.f;
