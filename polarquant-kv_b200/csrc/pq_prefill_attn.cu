@@ -528,15 +528,38 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             tc_fence_before();
             mbar_arrive(sm_addr(mbar + PF_S_FREE + sb));                // S buffer and dmaxK[sb] consumed
             m_run = fmaxf(m_run, mx);
-            // the previous tile's P V must be complete before P is rewritten or O rescaled
+            // Probabilities first (registers only), relative to the maximum this tile will use: that work
+            // overlaps the previous tile's P V, which must be complete before P is rewritten or O rescaled.
+            const bool grow = m_run > m_used + kPfRescaleGap;           // also true on the first finite maximum
+            const bool rescale = __any_sync(0xffffffffu, grow);         // same outcome in every warp of a row group
+            const float m_old = m_used;
+            if (rescale) m_used = m_run;
+            const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+            ok = mbar_wait(sm_addr(mbar + PF_V_FULL + sb), (i >> 1) & 1, abort_s) && ok;   // dmaxV[sb] is visible
+            const uint32_t dv4 = dv_addr + (uint32_t)((sb * kPfTok + hf * HT) * 4);
+            float sum = 0.f;
+            uint32_t ph[HT / 2], pl[HT / 2];
+#pragma unroll
+            for (int c = 0; c < HT / 8; ++c) {
+                const float4 da = lds_f4(dv4 + c * 32), db = lds_f4(dv4 + c * 32 + 16);
+                const float dv[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int t = c * 8 + 2 * e;
+                    const float p0 = fast_exp2(s[t] - m_sub), p1 = fast_exp2(s[t + 1] - m_sub);
+                    sum += p0 + p1;
+                    const float w0 = p0 * dv[2 * e], w1 = p1 * dv[2 * e + 1];
+                    const __half2 hh = __floats2half2_rn(w0, w1);
+                    const float2 hfl = __half22float2(hh);
+                    ph[c * 4 + e] = *reinterpret_cast<const uint32_t*>(&hh);
+                    pl[c * 4 + e] = pack_half2(w0 - hfl.x, w1 - hfl.y);
+                }
+            }
             if (i > 0) {
                 ok = mbar_wait(sm_addr(mbar + PF_PV_DONE + ((i - 1) & 1)), ((i - 1) >> 1) & 1, abort_s) && ok;
                 tc_fence_after();
-            }
-            const bool grow = m_run > m_used + kPfRescaleGap;           // also true on the first finite maximum
-            if (__any_sync(0xffffffffu, grow)) {                        // same outcome in both warps of a row group
-                if (i > 0) {
-                    const float alpha = (m_run == -INFINITY) ? 1.f : fast_exp2(m_used - m_run);   // exp2(-inf) = 0
+                if (rescale) {
+                    const float alpha = (m_used == -INFINITY) ? 1.f : fast_exp2(m_old - m_used);   // exp2(-inf) = 0
                     // the row's O columns in 32-column chunks, dealt round-robin to the row's threads
 #pragma unroll 1
                     for (int c = hf; c < D / 32; c += NSPLIT) {
@@ -550,31 +573,12 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
                     l_run *= alpha;
                     tc_fence_before();
                 }
-                m_used = m_run;
             }
-            const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
-            ok = mbar_wait(sm_addr(mbar + PF_V_FULL + sb), (i >> 1) & 1, abort_s) && ok;   // dmaxV[sb] is visible
-            const uint32_t dv4 = dv_addr + (uint32_t)((sb * kPfTok + hf * HT) * 4);
-            float sum = 0.f;
 #pragma unroll
             for (int c = 0; c < HT / 8; ++c) {
-                const float4 da = lds_f4(dv4 + c * 32), db = lds_f4(dv4 + c * 32 + 16);
-                const float dv[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
-                uint32_t h[4], l[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int t = c * 8 + 2 * e;
-                    const float p0 = fast_exp2(s[t] - m_sub), p1 = fast_exp2(s[t + 1] - m_sub);
-                    sum += p0 + p1;
-                    const float w0 = p0 * dv[2 * e], w1 = p1 * dv[2 * e + 1];
-                    const __half2 hh = __floats2half2_rn(w0, w1);
-                    const float2 hfl = __half22float2(hh);
-                    h[e] = *reinterpret_cast<const uint32_t*>(&hh);
-                    l[e] = pack_half2(w0 - hfl.x, w1 - hfl.y);
-                }
                 const uint32_t off = prow + (uint32_t)(((hf * (HT / 8) + c) ^ (r & 7)) << 4);
-                *reinterpret_cast<uint4*>(Ph + off) = make_uint4(h[0], h[1], h[2], h[3]);
-                *reinterpret_cast<uint4*>(Pl + off) = make_uint4(l[0], l[1], l[2], l[3]);
+                *reinterpret_cast<uint4*>(Ph + off) = make_uint4(ph[c * 4], ph[c * 4 + 1], ph[c * 4 + 2], ph[c * 4 + 3]);
+                *reinterpret_cast<uint4*>(Pl + off) = make_uint4(pl[c * 4], pl[c * 4 + 1], pl[c * 4 + 2], pl[c * 4 + 3]);
             }
             l_run += sum;
             fence_async_smem();
