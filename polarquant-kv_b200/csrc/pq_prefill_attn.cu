@@ -102,6 +102,13 @@ __device__ __forceinline__ float4 lds_f4(uint32_t saddr) {
     return v;
 }
 
+// 16 packed words into consecutive columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n\t"
+                 "tcgen05.wait::st.sync.aligned;\n" ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+                 : "memory");
+}
+
 // One float32 into / four out of this thread's TMEM lane (row-maximum exchange between the warps of a row group).
 __device__ __forceinline__ void tmem_st1(uint32_t taddr, float v) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};\n\t"
@@ -241,12 +248,13 @@ struct PrefillCfg {
     // Workspace record of one (kv row, 64-token tile): K hi | K lo | V hi | V lo tiles exactly as they
     // sit in shared memory, then the per-token largest radii of K and of V (64 floats each).
     static constexpr uint32_t kRec = 4 * KB + 2 * kPfTok * 4;
-    // TMEM columns: S0 | S1 (128 each: q_hi*k_hi + q_lo*k_hi in the first 64, q_hi*k_lo in the second 64) | O (D) |
-    // 2 parities x 4 partial row maxima.  The rotations before and after the loop use columns [0, 2D).
+    // TMEM columns: S0 | S1 (128 each: q_hi*k_hi + q_lo*k_hi in the first 64, q_hi*k_lo in the second 64) | O (128) |
+    // Q (the rotated query as the A operand of the score MMAs: hi term 64 columns, lo term 64, two float16
+    // per column).  The rotations before and after the loop use columns [0, 2D).
     static constexpr uint32_t kTmemCols = 512;
     static constexpr uint32_t kSCols = 2 * kPfTok;
     static constexpr uint32_t kOCol = 2 * kSCols;
-    static constexpr uint32_t kXchgCol = kOCol + D;
+    static constexpr uint32_t kQCol = kOCol + 128;
 };
 
 // Expands one 64-token tile of K and of V per CTA into the workspace (grid: tiles x kv rows).
@@ -391,22 +399,18 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
                 float vh[32], vl[32];
                 tmem_ld32(vh, tlane + c * 32);
                 tmem_ld32(vl, tlane + D + c * 32);
+                uint32_t h[16], l[16];
 #pragma unroll
-                for (int g8 = 0; g8 < 4; ++g8) {
-                    uint32_t h[4], l[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int k = g8 * 8 + 2 * e;
-                        const float x0 = (vh[k] + vl[k]) * sc, x1 = (vh[k + 1] + vl[k + 1]) * sc;
-                        const __half2 hh = __floats2half2_rn(x0, x1);
-                        const float2 hf = __half22float2(hh);
-                        h[e] = *reinterpret_cast<const uint32_t*>(&hh);
-                        l[e] = pack_half2(x0 - hf.x, x1 - hf.y);
-                    }
-                    const uint32_t off = sw128_off(kPfRows, tid, c * 32 + g8 * 8);
-                    *reinterpret_cast<uint4*>(Qh + off) = make_uint4(h[0], h[1], h[2], h[3]);
-                    *reinterpret_cast<uint4*>(Ql + off) = make_uint4(l[0], l[1], l[2], l[3]);
+                for (int e = 0; e < 16; ++e) {
+                    const float x0 = (vh[2 * e] + vl[2 * e]) * sc, x1 = (vh[2 * e + 1] + vl[2 * e + 1]) * sc;
+                    const __half2 hh = __floats2half2_rn(x0, x1);
+                    const float2 hf = __half22float2(hh);
+                    h[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                    l[e] = pack_half2(x0 - hf.x, x1 - hf.y);
                 }
+                // the query tile stays in tensor memory: lane = row, column j of a term = dims 2j, 2j + 1
+                tmem_st16(tlane + C::kQCol + c * 16, h);
+                tmem_st16(tlane + C::kQCol + 64 + c * 16, l);
             }
             if (!okq) { *abort_s = 1u; if (lane == 0) atomicOr(&g_prefill_error, 4u); }
         }
@@ -514,16 +518,13 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             }
             if (NSPLIT == 4) {
                 // partial maximum of this thread's 16 tokens; the four threads of a row swap partials through
-                // four spare TMEM columns of the row's lane (one set per tile parity), with the row group's
-                // named barrier between the stores and the loads
+                // shared memory (one set per tile parity), with the row group's named barrier in between
 #pragma unroll
                 for (int t = 0; t < HT; ++t) mx = fmaxf(mx, s[t]);
-                tmem_st1(tlane + C::kXchgCol + sb * 4 + hf, mx);
-                tc_fence_before();
+                float* xm = reinterpret_cast<float*>(Qh) + sb * 4 * kPfRows;          // [parity][part][row]
+                xm[hf * kPfRows + r] = mx;
                 asm volatile("bar.sync %0, %1;\n" ::"r"(1 + q), "r"(32 * NSPLIT) : "memory");
-                tc_fence_after();
-                const float4 pm = tmem_ld4(tlane + C::kXchgCol + sb * 4);
-                mx = fmaxf(fmaxf(pm.x, pm.y), fmaxf(pm.z, pm.w));
+                mx = fmaxf(fmaxf(xm[r], xm[kPfRows + r]), fmaxf(xm[2 * kPfRows + r], xm[3 * kPfRows + r]));
             }
             tc_fence_before();
             mbar_arrive(sm_addr(mbar + PF_S_FREE + sb));                // S buffer and dmaxK[sb] consumed
@@ -683,7 +684,6 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
         constexpr uint32_t idesc_s2 = umma_idesc_f16(2 * kPfTok);              // N 128: hi and lo rows of K at once
         constexpr uint32_t idesc_pv = umma_idesc_f16(D) | (1u << 16);          // M 128, N D, B MN-major
         constexpr uint32_t d_hi = (1024u >> 4) | (1u << 14) | (2u << 29);      // 8-row groups 1024 B apart, SWIZZLE_128B
-        const uint32_t q_h = ((sm_addr(Qh) >> 4) & 0x3FFFu) | (1u << 16), q_l = ((sm_addr(Ql) >> 4) & 0x3FFFu) | (1u << 16);
         const uint32_t k_h0 = ((sm_addr(Kh) >> 4) & 0x3FFFu) | (1u << 16);
         const uint32_t p_h = ((sm_addr(Ph) >> 4) & 0x3FFFu) | (1u << 16), p_l = ((sm_addr(Pl) >> 4) & 0x3FFFu) | (1u << 16);
         // V: 64-dim atoms kPfTok*128 B apart (leading offset), 8-token groups 1024 B apart
@@ -702,10 +702,9 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
                 const uint32_t k_b = k_h0 + (uint32_t)(sb * 2 * (C::KB >> 4));
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t qo = (uint32_t)(((ks >> 2) * (kPfRows * 128) + (ks & 3) * 32) >> 4);
                     const uint32_t ko = (uint32_t)(((ks >> 2) * (2 * kPfTok * 128) + (ks & 3) * 32) >> 4);
-                    umma_f16_split_pred(acc, q_h + qo, d_hi, k_b + ko, d_hi, idesc_s2, ks ? 1u : 0u, issue);
-                    umma_f16_split_pred(acc, q_l + qo, d_hi, k_b + ko, d_hi, idesc_s, 1u, issue);
+                    umma_f16_ts_pred(acc, tmem_base + C::kQCol + ks * 8, k_b + ko, d_hi, idesc_s2, ks ? 1u : 0u, issue);
+                    umma_f16_ts_pred(acc, tmem_base + C::kQCol + 64 + ks * 8, k_b + ko, d_hi, idesc_s, 1u, issue);
                 }
                 umma_commit_pred(sm_addr(mbar + PF_S_FULL + sb), issue);
             }

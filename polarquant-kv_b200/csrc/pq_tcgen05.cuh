@@ -105,6 +105,21 @@ __device__ __forceinline__ void umma_f16_split_pred(uint32_t tmem_d, uint32_t a_
         "}\n" ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(issue)
         : "memory");
 }
+// A operand from tensor memory (lane = row, each 32-bit column holds two consecutive float16 along K),
+// B from shared memory; warp-uniform form as above.
+__device__ __forceinline__ void umma_f16_ts_pred(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi,
+                                                 uint32_t idesc, uint32_t accumulate, uint32_t issue) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, pi;\n\t"
+        ".reg .b64 db;\n\t"
+        "setp.ne.b32 pi, %6, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "@pi tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+        "}\n" ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(issue)
+        : "memory");
+}
 __device__ __forceinline__ void umma_commit_pred(uint32_t mbar_addr, uint32_t issue) {
     asm volatile(
         "{\n\t.reg .pred pi;\n\t"
