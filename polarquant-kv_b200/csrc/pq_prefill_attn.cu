@@ -11,14 +11,20 @@
 // column / to the probability before its split); the tiles hold (d / dmax) * centroid * 1024.
 //
 // Roles (no CTA-wide barrier inside the loop; all waits are bounded mbarrier waits):
-//   8 dequant warps - expand tile i of K, then of V, into shared memory in the 128-byte-swizzled
-//                     layout the tensor core reads ([half of 64 dims][token][128 B]);
-//   1 MMA warp      - S(i+1) = Q K(i+1)^T into one of two TMEM buffers (64 columns each) while
-//                     the softmax of tile i runs, then O += P(i) V(i) (V as an MN-major operand);
-//   4 softmax warps - thread = query row: read S from TMEM, scale, mask, online softmax with a
-//                     lazy rescale of O (only when a row's maximum grew by more than 2^8), write
-//                     P * dmax_v as float16 hi/lo into shared memory for the second contraction.
-// The query rotation q @ R^T and the final o @ R run before and after the loop.
+//   dequant warps (8, fused kernel) - expand tile i+1 of K, then of V, into double-buffered shared-memory
+//                     tiles in the 128-byte-swizzled layout the tensor core reads; or
+//   copy warp (workspace kernel)    - the same tiles, expanded once by pq_prefill_expand_kernel, arrive by
+//                     cp.async.bulk from the workspace;
+//   MMA warp        - S(i+1) = Q K(i+1)^T into one of two TMEM buffers while the softmax of tile i runs
+//                     (A = the rotated query, resident in tensor memory; B = the K tile with its hi and lo
+//                     rows stacked, N = 128), then O += P(i) V(i) (A = P in tensor memory, B = V as an
+//                     MN-major operand);
+//   softmax warps   - two (fused) or four (workspace) threads per query row: read S from TMEM, scale, mask,
+//                     exchange partial row maxima, online softmax with a lazy rescale of O (only when a
+//                     row's maximum grew by more than 2^8), write P * dmax_v as float16 hi/lo back into the
+//                     S columns of the tile (the A operand of the second contraction).
+// Tensor memory (512 columns): S0 | S1 (128 each) | O (128) | Q hi, lo (64 each).
+// The query rotation q @ R^T and the final o @ R run before and after the loop, on the tensor core too.
 //
 // causal == 0 reproduces the reference (no mask, src/polarquant_kv_cuda/attention_kernel.py:
 // 92-113); causal == 1 lets query position i see tokens [0, seq_len - seq_q + i].
@@ -100,6 +106,13 @@ __device__ __forceinline__ float4 lds_f4(uint32_t saddr) {
     float4 v;
     asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(saddr));
     return v;
+}
+
+// 8 packed words into consecutive columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&v)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n\t"
+                 "tcgen05.wait::st.sync.aligned;\n" ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
 }
 
 // 16 packed words into consecutive columns of this thread's TMEM lane.
@@ -456,36 +469,6 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             ok = mbar_wait(sm_addr(mbar + PF_K_FULL + sb), (i >> 1) & 1, abort_s) && ok;   // dmaxK[sb] is visible
             tc_fence_after();
             float mx = -INFINITY;
-            if (NSPLIT == 2) {
-            // the row maximum needs all 64 scores of the row (every thread of the row computes the same
-            // value from the same numbers), the probabilities only this thread's HT tokens
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                float sa[32], sl[32];
-                tmem_ld32x2(sa, sl, tlane + sb * C::kSCols + half * 32, tlane + sb * C::kSCols + kPfTok + half * 32);
-#pragma unroll
-                for (int t = 0; t < 32; ++t) sa[t] += sl[t];
-                const uint32_t d4p = dk_addr + (uint32_t)((sb * kPfTok + half * 32) * 4);     // dmaxK holds dmax / 1024
-                const int tk = i * kPfTok + half * 32;
-                if (tk + 32 <= limit) {
-#pragma unroll
-                    for (int t4 = 0; t4 < 8; ++t4) {
-                        const float4 d4 = lds_f4(d4p + t4 * 16);
-                        mx = fmaxf(mx, fmaxf(fmaxf(sa[4 * t4 + 0] * d4.x, sa[4 * t4 + 1] * d4.y),
-                                             fmaxf(sa[4 * t4 + 2] * d4.z, sa[4 * t4 + 3] * d4.w)));
-                    }
-                } else {
-#pragma unroll
-                    for (int t4 = 0; t4 < 8; ++t4) {
-                        const float4 d4 = lds_f4(d4p + t4 * 16);
-                        const float dd[4] = {d4.x, d4.y, d4.z, d4.w};
-#pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            if (tk + 4 * t4 + e < limit) mx = fmaxf(mx, sa[4 * t4 + e] * dd[e]);
-                    }
-                }
-            }
-            }
             float s[HT];
             {
                 float sl[HT];                                            // the q_hi * k_lo part of the same scores
@@ -516,15 +499,17 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
                         if (tok0 + t >= limit) s[t] = -INFINITY;
                 }
             }
-            if (NSPLIT == 4) {
-                // partial maximum of this thread's 16 tokens; the four threads of a row swap partials through
-                // shared memory (one set per tile parity), with the row group's named barrier in between
+            {
+                // partial maximum of this thread's tokens; the threads of a row swap partials through shared
+                // memory (one set per tile parity) with the row group's named barrier in between.  After the
+                // barrier every thread of the row has its scores in registers: the S columns may be reused.
 #pragma unroll
                 for (int t = 0; t < HT; ++t) mx = fmaxf(mx, s[t]);
                 float* xm = reinterpret_cast<float*>(Qh) + sb * 4 * kPfRows;          // [parity][part][row]
                 xm[hf * kPfRows + r] = mx;
                 asm volatile("bar.sync %0, %1;\n" ::"r"(1 + q), "r"(32 * NSPLIT) : "memory");
-                mx = fmaxf(fmaxf(xm[r], xm[kPfRows + r]), fmaxf(xm[2 * kPfRows + r], xm[3 * kPfRows + r]));
+#pragma unroll
+                for (int k = 0; k < NSPLIT; ++k) mx = fmaxf(mx, xm[k * kPfRows + r]);
             }
             tc_fence_before();
             mbar_arrive(sm_addr(mbar + PF_S_FREE + sb));                // S buffer and dmaxK[sb] consumed
@@ -556,33 +541,35 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
                     pl[c * 4 + e] = pack_half2(w0 - hfl.x, w1 - hfl.y);
                 }
             }
-            if (i > 0) {
+            if (i > 0 && rescale) {
+                // O may only be touched once the previous tile's P V has completed
                 ok = mbar_wait(sm_addr(mbar + PF_PV_DONE + ((i - 1) & 1)), ((i - 1) >> 1) & 1, abort_s) && ok;
                 tc_fence_after();
-                if (rescale) {
-                    const float alpha = (m_used == -INFINITY) ? 1.f : fast_exp2(m_old - m_used);   // exp2(-inf) = 0
-                    // the row's O columns in 32-column chunks, dealt round-robin to the row's threads
+                const float alpha = (m_used == -INFINITY) ? 1.f : fast_exp2(m_old - m_used);   // exp2(-inf) = 0
+                // the row's O columns in 32-column chunks, dealt round-robin to the row's threads
 #pragma unroll 1
-                    for (int c = hf; c < D / 32; c += NSPLIT) {
-                        float o[32];
-                        const uint32_t col = C::kOCol + c * 32;
-                        tmem_ld32(o, tlane + col);
+                for (int c = hf; c < D / 32; c += NSPLIT) {
+                    float o[32];
+                    const uint32_t col = C::kOCol + c * 32;
+                    tmem_ld32(o, tlane + col);
 #pragma unroll
-                        for (int k = 0; k < 32; ++k) o[k] *= alpha;
-                        tmem_st32(tlane + col, o);
-                    }
-                    l_run *= alpha;
-                    tc_fence_before();
+                    for (int k = 0; k < 32; ++k) o[k] *= alpha;
+                    tmem_st32(tlane + col, o);
                 }
+                l_run *= alpha;
             }
-#pragma unroll
-            for (int c = 0; c < HT / 8; ++c) {
-                const uint32_t off = prow + (uint32_t)(((hf * (HT / 8) + c) ^ (r & 7)) << 4);
-                *reinterpret_cast<uint4*>(Ph + off) = make_uint4(ph[c * 4], ph[c * 4 + 1], ph[c * 4 + 2], ph[c * 4 + 3]);
-                *reinterpret_cast<uint4*>(Pl + off) = make_uint4(pl[c * 4], pl[c * 4 + 1], pl[c * 4 + 2], pl[c * 4 + 3]);
+            // P goes into the (now dead) S columns of this tile as the A operand of the second contraction:
+            // hi term in columns [0, 32) of the buffer, lo term in [32, 64), two tokens per column.  The MMA
+            // warp issues S(i + 2), which overwrites these columns, after P(i) V(i); the tensor core runs them in order.
+            if (HT == 16) {
+                tmem_st8(tlane + sb * C::kSCols + hf * (HT / 2), *reinterpret_cast<const uint32_t(*)[8]>(&ph[0]));
+                tmem_st8(tlane + sb * C::kSCols + kPfTok / 2 + hf * (HT / 2), *reinterpret_cast<const uint32_t(*)[8]>(&pl[0]));
+            } else {
+                tmem_st16(tlane + sb * C::kSCols + hf * (HT / 2), *reinterpret_cast<const uint32_t(*)[16]>(&ph[0]));
+                tmem_st16(tlane + sb * C::kSCols + kPfTok / 2 + hf * (HT / 2), *reinterpret_cast<const uint32_t(*)[16]>(&pl[0]));
             }
+            tc_fence_before();
             l_run += sum;
-            fence_async_smem();
             mbar_arrive(sm_addr(mbar + PF_P_FULL));
         }
         if (n_tiles > 0) {
@@ -685,7 +672,6 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
         constexpr uint32_t idesc_pv = umma_idesc_f16(D) | (1u << 16);          // M 128, N D, B MN-major
         constexpr uint32_t d_hi = (1024u >> 4) | (1u << 14) | (2u << 29);      // 8-row groups 1024 B apart, SWIZZLE_128B
         const uint32_t k_h0 = ((sm_addr(Kh) >> 4) & 0x3FFFu) | (1u << 16);
-        const uint32_t p_h = ((sm_addr(Ph) >> 4) & 0x3FFFu) | (1u << 16), p_l = ((sm_addr(Pl) >> 4) & 0x3FFFu) | (1u << 16);
         // V: 64-dim atoms kPfTok*128 B apart (leading offset), 8-token groups 1024 B apart
         constexpr uint32_t v_lbo = ((kPfTok * 128u) >> 4) << 16;
         const uint32_t v_h0 = ((sm_addr(Vh) >> 4) & 0x3FFFu) | v_lbo;
@@ -723,10 +709,11 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
                 const uint32_t v_h = v_h0 + (uint32_t)(sb * 2 * (C::KB >> 4)), v_l = v_h + (C::KB >> 4);
 #pragma unroll
                 for (int kt = 0; kt < kPfTok / 16; ++kt) {
-                    const uint32_t po = (uint32_t)((kt * 32) >> 4), vo = (uint32_t)((kt * 16 * 128) >> 4);
-                    umma_f16_split_pred(acc, p_h + po, d_hi, v_h + vo, d_hi, idesc_pv, (i > 0 || kt > 0) ? 1u : 0u, issue);
-                    umma_f16_split_pred(acc, p_h + po, d_hi, v_l + vo, d_hi, idesc_pv, 1u, issue);
-                    umma_f16_split_pred(acc, p_l + po, d_hi, v_h + vo, d_hi, idesc_pv, 1u, issue);
+                    const uint32_t vo = (uint32_t)((kt * 16 * 128) >> 4);
+                    const uint32_t p_h = tmem_base + sb * C::kSCols + kt * 8, p_l = p_h + kPfTok / 2;
+                    umma_f16_ts_pred(acc, p_h, v_h + vo, d_hi, idesc_pv, (i > 0 || kt > 0) ? 1u : 0u, issue);
+                    umma_f16_ts_pred(acc, p_h, v_l + vo, d_hi, idesc_pv, 1u, issue);
+                    umma_f16_ts_pred(acc, p_l, v_h + vo, d_hi, idesc_pv, 1u, issue);
                 }
                 umma_commit_pred(sm_addr(mbar + PF_PV_DONE + sb), issue);
             }
