@@ -46,7 +46,9 @@ constexpr int kPfDeqThreads = kPfDeqWarps * 32;
 __host__ __device__ constexpr int pf_split(bool pre) { return pre ? 4 : 2; }             // softmax threads per row
 __host__ __device__ constexpr int pf_soft_warps(bool pre) { return 4 * pf_split(pre); }
 __host__ __device__ constexpr int pf_mma_warp(bool pre) { return pre ? pf_soft_warps(pre) + 1 : pf_soft_warps(pre) + kPfDeqWarps; }
-__host__ __device__ constexpr int pf_threads(bool pre) { return (pf_mma_warp(pre) + 1) * 32; }
+// Workspace kernel: two MMA warps, the first issues the score MMAs (and the rotations), the second the value
+// MMAs (MMA issue is its critical path).  Fused kernel: one warp issues both, interleaved.
+__host__ __device__ constexpr int pf_threads(bool pre) { return (pf_mma_warp(pre) + (pre ? 2 : 1)) * 32; }
 constexpr float kPfValScale = 1024.0f;       // tiles hold 1024 * (d / dmax) * centroid
 constexpr float kPfRescaleGap = 8.0f;        // log2 units a row maximum may grow before O is rescaled
 
@@ -678,7 +680,13 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
         auto issue_s = [&](int i) {
             const int sb = i & 1;
             ok = mbar_wait(sm_addr(mbar + PF_K_FULL + sb), (i >> 1) & 1, abort_s, 32) && ok;
-            if (i >= 2) ok = mbar_wait(sm_addr(mbar + PF_S_FREE + sb), ((i >> 1) - 1) & 1, abort_s, 32) && ok;
+            if (i >= 2) {
+                // the buffer's scores have been read, and the P that replaced them has been consumed by P V
+                // (the value MMAs are issued by another warp, so that order has to be waited for)
+                ok = mbar_wait(sm_addr(mbar + PF_S_FREE + sb), ((i >> 1) - 1) & 1, abort_s, 32) && ok;
+                // (with one issuing warp the tensor core's in-order execution already gives that order)
+                if (PRE) ok = mbar_wait(sm_addr(mbar + PF_PV_DONE + sb), ((i >> 1) - 1) & 1, abort_s, 32) && ok;
+            }
             if (!ok) return;
             tc_fence_after();
             {
@@ -696,10 +704,15 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             }
             __syncwarp();
         };
-        if (n_tiles > 0) issue_s(0);
+        if (PRE && warp == kMmaWarp) {
+            for (int i = 0; i < n_tiles && ok; ++i) issue_s(i);
+        } else
         for (int i = 0; i < n_tiles && ok; ++i) {
             const int sb = i & 1;
-            if (i + 1 < n_tiles) issue_s(i + 1);
+            if (!PRE) {                       // one warp: S(i+1) goes out before P(i) V(i)
+                if (i == 0) issue_s(0);
+                if (i + 1 < n_tiles) issue_s(i + 1);
+            }
             ok = mbar_wait(sm_addr(mbar + PF_P_FULL), i & 1, abort_s, 32) && ok;
             ok = mbar_wait(sm_addr(mbar + PF_V_FULL + sb), (i >> 1) & 1, abort_s, 32) && ok;
             if (!ok) break;
