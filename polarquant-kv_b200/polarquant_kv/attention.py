@@ -196,14 +196,27 @@ def prefill_attention(query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, p
 def compressed_attention(query: torch.Tensor, compressed_keys, compressed_values, rotation_matrix,
                          jl_matrix=None, enable_qjl: bool = True, num_kv_heads: int | None = None,
                          n_bits: int = 4, group_size: int = 32,
-                         out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
-    """query [B, Hq, Sq, D] (or [Hq, Sq, D]) float16 on the GPU; keys/values either
+                         out_dtype: torch.dtype = torch.float32, return_scores: bool = False):
+    """query [B, Hq, Sq, D] (or [Hq, Sq, D], or the reference's 2-D form [n_q, D] with keys/values
+    [S, D]) float16 on the GPU; keys/values either
     CompressedKV caches (the GPU facade's signature) or raw float16 tensors
     [B, Hkv, S, D] / [Hkv, S, D], which are compressed first as the numpy reference does
     (attention.py:138-144).  Returns [B, Hq, Sq, D] (same rank as the query), float32 by
     default since float16 cannot hold the 2e-3 parity the path is checked to.
-    An empty cache gives zeros (attention.py:127-131)."""
+    An empty cache gives zeros (attention.py:127-131).  return_scores=True returns
+    {"output", "scores"} like the reference's 2-D form (attention.py:157-160); the pre-softmax
+    scores [.., Sq, S] come from a checking path (pq_dequant + a float32 matmul + the sketch
+    correction in torch), not from the attention kernels."""
     _require_cuda(query, "query")
+    if query.dim() == 2:                       # reference 2-D form: one head, n_q query rows
+        def lift(x):
+            return x if isinstance(x, CompressedKV) else x.reshape(1, 1, *x.shape)
+        res = compressed_attention(query.reshape(1, 1, *query.shape), lift(compressed_keys), lift(compressed_values),
+                                   rotation_matrix, jl_matrix, enable_qjl, num_kv_heads, n_bits, group_size,
+                                   out_dtype, return_scores)
+        if return_scores:
+            return {"output": res["output"][0, 0], "scores": res["scores"][0, 0]}
+        return res[0, 0]
     squeeze = query.dim() == 3
     q4 = query.unsqueeze(0) if squeeze else query
     if q4.dim() != 4:
@@ -236,4 +249,19 @@ def compressed_attention(query: torch.Tensor, compressed_keys, compressed_values
                                for i in range(Sq)], dim=2)
         else:
             out = prefill_attention(q4, ck, cv, plan, out_dtype=out_dtype)
+    if return_scores:
+        if ck.seq_len == 0:
+            scores = torch.empty((B, Hq, Sq, 0), dtype=torch.float32, device=dev)
+        else:
+            from . import qjl as _qjl
+            from .quantizer import decompress
+            k_hat = decompress(ck, rotation_matrix).repeat_interleave(Hq // Hkv, dim=1)       # [B, Hq, S, D]
+            scores = (q4.float() @ k_hat.transpose(-2, -1)) / math.sqrt(D)
+            if enable_qjl and jl_matrix is not None and ck.qjl_signs is not None:
+                S = ck.seq_len
+                corr = _qjl.compute_correction(q4.float(), ck.qjl_signs[:, :, :S].repeat_interleave(Hq // Hkv, dim=1),
+                                               ck.residual_norms[:, :, :S].repeat_interleave(Hq // Hkv, dim=1), jl_matrix)
+                scores = scores + (corr / math.sqrt(D)).float()
+        res = {"output": out[0] if squeeze else out, "scores": scores[0] if squeeze else scores}
+        return res
     return out[0] if squeeze else out

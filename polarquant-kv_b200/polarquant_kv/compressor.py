@@ -18,9 +18,9 @@ def decompress(cache, rotation_matrix, dtype=None):
 
 
 def compressed_attention(query, compressed_keys, compressed_values, rotation_matrix, jl_matrix=None,
-                         enable_qjl=True, num_kv_heads=None):
+                         enable_qjl=True, num_kv_heads=None, return_scores=False):
     return _attention(query, compressed_keys, compressed_values, rotation_matrix, jl_matrix,
-                      enable_qjl, num_kv_heads)
+                      enable_qjl, num_kv_heads, return_scores=return_scores)
 
 
 def get_memory_bytes(cache: CompressedKV) -> int:
