@@ -441,6 +441,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=WORKLOAD["batch"],
                     help="sequences per GPU (default: the headline workload's 32; smaller for profiler captures)")
+    ap.add_argument("--context", type=int, default=0, help="tokens per sequence (default: the headline workload's)")
+    ap.add_argument("--q-heads", type=int, default=0, help="query heads (default: the headline workload's)")
     ap.add_argument("--only-decode", action="store_true",
                     help="skip the compress and CPU-baseline measurements (profiler captures)")
     ap.add_argument("--splits", type=int, default=0, help="sequence splits per (batch, kv head); 0 = library default")
@@ -449,6 +451,10 @@ def main():
     ap.add_argument("--compress-vecs", type=int, default=COMPRESS_VECS, help="vectors per compress launch")
     args = ap.parse_args()
     WORKLOAD["batch"] = args.batch
+    if args.context or args.q_heads:           # other decode shapes (e.g. one long sequence): not the headline
+        WORKLOAD["context"] = args.context or WORKLOAD["context"]
+        WORKLOAD["q_heads"] = args.q_heads or WORKLOAD["q_heads"]
+        WORKLOAD["name"] = "custom PQ4 decode attention shape"
     if args.impl == "reference":
         run_reference(args)
     else:
