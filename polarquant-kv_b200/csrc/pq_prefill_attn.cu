@@ -11,7 +11,7 @@
 // column / to the probability before its split); the tiles hold (d / dmax) * centroid * 1024.
 //
 // Roles (no CTA-wide barrier inside the loop; all waits are bounded mbarrier waits):
-//   dequant warps (8, fused kernel) - expand tile i+1 of K, then of V, into double-buffered shared-memory
+//   dequant warps (16, fused kernel) - expand tile i+1 of K, then of V, into double-buffered shared-memory
 //                     tiles in the 128-byte-swizzled layout the tensor core reads; or
 //   copy warp (workspace kernel)    - the same tiles, expanded once by pq_prefill_expand_kernel, arrive by
 //                     cp.async.bulk from the workspace;
@@ -38,9 +38,9 @@ static __device__ unsigned int g_prefill_error = 0;
 constexpr int kPfRows = 128;                 // query rows per CTA = TMEM lanes
 constexpr int kPfTok = 64;                   // tokens per KV tile
 constexpr int kPfRowWarps = 4;               // warps that cover the 128 TMEM lanes once (rotation epilogues)
-constexpr int kPfDeqWarps = 8;
+constexpr int kPfDeqWarps = 16;
 constexpr int kPfDeqThreads = kPfDeqWarps * 32;
-// Warp roles.  Fused kernel: 8 softmax warps (two threads per query row), 8 dequant warps, 1 MMA warp.
+// Warp roles.  Fused kernel: 8 softmax warps (two threads per query row), 16 dequant warps, 1 MMA warp.
 // Workspace kernel: 16 softmax warps (four threads per row, row maxima exchanged through spare
 // TMEM columns), 1 copy warp, 1 MMA warp.
 __host__ __device__ constexpr int pf_split(bool pre) { return pre ? 4 : 2; }             // softmax threads per row
@@ -300,7 +300,7 @@ __global__ void __launch_bounds__(kPfDeqThreads) pq_prefill_expand_kernel(const 
 }
 
 // PRE: the tiles come expanded from the workspace (bulk copies by one warp) instead of being
-// dequantised by eight warps of this CTA.
+// dequantised by sixteen warps of this CTA.
 template <int D, int KBITS, int VBITS, bool PRE>
 __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(const PrefillParams p) {
     constexpr int kPfSoftWarps = pf_soft_warps(PRE), NSPLIT = pf_split(PRE), kMmaWarp = pf_mma_warp(PRE);
