@@ -20,7 +20,7 @@
 //                 that share 32 vectors meet at a named barrier and one lane sends those vectors'
 //                 packed bytes off with a bulk store.
 // With the sketch (a second contraction per tile) the older serial flow is kept: cp.async tile
-// loads, K groups with one accumulator each, CTA-wide barriers.
+// loads and CTA-wide barriers, the MMAs issued by the first warp.
 // Everything after the contraction follows the reference's float32 arithmetic exactly:
 //   radius  = sqrt(sum of squares), summed in numpy's axis-reduction order
 //             (eight strided partial sums, then a balanced tree),
@@ -47,11 +47,6 @@
 #include <cstring>
 
 #include "pq_tcgen05.cuh"
-
-// 16-wide k-steps accumulated inside the tensor core before a round-to-nearest float32 add
-#ifndef PQ_COMPRESS_KSTEPS_PER_GROUP
-#define PQ_COMPRESS_KSTEPS_PER_GROUP 4
-#endif
 
 namespace pq {
 
@@ -120,10 +115,9 @@ struct CompressCfg {
     static constexpr int VB = (D / 32) * block_bytes(BITS);   // bytes per stored vector
     static constexpr int kRBytes = 4 * D * D;                 // [2D/8 chunks][D rows][16 B]
     static constexpr int kXBytes = (D / 8) * 2048;            // [D/8 chunks][128 rows][16 B]
-    // With the sketch: K groups of KPG k-steps, one TMEM accumulator each.  Without: one MMA per k-step
-    // with N = 2D ([R_hi ; R_lo] stacked), i.e. two accumulators (hi and lo products) per tile.
-    static constexpr int KPG = PQ_COMPRESS_KSTEPS_PER_GROUP < D / 16 ? PQ_COMPRESS_KSTEPS_PER_GROUP : D / 16;
-    static constexpr int KG = QJL ? (D / 16) / KPG : 2;
+    // One MMA per k-step with N = 2D ([R_hi ; R_lo] stacked), i.e. two accumulators (hi and lo products)
+    // per tile.
+    static constexpr int KG = 2;
     // tensor-memory columns of one accumulator buffer (the sketch reuses it and needs jl_dim <= 128
     // columns); without QJL two buffers alternate so the next tile's MMAs overlap this tile's epilogue
     static constexpr int kBufCols = (KG * D < 128 && QJL) ? 128 : KG * D;
@@ -155,7 +149,6 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
     constexpr int VB = C::VB;
     constexpr int BREP = C::BREP;
     constexpr int NLEV = 1 << BITS;
-    constexpr uint32_t LBO_R = (D / 8) * 128;                 // K-chunk stride of the R / P tiles' row groups
     const int M = QJL ? p.jl_dim : 0;
 
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -203,9 +196,7 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
     // ---- one-time set-up: split matrices, tables, barrier, tensor memory
     for (int id = tid; id < D * (2 * D / 8); id += blockDim.x) {
         const int n = ((id >> 5) % (D / 8)) * 8 + (id & 7), kc = ((id >> 5) / (D / 8)) * 4 + ((id >> 3) & 3);
-        if (QJL) {      // B tile [D rows][K = 2D]: the lo term follows the hi term along K
-            cp_async_16(Rb + chunk_off(D, n, kc), p.rot_split + (size_t)n * 2 * D + kc * 8);
-        } else {        // B tile [2D rows][K = D]: the lo term's rows follow the hi term's (N = 2D)
+        {               // B tile [2D rows][K = D]: the lo term's rows follow the hi term's (N = 2D)
             const int half = kc / (D / 8), kk = kc % (D / 8);
             cp_async_16(Rb + chunk_off(2 * D, half * D + n, kk), p.rot_split + (size_t)n * 2 * D + kc * 8);
         }
@@ -272,25 +263,22 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
     };
     uint8_t* const Xcur = Xa;      // (sketch flow) vector tile, then residual hi term
     uint8_t* Elo = Xb;
-    // rotation of one tile: KG accumulators (KPG 16-wide k-steps each, hi then lo term)
+    // (sketch flow) rotation of one tile from the no-swizzle vector tile X: one MMA per k-step, N = 2D.
+    // Called by every lane of warp 0 with identical arguments; lane 0 issues.
     auto issue_rotation = [&](const uint8_t* X, uint32_t tcol, uint64_t* done_bar) {
         tc_fence_after();
-        const uint32_t xaddr = sm_addr(X), raddr = sm_addr(Rb);
-        constexpr uint32_t idesc = umma_idesc_f16(D);
-        constexpr int KG = C::KG, KPG = C::KPG;
+        constexpr uint32_t idesc = umma_idesc_f16(2 * D);
+        constexpr uint32_t kLboB = (2 * D / 8) * 128;
+        constexpr uint32_t ns_hi = (128u >> 4) | (1u << 14);               // 8-row groups 128 B apart, no swizzle
+        const uint32_t issue = lane == 0 ? 1u : 0u;
+        const uint32_t a_lo0 = ((sm_addr(X) >> 4) & 0x3FFFu) | ((2048u >> 4) << 16);
+        const uint32_t b_lo0 = ((sm_addr(Rb) >> 4) & 0x3FFFu) | ((kLboB >> 4) << 16);
 #pragma unroll
-        for (int grp = 0; grp < KG; ++grp) {
-#pragma unroll
-            for (int k2 = 0; k2 < KPG; ++k2) {
-                const int ks = grp * KPG + k2;
-                const uint64_t da = umma_desc(xaddr + ks * 2 * 2048, 2048, 128);
-                const uint64_t bh = umma_desc(raddr + (2 * ks) * LBO_R, LBO_R, 128);
-                const uint64_t bl = umma_desc(raddr + (D / 8 + 2 * ks) * LBO_R, LBO_R, 128);
-                umma_f16(tmem_base + tcol + grp * D, da, bh, idesc, k2 ? 1u : 0u);
-                umma_f16(tmem_base + tcol + grp * D, da, bl, idesc, 1u);
-            }
-        }
-        umma_commit(sm_addr(done_bar));
+        for (int ks = 0; ks < D / 16; ++ks)
+            umma_f16_split_pred(tmem_base + tcol, a_lo0 + (uint32_t)((ks * 2 * 2048) >> 4), ns_hi,
+                                b_lo0 + (uint32_t)((2 * ks * kLboB) >> 4), ns_hi, idesc, ks ? 1u : 0u, issue);
+        umma_commit_pred(sm_addr(done_bar), issue);
+        __syncwarp();
     };
     // TMA fetch of one tile into vector buffer `buf` (rows past the end of x arrive as zeros)
     auto fetch_tile = [&](int64_t tile, int buf) {
@@ -359,7 +347,7 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
             cp_async_wait<0>();
             fence_async_smem();      // the tensor core reads shared memory through the async proxy
             __syncthreads();
-            if (tid == 0) issue_rotation(Xcur, 0u, mbar);
+            if (warp == 0) issue_rotation(Xcur, 0u, mbar);
             // power-of-two scale per vector so the residual split stays in float16 range:
             // |e_j| < 32 * max|x_j|, scaled to below 2^15.  (Reads the vector tile while the MMAs run.)
             constexpr int PARTS = THREADS / kTileVecs;                  // threads per row
@@ -516,22 +504,25 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
             tc_fence_before();
             __syncthreads();
             // ---- sign sketch: proj[vec][i] = sum_j e[vec][j] * P'[i][j], three float16 product terms
-            if (tid == 0) {
+            if (warp == 0) {                       // every lane runs the loop, lane 0 issues
                 tc_fence_after();
-                const uint32_t ah = sm_addr(Xcur), al = sm_addr(Elo), pa = sm_addr(Pb);
+                const uint32_t issue = lane == 0 ? 1u : 0u;
                 const uint32_t lbo_p = (uint32_t)(M / 8) * 128;
                 const uint32_t idesc = umma_idesc_f16(M);
-#pragma unroll 1
+                constexpr uint32_t ns_hi = (128u >> 4) | (1u << 14);
+                const uint32_t ah0 = ((sm_addr(Xcur) >> 4) & 0x3FFFu) | ((2048u >> 4) << 16);
+                const uint32_t al0 = ((sm_addr(Elo) >> 4) & 0x3FFFu) | ((2048u >> 4) << 16);
+                const uint32_t pb0 = ((sm_addr(Pb) >> 4) & 0x3FFFu) | ((lbo_p >> 4) << 16);
+#pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint64_t dah = umma_desc(ah + ks * 2 * 2048, 2048, 128);
-                    const uint64_t dal = umma_desc(al + ks * 2 * 2048, 2048, 128);
-                    const uint64_t bh = umma_desc(pa + (2 * ks) * lbo_p, lbo_p, 128);
-                    const uint64_t bl = umma_desc(pa + (D / 8 + 2 * ks) * lbo_p, lbo_p, 128);
-                    umma_f16(tmem_base + tcol, dah, bh, idesc, ks ? 1u : 0u);
-                    umma_f16(tmem_base + tcol, dah, bl, idesc, 1u);
-                    umma_f16(tmem_base + tcol, dal, bh, idesc, 1u);
+                    const uint32_t ao = (uint32_t)((ks * 2 * 2048) >> 4);
+                    const uint32_t bh = pb0 + ((2 * ks * lbo_p) >> 4), bl = pb0 + (((D / 8 + 2 * ks) * lbo_p) >> 4);
+                    umma_f16_split_pred(tmem_base + tcol, ah0 + ao, ns_hi, bh, ns_hi, idesc, ks ? 1u : 0u, issue);
+                    umma_f16_split_pred(tmem_base + tcol, ah0 + ao, ns_hi, bl, ns_hi, idesc, 1u, issue);
+                    umma_f16_split_pred(tmem_base + tcol, al0 + ao, ns_hi, bh, ns_hi, idesc, 1u, issue);
                 }
-                umma_commit(sm_addr(mbar));
+                umma_commit_pred(sm_addr(mbar), issue);
+                __syncwarp();
             }
             ok = mbar_wait(sm_addr(mbar), phase) && ok;
             phase ^= 1u;
