@@ -257,11 +257,12 @@ def run_ours(args):
 
     prepared = [attention.prepare_decode(q_stage, sets[j][1], sets[j][2], plan, n_splits=args.splits) for j in range(2)]
 
+    # the serving-loop form of the public API: one CUDA graph per cache = copy of the query from pinned host
+    # memory, the attention kernel, copy of the result back to pinned host memory
+    graphs = [pd.capture(q_host, out_host) for pd in prepared]
+
     def step_e2e(i):
-        # the serving-loop form of the public API: query from pinned host memory, result back to the host
-        q_stage.copy_(q_host, non_blocking=True)
-        out = prepared[i & 1]()
-        out_host.copy_(out, non_blocking=True)
+        graphs[i & 1].replay()
         torch.cuda.current_stream().synchronize()     # the caller reads the result on the host
 
     def barrier():

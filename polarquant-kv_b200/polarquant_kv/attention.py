@@ -131,11 +131,29 @@ class PreparedDecode:
                       max(0, n_splits), self.scratch.data_ptr(), self.scratch.numel())
         self._stream = torch.cuda.current_stream(self.dev)
 
-    def __call__(self) -> torch.Tensor:
-        st = self._fn(*self._head, self.ck.seq_len, *self._tail, self._stream.cuda_stream)
+    def __call__(self, stream: torch.cuda.Stream | None = None) -> torch.Tensor:
+        """Enqueue on the stream the object was prepared on, or on `stream`."""
+        st = self._fn(*self._head, self.ck.seq_len, *self._tail, (stream or self._stream).cuda_stream)
         if st:
             _ext.check(st, "pq_decode_attn")
         return self.out
+
+    def capture(self, query_host: torch.Tensor | None = None, out_host: torch.Tensor | None = None):
+        """Record one decode step as a CUDA graph and return it (replay with ``graph.replay()``): optional
+        copy of the pinned ``query_host`` into the query buffer, the attention kernel, optional copy of the
+        output into the pinned ``out_host``.  One graph launch then replaces three stream operations.  The
+        sequence length is frozen at capture time: re-capture after the cache has grown."""
+        graph = torch.cuda.CUDAGraph()
+        self()                                    # first launch outside the capture (function attributes)
+        torch.cuda.current_stream(self.dev).synchronize()
+        with torch.cuda.graph(graph):
+            cur = torch.cuda.current_stream(self.dev)
+            if query_host is not None:
+                self.query.copy_(query_host, non_blocking=True)
+            self(cur)
+            if out_host is not None:
+                out_host.copy_(self.out, non_blocking=True)
+        return graph
 
 
 def prepare_decode(query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, plan, **kw) -> PreparedDecode:
