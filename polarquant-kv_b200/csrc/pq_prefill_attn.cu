@@ -15,15 +15,15 @@
 //                     tiles in the 128-byte-swizzled layout the tensor core reads; or
 //   copy warp (workspace kernel)    - the same tiles, expanded once by pq_prefill_expand_kernel, arrive by
 //                     cp.async.bulk from the workspace;
-//   MMA warp        - S(i+1) = Q K(i+1)^T into one of two TMEM buffers while the softmax of tile i runs
-//                     (A = the rotated query, resident in tensor memory; B = the K tile with its hi and lo
-//                     rows stacked, N = 128), then O += P(i) V(i) (A = P in tensor memory, B = V as an
-//                     MN-major operand);
+//   MMA warp(s)     - S(i) = Q K(i)^T into one of three TMEM buffers, ahead of the softmax (A = the rotated
+//                     query in shared memory; B = the K tile with its hi and lo rows stacked, N = 128), and
+//                     O += P(i) V(i) (A = P in tensor memory, B = V as an MN-major operand).  The fused kernel
+//                     issues both from one warp, the workspace kernel from two;
 //   softmax warps   - two (fused) or four (workspace) threads per query row: read S from TMEM, scale, mask,
 //                     exchange partial row maxima, online softmax with a lazy rescale of O (only when a
 //                     row's maximum grew by more than 2^8), write P * dmax_v as float16 hi/lo back into the
 //                     S columns of the tile (the A operand of the second contraction).
-// Tensor memory (512 columns): S0 | S1 (128 each) | O (128) | Q hi, lo (64 each).
+// Tensor memory (512 columns): S0 | S1 | S2 (128 each) | O (128).
 // The query rotation q @ R^T and the final o @ R run before and after the loop, on the tensor core too.
 //
 // causal == 0 reproduces the reference (no mask, src/polarquant_kv_cuda/attention_kernel.py:
@@ -68,7 +68,10 @@ struct PrefillParams {
 
 // Barriers that two roles wait on come in pairs, one per tile parity: a barrier's next phase can then
 // only complete after every waiter has seen the current one (a waiter never lags a whole phase).
-enum { PF_K_FULL = 0, PF_V_FULL = 2, PF_S_FULL = 4, PF_S_FREE = 6, PF_PV_DONE = 8, PF_P_FULL = 10, PF_AUX = 11, PF_NBAR = 12 };
+// K / V tiles and their radii are double-buffered (index = tile parity); the score buffers in tensor memory are
+// triple-buffered (index = tile mod 3), so S(i) does not have to wait for P(i-2) V(i-2).
+enum { PF_K_FULL = 0, PF_V_FULL = 2, PF_S_FULL = 4, PF_S_FREE = 7, PF_PV_DONE = 10, PF_P_FULL = 12, PF_AUX = 13,
+       PF_P_USED = 14, PF_NBAR = 17 };
 
 // Byte offset of element (row r, column col) of a [rows][64*h columns] float16 tile stored as
 // 64-column halves of `rows` 128-byte rows, 16-byte chunks XOR-swizzled with the row (SWIZZLE_128B).
@@ -263,13 +266,11 @@ struct PrefillCfg {
     // Workspace record of one (kv row, 64-token tile): K hi | K lo | V hi | V lo tiles exactly as they
     // sit in shared memory, then the per-token largest radii of K and of V (64 floats each).
     static constexpr uint32_t kRec = 4 * KB + 2 * kPfTok * 4;
-    // TMEM columns: S0 | S1 (128 each: q_hi*k_hi + q_lo*k_hi in the first 64, q_hi*k_lo in the second 64) | O (128) |
-    // Q (the rotated query as the A operand of the score MMAs: hi term 64 columns, lo term 64, two float16
-    // per column).  The rotations before and after the loop use columns [0, 2D).
+    // TMEM columns: S0 | S1 | S2 (128 each: q_hi*k_hi + q_lo*k_hi in the first 64, q_hi*k_lo in the second 64) |
+    // O (128).  The rotations before and after the loop use columns [0, 2D).
     static constexpr uint32_t kTmemCols = 512;
     static constexpr uint32_t kSCols = 2 * kPfTok;
-    static constexpr uint32_t kOCol = 2 * kSCols;
-    static constexpr uint32_t kQCol = kOCol + 128;
+    static constexpr uint32_t kOCol = 3 * kSCols;
 };
 
 // Expands one 64-token tile of K and of V per CTA into the workspace (grid: tiles x kv rows).
@@ -337,9 +338,12 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
         for (int k = 0; k < 2; ++k) {
             mbar_init(sm_addr(mbar + PF_K_FULL + k), PRE ? 1 : kPfDeqThreads);
             mbar_init(sm_addr(mbar + PF_V_FULL + k), PRE ? 1 : kPfDeqThreads);
+            mbar_init(sm_addr(mbar + PF_PV_DONE + k), 1);
+        }
+        for (int k = 0; k < 3; ++k) {
             mbar_init(sm_addr(mbar + PF_S_FULL + k), 1);
             mbar_init(sm_addr(mbar + PF_S_FREE + k), kPfSoftWarps * 32);
-            mbar_init(sm_addr(mbar + PF_PV_DONE + k), 1);
+            mbar_init(sm_addr(mbar + PF_P_USED + k), 1);      // P V(i) has consumed the P held in score buffer i mod 3
         }
         mbar_init(sm_addr(mbar + PF_P_FULL), kPfSoftWarps * 32);
         mbar_init(sm_addr(mbar + PF_AUX), 1);                 // the two rotations before and after the loop
@@ -423,9 +427,13 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
                     h[e] = *reinterpret_cast<const uint32_t*>(&hh);
                     l[e] = pack_half2(x0 - hf.x, x1 - hf.y);
                 }
-                // the query tile stays in tensor memory: lane = row, column j of a term = dims 2j, 2j + 1
-                tmem_st16(tlane + C::kQCol + c * 16, h);
-                tmem_st16(tlane + C::kQCol + 64 + c * 16, l);
+                // the query tile goes to shared memory in the swizzled K-major layout (A operand of the scores)
+#pragma unroll
+                for (int g8 = 0; g8 < 4; ++g8) {
+                    const uint32_t off = sw128_off(kPfRows, tid, c * 32 + g8 * 8);
+                    *reinterpret_cast<uint4*>(Qh + off) = make_uint4(h[4 * g8], h[4 * g8 + 1], h[4 * g8 + 2], h[4 * g8 + 3]);
+                    *reinterpret_cast<uint4*>(Ql + off) = make_uint4(l[4 * g8], l[4 * g8 + 1], l[4 * g8 + 2], l[4 * g8 + 3]);
+                }
             }
             if (!okq) { *abort_s = 1u; if (lane == 0) atomicOr(&g_prefill_error, 4u); }
         }
@@ -465,9 +473,11 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
         const uint32_t prow = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
         constexpr int HT = kPfTok / NSPLIT;                               // tokens per thread and tile
         const uint32_t dk_addr = sm_addr(dmaxK), dv_addr = sm_addr(dmaxV);
-        for (int i = 0; i < n_tiles && ok; ++i) {
-            const int sb = i & 1;
-            ok = mbar_wait(sm_addr(mbar + PF_S_FULL + sb), (i >> 1) & 1, abort_s) && ok;
+        int sk = 0;                                                       // score buffer of tile i: i mod 3
+        uint32_t sk_par = 0;                                              // phase parity of that buffer's barriers: (i / 3) & 1
+        for (int i = 0; i < n_tiles && ok; ++i, sk = (sk == 2 ? 0 : sk + 1), sk_par ^= (sk == 0 ? 1u : 0u)) {
+            const int sb = i & 1;                                         // K / V tile buffer and radii slot
+            ok = mbar_wait(sm_addr(mbar + PF_S_FULL + sk), sk_par, abort_s) && ok;
             ok = mbar_wait(sm_addr(mbar + PF_K_FULL + sb), (i >> 1) & 1, abort_s) && ok;   // dmaxK[sb] is visible
             tc_fence_after();
             float mx = -INFINITY;
@@ -476,10 +486,10 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
                 float sl[HT];                                            // the q_hi * k_lo part of the same scores
                 if (HT == 32) {
                     tmem_ld32x2(*reinterpret_cast<float(*)[32]>(&s[0]), *reinterpret_cast<float(*)[32]>(&sl[0]),
-                                tlane + sb * C::kSCols + hf * HT, tlane + sb * C::kSCols + kPfTok + hf * HT);
+                                tlane + sk * C::kSCols + hf * HT, tlane + sk * C::kSCols + kPfTok + hf * HT);
                 } else {
-                    tmem_ld16(*reinterpret_cast<float(*)[16]>(&s[0]), tlane + sb * C::kSCols + hf * HT);
-                    tmem_ld16(*reinterpret_cast<float(*)[16]>(&sl[0]), tlane + sb * C::kSCols + kPfTok + hf * HT);
+                    tmem_ld16(*reinterpret_cast<float(*)[16]>(&s[0]), tlane + sk * C::kSCols + hf * HT);
+                    tmem_ld16(*reinterpret_cast<float(*)[16]>(&sl[0]), tlane + sk * C::kSCols + kPfTok + hf * HT);
                 }
 #pragma unroll
                 for (int t = 0; t < HT; ++t) s[t] += sl[t];
@@ -507,14 +517,14 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
                 // barrier every thread of the row has its scores in registers: the S columns may be reused.
 #pragma unroll
                 for (int t = 0; t < HT; ++t) mx = fmaxf(mx, s[t]);
-                float* xm = reinterpret_cast<float*>(Qh) + sb * 4 * kPfRows;          // [parity][part][row]
+                float* xm = reinterpret_cast<float*>(Ph) + sb * 4 * kPfRows;          // [parity][part][row]
                 xm[hf * kPfRows + r] = mx;
                 asm volatile("bar.sync %0, %1;\n" ::"r"(1 + q), "r"(32 * NSPLIT) : "memory");
 #pragma unroll
                 for (int k = 0; k < NSPLIT; ++k) mx = fmaxf(mx, xm[k * kPfRows + r]);
             }
             tc_fence_before();
-            mbar_arrive(sm_addr(mbar + PF_S_FREE + sb));                // S buffer and dmaxK[sb] consumed
+            mbar_arrive(sm_addr(mbar + PF_S_FREE + sk));                // S buffer and dmaxK[sb] consumed
             m_run = fmaxf(m_run, mx);
             // Probabilities first (registers only), relative to the maximum this tile will use: that work
             // overlaps the previous tile's P V, which must be complete before P is rewritten or O rescaled.
@@ -564,11 +574,11 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             // hi term in columns [0, 32) of the buffer, lo term in [32, 64), two tokens per column.  The MMA
             // warp issues S(i + 2), which overwrites these columns, after P(i) V(i); the tensor core runs them in order.
             if (HT == 16) {
-                tmem_st8(tlane + sb * C::kSCols + hf * (HT / 2), *reinterpret_cast<const uint32_t(*)[8]>(&ph[0]));
-                tmem_st8(tlane + sb * C::kSCols + kPfTok / 2 + hf * (HT / 2), *reinterpret_cast<const uint32_t(*)[8]>(&pl[0]));
+                tmem_st8(tlane + sk * C::kSCols + hf * (HT / 2), *reinterpret_cast<const uint32_t(*)[8]>(&ph[0]));
+                tmem_st8(tlane + sk * C::kSCols + kPfTok / 2 + hf * (HT / 2), *reinterpret_cast<const uint32_t(*)[8]>(&pl[0]));
             } else {
-                tmem_st16(tlane + sb * C::kSCols + hf * (HT / 2), *reinterpret_cast<const uint32_t(*)[16]>(&ph[0]));
-                tmem_st16(tlane + sb * C::kSCols + kPfTok / 2 + hf * (HT / 2), *reinterpret_cast<const uint32_t(*)[16]>(&pl[0]));
+                tmem_st16(tlane + sk * C::kSCols + hf * (HT / 2), *reinterpret_cast<const uint32_t(*)[16]>(&ph[0]));
+                tmem_st16(tlane + sk * C::kSCols + kPfTok / 2 + hf * (HT / 2), *reinterpret_cast<const uint32_t(*)[16]>(&pl[0]));
             }
             tc_fence_before();
             l_run += sum;
@@ -579,7 +589,7 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             tc_fence_after();
         }
         // row sum over the row's threads (all kept relative to the same m_used), through the dead Ph tile
-        float* xchg = reinterpret_cast<float*>(Ph);
+        float* xchg = reinterpret_cast<float*>(Ph) + 8 * kPfRows;             // past the row-maximum slots
         xchg[hf * kPfRows + r] = l_run;
         asm volatile("bar.sync %0, %1;\n" ::"r"(1 + q), "r"(32 * NSPLIT) : "memory");
         l_run = 0.f;
@@ -594,9 +604,11 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
                 const int bb = i & 1;
                 const uint32_t par2 = (uint32_t)(((i >> 1) - 1) & 1);
                 const uint8_t* rec = rec0 + (size_t)i * C::kRec;
-                if (i >= 2) {
-                    ok = mbar_wait(sm_addr(mbar + PF_S_FULL + bb), par2, abort_s, 64) && ok;
-                    ok = mbar_wait(sm_addr(mbar + PF_S_FREE + bb), par2, abort_s, 64) && ok;
+                if (i >= 2) {        // tile i - 2 used this K buffer and radii slot; its scores sit in buffer (i - 2) mod 3
+                    const int k2 = (i - 2) % 3;
+                    const uint32_t p3 = (uint32_t)(((i - 2) / 3) & 1);
+                    ok = mbar_wait(sm_addr(mbar + PF_S_FULL + k2), p3, abort_s, 64) && ok;
+                    ok = mbar_wait(sm_addr(mbar + PF_S_FREE + k2), p3, abort_s, 64) && ok;
                 }
                 if (!ok) break;
                 if (lane == 0) {
@@ -645,9 +657,11 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             RawItems<D, KBITS>::issue(pk, k_row + tok1 * TBK, ntok1, it_tok, it_blk, it_qw);
             RawItems<D, VBITS>::issue(pv, v_row + tok1 * TBV, ntok1, it_tok, it_blk, it_qw);
             // K buffer bb: free once S(i-2) is complete; its dmaxK slot once the softmax of tile i-2 has read it
-            if (i >= 2) {
-                ok = mbar_wait(sm_addr(mbar + PF_S_FULL + bb), par2, abort_s) && ok;
-                ok = mbar_wait(sm_addr(mbar + PF_S_FREE + bb), par2, abort_s) && ok;
+            if (i >= 2) {            // tile i - 2 used this K buffer and radii slot; its scores sit in buffer (i - 2) mod 3
+                const int k2 = (i - 2) % 3;
+                const uint32_t p3 = (uint32_t)(((i - 2) / 3) & 1);
+                ok = mbar_wait(sm_addr(mbar + PF_S_FULL + k2), p3, abort_s) && ok;
+                ok = mbar_wait(sm_addr(mbar + PF_S_FREE + k2), p3, abort_s) && ok;
             }
             if (!ok) break;
             rk.expand(cbk_s, Kh + bb * 2 * C::KB, Kh + bb * 2 * C::KB + kPfTok * 128, dmaxK + bb * kPfTok,
@@ -677,30 +691,33 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
         // V: 64-dim atoms kPfTok*128 B apart (leading offset), 8-token groups 1024 B apart
         constexpr uint32_t v_lbo = ((kPfTok * 128u) >> 4) << 16;
         const uint32_t v_h0 = ((sm_addr(Vh) >> 4) & 0x3FFFu) | v_lbo;
+        const uint32_t q_h = ((sm_addr(Qh) >> 4) & 0x3FFFu) | (1u << 16), q_l = ((sm_addr(Ql) >> 4) & 0x3FFFu) | (1u << 16);
         auto issue_s = [&](int i) {
-            const int sb = i & 1;
-            ok = mbar_wait(sm_addr(mbar + PF_K_FULL + sb), (i >> 1) & 1, abort_s, 32) && ok;
-            if (i >= 2) {
-                // the buffer's scores have been read, and the P that replaced them has been consumed by P V
-                // (the value MMAs are issued by another warp, so that order has to be waited for)
-                ok = mbar_wait(sm_addr(mbar + PF_S_FREE + sb), ((i >> 1) - 1) & 1, abort_s, 32) && ok;
-                // (with one issuing warp the tensor core's in-order execution already gives that order)
-                if (PRE) ok = mbar_wait(sm_addr(mbar + PF_PV_DONE + sb), ((i >> 1) - 1) & 1, abort_s, 32) && ok;
+            const int sb = i & 1, sk = i % 3;                    // K tile buffer, score buffer
+            if (i >= 3) {
+                // score buffer sk: the scores of tile i - 3 have been read, and the P that replaced them has been
+                // consumed by P(i-3) V(i-3) (with one issuing warp the tensor core's in-order execution already
+                // gives that order; with two it has to be waited for)
+                const uint32_t p3 = (uint32_t)(((i - 3) / 3) & 1);
+                ok = mbar_wait(sm_addr(mbar + PF_S_FREE + sk), p3, abort_s, 32) && ok;
+                if (PRE) ok = mbar_wait(sm_addr(mbar + PF_P_USED + sk), p3, abort_s, 32) && ok;
             }
+            ok = mbar_wait(sm_addr(mbar + PF_K_FULL + sb), (i >> 1) & 1, abort_s, 32) && ok;
             if (!ok) return;
             tc_fence_after();
             {
                 // K tile: per 64-dim half 128 rows (64 hi tokens, then 64 lo).  q_hi against all 128 rows
                 // (one MMA, N = 128: columns [0, 64) hi products, [64, 128) lo products), q_lo against the hi rows.
-                const uint32_t acc = tmem_base + sb * C::kSCols;
+                const uint32_t acc = tmem_base + sk * C::kSCols;
                 const uint32_t k_b = k_h0 + (uint32_t)(sb * 2 * (C::KB >> 4));
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t qo = (uint32_t)(((ks >> 2) * (kPfRows * 128) + (ks & 3) * 32) >> 4);
                     const uint32_t ko = (uint32_t)(((ks >> 2) * (2 * kPfTok * 128) + (ks & 3) * 32) >> 4);
-                    umma_f16_ts_pred(acc, tmem_base + C::kQCol + ks * 8, k_b + ko, d_hi, idesc_s2, ks ? 1u : 0u, issue);
-                    umma_f16_ts_pred(acc, tmem_base + C::kQCol + 64 + ks * 8, k_b + ko, d_hi, idesc_s, 1u, issue);
+                    umma_f16_split_pred(acc, q_h + qo, d_hi, k_b + ko, d_hi, idesc_s2, ks ? 1u : 0u, issue);
+                    umma_f16_split_pred(acc, q_l + qo, d_hi, k_b + ko, d_hi, idesc_s, 1u, issue);
                 }
-                umma_commit_pred(sm_addr(mbar + PF_S_FULL + sb), issue);
+                umma_commit_pred(sm_addr(mbar + PF_S_FULL + sk), issue);
             }
             __syncwarp();
         };
@@ -723,12 +740,13 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
 #pragma unroll
                 for (int kt = 0; kt < kPfTok / 16; ++kt) {
                     const uint32_t vo = (uint32_t)((kt * 16 * 128) >> 4);
-                    const uint32_t p_h = tmem_base + sb * C::kSCols + kt * 8, p_l = p_h + kPfTok / 2;
+                    const uint32_t p_h = tmem_base + (i % 3) * C::kSCols + kt * 8, p_l = p_h + kPfTok / 2;
                     umma_f16_ts_pred(acc, p_h, v_h + vo, d_hi, idesc_pv, (i > 0 || kt > 0) ? 1u : 0u, issue);
                     umma_f16_ts_pred(acc, p_h, v_l + vo, d_hi, idesc_pv, 1u, issue);
                     umma_f16_ts_pred(acc, p_l, v_h + vo, d_hi, idesc_pv, 1u, issue);
                 }
                 umma_commit_pred(sm_addr(mbar + PF_PV_DONE + sb), issue);
+                if (PRE) umma_commit_pred(sm_addr(mbar + PF_P_USED + (i % 3)), issue);
             }
             __syncwarp();
         }
