@@ -90,7 +90,9 @@ int pq_compress(const void* x, int64_t n_vec, int head_dim, int n_bits,
  * the current device.  The tensor-core kernels wait for copies and MMAs through barriers with a time
  * limit (so that a lost completion can never hang the GPU); if a wait ever gives up a bit of
  * *flags_out is set and the output of that launch must be discarded: bit 0 compress (a wait gave
- * up), bit 1 compress (shared-memory window unusable), bit 2 prefill attention (a wait gave up).
+ * up), bit 1 compress (shared-memory window unusable), bit 2 prefill attention (a wait gave up),
+ * bit 3 decode attention (shared-memory window unusable, nothing computed), bit 4 decode attention (a
+ * wait for a tile copy gave up).
  * The flags are cleared by the call.  No counterpart in the reference (its kernels report nothing). */
 int pq_poll_device_errors(unsigned int* flags_out);
 

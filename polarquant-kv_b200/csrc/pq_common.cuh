@@ -71,5 +71,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 // Device error flags of the prefill kernel, read and cleared (defined in pq_prefill_attn.cu).
 int prefill_error_flags(unsigned int* flags);
+// Device error flags of the decode kernel, read and cleared (defined in pq_decode_attn.cu).
+int decode_error_flags(unsigned int* flags);
 
 }  // namespace pq

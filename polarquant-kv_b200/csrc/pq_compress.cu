@@ -678,7 +678,10 @@ extern "C" int pq_poll_device_errors(unsigned int* flags_out) {
     unsigned int pf = 0;
     const int st = pq::prefill_error_flags(&pf);
     if (st != PQ_OK) return st;
-    *flags_out = v | pf;
+    unsigned int df = 0;
+    const int sd = pq::decode_error_flags(&df);
+    if (sd != PQ_OK) return sd;
+    *flags_out = v | pf | (df << 3);
     return PQ_OK;
 }
 

@@ -31,17 +31,30 @@
 // memory and writes one (m, l, o) record per query head; the last segment of a row to
 // finish (atomic ticket, no spinning) merges the row's records, normalises, rotates back
 // and resets the ticket.
-#include "pq_common.cuh"
+#include <atomic>
+#include <cmath>
+#include <cstring>
+#include <mutex>
+
+#include "pq_tcgen05.cuh"
 
 namespace pq {
 
-constexpr int kDecWarps = 16;
-constexpr int kDecThreads = kDecWarps * 32;
 constexpr int kTileTok = 16;
-constexpr int kStages = 3;
 constexpr int kRecHeads = 8;        // head slots per record in the scratch buffer
-constexpr float kCbScale = 64.0f;   // centroids are stored x64 in the table (keeps lo terms normal)
+constexpr float kCbScale = 64.0f;   // key centroids are stored x64 in the table (keeps lo terms normal)
 constexpr int kTabBytes = 65536;    // 256 byte values x 256 B: K copies at +0, V copies at +128
+// float16 terms per VALUE centroid in the table.  1: the value centroids are scaled (host-side search,
+// value_table_scale) so that every one of them is a float16 number to about 3e-5 relative, which keeps
+// the output error near 5e-4 of the 2e-3 tolerance and halves the value-side lookups and MMAs;
+// 2: {hi, lo} pairs like the keys (float32-level accuracy).  One term fails the 2e-3 bar on short,
+// peaked sequences with large values (measured 2.9e-3), so two are used.
+constexpr int kVTerms = 2;
+
+// Device error flags of this file (read and cleared through pq_poll_device_errors):
+// bit 0: the shared-memory window started too high for the fixed-address table, nothing was computed;
+// bit 1: a bounded wait for a tile copy gave up.
+static __device__ unsigned int g_decode_error = 0;
 
 struct DecodeParams {
     const __half* q;           // [B, Hq, D]
@@ -61,6 +74,7 @@ struct DecodeParams {
     int jl_dim;
     int out_is_fp16;
     float scale_log2;          // softmax scale * log2(e)
+    float v_scale, v_inv;      // value centroids are stored x v_scale; v_inv = 1 / v_scale
     float cbk[16], cbv[16];
 };
 
@@ -78,11 +92,6 @@ __device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
     asm volatile("{ .reg .u16 t; ld.shared.u16 t, [%1]; cvt.u32.u16 %0, t; }\n" : "=r"(v) : "r"(a));
     return v;
 }
-__device__ __forceinline__ uint32_t lds_u8(uint32_t a) {
-    uint32_t v;
-    asm volatile("ld.shared.u8 %0, [%1];\n" : "=r"(v) : "r"(a));
-    return v;
-}
 __device__ __forceinline__ uint2 lds_v2(uint32_t a) {
     uint2 v;
     asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(a));
@@ -92,6 +101,9 @@ __device__ __forceinline__ uint4 lds_v4(uint32_t a) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
     return v;
+}
+__device__ __forceinline__ void sts_u32(uint32_t a, uint32_t v) {
+    asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(a), "r"(v) : "memory");
 }
 __device__ __forceinline__ float lds_half_as_float(uint32_t a) {
     float v;
@@ -106,88 +118,104 @@ template <int J>
 __device__ __forceinline__ uint32_t entry_addr(uint32_t w, uint32_t lane_const) {
     return __byte_perm(w, lane_const, 0x7604u | (J << 4));
 }
+// the same with the byte number held in a register: sel = byte_selector(j)
+__device__ __forceinline__ uint32_t byte_selector(int j) { return 0x7604u | ((uint32_t)j << 4); }
+__device__ __forceinline__ uint32_t entry_addr_sel(uint32_t w, uint32_t lane_const, uint32_t sel) {
+    return __byte_perm(w, lane_const, sel);
+}
 // 32 bits of packed indices at a shared address whose alignment class is known statically
 template <bool ALIGNED4>
 __device__ __forceinline__ uint32_t lds_word(uint32_t a) {
     if (ALIGNED4) return lds_u32(a);
-    return lds_u16(a) | (lds_u16(a + 2) << 16);
+    return __byte_perm(lds_u16(a), lds_u16(a + 2), 0x5410);
 }
 
 // ------------------------------------------------------------------ centroid tables
-// Row r (256 B) belongs to byte value r.  4-bit: entry = {half2(c[r&15], c[r>>4]) hi, same lo},
-// 8 bytes, 16 lane copies.  2-bit: entry = {hi(c[r&3], c[r>>2&3]), lo(same), hi(c[r>>4&3], c[r>>6]), lo(same)},
-// 16 bytes, 8 lane copies.  `half_off` is 0 for the K copies and 128 for the V copies.
-// `cs` holds the split centroids as bit patterns: cs[i] = hi16(64*c[i]) | lo16 << 16.
-template <int BITS>
-__device__ __forceinline__ void build_table(uint8_t* tab, int half_off, const uint32_t* cs, int tid) {
-    if (BITS == 4) {
-        for (int e = tid; e < 256 * 16; e += kDecThreads) {
+// Row r (256 B) belongs to byte value r; `half_off` is 0 for the K copies and 128 for the V copies;
+// `cs` holds the split centroids as bit patterns: cs[i] = hi16(scale*c[i]) | lo16 << 16.
+// TERMS == 2 (two float16 terms per centroid):
+//   4-bit: entry = {half2(c[r&15], c[r>>4]) hi, same lo}, 8 bytes, 16 lane copies;
+//   2-bit: entry = {hi(c[r&3], c[r>>2&3]), lo(same), hi(c[r>>4&3], c[r>>6]), lo(same)}, 16 bytes, 8 copies.
+// TERMS == 1 (hi terms only):
+//   4-bit: entry = half2(c[r&15], c[r>>4]), 4 bytes, 32 lane copies;
+//   2-bit: entry = {hi(c[r&3], c[r>>2&3]), hi(c[r>>4&3], c[r>>6])}, 8 bytes, 16 copies.
+template <int BITS, int TERMS>
+__device__ __forceinline__ void build_table(uint8_t* tab, int half_off, const uint32_t* cs, int tid, int nthreads) {
+    if (BITS == 4 && TERMS == 2) {
+        for (int e = tid; e < 256 * 16; e += nthreads) {
             const int b = e >> 4, copy = e & 15;
             const uint32_t c0 = cs[b & 15], c1 = cs[b >> 4];
             *reinterpret_cast<uint2*>(tab + b * 256 + half_off + copy * 8) =
                 make_uint2(__byte_perm(c0, c1, 0x5410), __byte_perm(c0, c1, 0x7632));
         }
-    } else {
-        for (int e = tid; e < 256 * 8; e += kDecThreads) {
+    } else if (BITS == 4) {
+        for (int e = tid; e < 256 * 32; e += nthreads) {
+            const int b = e >> 5, copy = e & 31;
+            *reinterpret_cast<uint32_t*>(tab + b * 256 + half_off + copy * 4) =
+                __byte_perm(cs[b & 15], cs[b >> 4], 0x5410);
+        }
+    } else if (TERMS == 2) {
+        for (int e = tid; e < 256 * 8; e += nthreads) {
             const int b = e >> 3, copy = e & 7;
             const uint32_t c0 = cs[b & 3], c1 = cs[(b >> 2) & 3], c2 = cs[(b >> 4) & 3], c3 = cs[b >> 6];
             *reinterpret_cast<uint4*>(tab + b * 256 + half_off + copy * 16) =
                 make_uint4(__byte_perm(c0, c1, 0x5410), __byte_perm(c0, c1, 0x7632),
                            __byte_perm(c2, c3, 0x5410), __byte_perm(c2, c3, 0x7632));
         }
+    } else {
+        for (int e = tid; e < 256 * 16; e += nthreads) {
+            const int b = e >> 4, copy = e & 15;
+            const uint32_t c0 = cs[b & 3], c1 = cs[(b >> 2) & 3], c2 = cs[(b >> 4) & 3], c3 = cs[b >> 6];
+            *reinterpret_cast<uint2*>(tab + b * 256 + half_off + copy * 8) =
+                make_uint2(__byte_perm(c0, c1, 0x5410), __byte_perm(c2, c3, 0x5410));
+        }
     }
 }
 
-// ------------------------------------------------------------------ tile staging
-// Copies `n` bytes (multiple of 4) from global `src` (4-byte aligned) to `dst_base +
-// (src & 15)`, so source and destination share their 16-byte phase; the middle goes as
-// 16-byte cp.async, the ragged ends as 4-byte ones.  The caller commits the group.
-__device__ __forceinline__ void stage_bytes(uint8_t* dst_base, const uint8_t* src, int n, int lane) {
-    const uint32_t phase = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(src)) & 15u;
-    uint8_t* dst = dst_base + phase;
-    if (phase == 0 && (n & 15) == 0) {                      // the common, fully aligned case
-        for (int c = lane; c < (n >> 4); c += 32) cp_async_16(dst + c * 16, src + c * 16);
-        return;
-    }
-    int head = phase ? (int)(16u - phase) : 0;
-    if (head > n) head = n;
-    const int mid = (n - head) & ~15;
-    const int tail = n - head - mid;
-    if (lane < (head >> 2)) {
-        uint32_t d = smem_addr(dst + lane * 4);
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src + lane * 4));
-    }
-    for (int c = lane; c < (mid >> 4); c += 32) cp_async_16(dst + head + c * 16, src + head + c * 16);
-    if (lane < (tail >> 2)) {
-        uint32_t d = smem_addr(dst + head + mid + lane * 4);
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src + head + mid + lane * 4));
-    }
+// ------------------------------------------------------------------ tile staging (slow path)
+// Rows whose byte streams are not 16-byte aligned, and the ragged last tile of a sequence, are
+// copied by the warp itself: `n` bytes from `src`, the rest of the `cap` bytes cleared (tokens past
+// the end must read as finite numbers: radius 0).  K/V tiles go as 4-byte words (block sizes are
+// multiples of 2 and tokens of 4 bytes), the sketch side band byte by byte.
+__device__ __forceinline__ void copy_words(uint8_t* dst, const uint8_t* src, int n, int cap, int lane) {
+    for (int c = lane; c < (cap >> 2); c += 32)
+        reinterpret_cast<uint32_t*>(dst)[c] = c < (n >> 2) ? __ldg(reinterpret_cast<const uint32_t*>(src) + c) : 0u;
+}
+__device__ __forceinline__ void copy_bytes(uint8_t* dst, const uint8_t* src, int n, int cap, int lane) {
+    for (int c = lane; c < cap; c += 32) dst[c] = c < n ? __ldg(src + c) : (uint8_t)0;
 }
 
 template <int D, int KBITS, int VBITS, int NH, bool QJL>
 struct DecodeCfg {
     static constexpr int NBLK = D / 32;
     static constexpr int HPC = 4 * NH;                            // query heads per CTA
+    // Warps per CTA and tile stages per warp.  The loop is bound by instruction latency, so with four
+    // query heads per KV head 20 warps of at most 102 registers replace 16 of 128.
+    static constexpr int NWARPS = (NH == 1 && !QJL) ? 20 : 16;
+    static constexpr int NTHREADS = NWARPS * 32;
+    static constexpr int kStages = 3;
     static constexpr int BBK = block_bytes(KBITS), BBV = block_bytes(VBITS);
     static constexpr int TBK = NBLK * BBK, TBV = NBLK * BBV;     // bytes per token
-    static constexpr int kStageK = kTileTok * TBK + 16;
-    static constexpr int kStageV = kTileTok * TBV + 16;
-    static constexpr int kStageN = 48;                            // 16 float16 norms + slack
+    static constexpr int kStageK = kTileTok * TBK;                // multiples of 64 bytes
+    static constexpr int kStageV = kTileTok * TBV;
+    static constexpr int kStageN = QJL ? 32 : 0;                  // 16 float16 norms
     static constexpr int kSignTab = QJL ? 16 * 16 * 8 : 0;
-    __host__ __device__ static int stage_bits(int jl_dim) { return QJL ? kTileTok * (jl_dim / 8) + 16 : 0; }
+    // head of a warp's ring: kStages mbarriers (32 bytes) + the tile's value radii, compacted
+    static constexpr int kRingHead = 32 + kTileTok * NBLK * 2;
+    __host__ __device__ static int stage_bits(int jl_dim) { return QJL ? kTileTok * (jl_dim / 8) : 0; }
     __host__ __device__ static int stage_bytes_total(int jl_dim) {
-        return kStageK + kStageV + (QJL ? stage_bits(jl_dim) + kStageN : 0);
+        return kStageK + kStageV + stage_bits(jl_dim) + kStageN;
     }
     __host__ __device__ static int qjl_frag_bytes(int jl_dim) { return QJL ? (jl_dim / 16) * 32 * 16 : 0; }
     // Shared-memory plan (byte addresses in the shared window):
     //   [base, 64K)        query buffers, split codebooks, the rings of the first n_low warps
     //   [64K, 128K)        centroid table (its address is baked into the lookups)
     //   [128K, ...)        sign table, JL query fragments, the rings of the remaining warps
-    // At the end of a work item every warp parks its (m, l, o) record in its own ring.
-    // a warp's ring also holds its (m, l, o) record at the end of an item
+    // A ring = head (see kRingHead) + kStages tile stages; at the end of a work item the warp parks
+    // its (m, l, o) record over the stages.
     __host__ __device__ static int ring_bytes(int jl_dim) {
         const int r = kStages * stage_bytes_total(jl_dim), rec = HPC * (D + 2) * 4;
-        return ((r > rec ? r : rec) + 15) & ~15;
+        return kRingHead + (((r > rec ? r : rec) + 15) & ~15);
     }
     __host__ __device__ static int low_fixed(int jl_dim) {
         return ((HPC * (3 * D + (QJL ? jl_dim : 0)) * 4 + 2 * 16 * 4) + 15) & ~15;
@@ -195,10 +223,10 @@ struct DecodeCfg {
     // rings that fit below the table when the dynamic window starts at or below 8 KB
     __host__ __device__ static int n_low(int jl_dim) {
         int n = (65536 - 8192 - low_fixed(jl_dim)) / ring_bytes(jl_dim);
-        return n > kDecWarps ? kDecWarps : n;
+        return n > NWARPS ? NWARPS : n;
     }
     __host__ __device__ static size_t smem_bytes(int jl_dim) {
-        size_t high = kSignTab + qjl_frag_bytes(jl_dim) + (size_t)(kDecWarps - n_low(jl_dim)) * ring_bytes(jl_dim);
+        size_t high = kSignTab + qjl_frag_bytes(jl_dim) + (size_t)(NWARPS - n_low(jl_dim)) * ring_bytes(jl_dim);
         return 2 * 65536 + high + 16;
     }
 };
@@ -209,11 +237,30 @@ __device__ __forceinline__ float term_of(float v, bool want_lo) {
     return want_lo ? v - hi : v;
 }
 
+__device__ __forceinline__ __half2 as_half2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
+__device__ __forceinline__ uint32_t as_u32(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+
+// Two float16 terms of (ph + pl) * d per half: hi = rn(ph*d), lo = rn(pl*d + (ph*d - hi)); the inner
+// difference is exact in float16 (error-free product), so hi + lo carries about 22 bits.
+__device__ __forceinline__ void weight_terms(uint32_t ph, uint32_t pl, uint32_t dd, uint32_t& bh, uint32_t& bl) {
+    const __half2 P = as_half2(ph), L = as_half2(pl), R = as_half2(dd);
+    const __half2 hi = __hmul2(P, R);
+    const __half2 err = __hfma2(P, R, __hneg2(hi));
+    bh = as_u32(hi);
+    bl = as_u32(__hfma2(L, R, err));
+}
+
 template <int D, int KBITS, int VBITS, int NH, bool QJL>
-__global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(DecodeCfg<D, KBITS, VBITS, NH, QJL>::NTHREADS, 1)
+pq_decode_attn_kernel(const DecodeParams p) {
     using C = DecodeCfg<D, KBITS, VBITS, NH, QJL>;
+    constexpr int NW = C::NWARPS;
+    constexpr int NT = C::NTHREADS;
+    constexpr int kStages = C::kStages;
     constexpr int NBLK = C::NBLK;
     constexpr int HPC = C::HPC;
+    constexpr int VT = kVTerms;
+    constexpr int VENT = (VBITS == 4 ? 4 : 8) * VT;                      // bytes per value-table entry
     extern __shared__ __align__(16) uint8_t smem[];
     float* q_in = reinterpret_cast<float*>(smem);                        // [HPC][D] (spare)
     float* q_rot = q_in + HPC * D;                                       // [HPC][D] rotated, scaled
@@ -234,22 +281,35 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
     const int M = QJL ? p.jl_dim : 0;
     const int stage_sz = C::stage_bytes_total(M);
     const int n_low = C::n_low(M);
-    if (smem_base + C::low_fixed(M) + n_low * C::ring_bytes(M) > kTabAddr) return;   // window starts too high
+    if (smem_base + C::low_fixed(M) + n_low * C::ring_bytes(M) > kTabAddr) {   // window starts too high
+        if (tid == 0) atomicOr(&g_decode_error, 1u);
+        return;
+    }
     auto ring_of = [&](int w) -> uint8_t* {
         return w < n_low ? low_ring + (size_t)w * C::ring_bytes(M) : high_ring + (size_t)(w - n_low) * C::ring_bytes(M);
     };
+    auto rec_of = [&](int w) -> float* { return reinterpret_cast<float*>(ring_of(w) + C::kRingHead); };
     uint8_t* my_ring = ring_of(warp);
+    uint8_t* my_stages = my_ring + C::kRingHead;
+    const uint32_t ring_addr = smem_addr(my_ring);
+    const uint32_t mbar0 = ring_addr;                                    // kStages mbarriers, 8 bytes each
+    const uint32_t vrad_addr = ring_addr + 32;                           // [16 tokens][NBLK] float16 radii
+    const uint32_t stage_addr0 = ring_addr + C::kRingHead;
 
     // ---- once per CTA: the lookup tables (the CTA is persistent and walks over work items)
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) mbar_init(mbar0 + 8 * s, 1);
+    }
     if (tid < 32) {
-        const float c = (tid < 16 ? p.cbk[tid] : p.cbv[tid - 16]) * kCbScale;
+        const float c = tid < 16 ? p.cbk[tid] * kCbScale : p.cbv[tid - 16] * p.v_scale;
         __half h, l;
         split_half(c, h, l);
         cs_k[tid] = (uint32_t)__half_as_ushort(h) | ((uint32_t)__half_as_ushort(l) << 16);   // cs_v = cs_k + 16
     }
     if (QJL) {
         // sign table: nibble -> 4 halves of +-1; entry 8 bytes, 16 lane copies
-        for (int e = tid; e < 16 * 16; e += kDecThreads) {
+        for (int e = tid; e < 16 * 16; e += NT) {
             const int nib = e >> 4;
             __half2 a = __floats2half2_rn((nib & 1) ? 1.f : -1.f, (nib & 2) ? 1.f : -1.f);
             __half2 c = __floats2half2_rn((nib & 4) ? 1.f : -1.f, (nib & 8) ? 1.f : -1.f);
@@ -258,15 +318,35 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
         }
     }
     __syncthreads();
-    build_table<KBITS>(tab, 0, cs_k, tid);
-    build_table<VBITS>(tab, 128, cs_v, tid);
+    build_table<KBITS, 2>(tab, 0, cs_k, tid, NT);
+    build_table<VBITS, VT>(tab, 128, cs_v, tid, NT);
     // this lane's private table copies (shared-memory byte addresses)
     const uint32_t kconst = kTabAddr | (KBITS == 4 ? (lane & 15) * 8 : (lane & 7) * 16);
-    const uint32_t vconst = kTabAddr | (128 + (VBITS == 4 ? (lane & 15) * 8 : (lane & 7) * 16));
+    const uint32_t vconst = kTabAddr | (128 + (lane % (128 / VENT)) * VENT);
     const uint32_t sign_lane = smem_addr(signtab) + (lane & 15) * 8;
     const uint32_t qjl_frag_lane = smem_addr(qjl_frag) + lane * 16;
-    const uint32_t ring_addr = smem_addr(my_ring);
     const int64_t tiles_total = (p.S + kTileTok - 1) / kTileTok;
+
+    // ---- value side: which bytes of a stored block this lane feeds into the MMAs.  Lane group g owns
+    // the dims 4g .. 4g+3 of every 32-dim block: two packed bytes (4-bit) or one (2-bit).  The packed
+    // bytes of a block start 2 bytes after the block, so they are 4-byte aligned in every second block
+    // ("aligned" class) and 2 bytes off in the others ("shifted" class); in both classes the lane's
+    // bytes lie inside ONE aligned 32-bit word, at a per-lane offset and byte position.
+    uint32_t voff_al, voff_sh, vselA_al, vselA_sh;
+    if (VBITS == 4) {
+        voff_al = 2 + 4 * (g >> 1);
+        voff_sh = 4 * ((g + 1) >> 1);
+        vselA_al = byte_selector(2 * (g & 1));
+        vselA_sh = byte_selector((g & 1) ? 0 : 2);
+    } else {
+        voff_al = 2 + 4 * (g >> 2);
+        voff_sh = 4 * ((g + 2) >> 2);
+        vselA_al = byte_selector(g & 3);
+        vselA_sh = byte_selector((g + 2) & 3);
+    }
+    const uint32_t pshift = (g & 1) ? 16u : 0u;       // odd MMA columns carry the odd dim of a pair
+    uint32_t phase = 0;                               // expected parity of each stage's mbarrier
+    bool dead = false;                                // a copy wait gave up: finish without waiting again
 
     // ---- work distribution.  A "virtual row" is one (batch, kv head, head group); its tiles
     // are numbered 0..tiles_total-1.  Balanced mode (p.splits == 0): the tiles of all virtual
@@ -311,56 +391,47 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
     const uint8_t* bits_row = QJL ? p.qjl_bits + (size_t)row * p.Scap * (M / 8) : nullptr;
     const uint8_t* norm_row = QJL ? reinterpret_cast<const uint8_t*>(p.qjl_norms + (size_t)row * p.Scap) : nullptr;
 
-    // Rows whose byte streams start on a 16-byte boundary take the short path: every full
-    // tile is copied as whole 16-byte chunks at fixed per-lane offsets.
-    const bool k_al = ((reinterpret_cast<uintptr_t>(k_row) & 15) == 0), v_al = ((reinterpret_cast<uintptr_t>(v_row) & 15) == 0);
-    auto issue_tile = [&](int64_t tile, int slot) {
-        if (tile < tile_end) {
-            const int64_t tok0 = tile * kTileTok;
-            const int ntok = (int)min((int64_t)kTileTok, p.S - tok0);
-            uint8_t* st = my_ring + slot * stage_sz;
-            if (ntok == kTileTok && k_al && v_al) {
-                const uint8_t* ks = k_row + tok0 * C::TBK + lane * 16;
-                const uint8_t* vs = v_row + tok0 * C::TBV + lane * 16;
-                uint8_t* kd = st + lane * 16;
-                uint8_t* vd = st + C::kStageK + lane * 16;
-#pragma unroll
-                for (int c = 0; c < (C::TBK + 31) / 32; ++c)
-                    if (c * 32 + 32 <= C::TBK || lane + c * 32 < C::TBK) cp_async_16(kd + c * 512, ks + c * 512);
-#pragma unroll
-                for (int c = 0; c < (C::TBV + 31) / 32; ++c)
-                    if (c * 32 + 32 <= C::TBV || lane + c * 32 < C::TBV) cp_async_16(vd + c * 512, vs + c * 512);
-            } else {
-                const uint8_t* ksrc = k_row + tok0 * C::TBK;
-                const uint8_t* vsrc = v_row + tok0 * C::TBV;
-                if (ntok < kTileTok) {
-                    // tokens past the end must read as finite numbers (radius 0): clear their bytes
-                    uint8_t* kz = st + (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(ksrc)) & 15u) + ntok * C::TBK;
-                    uint8_t* vz = st + C::kStageK + (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(vsrc)) & 15u) + ntok * C::TBV;
-                    for (int c = lane; c < (kTileTok - ntok) * C::TBK / 4; c += 32) reinterpret_cast<uint32_t*>(kz)[c] = 0u;
-                    for (int c = lane; c < (kTileTok - ntok) * C::TBV / 4; c += 32) reinterpret_cast<uint32_t*>(vz)[c] = 0u;
+    // Full tiles of rows whose byte streams start on a 16-byte boundary arrive by bulk copy (one lane
+    // issues, the stage's mbarrier counts the bytes); everything else is copied by the warp itself.
+    const bool bulk_row = ((reinterpret_cast<uintptr_t>(k_row) | reinterpret_cast<uintptr_t>(v_row) |
+                            (QJL ? reinterpret_cast<uintptr_t>(bits_row) | reinterpret_cast<uintptr_t>(norm_row) : 0)) & 15) == 0;
+    // Tile numbers inside a row fit 32 bits (the host rejects longer sequences).
+    const int t_first = (int)tile_begin + warp, t_end = (int)tile_end;
+    const int full_tiles = (int)(p.S / kTileTok);                  // tiles below this number hold 16 tokens
+    auto issue_tile = [&](int tile, int slot) {
+        if (tile >= t_end) return;
+        const size_t tok0 = (size_t)tile * kTileTok;
+        if (bulk_row && tile < full_tiles) {
+            if (lane == 0) {
+                const uint32_t sa = stage_addr0 + slot * stage_sz, mb = mbar0 + 8 * slot;
+                mbar_expect_tx(mb, (uint32_t)stage_sz);
+                bulk_load(sa, k_row + tok0 * C::TBK, C::kStageK, mb);
+                bulk_load(sa + C::kStageK, v_row + tok0 * C::TBV, C::kStageV, mb);
+                if (QJL) {
+                    bulk_load(sa + C::kStageK + C::kStageV, bits_row + tok0 * (M / 8), C::stage_bits(M), mb);
+                    bulk_load(sa + C::kStageK + C::kStageV + C::stage_bits(M), norm_row + tok0 * 2, C::kStageN, mb);
                 }
-                stage_bytes(st, ksrc, ntok * C::TBK, lane);
-                stage_bytes(st + C::kStageK, vsrc, ntok * C::TBV, lane);
             }
+        } else {
+            const int ntok = tile < full_tiles ? kTileTok : (int)(p.S - (int64_t)tok0);
+            uint8_t* st = my_stages + slot * stage_sz;
+            copy_words(st, k_row + tok0 * C::TBK, ntok * C::TBK, C::kStageK, lane);
+            copy_words(st + C::kStageK, v_row + tok0 * C::TBV, ntok * C::TBV, C::kStageV, lane);
             if (QJL) {
-                stage_bytes(st + C::kStageK + C::kStageV, bits_row + tok0 * (M / 8),
-                            (ntok * (M / 8) + 3) & ~3, lane);
-                stage_bytes(st + C::kStageK + C::kStageV + C::stage_bits(M), norm_row + tok0 * 2,
-                            (ntok * 2 + 3) & ~3, lane);
+                copy_bytes(st + C::kStageK + C::kStageV, bits_row + tok0 * (M / 8), ntok * (M / 8), C::stage_bits(M), lane);
+                copy_bytes(st + C::kStageK + C::kStageV + C::stage_bits(M), norm_row + tok0 * 2, ntok * 2, C::kStageN, lane);
             }
         }
-        cp_async_commit();
     };
     // first tiles in flight before the prologue math
-    issue_tile(tile_begin + warp, 0);
-    issue_tile(tile_begin + warp + kDecWarps, 1);
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) issue_tile(t_first + s * NW, s);
 
     // ---- per item: query rotation (and JL projection of the query)
     // q_rot[h][i] = sum_j q[h][j] * R[i][j] (and the JL projection P q) on tensor cores: rows =
     // heads (the float16 query is exact), columns = 8 outputs per warp-step, R split into two
     // float16 terms of 4096*R on the fly.  Matrix rows are read as 32-byte pieces by 4 lanes.
-    for (int nt = warp; nt < (D + M) / 8; nt += kDecWarps) {
+    for (int nt = warp; nt < (D + M) / 8; nt += NW) {
         const int i = nt * 8 + g;                                        // this lane's output column
         const float* mrow = i < D ? p.rot + (size_t)i * D : p.jl + (size_t)(i - D) * D;
         const __half* qrow = p.q + ((size_t)b * p.Hq + head0 + g) * D;   // row g = head g (if it exists)
@@ -395,12 +466,13 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
 
     // ---- B fragments of the query.  MMA column n = lane group g.
     //   NH == 1: column g is head g>>1, term hi (g even) or lo (g odd);
-    //   NH == 2: column g is head g; a hi tile and a lo tile.
+    //   NH == 2: column g is head (g>>1) + 4*(g&1); a hi tile and a lo tile.  (Accumulator columns
+    //            2t, 2t+1 of a lane are then heads t and t+4.)
     // k-slot mapping inside a 32-dim block, k-step ks: slots (2t,2t+1) <-> dims 8t+4ks+(0,1),
     // slots (2t+8,2t+9) <-> dims 8t+4ks+(2,3): the 8 nibbles of the 32-bit word lane t reads.
     uint32_t qb[NBLK][2][2 * NH];
     {
-        const int hq = NH == 1 ? (g >> 1) : g;
+        const int hq = NH == 1 ? (g >> 1) : (g >> 1) + 4 * (g & 1);
         const bool lo1 = (g & 1) != 0;
 #pragma unroll
         for (int blk = 0; blk < NBLK; ++blk)
@@ -419,7 +491,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
             }
         if (QJL) {
             // fragments of the projected query, one uint4 per (k-step, lane): {b0, b1 | lo b0, lo b1}
-            for (int ks = warp; ks < M / 16; ks += kDecWarps) {
+            for (int ks = warp; ks < M / 16; ks += NW) {
                 const float* src = q_jl + hq * M + ks * 16 + 4 * t;
                 uint4 f;
                 if (NH == 1) {
@@ -438,47 +510,68 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
     }
     __syncthreads();
 
-    // ---- running softmax state.  A lane holds scores of NH heads (NH == 1: head t;
-    // NH == 2: heads 2t, 2t+1) for tokens g and g+8 of the tile.
+    // ---- running softmax state.  A lane holds the scores of its head(s) (NH == 1: head t;
+    // NH == 2: heads t and t+4) for tokens 2g and 2g+1 of the tile.
     float m_run[NH], l_run[NH];
 #pragma unroll
     for (int h = 0; h < NH; ++h) { m_run[h] = -INFINITY; l_run[h] = 0.f; }
-    // output accumulators: o_main[block][j][h] = dim 32*block + 4g + j of head (NH == 1: t; else 2t + h)
-    float o_main[NBLK][4][NH];
+    // output accumulators (MMA C fragments, kept across tiles).  VACC == 1: acc[blk][0][h][j] is dim
+    // 32*blk + 4g + j of head t + 4h.  VACC == 2 (two-term value table, four heads): acc[blk][f][h][0..1]
+    // are the hi-term sums of dims 32*blk + 4g + 2f + (0, 1) and [2..3] their lo-term sums: rows g / g+8
+    // of an MMA are the hi / lo term of one stored byte, so a table entry is an A register pair as loaded.
+    // With eight heads that would be 64 accumulators; there the hi terms of the lane's two bytes share
+    // one MMA and their lo terms another (a few register moves instead).
+    constexpr int VACC = (VT == 2 && NH == 1) ? 2 : 1;
+    float acc[NBLK][VACC][NH][4];
 #pragma unroll
     for (int blk = 0; blk < NBLK; ++blk)
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int f = 0; f < VACC; ++f)
 #pragma unroll
-            for (int h = 0; h < NH; ++h) o_main[blk][j][h] = 0.f;
+            for (int h = 0; h < NH; ++h)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[blk][f][h][j] = 0.f;
 
     int slot = 0;
-    for (int64_t tile = tile_begin + warp; tile < tile_end; tile += kDecWarps) {
-        issue_tile(tile + 2 * kDecWarps, slot >= 1 ? slot - 1 : kStages - 1);
-        cp_async_wait<2>();
+    for (int tile = t_first; tile < t_end; tile += NW) {
+        issue_tile(tile + (kStages - 1) * NW, slot >= 1 ? slot - 1 : kStages - 1);
+        const bool full = tile < full_tiles;
+        if (bulk_row && full) {
+            if (!dead && !mbar_wait(mbar0 + 8 * slot, (phase >> slot) & 1u)) {
+                dead = true;
+                atomicOr(&g_decode_error, 2u);
+            }
+            phase ^= 1u << slot;
+        }
         __syncwarp();
-        const int64_t tok0 = tile * kTileTok;
-        const int ntok = (int)min((int64_t)kTileTok, p.S - tok0);
-        const uint32_t st = ring_addr + slot * stage_sz;
-        const uint32_t ks_base = st + (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(k_row + tok0 * C::TBK)) & 15u);
-        const uint32_t vs_base = st + C::kStageK +
-                                 (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(v_row + tok0 * C::TBV)) & 15u);
+        const uint32_t ks_base = stage_addr0 + slot * stage_sz;
+        const uint32_t vs_base = ks_base + C::kStageK;
+
+        // value radii of the tile -> [token][block] float16, so that a lane later fetches the radii of
+        // its four tokens with one or two 16-byte loads
+        if (NBLK == 4 || lane < 16) {
+            const int tok = NBLK == 4 ? (lane >> 1) : lane;
+            const int b0 = NBLK == 4 ? 2 * (lane & 1) : 0;
+            const uint32_t a = vs_base + tok * C::TBV + b0 * C::BBV;
+            sts_u32(vrad_addr + lane * 4, __byte_perm(lds_u16(a), lds_u16(a + C::BBV), 0x5410));
+        }
 
         // ================= scores.  One MMA covers 8 tokens: row g carries the hi term of token
-        // grp*8+g and row g+8 its lo term, so one 64-bit table entry {hi, lo} fills the register
-        // pair (a0, a1) or (a2, a3) as loaded.  Columns = query heads.
+        // 2g+grp and row g+8 its lo term, so one 64-bit table entry {hi, lo} fills the register
+        // pair (a0, a1) or (a2, a3) as loaded.  Columns = query heads.  (Even and odd tokens form the
+        // two groups because 8 tokens that are two apart start in 8 different bank quads.)
         float sc[NH][2];                                            // [head][token group]
 #pragma unroll
         for (int h = 0; h < NH; ++h) { sc[h][0] = 0.f; sc[h][1] = 0.f; }
 #pragma unroll
         for (int grp = 0; grp < 2; ++grp) {
-            const uint32_t tok = ks_base + (grp * 8 + g) * C::TBK;
+            const uint32_t tok = ks_base + (2 * g + grp) * C::TBK;
 #pragma unroll
             for (int blk = 0; blk < NBLK; ++blk) {
                 float c[4] = {0.f, 0.f, 0.f, 0.f};
                 if (KBITS == 4) {
                     const uint32_t off = blk * C::BBK + 2 + 4 * t;
-                    const bool al4 = ((blk * C::BBK + 2) & 3) == 0; // tile base and token stride are 4-aligned
+                    const bool al4 = ((blk * C::BBK + 2) & 3) == 0; // stage base and token stride are 4-aligned
                     const uint32_t w = al4 ? lds_word<true>(tok + off) : lds_word<false>(tok + off);
                     const uint2 e0 = lds_v2(entry_addr<0>(w, kconst)), e1 = lds_v2(entry_addr<1>(w, kconst));
                     const uint2 e2 = lds_v2(entry_addr<2>(w, kconst)), e3 = lds_v2(entry_addr<3>(w, kconst));
@@ -502,7 +595,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
                 const float d = lds_half_as_float(tok + blk * C::BBK);
                 if (NH == 1) {      // columns = hi and lo term of head t
                     sc[0][grp] = fmaf(d, (c[0] + c[1]) + (c[2] + c[3]), sc[0][grp]);
-                } else {            // columns = heads 2t, 2t+1
+                } else {            // columns = heads t, t+4
                     sc[0][grp] = fmaf(d, c[0] + c[2], sc[0][grp]);
                     sc[NH - 1][grp] = fmaf(d, c[1] + c[3], sc[NH - 1][grp]);
                 }
@@ -512,13 +605,12 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
         for (int h = 0; h < NH; ++h) { sc[h][0] *= (1.0f / kCbScale); sc[h][1] *= (1.0f / kCbScale); }
 
         if (QJL) {
-            // corr[token][head] = sum_i (+-1) * qp[head][i] (qp already scaled by scale*log2e/M)
-            const uint32_t bs_base = st + C::kStageK + C::kStageV +
-                                     (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(bits_row + tok0 * (M / 8))) & 15u);
-            const uint32_t ns_base = st + C::kStageK + C::kStageV + C::stage_bits(M) +
-                                     (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(norm_row + tok0 * 2)) & 15u);
+            // corr[token][head] = sum_i (+-1) * qp[head][i] (qp already scaled by scale*log2e/M);
+            // rows g = token 2g, rows g+8 = token 2g+1
+            const uint32_t bs_base = vs_base + C::kStageV;
+            const uint32_t ns_base = bs_base + C::stage_bits(M);
             float c[4] = {0.f, 0.f, 0.f, 0.f};
-            const uint32_t ta = bs_base + g * (M / 8), tb = ta + 8 * (M / 8);
+            const uint32_t ta = bs_base + (2 * g) * (M / 8), tb = ta + (M / 8);
             for (int ks = 0; ks < M / 16; ++ks) {
                 const uint32_t ha = lds_u16(ta + 2 * ks), hb = lds_u16(tb + 2 * ks);
                 const uint2 ea = lds_v2(sign_lane + (((ha >> (4 * t)) & 0xFu) << 7));
@@ -528,8 +620,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
                 if (NH == 2) mma_16816(c, ea.x, eb.x, ea.y, eb.y, f.z, f.w);
             }
             // a zero residual norm switches the correction off (qjl.py:49-50)
-            const bool on0 = lds_u16(ns_base + 2 * g) != 0u;
-            const bool on1 = lds_u16(ns_base + 2 * (g + 8)) != 0u;
+            const bool on0 = lds_u16(ns_base + 2 * (2 * g)) != 0u;
+            const bool on1 = lds_u16(ns_base + 2 * (2 * g + 1)) != 0u;
             if (NH == 1) {
                 if (on0) sc[0][0] += c[0] + c[1];
                 if (on1) sc[0][1] += c[2] + c[3];
@@ -539,14 +631,14 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
             }
         }
 
-        // mask tokens past the end of the sequence
-        if (g >= ntok) {
+        // mask tokens past the end of the sequence (only the ragged last tile of a row has any)
+        if (!full) {
+            const int ntok = (int)(p.S - (int64_t)tile * kTileTok);
 #pragma unroll
-            for (int h = 0; h < NH; ++h) sc[h][0] = -INFINITY;
-        }
-        if (g + 8 >= ntok) {
-#pragma unroll
-            for (int h = 0; h < NH; ++h) sc[h][1] = -INFINITY;
+            for (int h = 0; h < NH; ++h) {
+                if (2 * g >= ntok) sc[h][0] = -INFINITY;
+                if (2 * g + 1 >= ntok) sc[h][1] = -INFINITY;
+            }
         }
 
         // ================= online softmax over the 16 tokens of the tile (lanes with equal t)
@@ -571,111 +663,122 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
 #pragma unroll
             for (int blk = 0; blk < NBLK; ++blk)
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int f = 0; f < VACC; ++f)
 #pragma unroll
-                    for (int h = 0; h < NH; ++h) o_main[blk][j][h] *= alpha[h];
+                    for (int h = 0; h < NH; ++h)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) acc[blk][f][h][j] *= alpha[h];
         }
 
-        // ================= values: O[dim][column] += V^T[dim][token] * (p*d)[token][column]
-        // B column g needs p of its head for tokens (2t, 2t+1 | 8+2t, 9+2t); the lane that
-        // holds p[head h][token tau] is (tau % 8) * 4 + (NH == 1 ? h : h >> 1).
-        float pv[4];
-        {
-            const int hsel = NH == 1 ? (g >> 1) : (g >> 1);
-            const int la = (2 * t) * 4 + hsel, lb = (2 * t + 1) * 4 + hsel;
-            float x0 = __shfl_sync(0xffffffffu, pr[0][0], la), x1 = __shfl_sync(0xffffffffu, pr[0][0], lb);
-            float x2 = __shfl_sync(0xffffffffu, pr[0][1], la), x3 = __shfl_sync(0xffffffffu, pr[0][1], lb);
-            if (NH == 2) {
-                const float y0 = __shfl_sync(0xffffffffu, pr[NH - 1][0], la), y1 = __shfl_sync(0xffffffffu, pr[NH - 1][0], lb);
-                const float y2 = __shfl_sync(0xffffffffu, pr[NH - 1][1], la), y3 = __shfl_sync(0xffffffffu, pr[NH - 1][1], lb);
-                if (g & 1) { x0 = y0; x1 = y1; x2 = y2; x3 = y3; }
-            }
-            pv[0] = x0; pv[1] = x1; pv[2] = x2; pv[3] = x3;   // masked tokens: p == 0 and radius == 0
-        }
-        const float lo_col = (NH == 1 && (g & 1)) ? 1.f : 0.f;     // odd columns carry the lo term
-        const uint32_t vtok = vs_base + (2 * t) * C::TBV;            // tokens 2t, 2t+1, 2t+8, 2t+9
+        // ================= values: O[dim][head] += sum_tokens centroid[token][dim] * (p * radius)[token][head]
+        // One MMA has a dim PAIR per row, k slots (2t, 2t+1) = the even and the odd dim of the pair for
+        // token 4t+2u, slots (2t+8, 2t+9) the same for token 4t+2u+1; a table entry, which holds the two
+        // dims of a stored byte side by side, is therefore an A register as loaded.  The B column n = g
+        // carries head g>>1 and dim parity g&1: the weight sits in the low half (even dim) or the high
+        // half (odd dim) and the other half is zero, which splits the pair into two accumulator columns.
+        // Weights: p split into two float16 terms once per tile; times the float16 block radius with an
+        // error-free product, again two terms, issued as two MMAs.
+        __syncwarp();                                               // the compacted radii are in place
+        const uint32_t vb_al = vs_base + (4 * t) * C::TBV + voff_al;
+        const uint32_t vb_sh = vs_base + (4 * t) * C::TBV + voff_sh;
 #pragma unroll
-        for (int blk = 0; blk < NBLK; ++blk) {
-            float w[4];
+        for (int u = 0; u < 2; ++u) {
+            // weights of tokens 4t+2u, 4t+2u+1 for head (g>>1) + 4h, two float16 terms each:
+            // p[token 4t+k][head] lives in lane (g' = (4t+k)>>1, t' = g>>1), register pr[h][k&1]
+            uint32_t PH[NH][2], PL[NH][2];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const uint32_t a = vtok + ((k >> 1) * 8 + (k & 1)) * C::TBV + blk * C::BBV;
-                w[k] = pv[k] * lds_half_as_float(a);
-            }
-            uint32_t bh0, bh1, bl0 = 0u, bl1 = 0u;
-            if (NH == 1) {
-                // even column: w itself (rounded to its hi term by the pack); odd column: w - hi
-                const float2 h01 = __half22float2(__floats2half2_rn(w[0], w[1]));
-                const float2 h23 = __half22float2(__floats2half2_rn(w[2], w[3]));
-                bh0 = pack_half2(fmaf(-lo_col, h01.x, w[0]), fmaf(-lo_col, h01.y, w[1]));
-                bh1 = pack_half2(fmaf(-lo_col, h23.x, w[2]), fmaf(-lo_col, h23.y, w[3]));
-            } else {
-                bh0 = pack_half2(w[0], w[1]);
-                bh1 = pack_half2(w[2], w[3]);
-                bl0 = pack_half2(term_of(w[0], true), term_of(w[1], true));
-                bl1 = pack_half2(term_of(w[2], true), term_of(w[3], true));
-            }
-            float o_tmp[4][4];
+            for (int h = 0; h < NH; ++h)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) { o_tmp[j][0] = 0.f; o_tmp[j][1] = 0.f; o_tmp[j][2] = 0.f; o_tmp[j][3] = 0.f; }
-            // One MMA per dim j of this lane's 4 dims: row g carries the hi term of dim 4g+j,
-            // row g+8 its lo term; k slots = tokens (2t, 2t+1 | 8+2t, 9+2t).  A table entry
-            // {hi, lo} of a (token a, token b) nibble pair fills (a0, a1) / (a2, a3) as loaded.
-            if (VBITS == 4) {
-                uint32_t m1[2], m2[2];
-#pragma unroll
-                for (int pair = 0; pair < 2; ++pair) {
-                    const uint32_t pa = vtok + pair * 8 * C::TBV + blk * C::BBV + 2;
-                    const uint32_t ha = lds_u16(pa + 2 * g), hb = lds_u16(pa + C::TBV + 2 * g);
-                    // byte k of m1: dims 0 / 2, of m2: dims 1 / 3; low nibble token a, high nibble token b
-                    m1[pair] = (ha & 0x0F0Fu) | ((hb << 4) & 0xF0F0u);
-                    m2[pair] = ((ha >> 4) & 0x0F0Fu) | (hb & 0xF0F0u);
+                for (int k = 0; k < 2; ++k) {
+                    const float x = __shfl_sync(0xffffffffu, pr[h][k], ((2 * t + u) << 2) | (g >> 1));
+                    const __half hh = __float2half_rn(x);
+                    const __half hl = __float2half_rn(x - __half2float(hh));
+                    PH[h][k] = (uint32_t)__half_as_ushort(hh) << pshift;
+                    PL[h][k] = (uint32_t)__half_as_ushort(hl) << pshift;
                 }
+            // radii of the two tokens: NBLK/2 words each, two float16 per word
+            uint32_t rw[2][NBLK / 2];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t s0 = (j & 1) ? m2[0] : m1[0], s1 = (j & 1) ? m2[1] : m1[1];
-                    const uint2 e0 = (j >> 1) ? lds_v2(entry_addr<1>(s0, vconst)) : lds_v2(entry_addr<0>(s0, vconst));
-                    const uint2 e1 = (j >> 1) ? lds_v2(entry_addr<1>(s1, vconst)) : lds_v2(entry_addr<0>(s1, vconst));
-                    mma_16816(o_tmp[j], e0.x, e0.y, e1.x, e1.y, bh0, bh1);
-                    if (NH == 2) mma_16816(o_tmp[j], e0.x, e0.y, e1.x, e1.y, bl0, bl1);
-                }
-            } else {
-                uint4 e[2][2];      // [pair][dims 0,1 | dims 2,3] = {hi d, lo d, hi d+1, lo d+1}
-#pragma unroll
-                for (int pair = 0; pair < 2; ++pair) {
-                    const uint32_t pa = vtok + pair * 8 * C::TBV + blk * C::BBV + 2;
-                    const uint32_t ba = lds_u8(pa + g), bb = lds_u8(pa + C::TBV + g);
-                    const uint32_t m1 = (ba & 3u) | ((bb & 3u) << 2) | ((ba & 0xCu) << 2) | ((bb & 0xCu) << 4);
-                    const uint32_t ua = ba >> 4, ub = bb >> 4;
-                    const uint32_t m2 = (ua & 3u) | ((ub & 3u) << 2) | ((ua & 0xCu) << 2) | ((ub & 0xCu) << 4);
-                    e[pair][0] = lds_v4(entry_addr<0>(m1, vconst));
-                    e[pair][1] = lds_v4(entry_addr<0>(m2, vconst));
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint4 x = e[0][j >> 1], y = e[1][j >> 1];
-                    const uint32_t a0 = (j & 1) ? x.z : x.x, a1 = (j & 1) ? x.w : x.y;
-                    const uint32_t a2 = (j & 1) ? y.z : y.x, a3 = (j & 1) ? y.w : y.y;
-                    mma_16816(o_tmp[j], a0, a1, a2, a3, bh0, bh1);
-                    if (NH == 2) mma_16816(o_tmp[j], a0, a1, a2, a3, bl0, bl1);
-                }
-            }
-            // fold: rows g / g+8 are the hi / lo term of the dim; columns 2t, 2t+1 are the hi / lo
-            // term of head t's weights (NH == 1) or heads 2t, 2t+1 (NH == 2)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (NH == 1) {
-                    o_main[blk][j][0] += (o_tmp[j][0] + o_tmp[j][1]) + (o_tmp[j][2] + o_tmp[j][3]);
+            for (int k = 0; k < 2; ++k) {
+                const uint32_t a = vrad_addr + (4 * t + 2 * u + k) * (2 * NBLK);
+                if (NBLK == 4) {
+                    const uint2 v = lds_v2(a);
+                    rw[k][0] = v.x; rw[k][NBLK / 2 - 1] = v.y;
                 } else {
-                    o_main[blk][j][0] += o_tmp[j][0] + o_tmp[j][2];
-                    o_main[blk][j][NH - 1] += o_tmp[j][1] + o_tmp[j][3];
+                    rw[k][0] = lds_u32(a);
+                }
+            }
+#pragma unroll
+            for (int blk = 0; blk < NBLK; ++blk) {
+                const bool shifted = ((blk * C::BBV + 2) & 3) != 0;
+                const uint32_t base = (shifted ? vb_sh : vb_al) + blk * C::BBV;
+                const uint32_t selA = shifted ? vselA_sh : vselA_al;
+                const uint32_t selB = selA + 0x10u;                  // the next byte of the same word
+                const uint32_t w0 = lds_u32(base + (2 * u) * C::TBV), w1 = lds_u32(base + (2 * u + 1) * C::TBV);
+                // (d, d) of the two tokens for this block
+                const uint32_t d0 = __byte_perm(rw[0][blk >> 1], 0u, (blk & 1) ? 0x3232 : 0x1010);
+                const uint32_t d1 = __byte_perm(rw[1][blk >> 1], 0u, (blk & 1) ? 0x3232 : 0x1010);
+                uint32_t bh0[NH], bh1[NH], bl0[NH], bl1[NH];
+#pragma unroll
+                for (int h = 0; h < NH; ++h) {
+                    weight_terms(PH[h][0], PL[h][0], d0, bh0[h], bl0[h]);
+                    weight_terms(PH[h][1], PL[h][1], d1, bh1[h], bl1[h]);
+                }
+                if (VBITS == 4 && VT == 1) {
+                    const uint32_t a0 = lds_u32(entry_addr_sel(w0, vconst, selA)), a1 = lds_u32(entry_addr_sel(w0, vconst, selB));
+                    const uint32_t a2 = lds_u32(entry_addr_sel(w1, vconst, selA)), a3 = lds_u32(entry_addr_sel(w1, vconst, selB));
+#pragma unroll
+                    for (int h = 0; h < NH; ++h) {
+                        mma_16816(acc[blk][0][h], a0, a1, a2, a3, bh0[h], bh1[h]);
+                        mma_16816(acc[blk][0][h], a0, a1, a2, a3, bl0[h], bl1[h]);
+                    }
+                } else if (VBITS == 4) {
+                    const uint2 e0 = lds_v2(entry_addr_sel(w0, vconst, selA)), e1 = lds_v2(entry_addr_sel(w1, vconst, selA));
+                    const uint2 f0 = lds_v2(entry_addr_sel(w0, vconst, selB)), f1 = lds_v2(entry_addr_sel(w1, vconst, selB));
+#pragma unroll
+                    for (int h = 0; h < NH; ++h) {
+                        if constexpr (VACC == 2) {
+                            // {hi, lo} entries fill the register pairs (a0, a1) / (a2, a3) as loaded
+                            mma_16816(acc[blk][0][h], e0.x, e0.y, e1.x, e1.y, bh0[h], bh1[h]);
+                            mma_16816(acc[blk][0][h], e0.x, e0.y, e1.x, e1.y, bl0[h], bl1[h]);
+                            mma_16816(acc[blk][VACC - 1][h], f0.x, f0.y, f1.x, f1.y, bh0[h], bh1[h]);
+                            mma_16816(acc[blk][VACC - 1][h], f0.x, f0.y, f1.x, f1.y, bl0[h], bl1[h]);
+                        } else {
+                            // hi terms of the two bytes in rows g / g+8, then their lo terms; lo x lo is dropped
+                            mma_16816(acc[blk][0][h], e0.x, f0.x, e1.x, f1.x, bh0[h], bh1[h]);
+                            mma_16816(acc[blk][0][h], e0.x, f0.x, e1.x, f1.x, bl0[h], bl1[h]);
+                            mma_16816(acc[blk][0][h], e0.y, f0.y, e1.y, f1.y, bh0[h], bh1[h]);
+                        }
+                    }
+                } else if (VT == 1) {
+                    const uint2 e0 = lds_v2(entry_addr_sel(w0, vconst, selA)), e1 = lds_v2(entry_addr_sel(w1, vconst, selA));
+#pragma unroll
+                    for (int h = 0; h < NH; ++h) {
+                        mma_16816(acc[blk][0][h], e0.x, e0.y, e1.x, e1.y, bh0[h], bh1[h]);
+                        mma_16816(acc[blk][0][h], e0.x, e0.y, e1.x, e1.y, bl0[h], bl1[h]);
+                    }
+                } else {
+                    // 2-bit {hi A, lo A, hi B, lo B}: A = dims 4g, 4g+1, B = dims 4g+2, 4g+3
+                    const uint4 e0 = lds_v4(entry_addr_sel(w0, vconst, selA)), e1 = lds_v4(entry_addr_sel(w1, vconst, selA));
+#pragma unroll
+                    for (int h = 0; h < NH; ++h) {
+                        if constexpr (VACC == 2) {
+                            mma_16816(acc[blk][0][h], e0.x, e0.y, e1.x, e1.y, bh0[h], bh1[h]);
+                            mma_16816(acc[blk][0][h], e0.x, e0.y, e1.x, e1.y, bl0[h], bl1[h]);
+                            mma_16816(acc[blk][VACC - 1][h], e0.z, e0.w, e1.z, e1.w, bh0[h], bh1[h]);
+                            mma_16816(acc[blk][VACC - 1][h], e0.z, e0.w, e1.z, e1.w, bl0[h], bl1[h]);
+                        } else {
+                            mma_16816(acc[blk][0][h], e0.x, e0.z, e1.x, e1.z, bh0[h], bh1[h]);
+                            mma_16816(acc[blk][0][h], e0.x, e0.z, e1.x, e1.z, bl0[h], bl1[h]);
+                            mma_16816(acc[blk][0][h], e0.y, e0.w, e1.y, e1.w, bh0[h], bh1[h]);
+                        }
+                    }
                 }
             }
         }
         __syncwarp();
         slot = slot + 1 == kStages ? 0 : slot + 1;
     }
-    cp_async_wait<0>();
 
     // ---- reduce the row sums over the 8 lanes that share a head
 #pragma unroll
@@ -686,47 +789,45 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
     }
     __syncwarp();
 
-    // per-warp record in the warp's own (now idle) ring: [head][0] = m, [1] = l, [2 + dim] = o
+    // per-warp record over the warp's own (now idle) stages: [head][0] = m, [1] = l, [2 + dim] = o
     {
-        float* rec = reinterpret_cast<float*>(my_ring);
+        float* rec = rec_of(warp);
         if (g == 0) {
 #pragma unroll
             for (int h = 0; h < NH; ++h) {
-                const int head = NH == 1 ? t : 2 * t + h;
-                rec[head * (D + 2) + 0] = m_run[h];
-                rec[head * (D + 2) + 1] = l_run[h];
+                rec[(t + 4 * h) * (D + 2) + 0] = m_run[h];
+                rec[(t + 4 * h) * (D + 2) + 1] = l_run[h];
             }
         }
 #pragma unroll
         for (int blk = 0; blk < NBLK; ++blk)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int dim = blk * 32 + 4 * g + j;
-                if (NH == 1) {
-                    rec[t * (D + 2) + 2 + dim] = o_main[blk][j][0] * (1.0f / kCbScale);
-                } else {
-                    rec[(2 * t) * (D + 2) + 2 + dim] = o_main[blk][j][0] * (1.0f / kCbScale);
-                    rec[(2 * t + 1) * (D + 2) + 2 + dim] = o_main[blk][j][NH - 1] * (1.0f / kCbScale);
+            for (int h = 0; h < NH; ++h)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int dim = blk * 32 + 4 * g + j;
+                    float v;
+                    if constexpr (VACC == 1) v = acc[blk][0][h][j];
+                    else v = acc[blk][j >> 1][h][j & 1] + acc[blk][j >> 1][h][2 + (j & 1)];
+                    rec[(t + 4 * h) * (D + 2) + 2 + dim] = v * p.v_inv;
                 }
-            }
     }
     __syncthreads();
 
     // ---- item record = merge of the warp records
     const size_t group = (size_t)vrow;
     float* cta_rec = p.records + (group * p.max_segs + seg_idx) * kRecHeads * (D + 2);
-    for (int e = tid; e < HPC * (D + 2); e += kDecThreads) {
+    for (int e = tid; e < HPC * (D + 2); e += NT) {
         const int head = e / (D + 2), col = e % (D + 2);
         float mx = -INFINITY;
-        for (int w = 0; w < kDecWarps; ++w)
-            mx = fmaxf(mx, reinterpret_cast<const float*>(ring_of(w))[head * (D + 2)]);
+        for (int w = 0; w < NW; ++w) mx = fmaxf(mx, rec_of(w)[head * (D + 2)]);
         float val;
         if (col == 0) {
             val = mx;
         } else {
             val = 0.f;
-            for (int w = 0; w < kDecWarps; ++w) {
-                const float* r = reinterpret_cast<const float*>(ring_of(w)) + head * (D + 2);
+            for (int w = 0; w < NW; ++w) {
+                const float* r = rec_of(w) + head * (D + 2);
                 const float mw = r[0];
                 const float s = (mw == -INFINITY) ? 0.f : fast_exp2(mw - mx);
                 val = fmaf(s, r[col], val);
@@ -742,7 +843,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
         // ---- last segment of this virtual row to finish: merge the segment records
         __threadfence();
         const float* recs = p.records + group * p.max_segs * kRecHeads * (D + 2);
-        for (int e = tid; e < HPC * D; e += kDecThreads) {
+        for (int e = tid; e < HPC * D; e += NT) {
             const int head = e / D, dim = e % D;
             float mx = -INFINITY;
             for (int s = 0; s < n_segs; ++s) mx = fmaxf(mx, __ldcg(recs + (s * kRecHeads + head) * (D + 2)));
@@ -768,23 +869,26 @@ __global__ void __launch_bounds__(kDecThreads, 1) pq_decode_attn_kernel(const De
         if (!p.partial_out) {
             __syncthreads();
             // out[head][i] = sum_j o_fin[head][j] * R[j][i]
-            for (int e = tid; e < HPC * D; e += kDecThreads) {
+            for (int e = tid; e < HPC * D; e += NT) {
                 const int head = e / D, i = e % D;
                 if (head >= Gp) continue;
-                float acc = 0.f;
+                float acc_o = 0.f;
                 // 32 independent loads in flight per thread: the column of R comes from L2, and with a short
                 // unroll the D dependent round trips dominate the merge
 #pragma unroll 32
-                for (int j = 0; j < D; ++j) acc = fmaf(o_fin[head * D + j], __ldg(p.rot + (size_t)j * D + i), acc);
+                for (int j = 0; j < D; ++j) acc_o = fmaf(o_fin[head * D + j], __ldg(p.rot + (size_t)j * D + i), acc_o);
                 const size_t off = ((size_t)b * p.Hq + head0 + head) * D + i;
                 if (p.out_is_fp16)
-                    static_cast<__half*>(p.out)[off] = __float2half_rn(fminf(fmaxf(acc, -65504.f), 65504.f));
+                    static_cast<__half*>(p.out)[off] = __float2half_rn(fminf(fmaxf(acc_o, -65504.f), 65504.f));
                 else
-                    static_cast<float*>(p.out)[off] = acc;
+                    static_cast<float*>(p.out)[off] = acc_o;
             }
         }
     }
-    __syncthreads();   // the next segment reuses the rings and the query buffers
+    // the next segment reuses the rings (bulk copies land where this segment wrote records and
+    // slow-path tiles with ordinary stores) and the query buffers
+    fence_async_smem();
+    __syncthreads();
     }   // segments
 }
 
@@ -802,14 +906,20 @@ static int heads_per_cta(int G) { return G <= 4 ? 4 : 8; }
 static int head_groups(int G) { const int h = heads_per_cta(G); return (G + h - 1) / h; }
 
 // Balanced mode: number of persistent CTAs and the largest number of segments a row can have.
+// A row of T tiles inside a sequence cut into n equal ranges of floor/ceil(all/n) tiles touches at
+// most ceil(n / n_vrows) + 1 ranges and never more than T; the bound does not shrink when T grows,
+// so scratch sized for a cache's capacity serves every shorter sequence length.
 static void balanced_plan(int64_t n_vrows, int64_t tiles_per_row, int sms, int* n_cta, int* max_segs) {
     if (sms <= 0) sms = 148;
+    if (n_vrows < 1) n_vrows = 1;
     const int64_t all_tiles = n_vrows * tiles_per_row;
     int64_t n = all_tiles < sms ? all_tiles : sms;
     if (n < 1) n = 1;
-    const int64_t per = all_tiles / n > 0 ? all_tiles / n : 1;
     *n_cta = (int)n;
-    *max_segs = (int)(tiles_per_row / per + 2);
+    const int64_t by_cta = (sms + n_vrows - 1) / n_vrows + 1;
+    int64_t segs = tiles_per_row < by_cta ? tiles_per_row : by_cta;
+    if (segs < 1) segs = 1;
+    *max_segs = (int)segs;
 }
 
 // Split count offered to callers that want the static scheme: enough segments to fill the
@@ -819,7 +929,7 @@ static int choose_splits(int batch, int q_heads, int kv_heads, int64_t seq_len, 
     const int G = q_heads / kv_heads;
     const int64_t groups = (int64_t)batch * kv_heads * head_groups(G);
     const int64_t tiles = (seq_len + kTileTok - 1) / kTileTok;
-    int64_t max_s = tiles / (2 * kDecWarps);
+    int64_t max_s = tiles / 32;
     if (max_s > 64) max_s = 64;
     if (max_s < 1) max_s = 1;
     int best = 1;
@@ -831,6 +941,49 @@ static int choose_splits(int batch, int q_heads, int kv_heads, int64_t seq_len, 
         if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
     }
     return best;
+}
+
+// Scale for the single-term value table: the power-of-two-free factor a in [1, 2) for which
+// 64 * a * c[i] is closest to a float16 number for every centroid at once (largest rounding error
+// relative to the largest centroid; about 3e-5 for the 16-centroid block codebook against 2.4e-4 for
+// an arbitrary scale).  The search runs once per codebook; the last result is cached.
+static float value_table_scale(const float* cb, int n) {
+    if (kVTerms != 1) return kCbScale;
+    static std::mutex mu;
+    static float cached_cb[16];
+    static int cached_n = 0;
+    static float cached_scale = 0.f;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached_n == n && std::memcmp(cached_cb, cb, n * sizeof(float)) == 0) return cached_scale;
+    float cmax = 0.f;
+    for (int i = 0; i < n; ++i) cmax = std::fmax(cmax, std::fabs(cb[i]));
+    float best_a = 1.f;
+    double best_err = 1e30;
+    constexpr int kSteps = 1 << 14;
+    for (int s = 0; s < kSteps && cmax > 0.f; ++s) {
+        const float a = 1.f + (float)s / kSteps;
+        double worst = 0.0;
+        for (int i = 0; i < n; ++i) {
+            const float x = kCbScale * a * cb[i];
+            const double e = std::fabs((double)__half2float(__float2half_rn(x)) - (double)x);
+            if (e > worst) worst = e;
+        }
+        worst /= (double)(kCbScale * a * cmax);
+        if (worst < best_err) { best_err = worst; best_a = a; }
+    }
+    std::memcpy(cached_cb, cb, n * sizeof(float));
+    cached_n = n;
+    cached_scale = kCbScale * best_a;
+    return cached_scale;
+}
+
+// Read and clear this file's device error flags (for pq_poll_device_errors).
+int decode_error_flags(unsigned int* flags) {
+    unsigned int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_decode_error, sizeof(v)) != cudaSuccess) return PQ_ERR_CUDA;
+    if (v && cudaMemcpyToSymbol(g_decode_error, &zero, sizeof(zero)) != cudaSuccess) return PQ_ERR_CUDA;
+    *flags = v;
+    return PQ_OK;
 }
 
 template <int D, int KBITS, int VBITS, int NH, bool QJL>
@@ -850,7 +1003,7 @@ static int launch_decode(const DecodeParams& p, int rows, cudaStream_t st) {
         int ms = 0;
         balanced_plan((int64_t)rows * p.HG, (p.S + kTileTok - 1) / kTileTok, sms, &grid, &ms);
     }
-    kern<<<grid, kDecThreads, smem, st>>>(p);
+    kern<<<grid, C::NTHREADS, smem, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? PQ_OK : PQ_ERR_CUDA;
 }
 
@@ -876,6 +1029,38 @@ extern "C" size_t pq_decode_attn_scratch_bytes(int batch, int q_heads, int kv_he
     return tickets + groups * segs * pq::kRecHeads * (head_dim + 2) * sizeof(float);
 }
 
+// Argument checks shared by pq_decode_attn and pq_decode_attn_static.  Returns PQ_OK when a launch (or
+// the empty-input shortcut) may proceed; *n_splits_io is clamped to [0, tiles].
+static int check_decode_args(const void* q, const void* k_blocks, const void* v_blocks, int batch, int q_heads,
+                             int kv_heads, int64_t seq_len, int64_t seq_capacity, int head_dim, int k_bits,
+                             int v_bits, const float* codebook_k, const float* codebook_v, const float* rot,
+                             const float* jl_matrix, int jl_dim, const void* qjl_bits, const void* qjl_norms,
+                             const void* out, const void* partial_out, int* n_splits_io) {
+    if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads || seq_len < 0 || seq_capacity < seq_len)
+        return PQ_ERR_BAD_SHAPE;
+    if (head_dim != 64 && head_dim != 128) return PQ_ERR_BAD_HEAD_DIM;
+    if ((k_bits != 2 && k_bits != 4) || (v_bits != 2 && v_bits != 4)) return PQ_ERR_BAD_BITS;
+    const int64_t tiles = (seq_len + pq::kTileTok - 1) / pq::kTileTok;
+    if (tiles > 0x7FFFFFF0) return PQ_ERR_TOO_LARGE;
+    if (*n_splits_io < 0) *n_splits_io = 0;
+    if (*n_splits_io > tiles) *n_splits_io = (int)tiles;
+    if (batch == 0) return PQ_OK;
+    if (!q || !rot || !codebook_k || !codebook_v || (!out && !partial_out)) return PQ_ERR_NULL_POINTER;
+    if (jl_matrix != nullptr) {
+        if (jl_dim < 16 || jl_dim > 128 || (jl_dim % 16)) return PQ_ERR_BAD_JL_DIM;
+        if (!qjl_bits || !qjl_norms) return PQ_ERR_NULL_POINTER;
+        if ((reinterpret_cast<uintptr_t>(qjl_bits) & 15) || (reinterpret_cast<uintptr_t>(qjl_norms) & 15) ||
+            (seq_capacity & 1))
+            return PQ_ERR_MISALIGNED;
+    }
+    if (seq_len == 0) return PQ_OK;
+    if (!k_blocks || !v_blocks) return PQ_ERR_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(k_blocks) & 15) || (reinterpret_cast<uintptr_t>(v_blocks) & 15) ||
+        (reinterpret_cast<uintptr_t>(rot) & 15))
+        return PQ_ERR_MISALIGNED;
+    return PQ_OK;
+}
+
 extern "C" int pq_decode_attn(const void* q, const void* k_blocks, const void* v_blocks,
                               int batch, int q_heads, int kv_heads, int64_t seq_len, int64_t seq_capacity,
                               int head_dim, int k_bits, int v_bits,
@@ -884,21 +1069,14 @@ extern "C" int pq_decode_attn(const void* q, const void* k_blocks, const void* v
                               void* out, int out_is_fp16, void* partial_out,
                               int n_splits, void* scratch, size_t scratch_bytes, void* stream) {
     using namespace pq;
-    if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads || seq_len < 0 || seq_capacity < seq_len)
-        return PQ_ERR_BAD_SHAPE;
-    if (head_dim != 64 && head_dim != 128) return PQ_ERR_BAD_HEAD_DIM;
-    if ((k_bits != 2 && k_bits != 4) || (v_bits != 2 && v_bits != 4)) return PQ_ERR_BAD_BITS;
+    const int chk = check_decode_args(q, k_blocks, v_blocks, batch, q_heads, kv_heads, seq_len, seq_capacity, head_dim,
+                                      k_bits, v_bits, codebook_k, codebook_v, rot, jl_matrix, jl_dim, qjl_bits,
+                                      qjl_norms, out, partial_out, &n_splits);
+    if (chk != PQ_OK) return chk;
     if (batch == 0) return PQ_OK;
-    if (!q || !rot || !codebook_k || !codebook_v || (!out && !partial_out) || !scratch) return PQ_ERR_NULL_POINTER;
+    if (!scratch) return PQ_ERR_NULL_POINTER;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const bool qjl = jl_matrix != nullptr;
-    if (qjl) {
-        if (jl_dim < 16 || jl_dim > 128 || (jl_dim % 16)) return PQ_ERR_BAD_JL_DIM;
-        if (!qjl_bits || !qjl_norms) return PQ_ERR_NULL_POINTER;
-        if ((reinterpret_cast<uintptr_t>(qjl_bits) & 15) || (reinterpret_cast<uintptr_t>(qjl_norms) & 15) ||
-            (seq_capacity & 1))
-            return PQ_ERR_MISALIGNED;
-    }
     if (seq_len == 0) {
         // empty sequence -> zeros (attention.py:127-131); partial: m = -inf, l = 0, o = 0
         const size_t n = (size_t)batch * q_heads;
@@ -909,13 +1087,8 @@ extern "C" int pq_decode_attn(const void* q, const void* k_blocks, const void* v
         if (cudaMemsetAsync(out, 0, n * head_dim * (out_is_fp16 ? 2 : 4), st) != cudaSuccess) return PQ_ERR_CUDA;
         return PQ_OK;
     }
-    if (!k_blocks || !v_blocks) return PQ_ERR_NULL_POINTER;
-    if ((reinterpret_cast<uintptr_t>(k_blocks) & 15) || (reinterpret_cast<uintptr_t>(v_blocks) & 15) ||
-        (reinterpret_cast<uintptr_t>(scratch) & 255) || (reinterpret_cast<uintptr_t>(rot) & 15))
-        return PQ_ERR_MISALIGNED;
+    if (reinterpret_cast<uintptr_t>(scratch) & 255) return PQ_ERR_MISALIGNED;
     const int64_t tiles = (seq_len + kTileTok - 1) / kTileTok;
-    if (n_splits < 0) n_splits = 0;
-    if (n_splits > tiles) n_splits = (int)tiles;
     if (scratch_bytes < pq_decode_attn_scratch_bytes(batch, q_heads, kv_heads, seq_len, head_dim, n_splits))
         return PQ_ERR_SCRATCH_TOO_SMALL;
     const int rows = batch * kv_heads;
@@ -948,6 +1121,8 @@ extern "C" int pq_decode_attn(const void* q, const void* k_blocks, const void* v
     p.jl_dim = qjl ? jl_dim : 0;
     p.out_is_fp16 = out_is_fp16;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.v_scale = value_table_scale(codebook_v, 1 << v_bits);
+    p.v_inv = 1.0f / p.v_scale;
     for (int i = 0; i < 16; ++i) {
         p.cbk[i] = i < (1 << k_bits) ? codebook_k[i] : 0.f;
         p.cbv[i] = i < (1 << v_bits) ? codebook_v[i] : 0.f;
@@ -989,20 +1164,20 @@ constexpr size_t kStaticScratchBytes = size_t(8) << 20;   // 8 MiB per GPU
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-static void* g_static_scratch_ptr[kMaxDevices] = {};
-static bool g_static_scratch_ready[kMaxDevices] = {};
+// Published once per device; racing first calls from several host threads all store the same
+// address, and the release/acquire pair orders the store against later readers.
+static std::atomic<void*> g_static_scratch_ptr[kMaxDevices];
 
 // Device address of the static scratch on the current device, or nullptr on failure.
 static void* static_scratch_for_current_device() {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
-    if (!g_static_scratch_ready[dev]) {
-        void* ptr = nullptr;
+    void* ptr = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
         if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return nullptr;
-        g_static_scratch_ptr[dev] = ptr;
-        g_static_scratch_ready[dev] = true;
+        g_static_scratch_ptr[dev].store(ptr, std::memory_order_release);
     }
-    return g_static_scratch_ptr[dev];
+    return ptr;
 }
 
 }  // namespace pq
@@ -1017,13 +1192,14 @@ extern "C" int pq_decode_attn_static(const void* q, const void* k_blocks, const 
                                      void* out, int out_is_fp16, void* partial_out,
                                      int n_splits, void* stream) {
     using namespace pq;
-    if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads || seq_len < 0) return PQ_ERR_BAD_SHAPE;
-    if (head_dim != 64 && head_dim != 128) return PQ_ERR_BAD_HEAD_DIM;
+    // Every argument is checked before anything touches the shared array, so a rejected call cannot
+    // disturb another call that is still using it.  The split count is fixed here as well, so the
+    // size check below and the launch agree.
+    const int chk = check_decode_args(q, k_blocks, v_blocks, batch, q_heads, kv_heads, seq_len, seq_capacity, head_dim,
+                                      k_bits, v_bits, codebook_k, codebook_v, rot, jl_matrix, jl_dim, qjl_bits,
+                                      qjl_norms, out, partial_out, &n_splits);
+    if (chk != PQ_OK) return chk;
     if (batch == 0) return PQ_OK;
-    // Fix the split count here so the size check below and the launch agree.
-    const int64_t tiles = (seq_len + kTileTok - 1) / kTileTok;
-    if (n_splits < 0) n_splits = 0;
-    if (n_splits > tiles) n_splits = (int)tiles;
     const size_t need = pq_decode_attn_scratch_bytes(batch, q_heads, kv_heads, seq_len, head_dim, n_splits);
     if (need > kStaticScratchBytes) return PQ_ERR_STATIC_SCRATCH_EXCEEDED;
     void* scratch = static_scratch_for_current_device();

@@ -62,8 +62,25 @@ CompressedKVCacheGPU = CompressedKV
 
 
 @dataclass
+class QJLSignatures:
+    """Sign sketch of quantisation residuals (python/polarquant_kv/types.py:21-27 of the reference).
+
+    signs          bool [..., jl_dim]: sign(P e) >= 0
+    jl_dim         number of projections
+    residual_norm  ||e||: a float for one vector (as in the reference) or a tensor [...] for a batch
+    """
+
+    signs: torch.Tensor
+    jl_dim: int
+    residual_norm: float | torch.Tensor = 0.0
+
+
+@dataclass
 class CompressedKVCache:
-    """Key + value (+ the keys' QJL side band lives inside compressed_keys)."""
+    """Key + value + optional key signatures (python/polarquant_kv/types.py:30-35).  On the GPU path
+    the keys' sketch normally lives inside compressed_keys (qjl_signs / residual_norms);
+    key_signatures is kept for code written against the reference's container."""
 
     compressed_keys: CompressedKV
     compressed_values: CompressedKV
+    key_signatures: QJLSignatures | None = None

@@ -52,6 +52,17 @@ def estimate_memory_bytes(batch: int, num_heads: int, seq_len: int, head_dim: in
     return math.ceil(batch * num_heads * seq_len * block_pq4_bits_per_vector(head_dim, n_bits, jl_dim) / 8)
 
 
+def check_memory_warning(estimated_bytes: int, device=None) -> bool:
+    """True when ``estimated_bytes`` exceeds 80 % of the free memory (utils.py:56-59 of the
+    reference, which asks psutil for host RAM).  With ``device`` (a CUDA device) the free HBM of
+    that GPU is the yardstick, which is what matters for a cache that lives on the GPU."""
+    if device is not None:
+        free, _total = torch.cuda.mem_get_info(device)
+        return estimated_bytes > free * 0.8
+    import psutil
+    return estimated_bytes > psutil.virtual_memory().available * 0.8
+
+
 def attention_score_mse(a, b) -> float:
     a = a.detach().double().cpu().numpy() if isinstance(a, torch.Tensor) else np.asarray(a, dtype=np.float64)
     b = b.detach().double().cpu().numpy() if isinstance(b, torch.Tensor) else np.asarray(b, dtype=np.float64)

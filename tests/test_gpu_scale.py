@@ -1,0 +1,160 @@
+"""GPU parity at the sizes the benchmark runs at.
+
+The small parity cases never reach the regime the measured launches run in: persistent CTAs that each
+walk several segments, rows cut across CTAs and merged through the ticket counters, compress launches
+of more than a million vectors.  These tests run such shapes and pull SAMPLES back to the numpy oracle
+(the oracle cannot walk the whole workload in seconds): a few (batch, kv-head) rows of a decode, a
+strided subset of the vectors of a bulk compress.
+
+Tolerances as in test_gpu_parity.py: attention max-abs <= 2e-3; packed indices bit-exact except
+coordinates within 1e-6 of a decision boundary (counted, none unexplained), radii within one
+float16 ulp (counted).
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import pq_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+ATTN_TOL = 2e-3
+
+
+def _cuda():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    return torch.device("cuda:0")
+
+
+def _synthetic(shape, dev, seed):
+    """The benchmark distribution on the GPU: N(0,1) x per-channel lognormal(0,1), two channels x10."""
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+    D = shape[-1]
+    scale = torch.exp(torch.randn(D, generator=gen, device=dev))
+    hot = torch.randperm(D, generator=gen, device=dev)[:2]
+    scale[hot] *= 10.0
+    return (torch.randn(shape, generator=gen, device=dev) * scale).to(torch.float16)
+
+
+def _build(B, Hkv, S, D, dev, seed, bits=4, cap=None):
+    from polarquant_kv import quantizer
+    from polarquant_kv.rotation import device_plan
+    R = O.rotation_matrix(D, 0)
+    plan = device_plan(R, dev)
+    caches = []
+    for i in range(2):
+        cache = quantizer.allocate_cache(B, Hkv, cap or S, D, bits, 0, dev)
+        for b in range(B):
+            x = _synthetic((1, Hkv, S, D), dev, seed + 100 * i + b)
+            quantizer.compress(x, plan, bits, out=_row_view(cache, b), position=0)
+        cache.seq_len = S
+        caches.append(cache)
+    return R, plan, caches[0], caches[1]
+
+
+def _row_view(cache, b):
+    from polarquant_kv.types import CompressedKV
+    return CompressedKV(cache.blocks[b:b + 1], None, None, cache.n_bits, 32, cache.original_dim, 0, cache.max_seq_len)
+
+
+def _check_rows(out, q, ck, cv, R, rows, S, label):
+    cb, _ = O.lloyd_max_codebook(32, 4)
+    Hq, Hkv = q.shape[1], ck.blocks.shape[1]
+    G = Hq // Hkv
+    worst = 0.0
+    for b, h in rows:
+        kb = ck.blocks[b, h:h + 1, :S].cpu().numpy()
+        vb = cv.blocks[b, h:h + 1, :S].cpu().numpy()
+        qh = q[b, h * G:(h + 1) * G].cpu().numpy()[:, None, :]
+        ref = O.attention_from_blocks(qh, kb, vb, R, cb, cb)[:, 0]
+        err = float(np.abs(out[b, h * G:(h + 1) * G].cpu().numpy() - ref).max())
+        worst = max(worst, err)
+    print(f"{label}: {len(rows)} sampled (batch, kv-head) rows, max-abs {worst:.3e}")
+    assert worst <= ATTN_TOL
+
+
+@pytest.mark.parametrize("B,Hkv,Hq,S", [(4, 8, 32, 8192), (3, 2, 32, 4099)])
+def test_decode_multi_segment_vs_oracle(B, Hkv, Hq, S):
+    """Balanced persistent partition with many tiles per CTA (n_splits = 0): sampled rows against the
+    oracle, all rows against the one-segment-per-row schedule (n_splits = 1).  The second shape has 16
+    query heads per KV head (two head groups) and a ragged last tile."""
+    from polarquant_kv import attention
+    dev = _cuda()
+    D = 128
+    R, plan, ck, cv = _build(B, Hkv, S, D, dev, seed=5)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(3)
+    q = torch.randn((B, Hq, D), generator=gen, device=dev).to(torch.float16)
+    out = attention.decode_attention(q, ck, cv, plan, enable_qjl=False, n_splits=0)
+    one = attention.decode_attention(q, ck, cv, plan, enable_qjl=False, n_splits=1)
+    torch.cuda.synchronize()
+    diff = float((out - one).abs().max())
+    print(f"B{B} Hkv{Hkv} Hq{Hq} S{S}: balanced vs one segment per row: max-abs {diff:.3e}")
+    assert diff <= 2e-4
+    rows = [(0, 0), (B - 1, Hkv - 1), (B // 2, Hkv // 2), (1, 1), (B - 1, 0), (0, Hkv - 1)]
+    _check_rows(out, q, ck, cv, R, rows, S, f"decode B{B} Hkv{Hkv} Hq{Hq} S{S}")
+
+
+def test_decode_long_context_shape_vs_oracle():
+    """One 131072-token sequence, 8 KV heads, 64 query heads (8 per KV head): two sampled KV heads."""
+    from polarquant_kv import attention
+    dev = _cuda()
+    B, Hkv, Hq, S, D = 1, 8, 64, 131072, 128
+    R, plan, ck, cv = _build(B, Hkv, S, D, dev, seed=11)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4)
+    q = torch.randn((B, Hq, D), generator=gen, device=dev).to(torch.float16)
+    out = attention.decode_attention(q, ck, cv, plan, enable_qjl=False)
+    torch.cuda.synchronize()
+    _check_rows(out, q, ck, cv, R, [(0, 1), (0, 6)], S, "decode long context")
+
+
+@pytest.mark.parametrize("n_bits,with_qjl", [(4, False), (2, False), (4, True)])
+def test_compress_million_vectors_sampled_vs_oracle(n_bits, with_qjl):
+    from polarquant_kv import quantizer
+    from polarquant_kv.rotation import device_plan
+    from test_gpu_parity import compare_blocks
+    dev = _cuda()
+    n, D = 1 << 20, 128
+    R = O.rotation_matrix(D, 0)
+    P = O.jl_matrix(D, D, 1) if with_qjl else None
+    cb, _ = O.lloyd_max_codebook(32, n_bits)
+    x = _synthetic((1, 1, n, D), dev, seed=23)
+    c = quantizer.compress(x, device_plan(R, dev, P), n_bits, 32, P)
+    torch.cuda.synchronize()
+    idx = torch.arange(17, n, 64, device=dev)
+    xs = x[0, 0, idx].cpu().numpy()
+    got = c.blocks[0, 0, idx].cpu().numpy()
+    rep = compare_blocks(xs, R, n_bits, got, cb)
+    print(f"compress 2^20 vectors, b{n_bits}, qjl={with_qjl}, 1-in-64 sample: {rep}")
+    assert rep["unexplained"] == 0 and rep["radius_bad"] == 0
+    assert rep["mismatch"] <= max(3, xs.size // 20000)
+    # the last tile of the launch
+    tail = slice(n - 300, n)
+    rep = compare_blocks(x[0, 0, tail].cpu().numpy(), R, n_bits, c.blocks[0, 0, tail].cpu().numpy(), cb)
+    assert rep["unexplained"] == 0 and rep["radius_bad"] == 0
+
+
+def test_prepared_decode_growing_sequence():
+    """A PreparedDecode sized for the cache capacity serves every shorter length (few rows, so the
+    balanced partition cuts each row into many segments whose number changes with the length)."""
+    from polarquant_kv import attention
+    dev = _cuda()
+    B, Hkv, Hq, cap, D = 1, 2, 8, 8192, 128
+    R, plan, ck, cv = _build(B, Hkv, cap, D, dev, seed=31)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(6)
+    q = torch.randn((B, Hq, D), generator=gen, device=dev).to(torch.float16)
+    ck.seq_len = cv.seq_len = cap
+    pd = attention.prepare_decode(q, ck, cv, plan)
+    for S in (16, 576, 577, 1000, 2368, 4097, 8192):
+        ck.seq_len = cv.seq_len = S
+        got = pd().clone()
+        ref = attention.decode_attention(q, ck, cv, plan, enable_qjl=False, n_splits=1)
+        torch.cuda.synchronize()
+        err = float((got - ref).abs().max())
+        assert err <= 2e-4, (S, err)
+    _check_rows(got, q, ck, cv, R, [(0, 1)], 8192, "prepared decode at capacity")
