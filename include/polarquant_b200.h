@@ -86,6 +86,26 @@ int pq_compress(const void* x, int64_t n_vec, int head_dim, int n_bits,
                 const void* jl_split, int jl_dim, void* qjl_bits_out, void* qjl_norm_out,
                 void* stream);
 
+/* ---------------------------------------------------------------------------------
+ * pq_compress_rows — pq_compress that writes into preallocated cache tensors in ONE launch:
+ * the input holds n_rows x tokens_per_row vectors ([batch*heads, new tokens, head_dim]); vector
+ * (r, t) lands in token slot r * row_capacity + position + t of blocks_out (and of the sketch
+ * outputs), i.e. at sequence offset `position` of row r of a cache whose rows hold row_capacity
+ * tokens.  This is the append-on-write step of a decode loop (one new token for every
+ * (batch, head) row in one launch) and of a prefill (all prompt tokens of all rows at once).
+ *
+ * Replaces KVCacheManager.append's compress-then-concatenate
+ * (src/polarquant_kv_cuda/inference/kv_cache.py:68-116) and the per-(head, token) compress calls
+ * of the ggml dispatch (integration/polarquant-kv.patch, decoded lines 802-835).
+ * Other arguments as pq_compress.  Requires position + tokens_per_row <= row_capacity.
+ */
+int pq_compress_rows(const void* x, int64_t n_rows, int64_t tokens_per_row, int64_t row_capacity,
+                     int64_t position, int head_dim, int n_bits,
+                     const void* rot_split, const float* thresholds, const float* codebook,
+                     void* blocks_out,
+                     const void* jl_split, int jl_dim, void* qjl_bits_out, void* qjl_norm_out,
+                     void* stream);
+
 /* pq_poll_device_errors — HOST-synchronising check for device-side failures of earlier launches on
  * the current device.  The tensor-core kernels wait for copies and MMAs through barriers with a time
  * limit (so that a lost completion can never hang the GPU); if a wait ever gives up a bit of
@@ -95,6 +115,20 @@ int pq_compress(const void* x, int64_t n_vec, int head_dim, int n_bits,
  * wait for a tile copy gave up).
  * The flags are cleared by the call.  No counterpart in the reference (its kernels report nothing). */
 int pq_poll_device_errors(unsigned int* flags_out);
+
+/* ---------------------------------------------------------------------------------
+ * pq_qjl_sketch — sign sketch of caller-provided residual vectors: bits = (P e >= 0), norms = ||e||,
+ * evaluated in float64.  Replaces qjl.compute_signatures (python/polarquant_kv/qjl.py:25-35) and
+ * compute_signatures_gpu (src/polarquant_kv_cuda/qjl_kernel.py:6-37) for residuals that do not come from
+ * pq_compress (which sketches its own residual in-kernel).
+ *
+ *   residual   float32 [n_vec, dim]
+ *   jl_matrix  float64 [jl_dim, dim] row-major P (device memory)
+ *   bits_out   uint8 [n_vec, ceil(jl_dim/8)], bit k of byte j = sign[8j + k]
+ *   norms_out  float32 [n_vec]
+ */
+int pq_qjl_sketch(const float* residual, const double* jl_matrix, int64_t n_vec, int dim, int jl_dim,
+                  void* bits_out, float* norms_out, void* stream);
 
 /* ---------------------------------------------------------------------------------
  * pq_dequant — blocks -> centroid * d -> inverse rotation (v @ R).

@@ -19,8 +19,9 @@
 //   epilogue    - a thread owns one vector x one 32-element block (TMEM lane = vector).  The warps
 //                 that share 32 vectors meet at a named barrier and one lane sends those vectors'
 //                 packed bytes off with a bulk store.
-// With the sketch (a second contraction per tile) the older serial flow is kept: cp.async tile
-// loads and CTA-wide barriers, the MMAs issued by the first warp.
+// With the sketch the same three roles run; the residual goes back into tensor memory as the A operand
+// of a second contraction (with P R^T, three float16 product terms) that the MMA warp issues behind the
+// next tile's rotation, and the epilogue picks up a tile's sign bits one tile later.
 // Everything after the contraction follows the reference's float32 arithmetic exactly:
 //   radius  = sqrt(sum of squares), summed in numpy's axis-reduction order
 //             (eight strided partial sums, then a balanced tree),
@@ -36,13 +37,12 @@
 // rotated space; signs of P e equal signs of (P R^T) e_rot, evaluated as a second
 // three-term float16 contraction (e_hi*P_hi + e_hi*P_lo + e_lo*P_hi) on the same path.
 //
-// Shared-memory operand layout (K-major, no swizzle): 16-byte chunks of 8 halves; chunk kc of
-// row r sits at  kc * (rows/8 * 128) + (r / 8) * 128 + (r % 8) * 16  — 8x16-byte core
-// matrices, stride 128 B between 8-row groups (SBO), rows/8*128 B between K chunks (LBO).
-// Without the sketch the vector tiles instead arrive by TMA (cp.async.bulk.tensor, one thread
-// issues, an mbarrier counts the bytes) in the 128-byte-swizzled K-major layout: boxes of
-// 128 vectors x 64 halves, rows 128 B apart, 8-row groups 1024 B apart; the packed tile
-// leaves by one bulk store.  A tile then costs one CTA-wide barrier.
+// Shared-memory operand layout of the constant matrices (K-major, no swizzle): 16-byte chunks of 8
+// halves; chunk kc of row r sits at  kc * (rows/8 * 128) + (r / 8) * 128 + (r % 8) * 16  — 8x16-byte
+// core matrices, stride 128 B between 8-row groups (SBO), rows/8*128 B between K chunks (LBO).
+// The vector tiles arrive by TMA (cp.async.bulk.tensor, one thread issues, an mbarrier counts the
+// bytes) in the 128-byte-swizzled K-major layout: boxes of 128 vectors x 64 halves, rows 128 B apart,
+// 8-row groups 1024 B apart; the packed tile leaves by bulk stores of 32 vectors.
 #include <cmath>
 #include <cstring>
 
@@ -58,8 +58,8 @@ static __device__ unsigned int g_compress_error = 0;
 constexpr int kTileVecs = 128;
 // warps: 4 per warpgroup (TMEM lanes 0..127 = vectors) x D/32 warpgroups (one block each)
 __host__ __device__ constexpr int compress_threads(int D) { return 32 * 4 * (D / 32); }
-// Without the sketch two more warps run beside them: one issues the MMAs, one the tile copies.
-__host__ __device__ constexpr int compress_launch_threads(int D, bool qjl) { return compress_threads(D) + (qjl ? 0 : 64); }
+// Two more warps run beside them: one issues the MMAs, one the tile copies.
+__host__ __device__ constexpr int compress_launch_threads(int D) { return compress_threads(D) + 64; }
 
 struct CompressParams {
     const __half* x;
@@ -69,13 +69,16 @@ struct CompressParams {
     uint8_t* qjl_bits_out;
     __half* qjl_norm_out;
     int64_t n_vec;
+    // Output addressing: input vector v = row * tokens_per_row + t lands in token slot
+    // row * row_capacity + position + t of the output tensors (one row with capacity n_vec at position 0
+    // is the plain contiguous case).
+    int64_t tokens_per_row, row_capacity, position;
     int jl_dim;
     float cb[16];
-    // Index search table: a normalised coordinate y falls into bucket k = round(64 y) + 64;
+    // Index search table: a normalised coordinate y falls into bucket k = floor(64 y + 64);
     // index = base[k] + (y > t[k]).  A bucket holds at most one decision threshold.
     float bucket_t[132];
     uint32_t bucket_base[132];
-    int floor_buckets;         // 1: k = floor(64 y + 64) (fixed-address table, no sketch); 0: k = round(64 y) + 128
 };
 
 // Packed float32x2 arithmetic (sm_100): two IEEE round-to-nearest operations per instruction.
@@ -101,46 +104,102 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
           "l"(*reinterpret_cast<unsigned long long*>(&c)));
     return d;
 }
+// 16 packed words into consecutive columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_store16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::"r"(taddr),
+                 "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+                 "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+// Named barrier over `count` threads.
+__device__ __forceinline__ void group_barrier(uint32_t id, uint32_t count) {
+    asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(count) : "memory");
+}
 
 // Byte offset of 16-byte chunk `kc` of row `r` in a K-major operand tile with `rows` rows.
 __device__ __forceinline__ uint32_t chunk_off(int rows, int r, int kc) {
     return (uint32_t)(kc * (rows / 8) * 128 + (r >> 3) * 128 + (r & 7) * 16);
 }
 
+// Packed vectors g0 .. g0+rows-1 of a tile (staged at `src`) to their token slots when the output has
+// several rows: one bulk store when the group stays inside a row and is aligned, word copies otherwise.
+template <int VB, int WG>
+__device__ __noinline__ void store_rows_impl(uint8_t* blocks_out, int64_t tokens_per_row, int64_t row_capacity,
+                                             int64_t position, int64_t g0, int rows, const uint8_t* src,
+                                             int lane, int wg, bool leader) {
+    auto slot_of = [&](int64_t v) -> int64_t {
+        const int64_t r = v / tokens_per_row;
+        return r * row_capacity + position + (v - r * tokens_per_row);
+    };
+    const int64_t s0 = slot_of(g0);
+    const bool contig = slot_of(g0 + rows - 1) == s0 + rows - 1;         // the group stays inside one row
+    uint8_t* dst = blocks_out + s0 * VB;
+    if (rows == 32 && contig && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+        if (leader) bulk_store(dst, sm_addr(src), 32u * VB);
+    } else if (contig) {
+        for (int c = wg * 32 + lane; c < rows * VB / 4; c += 32 * WG)
+            reinterpret_cast<uint32_t*>(dst)[c] = reinterpret_cast<const uint32_t*>(src)[c];
+    } else if (lane < rows) {                                            // vectors of several rows: one lane each
+        uint32_t* d32p = reinterpret_cast<uint32_t*>(blocks_out + slot_of(g0 + lane) * VB);
+        for (int c = wg; c < VB / 4; c += WG) d32p[c] = reinterpret_cast<const uint32_t*>(src + lane * VB)[c];
+    }
+}
+
 template <int D, int BITS, bool QJL>
 struct CompressCfg {
     static constexpr int THREADS = compress_threads(D);
     static constexpr int WG = D / 32;                         // warpgroups = blocks per vector
-    static constexpr int BREP = QJL ? 1 : 16;                 // lane copies of the index-search table
     static constexpr int VB = (D / 32) * block_bytes(BITS);   // bytes per stored vector
     static constexpr int kRBytes = 4 * D * D;                 // [2D/8 chunks][D rows][16 B]
     static constexpr int kXBytes = (D / 8) * 2048;            // [D/8 chunks][128 rows][16 B]
     // One MMA per k-step with N = 2D ([R_hi ; R_lo] stacked), i.e. two accumulators (hi and lo products)
     // per tile.
     static constexpr int KG = 2;
-    // tensor-memory columns of one accumulator buffer (the sketch reuses it and needs jl_dim <= 128
-    // columns); without QJL two buffers alternate so the next tile's MMAs overlap this tile's epilogue
-    static constexpr int kBufCols = (KG * D < 128 && QJL) ? 128 : KG * D;
-    static constexpr int kTmemCols = QJL ? kBufCols : 2 * kBufCols;
+    // Index table: 129 buckets x 128 bytes at a fixed shared address.  Without the sketch an entry is
+    // {threshold, replicated count} (8 bytes, 16 lane copies); with it {threshold, replicated count,
+    // centroid below, centroid above} (16 bytes, 8 lane copies), which also yields the dequantised value
+    // the residual needs.
+    static constexpr int kEntry = QJL ? 16 : 8;
+    static constexpr int BREP = 128 / kEntry;
+    // Tensor memory.  Without the sketch two rotation accumulators (2D columns each) alternate.  With it:
+    // one rotation accumulator (the epilogue reads it out right away, which frees it for the next tile's
+    // rotation long before that tile's epilogue starts), the sketch accumulator, and the residual as
+    // the A operand of the sketch contraction: hi and lo float16 terms, two dims per 32-bit column.
+    static constexpr int kRotCols = KG * D;
+    static constexpr int kAccCol = kRotCols;
+    static constexpr int kEhiCol = kRotCols + 128;
+    static constexpr int kEloCol = kEhiCol + D / 2;
+    static constexpr int kTmemCols = QJL ? 512 : 2 * kRotCols;
     static constexpr int kOutBufs = QJL ? 1 : 2;              // packed-tile staging buffers
-    // Without the sketch the layout is pinned to absolute shared-memory addresses so that a bucket's
-    // address is a single AND-OR of the fused-multiply-add result: the index table sits on a 32 KB
-    // boundary, small buffers below it, the operand tiles above.
-    static constexpr uint32_t kTabAddr = 0x8000u;              // 129 buckets x 16 lane copies x 8 B
-    static constexpr uint32_t kRAddr = 0x10000u;
-    static constexpr int kXBufs = 3;                           // vector tiles in flight or in use
-    static constexpr uint32_t kLowBytes = kOutBufs * kTileVecs * VB + 64 + 128;
-    __host__ __device__ static size_t smem_bytes(int jl_dim) {
-        if (!QJL) return (size_t)kRAddr + kRBytes + kXBufs * (size_t)kXBytes;
-        size_t b = kRBytes + 2 * (size_t)kXBytes + (size_t)kOutBufs * kTileVecs * VB + 256 * 8 * BREP + 64 +
-                   kTileVecs * 4 + kTileVecs * WG * 4 + 128;
-        if (QJL) b += (size_t)(2 * D / 8) * jl_dim * 16 + (size_t)kTileVecs * (jl_dim / 8);
-        return b + 1024;                                      // the swizzled tiles sit on 1024-byte boundaries
+    static constexpr int kXBufs = QJL ? 2 : 3;                // vector tiles in flight or in use
+    // The layout is pinned to absolute shared-memory addresses so that a bucket's address is a single
+    // AND-OR of the fused-multiply-add result: the index table sits on a 32 KB boundary, small buffers
+    // below it, the operand tiles above.
+    //   no sketch:  [low: packed tiles, codebook, barriers][0x8000 table][0x10000 R][X x 3]
+    //   sketch:     [low: packed tile, codebook, barriers, exchange, first chunks of P'][0x8000 table]
+    //               [rest of P'][R][X x 2]          (P' = the split of P R^T, K-chunk by K-chunk)
+    static constexpr uint32_t kTabAddr = 0x8000u;
+    static constexpr uint32_t kTabBytes = 129 * 128;
+    static constexpr uint32_t kExchBytes = QJL ? 2 * kTileVecs * WG * 4 : 0;      // radii and residual norms
+    static constexpr uint32_t kPLowBytes = QJL ? 16384 : 0;
+    static constexpr uint32_t kLowBytes = kOutBufs * kTileVecs * VB + 64 + 128 + kExchBytes + kPLowBytes;
+    static constexpr uint32_t kPHiAddr = 0xC100u;
+    static constexpr uint32_t kPHiMax = (2 * D / 8 > 8 ? 2 * D / 8 - 8 : 0) * 2048;   // at jl_dim 128
+    static constexpr uint32_t kRAddr = QJL ? kPHiAddr + kPHiMax : 0x10000u;
+    static constexpr uint32_t kXAddr = (kRAddr + kRBytes + 1023u) & ~1023u;
+    __host__ __device__ static size_t smem_bytes() { return (size_t)kXAddr + kXBufs * (size_t)kXBytes; }
+    // K chunks of P' that live in the low region (an even number: a k-step reads two neighbours)
+    __host__ __device__ static int p_low_chunks(int jl_dim) {
+        if (!QJL) return 0;
+        const int lbo = (jl_dim / 8) * 128, total = 2 * D / 8;
+        int n = (int)(kPLowBytes / lbo) & ~1;
+        return n < total ? n : total;
     }
 };
 
 template <int D, int BITS, bool QJL>
-__global__ void __launch_bounds__(compress_launch_threads(D, QJL), 1)
+__global__ void __launch_bounds__(compress_launch_threads(D), 1)
 pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x_map) {
     using C = CompressCfg<D, BITS, QJL>;
     constexpr int THREADS = C::THREADS;
@@ -152,77 +211,73 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
     const int M = QJL ? p.jl_dim : 0;
 
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    uint8_t *Rb, *Xa, *Xb, *outs0, *Pb = nullptr, *bits_s = nullptr;
-    uint2* bucket_s;
-    float *cb_s, *escale = nullptr, *enorm2 = nullptr;
-    uint64_t* mbar;
-    if (QJL) {
-        uint8_t* sp = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-        Rb = sp;                            sp += C::kRBytes;
-        Xa = sp;                            sp += C::kXBytes;      // vector tile, then residual hi term
-        Xb = sp;                            sp += C::kXBytes;      // residual lo term
-        outs0 = sp;                         sp += C::kOutBufs * kTileVecs * VB;
-        bucket_s = reinterpret_cast<uint2*>(sp);  sp += 256 * 8 * BREP;
-        cb_s = reinterpret_cast<float*>(sp);      sp += 64;
-        escale = reinterpret_cast<float*>(sp);    sp += kTileVecs * 4;
-        enorm2 = reinterpret_cast<float*>(sp);    sp += kTileVecs * WG * 4;
-        mbar = reinterpret_cast<uint64_t*>(sp);   sp += 128;
-        Pb = sp;                            sp += (2 * D / 8) * M * 16;
-        bits_s = sp;
-    } else {
-        const uint32_t base = sm_addr(smem_raw);
-        uint8_t* sp = smem_raw + ((128u - (base & 127u)) & 127u);
-        // the dynamic window must start low enough for the small buffers to end below the table
-        if (sm_addr(sp) + C::kLowBytes > C::kTabAddr) {
-            if (threadIdx.x == 0) atomicOr(&g_compress_error, 2u);
-            return;
-        }
-        outs0 = sp;                         sp += C::kOutBufs * kTileVecs * VB;
-        cb_s = reinterpret_cast<float*>(sp);      sp += 64;
-        mbar = reinterpret_cast<uint64_t*>(sp);
-        uint8_t* zero = smem_raw - base;           // generic address of shared address 0
-        bucket_s = reinterpret_cast<uint2*>(zero + C::kTabAddr);
-        Rb = zero + C::kRAddr;
-        Xa = Rb + C::kRBytes;
-        Xb = Xa + C::kXBytes;
+    const uint32_t base = sm_addr(smem_raw);
+    uint8_t* sp = smem_raw + ((128u - (base & 127u)) & 127u);
+    // the dynamic window must start low enough for the small buffers to end below the table
+    if (sm_addr(sp) + C::kLowBytes > C::kTabAddr) {
+        if (threadIdx.x == 0) atomicOr(&g_compress_error, 2u);
+        return;
     }
+    uint8_t* outs0 = sp;                        sp += C::kOutBufs * kTileVecs * VB;
+    float* cb_s = reinterpret_cast<float*>(sp); sp += 64;
+    uint64_t* mbar = reinterpret_cast<uint64_t*>(sp);  sp += 128;
+    float* exch_d = reinterpret_cast<float*>(sp);       // [128][WG] radii x 4096 of the tile's blocks
+    float* exch_n = exch_d + kTileVecs * WG;            // [128][WG] squared residual norms
+    sp += C::kExchBytes;
+    uint8_t* p_low = sp;                                // first K chunks of P'
+    uint8_t* zero = smem_raw - base;                    // generic address of shared address 0
+    uint8_t* bucket_s = zero + C::kTabAddr;
+    uint8_t* p_high = zero + C::kPHiAddr;
+    uint8_t* Rb = zero + C::kRAddr;
+    uint8_t* Xa = zero + C::kXAddr;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(mbar) + 96);
     volatile uint32_t* abort_s = reinterpret_cast<volatile uint32_t*>(reinterpret_cast<uint8_t*>(mbar) + 100);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wg = warp >> 2;                                   // block (32 output dims) this thread owns
     const int row = (warp & 3) * 32 + lane;                     // vector of the tile = TMEM lane
+    const int n_plow = C::p_low_chunks(M);
+    const uint32_t lbo_p = (uint32_t)(M / 8) * 128;             // bytes between K chunks of P'
+    auto p_chunk = [&](int c) -> uint8_t* {
+        return c < n_plow ? p_low + (size_t)c * lbo_p : p_high + (size_t)(c - n_plow) * lbo_p;
+    };
 
-    // ---- one-time set-up: split matrices, tables, barrier, tensor memory
+    // ---- one-time set-up: split matrices, tables, barriers, tensor memory
     for (int id = tid; id < D * (2 * D / 8); id += blockDim.x) {
         const int n = ((id >> 5) % (D / 8)) * 8 + (id & 7), kc = ((id >> 5) / (D / 8)) * 4 + ((id >> 3) & 3);
-        {               // B tile [2D rows][K = D]: the lo term's rows follow the hi term's (N = 2D)
-            const int half = kc / (D / 8), kk = kc % (D / 8);
-            cp_async_16(Rb + chunk_off(2 * D, half * D + n, kk), p.rot_split + (size_t)n * 2 * D + kc * 8);
-        }
+        // B tile [2D rows][K = D]: the lo term's rows follow the hi term's (N = 2D)
+        const int half = kc / (D / 8), kk = kc % (D / 8);
+        cp_async_16(Rb + chunk_off(2 * D, half * D + n, kk), p.rot_split + (size_t)n * 2 * D + kc * 8);
     }
     if (QJL) {
-        const int m8 = M >= 8 ? M / 8 : 1;
-        for (int id = tid; id < M * (2 * D / 8); id += THREADS) {
-            const int n = ((id >> 5) % m8) * 8 + (id & 7), kc = ((id >> 5) / m8) * 4 + ((id >> 3) & 3);
-            cp_async_16(Pb + chunk_off(M, n, kc), p.jl_split + (size_t)n * 2 * D + kc * 8);
+        // P' [M rows][K = 2D]: chunk kc holds halves 8kc .. 8kc+7 of every row (hi term first, then lo)
+        for (int id = tid; id < M * (2 * D / 8); id += blockDim.x) {
+            const int n = id % M, kc = id / M;
+            cp_async_16(p_chunk(kc) + (n >> 3) * 128 + (n & 7) * 16, p.jl_split + (size_t)n * 2 * D + kc * 8);
         }
     }
     if (tid < 16) cb_s[tid] = p.cb[tid < NLEV ? tid : 0];
-    for (int e = tid; e < (QJL ? 256 : 129) * BREP; e += blockDim.x) {
+    for (int e = tid; e < 129 * BREP; e += blockDim.x) {
         const int b = e / BREP;
         const int k = b < 132 ? b : 131;          // buckets past 128 only see out-of-range garbage
-        // without the sketch the count is replicated into every index field of the word, so packing
-        // a coordinate is one AND-OR with that field's mask
-        const uint32_t rep = QJL ? 1u : (BITS == 4 ? 0x11111111u : 0x55555555u);
-        bucket_s[e] = make_uint2(__float_as_uint(p.bucket_t[k]), p.bucket_base[k] * rep);
+        // the count is replicated into every index field of the word, so packing a coordinate is one
+        // AND-OR with that field's mask
+        const uint32_t rep = BITS == 4 ? 0x11111111u : 0x55555555u;
+        const uint32_t cnt = p.bucket_base[k];
+        if (QJL) {
+            const float below = p.cb[cnt < NLEV ? cnt : NLEV - 1], above = p.cb[cnt + 1 < NLEV ? cnt + 1 : NLEV - 1];
+            reinterpret_cast<uint4*>(bucket_s)[e] =
+                make_uint4(__float_as_uint(p.bucket_t[k]), cnt * rep, __float_as_uint(below), __float_as_uint(above));
+        } else {
+            reinterpret_cast<uint2*>(bucket_s)[e] = make_uint2(__float_as_uint(p.bucket_t[k]), cnt * rep);
+        }
     }
-    const uint2* bucket_lane = bucket_s + (lane % BREP);
-    const uint32_t tab_lane = C::kTabAddr | ((uint32_t)(lane & 15) << 3);     // this lane's copy
+    const uint32_t tab_lane = C::kTabAddr | ((uint32_t)(lane & (BREP - 1)) * C::kEntry);     // this lane's copy
+    // Barriers.  [0], [1]: MMAs of rotation accumulator 0 / 1 done; [2..4]: vector buffer landed;
+    // [5], [6]: rotation accumulator 0 / 1 read out by every epilogue thread; [7..9]: vector buffer
+    // consumed by its MMAs.  With the sketch there is one rotation accumulator ([0], [5]) and
+    // [1]: sketch MMAs done, [6]: residual written (and the previous tile's signs read) by every thread.
     if (tid == 0) {
-        // [0], [1]: MMAs of accumulator buffer 0 / 1 done; [2..4]: vector buffer 0 / 1 / 2 landed;
-        // [5], [6]: accumulator buffer 0 / 1 read out by every epilogue thread; [7..9]: vector buffer
-        // 0 / 1 / 2 consumed by its MMAs
         for (int i = 0; i < 5; ++i) mbar_init(sm_addr(mbar + i), 1);
         for (int i = 5; i < 7; ++i) mbar_init(sm_addr(mbar + i), THREADS);
         for (int i = 7; i < 10; ++i) mbar_init(sm_addr(mbar + i), 1);
@@ -237,49 +292,9 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-    uint32_t phase = 0;
     bool ok = true;
 
     const int64_t n_tiles = (p.n_vec + kTileVecs - 1) / kTileVecs;
-    // every tile is copied with the same per-thread chunk pattern: keep the offsets in registers
-    constexpr int NCH = kTileVecs * (D / 8) / THREADS;               // 16-byte chunks per thread
-    uint32_t ch_soff[NCH], ch_goff[NCH];
-#pragma unroll
-    for (int i = 0; i < NCH; ++i) {
-        const int id = tid + i * THREADS;
-        const int m = ((id >> 5) & 15) * 8 + (id & 7), kc = (id >> 9) * 4 + ((id >> 3) & 3);
-        ch_soff[i] = chunk_off(kTileVecs, m, kc);
-        ch_goff[i] = (uint32_t)(m * D + kc * 8);                     // in halves; row = goff / D
-    }
-    auto load_tile = [&](int64_t tile, uint8_t* dst) {
-        const int64_t v0 = tile * kTileVecs;
-        const uint32_t valid_halves = (uint32_t)min((int64_t)kTileVecs, p.n_vec - v0) * D;
-        const __half* src = p.x + v0 * D;
-#pragma unroll
-        for (int i = 0; i < NCH; ++i) {
-            if (ch_goff[i] < valid_halves) cp_async_16(dst + ch_soff[i], src + ch_goff[i]);
-            else *reinterpret_cast<uint4*>(dst + ch_soff[i]) = make_uint4(0, 0, 0, 0);   // rows past the end
-        }
-    };
-    uint8_t* const Xcur = Xa;      // (sketch flow) vector tile, then residual hi term
-    uint8_t* Elo = Xb;
-    // (sketch flow) rotation of one tile from the no-swizzle vector tile X: one MMA per k-step, N = 2D.
-    // Called by every lane of warp 0 with identical arguments; lane 0 issues.
-    auto issue_rotation = [&](const uint8_t* X, uint32_t tcol, uint64_t* done_bar) {
-        tc_fence_after();
-        constexpr uint32_t idesc = umma_idesc_f16(2 * D);
-        constexpr uint32_t kLboB = (2 * D / 8) * 128;
-        constexpr uint32_t ns_hi = (128u >> 4) | (1u << 14);               // 8-row groups 128 B apart, no swizzle
-        const uint32_t issue = lane == 0 ? 1u : 0u;
-        const uint32_t a_lo0 = ((sm_addr(X) >> 4) & 0x3FFFu) | ((2048u >> 4) << 16);
-        const uint32_t b_lo0 = ((sm_addr(Rb) >> 4) & 0x3FFFu) | ((kLboB >> 4) << 16);
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks)
-            umma_f16_split_pred(tmem_base + tcol, a_lo0 + (uint32_t)((ks * 2 * 2048) >> 4), ns_hi,
-                                b_lo0 + (uint32_t)((2 * ks * kLboB) >> 4), ns_hi, idesc, ks ? 1u : 0u, issue);
-        umma_commit_pred(sm_addr(done_bar), issue);
-        __syncwarp();
-    };
     // TMA fetch of one tile into vector buffer `buf` (rows past the end of x arrive as zeros)
     auto fetch_tile = [&](int64_t tile, int buf) {
         const uint32_t bar = sm_addr(mbar + 2 + buf), dst = sm_addr(Xa) + (uint32_t)buf * C::kXBytes;
@@ -288,27 +303,48 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
         for (int h = 0; h < D / 64; ++h) tma_load_2d(dst + h * 16384, &x_map, h * 64, (int)(tile * kTileVecs), bar);
     };
     const int64_t n_my = (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;      // tiles of this CTA
-    if (!QJL && warp == THREADS / 32) {
-        // ---- MMA warp: a tile's MMAs go out as soon as its vectors have landed and the accumulator
-        // buffer they write has been read out.  One MMA per k-step, N = 2D: columns [0, D) receive the
-        // products with R's hi term, [D, 2D) those with its lo term.  Every lane runs the loop (so the
-        // waits and the descriptor arithmetic stay warp-uniform); lane 0 issues.
+    if (warp == THREADS / 32) {
+        // ---- MMA warp.  A tile's rotation goes out as soon as its vectors have landed and the
+        // accumulator it writes has been read out: one MMA per k-step, N = 2D, columns [0, D) receive the
+        // products with R's hi term, [D, 2D) those with its lo term.  With the sketch, the contraction of
+        // tile i-1's residual (A operand in tensor memory) with P' follows the rotation of tile i.
+        // Every lane runs the loop (so the waits and the descriptor arithmetic stay warp-uniform); lane 0
+        // issues.
         constexpr uint32_t idesc = umma_idesc_f16(2 * D);
         constexpr uint32_t kLboB = (2 * D / 8) * 128;                     // K-chunk stride of the stacked R tile
         constexpr uint32_t a_hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // 8-row groups 1024 B apart, 128-B swizzle
         constexpr uint32_t b_hi = (128u >> 4) | (1u << 14);                // 8-row groups 128 B apart, no swizzle
         const uint32_t a_lo0 = ((sm_addr(Xa) >> 4) & 0x3FFFu) | (1u << 16);
         const uint32_t b_lo0 = ((sm_addr(Rb) >> 4) & 0x3FFFu) | ((kLboB >> 4) << 16);
+        const uint32_t issue = lane == 0 ? 1u : 0u;
+        auto issue_sketch = [&]() {
+            const uint32_t idesc_p = umma_idesc_f16(M);
+            const uint32_t acc = tmem_base + C::kAccCol;
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                const uint32_t ah = tmem_base + C::kEhiCol + ks * 8, al = tmem_base + C::kEloCol + ks * 8;
+                const uint32_t bh = ((sm_addr(p_chunk(2 * ks)) >> 4) & 0x3FFFu) | ((lbo_p >> 4) << 16);
+                const uint32_t bl = ((sm_addr(p_chunk(D / 8 + 2 * ks)) >> 4) & 0x3FFFu) | ((lbo_p >> 4) << 16);
+                umma_f16_ts_pred(acc, ah, bh, b_hi, idesc_p, ks ? 1u : 0u, issue);
+                umma_f16_ts_pred(acc, ah, bl, b_hi, idesc_p, 1u, issue);
+                umma_f16_ts_pred(acc, al, bh, b_hi, idesc_p, 1u, issue);
+            }
+            umma_commit_pred(sm_addr(mbar + 1), issue);
+        };
         uint32_t xb = 0, xuse = 0;                          // vector buffer of tile i and how often it was used
         for (int64_t i = 0; i < n_my && ok; ++i) {
-            const uint32_t b = (uint32_t)i & 1u, use = (uint32_t)(i >> 1);
+            const uint32_t b = QJL ? 0u : ((uint32_t)i & 1u);
             ok = mbar_wait(sm_addr(mbar + 2 + xb), xuse & 1u, abort_s, 32) && ok;
-            if (i >= 2) ok = mbar_wait(sm_addr(mbar + 5 + b), (use - 1u) & 1u, abort_s, 32) && ok;
+            if (QJL) {
+                if (i >= 1) ok = mbar_wait(sm_addr(mbar + 5), (uint32_t)(i - 1) & 1u, abort_s, 32) && ok;
+            } else {
+                if (i >= 2) ok = mbar_wait(sm_addr(mbar + 5 + b), ((uint32_t)(i >> 1) - 1u) & 1u, abort_s, 32) && ok;
+            }
             if (!ok) break;
             tc_fence_after();
             if (lane == 0) {
                 const uint32_t a_lo = a_lo0 + xb * (uint32_t)(C::kXBytes >> 4);
-                const uint32_t acc = tmem_base + b * C::kBufCols;
+                const uint32_t acc = tmem_base + b * C::kRotCols;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     // a k-step is 32 B further inside the swizzled 128-byte row, 64 halves fill a 16 KB box
@@ -319,10 +355,25 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
                 umma_commit(sm_addr(mbar + 7 + xb));        // vector buffer free for the next copy
             }
             __syncwarp();
+            if (QJL && i >= 1) {
+                ok = mbar_wait(sm_addr(mbar + 6), (uint32_t)(i - 1) & 1u, abort_s, 32) && ok;
+                if (!ok) break;
+                tc_fence_after();
+                issue_sketch();
+                __syncwarp();
+            }
             if (++xb == C::kXBufs) { xb = 0; ++xuse; }
         }
+        if (QJL && ok && n_my > 0) {                        // the last tile's sketch
+            ok = mbar_wait(sm_addr(mbar + 6), (uint32_t)(n_my - 1) & 1u, abort_s, 32) && ok;
+            if (ok) {
+                tc_fence_after();
+                issue_sketch();
+                __syncwarp();
+            }
+        }
         if (!ok && lane == 0) { *abort_s = 1u; atomicOr(&g_compress_error, 1u); }
-    } else if (!QJL && warp == THREADS / 32 + 1) {
+    } else if (warp == THREADS / 32 + 1) {
         // ---- copy warp: keeps kXBufs tiles in flight or in use; a buffer is refilled as soon as the
         // MMAs that read it have completed
         uint32_t xb = 0, xuse = 0;
@@ -336,53 +387,53 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
         if (!ok && lane == 0) { *abort_s = 1u; atomicOr(&g_compress_error, 1u); }
     } else {
 
+    // ---- epilogue warps
+    // token slot of input vector v in the output tensors
+    const bool one_row = p.tokens_per_row >= p.n_vec;            // no 64-bit division on the common path
+    auto slot_of = [&](int64_t v) -> int64_t {
+        if (one_row) return p.position + v;
+        const int64_t r = v / p.tokens_per_row;
+        return r * p.row_capacity + p.position + (v - r * p.tokens_per_row);
+    };
+    // signs of the sketch of the tile whose vector `row` sits in token slot `slot`: every thread reads 32
+    // projections of its vector from the sketch accumulator and stores their sign bits
+    auto store_signs = [&](int64_t slot, bool valid) {
+        const int M8 = M / 8;
+        for (int cg = wg; cg * 32 < M; cg += WG) {
+            float pr[32];
+            tmem_ld32(pr, tmem_lane + C::kAccCol + cg * 32);
+            uint32_t w = 0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) w |= (pr[j] >= 0.f ? 1u : 0u) << j;
+            if (!valid) continue;
+            uint8_t* dst = p.qjl_bits_out + slot * M8 + cg * 4;
+            if (cg * 32 + 32 <= M && (reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
+                *reinterpret_cast<uint32_t*>(dst) = w;
+            } else {
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    if (cg * 32 + k * 8 < M) dst[k] = (uint8_t)(w >> (8 * k));
+            }
+        }
+    };
+    auto store_rows = [&](int64_t g0, int rows, const uint8_t* src, int ln, int w, bool lead) {
+        store_rows_impl<VB, WG>(p.blocks_out, p.tokens_per_row, p.row_capacity, p.position, g0, rows, src, ln, w, lead);
+    };
     uint32_t it = 0;
+    int64_t slot_prev = 0;
+    bool valid_prev = false;
     for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
         const int64_t v0 = tile * kTileVecs;
         const int n_valid = (int)min((int64_t)kTileVecs, p.n_vec - v0);
-        const uint32_t tcol = QJL ? 0u : (it & 1u) * C::kBufCols;     // this tile's accumulator buffer
-        if (QJL) {
-            load_tile(tile, Xcur);
-            cp_async_commit();
-            cp_async_wait<0>();
-            fence_async_smem();      // the tensor core reads shared memory through the async proxy
-            __syncthreads();
-            if (warp == 0) issue_rotation(Xcur, 0u, mbar);
-            // power-of-two scale per vector so the residual split stays in float16 range:
-            // |e_j| < 32 * max|x_j|, scaled to below 2^15.  (Reads the vector tile while the MMAs run.)
-            constexpr int PARTS = THREADS / kTileVecs;                  // threads per row
-            const int r = tid / PARTS, part = tid % PARTS;
-            float vmax = 0.f;
-#pragma unroll
-            for (int i = 0; i < D / 8 / PARTS; ++i) {
-                const uint4 u = *reinterpret_cast<const uint4*>(Xcur + chunk_off(kTileVecs, r, part * (D / 8 / PARTS) + i));
-                const __half2* h = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    float2 f = __half22float2(__habs2(h[k]));
-                    vmax = fmaxf(vmax, fmaxf(f.x, f.y));
-                }
-            }
-#pragma unroll
-            for (int o = 1; o < PARTS; o <<= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
-            if (part == 0) {
-                const uint32_t be = __float_as_uint(vmax) >> 23;
-                escale[r] = (vmax > 0.f) ? __uint_as_float((263u - be) << 23) : 1.0f;
-            }
-            __syncthreads();
-            ok = mbar_wait(sm_addr(mbar), phase) && ok;
-            phase ^= 1u;
-            tc_fence_after();
-        } else {
-            // The issuing warp runs ahead; accumulator buffers alternate, so their barriers flip parity
-            // every second tile.
-            ok = mbar_wait(sm_addr(mbar + (it & 1u)), (it >> 1) & 1u, abort_s) && ok;
-            tc_fence_after();
-        }
+        const uint32_t rb = QJL ? 0u : (it & 1u);                         // this tile's rotation accumulator
+        // The issuing warp runs ahead; without the sketch the accumulators alternate, so their barriers
+        // flip parity every second tile.
+        ok = mbar_wait(sm_addr(mbar + rb), (QJL ? it : (it >> 1)) & 1u, abort_s) && ok;
+        tc_fence_after();
         uint8_t* outs = outs0 + (QJL ? 0u : (it & 1u) * (uint32_t)(kTileVecs * VB));
-        const uint32_t tmem_tile = tmem_lane + tcol;
+        const uint32_t tmem_tile = tmem_lane + rb * C::kRotCols;
 
-        // ---- epilogue: this thread owns vector `row`, block `wg`
+        // ---- this thread owns vector `row`, block `wg`
         float2 v2[16];                  // 4096 * rotated coordinates, pairs (2k, 2k+1); the scale is a
         tmem_ld32(v2, tmem_tile + wg * 32);  // power of two: every rounding below commutes with it
 #pragma unroll
@@ -392,10 +443,9 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
 #pragma unroll
             for (int k = 0; k < 16; ++k) v2[k] = add2(v2[k], part[k]);
         }
-        if (!QJL) {                      // this thread's part of the accumulator buffer is in registers
-            tc_fence_before();
-            mbar_arrive(sm_addr(mbar + 5 + (it & 1u)));
-        }
+        // this thread's part of the accumulator is in registers
+        tc_fence_before();
+        mbar_arrive(sm_addr(mbar + 5 + rb));
         // numpy's float32 axis-reduction order: r[j] over j, j+8, j+16, j+24 (products rounded
         // separately), then a balanced tree
         float2 r2[4];
@@ -418,16 +468,13 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
         const float dsafe = zero ? 1.f : d_raw;
         const float rinv = __frcp_rn(dsafe);
         const float2 rinv2 = make_float2(rinv, rinv), negd2 = make_float2(-dsafe, -dsafe);
-        // bucket key in the low mantissa bits of 64 y + magic: with the sketch  round(64 y) + 128  in bits
-        // 0..7; without it the unit in the last place is 2^-7 and bits 7..14 hold  floor(64 y + 64)
-        const float magic = QJL ? 8388672.f : 98368.f;
-        const float2 c64 = make_float2(64.f, 64.f), cmagic = make_float2(magic, magic);
-        const float es = QJL ? escale[row] * (1.0f / 4096.0f) : 1.f;
+        // bucket key in the mantissa bits of 64 y + 98368: the unit in the last place is 2^-7 and bits
+        // 7..14 hold  floor(64 y + 64)
+        const float2 c64 = make_float2(64.f, 64.f), cmagic = make_float2(98368.f, 98368.f);
         float en2 = 0.f;
         uint32_t packed[BITS];                                        // 32 indices, low index first
 #pragma unroll
         for (int w = 0; w < BITS; ++w) packed[w] = 0u;
-        uint32_t ehi[16], elo[16];
         float* v = reinterpret_cast<float*>(&v2[0]);
 #pragma unroll
         for (int k = 0; k < 16; ++k) {
@@ -438,35 +485,47 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
             for (int e = 0; e < 2; ++e) {
                 const int j = 2 * k + e;
                 const float dj = e ? dir.y : dir.x;
-                uint2 be;
-                if (!QJL) {
-                    const uint32_t a = (__float_as_uint(e ? u.y : u.x) & 0x7F80u) | tab_lane;
+                const uint32_t a = (__float_as_uint(e ? u.y : u.x) & 0x7F80u) | tab_lane;
+                // field = count of thresholds in lower buckets, plus one if y is above this bucket's
+                const uint32_t sh = (j * BITS) & 31;
+                uint32_t& pw = packed[(j * BITS) >> 5];
+                if (QJL) {
+                    uint4 be;
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(be.x), "=r"(be.y), "=r"(be.z), "=r"(be.w) : "r"(a));
+                    const bool up = dj > __uint_as_float(be.x);
+                    pw |= be.y & (((1u << BITS) - 1u) << sh);
+                    if (up) pw += 1u << sh;
+                    // residual in rotated space (scaled by 4096): coordinate minus radius * centroid
+                    const float ee = v[j] - __fmul_rn(dq, __uint_as_float(up ? be.w : be.z));
+                    en2 = fmaf(ee, ee, en2);
+                    v[j] = ee;
+                } else {
+                    uint2 be;
                     asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];\n" : "=r"(be.x), "=r"(be.y) : "r"(a));
-                    // field = count of thresholds in lower buckets, plus one if y is above this bucket's
-                    const uint32_t sh = (j * BITS) & 31;
-                    uint32_t& pw = packed[(j * BITS) >> 5];
                     pw |= be.y & (((1u << BITS) - 1u) << sh);
                     asm("{\n\t.reg .pred p;\n\t"
                         "setp.gt.f32 p, %1, %2;\n\t"
                         "@p add.u32 %0, %0, %3;\n\t}\n"
                         : "+r"(pw)
                         : "f"(dj), "f"(__uint_as_float(be.x)), "r"(1u << sh));
-                    continue;
-                }
-                const uint32_t bk = __float_as_uint(e ? u.y : u.x) & 0xFFu;
-                be = bucket_lane[bk * BREP];
-                const uint32_t id = be.y + ((dj > __uint_as_float(be.x)) ? 1u : 0u);
-                packed[(j * BITS) >> 5] |= id << ((j * BITS) & 31);
-                if (QJL) {
-                    const float ee = (v[j] - __fmul_rn(dq, cb_s[zero ? 0u : id])) * es;
-                    en2 = fmaf(ee, ee, en2);
-                    v[j] = ee;
                 }
             }
         }
         if (zero) {                                                   // all-zero block: indices 0
 #pragma unroll
             for (int w = 0; w < BITS; ++w) packed[w] = 0u;
+        }
+        const int q = warp & 3;                                  // row group = TMEM lane quarter
+        const bool leader = wg == 0 && lane == 0;
+        if (QJL) {
+            // the four blocks of a vector live in four warps: exchange radii (for one power-of-two scale
+            // per vector) and squared residual norms through shared memory.  The row group meets at a
+            // barrier, before which its leader makes sure the bulk store that last read the packed-tile
+            // buffer is done.
+            exch_d[row * WG + wg] = d_raw;
+            exch_n[row * WG + wg] = en2;
+            if (leader) bulk_wait_read();
+            group_barrier(5u + q, 32u * WG);
         }
         {
             // 2 + 4*BITS bytes at a 2-byte aligned offset: whole words where the alignment allows
@@ -484,131 +543,80 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
                 *reinterpret_cast<uint16_t*>(ob + 4 * BITS) = (uint16_t)(packed[BITS - 1] >> 16);
             }
         }
+        int64_t slot = 0;                  // token slot of this thread's vector (padding rows: the last vector's)
+        if (QJL) slot = slot_of(v0 + row < p.n_vec ? v0 + row : p.n_vec - 1);
         if (QJL) {
-            // residual as two float16 terms, written in operand layout: 4 chunks of this block
+            // One power-of-two scale per vector keeps both residual terms inside the float16 range:
+            // |e_j| < 2 * (largest block radius), scaled to below 2^15.
+            float dmax = 0.f, n2 = 0.f;
+#pragma unroll
+            for (int k = 0; k < WG; ++k) {
+                dmax = fmaxf(dmax, exch_d[row * WG + k]);
+                n2 += exch_n[row * WG + k];
+            }
+            const uint32_t be = __float_as_uint(dmax) >> 23;
+            const float es = be ? __uint_as_float((267u - be) << 23) : 1.0f;
+            if (wg == 0 && row < n_valid)
+                p.qjl_norm_out[slot] = __float2half_rn(fminf(sqrtf(n2) * (1.0f / 4096.0f), 65504.0f));
+            uint32_t ehi[16], elo[16];
 #pragma unroll
             for (int j = 0; j < 32; j += 2) {
-                const __half2 h = __floats2half2_rn(v[j], v[j + 1]);
+                const float a0 = v[j] * es, a1 = v[j + 1] * es;
+                const __half2 h = __floats2half2_rn(a0, a1);
                 const float2 f = __half22float2(h);
                 ehi[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
-                elo[j >> 1] = pack_half2(v[j] - f.x, v[j + 1] - f.y);
+                elo[j >> 1] = pack_half2(a0 - f.x, a1 - f.y);
             }
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const uint32_t off = chunk_off(kTileVecs, row, wg * 4 + c);
-                *reinterpret_cast<uint4*>(Xcur + off) = make_uint4(ehi[4 * c], ehi[4 * c + 1], ehi[4 * c + 2], ehi[4 * c + 3]);
-                *reinterpret_cast<uint4*>(Elo + off) = make_uint4(elo[4 * c], elo[4 * c + 1], elo[4 * c + 2], elo[4 * c + 3]);
-            }
-            enorm2[row * WG + wg] = en2;
-            fence_async_smem();
-            tc_fence_before();
-            __syncthreads();
-            // ---- sign sketch: proj[vec][i] = sum_j e[vec][j] * P'[i][j], three float16 product terms
-            if (warp == 0) {                       // every lane runs the loop, lane 0 issues
+            // the residual columns and the sketch accumulator are in use until the previous tile's
+            // sketch MMAs have completed
+            if (it >= 1) {
+                ok = mbar_wait(sm_addr(mbar + 1), (it - 1u) & 1u, abort_s) && ok;
                 tc_fence_after();
-                const uint32_t issue = lane == 0 ? 1u : 0u;
-                const uint32_t lbo_p = (uint32_t)(M / 8) * 128;
-                const uint32_t idesc = umma_idesc_f16(M);
-                constexpr uint32_t ns_hi = (128u >> 4) | (1u << 14);
-                const uint32_t ah0 = ((sm_addr(Xcur) >> 4) & 0x3FFFu) | ((2048u >> 4) << 16);
-                const uint32_t al0 = ((sm_addr(Elo) >> 4) & 0x3FFFu) | ((2048u >> 4) << 16);
-                const uint32_t pb0 = ((sm_addr(Pb) >> 4) & 0x3FFFu) | ((lbo_p >> 4) << 16);
-#pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t ao = (uint32_t)((ks * 2 * 2048) >> 4);
-                    const uint32_t bh = pb0 + ((2 * ks * lbo_p) >> 4), bl = pb0 + (((D / 8 + 2 * ks) * lbo_p) >> 4);
-                    umma_f16_split_pred(tmem_base + tcol, ah0 + ao, ns_hi, bh, ns_hi, idesc, ks ? 1u : 0u, issue);
-                    umma_f16_split_pred(tmem_base + tcol, ah0 + ao, ns_hi, bl, ns_hi, idesc, 1u, issue);
-                    umma_f16_split_pred(tmem_base + tcol, al0 + ao, ns_hi, bh, ns_hi, idesc, 1u, issue);
-                }
-                umma_commit_pred(sm_addr(mbar), issue);
-                __syncwarp();
             }
-            ok = mbar_wait(sm_addr(mbar), phase) && ok;
-            phase ^= 1u;
-            tc_fence_after();
-            if (wg * 32 < M) {
-                float pr[32];
-                tmem_ld32(pr, tmem_tile + wg * 32);
-                uint32_t w = 0;
-#pragma unroll
-                for (int j = 0; j < 32; ++j) w |= (pr[j] >= 0.f ? 1u : 0u) << j;
-                uint8_t* dst = bits_s + row * (M / 8) + wg * 4;
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    if (wg * 32 + k * 8 < M) dst[k] = (uint8_t)(w >> (8 * k));
-            }
+            tmem_store16(tmem_lane + C::kEhiCol + wg * 16, ehi);
+            tmem_store16(tmem_lane + C::kEloCol + wg * 16, elo);
+            tmem_store_wait();
+            if (it >= 1) store_signs(slot_prev, valid_prev);
+            tc_fence_before();
+            mbar_arrive(sm_addr(mbar + 6));
+            slot_prev = slot;
+            valid_prev = row < n_valid;
         }
-        if (!QJL) {
-            // ---- the warps that share 32 vectors (one per block) meet at their own barrier; its first
-            // lane then sends the 32 packed vectors off with one bulk store.  No CTA-wide barrier.
-            const int q = warp & 3;                                  // row group = TMEM lane quarter
-            const bool leader = wg == 0 && lane == 0;
-            fence_async_smem();                  // the bulk store reads `outs` through the async proxy
-            if (leader) bulk_wait_read();        // the store that last read the other staging buffer is done
-            // the barrier also votes: a wait that gave up anywhere in the CTA stops every group
-            if (group_barrier_any(1u + q, 32u * WG, !ok || *abort_s != 0u)) {
-                *abort_s = 1u;
-                break;
-            }
-            const int rows = min(32, n_valid - 32 * q);
-            if (rows > 0) {
-                uint8_t* dst = p.blocks_out + (v0 + 32 * q) * VB;
-                const uint8_t* src = outs + 32 * q * VB;
+        // ---- the warps that share 32 vectors (one per block) meet at their own barrier; its first
+        // lane then sends the 32 packed vectors off with one bulk store.  No CTA-wide barrier.
+        fence_async_smem();                  // the bulk store reads `outs` through the async proxy
+        if (!QJL && leader) bulk_wait_read();        // the store that last read the other staging buffer is done
+        // the barrier also votes: a wait that gave up anywhere in the CTA stops every group
+        if (group_barrier_any(1u + q, 32u * WG, !ok || *abort_s != 0u)) {
+            *abort_s = 1u;
+            break;
+        }
+        const int rows = min(32, n_valid - 32 * q);
+        if (rows > 0) {
+            const int64_t g0 = v0 + 32 * q;
+            const uint8_t* src = outs + 32 * q * VB;
+            if (one_row) {
+                uint8_t* dst = p.blocks_out + (p.position + g0) * VB;
                 if (rows == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
                     if (leader) bulk_store(dst, sm_addr(src), 32u * VB);
                 } else {                                             // ragged end or odd token offset
                     for (int c = wg * 32 + lane; c < rows * VB / 4; c += 32 * WG)
                         reinterpret_cast<uint32_t*>(dst)[c] = reinterpret_cast<const uint32_t*>(src)[c];
                 }
-            }
-            continue;
-        }
-        if (!ok) *abort_s = 1u;                  // a wait gave up: the whole CTA stops after this barrier
-        tc_fence_before();
-        __syncthreads();
-        if (*abort_s) break;
-
-        // ---- coalesced copy-out of the tile
-        {
-            const int n_bytes = n_valid * VB;                       // multiple of 4
-            uint8_t* dst = p.blocks_out + v0 * VB;
-            if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-                const int n16 = n_bytes / 16;
-                for (int c = tid; c < n16; c += THREADS)
-                    reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(outs)[c];
-                const int rest4 = (n_bytes & 15) >> 2;              // ragged end in 4-byte words
-                if (tid < rest4)
-                    reinterpret_cast<uint32_t*>(dst)[n16 * 4 + tid] = reinterpret_cast<const uint32_t*>(outs)[n16 * 4 + tid];
-            } else {                                                // appended at an odd token offset
-                for (int c = tid; c < n_bytes / 4; c += THREADS)
-                    reinterpret_cast<uint32_t*>(dst)[c] = reinterpret_cast<const uint32_t*>(outs)[c];
-            }
-            if (QJL) {
-                const int M8 = M / 8;
-                uint8_t* bd = p.qjl_bits_out + v0 * M8;
-                const int nb = n_valid * M8;
-                if ((M8 & 3) == 0) {
-                    for (int c = tid; c < nb / 4; c += THREADS)
-                        reinterpret_cast<uint32_t*>(bd)[c] = reinterpret_cast<const uint32_t*>(bits_s)[c];
-                } else {
-                    for (int c = tid; c < nb; c += THREADS) bd[c] = bits_s[c];
-                }
-                for (int r = tid; r < n_valid; r += THREADS) {
-                    float n2 = 0.f;
-#pragma unroll
-                    for (int k = 0; k < WG; ++k) n2 += enorm2[r * WG + k];
-                    p.qjl_norm_out[v0 + r] = __float2half_rn(fminf(sqrtf(n2) / escale[r], 65504.0f));
-                }
+            } else {
+                store_rows(g0, rows, src, lane, wg, leader);
             }
         }
-        __syncthreads();   // outs and the tiles are rewritten by the next iteration
     }
-    cp_async_wait<0>();
-    if (!QJL && wg == 0 && lane == 0) bulk_wait_all();
+    if (QJL && ok && it >= 1 && !*abort_s) {             // the last tile's signs
+        ok = mbar_wait(sm_addr(mbar + 1), (it - 1u) & 1u, abort_s) && ok;
+        tc_fence_after();
+        if (ok) store_signs(slot_prev, valid_prev);
+    }
+    if (wg == 0 && lane == 0) bulk_wait_all();
     if (!ok && lane == 0) atomicOr(&g_compress_error, 1u);
     }   // epilogue warps
-    if (!QJL && *abort_s && tid == 0) {          // give tile copies still in flight time to land
+    if (*abort_s && tid == 0) {          // give tile copies still in flight time to land
         const long long t0 = clock64();
         while (clock64() - t0 < (1ll << 20)) {}
     }
@@ -650,7 +658,7 @@ static int launch_compress(const CompressParams& p, cudaStream_t stream) {
     if (cudaGetDevice(&dev) != cudaSuccess) return PQ_ERR_CUDA;
     if (sm_count == 0 && cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
         return PQ_ERR_CUDA;
-    const size_t smem = C::smem_bytes(p.jl_dim);
+    const size_t smem = C::smem_bytes();
     auto kern = pq_compress_kernel<D, BITS, QJL>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return PQ_ERR_CUDA;
@@ -659,11 +667,9 @@ static int launch_compress(const CompressParams& p, cudaStream_t stream) {
     const int grid = (int)(n_tiles < sm_count ? n_tiles : sm_count);
     CUtensorMap x_map;
     memset(&x_map, 0, sizeof(x_map));
-    if (!QJL) {
-        const int st = make_x_map(p, D, &x_map);
-        if (st != PQ_OK) return st;
-    }
-    kern<<<grid, compress_launch_threads(D, QJL), smem, stream>>>(p, x_map);
+    const int st = make_x_map(p, D, &x_map);
+    if (st != PQ_OK) return st;
+    kern<<<grid, compress_launch_threads(D), smem, stream>>>(p, x_map);
     return cudaGetLastError() == cudaSuccess ? PQ_OK : PQ_ERR_CUDA;
 }
 
@@ -685,13 +691,16 @@ extern "C" int pq_poll_device_errors(unsigned int* flags_out) {
     return PQ_OK;
 }
 
-extern "C" int pq_compress(const void* x, int64_t n_vec, int head_dim, int n_bits,
-                           const void* rot_split, const float* thresholds, const float* codebook,
-                           void* blocks_out,
-                           const void* jl_split, int jl_dim, void* qjl_bits_out, void* qjl_norm_out,
-                           void* stream) {
+extern "C" int pq_compress_rows(const void* x, int64_t n_rows, int64_t tokens_per_row, int64_t row_capacity,
+                                int64_t position, int head_dim, int n_bits,
+                                const void* rot_split, const float* thresholds, const float* codebook,
+                                void* blocks_out,
+                                const void* jl_split, int jl_dim, void* qjl_bits_out, void* qjl_norm_out,
+                                void* stream) {
     using namespace pq;
-    if (n_vec < 0) return PQ_ERR_BAD_SHAPE;
+    if (n_rows < 0 || tokens_per_row < 0 || position < 0 || row_capacity < position + tokens_per_row)
+        return PQ_ERR_BAD_SHAPE;
+    const int64_t n_vec = n_rows * tokens_per_row;
     if (n_vec > (int64_t)0x7FFFFF00) return PQ_ERR_TOO_LARGE;   // tile coordinates are 32-bit
     if (head_dim != 64 && head_dim != 128) return PQ_ERR_BAD_HEAD_DIM;
     if (n_bits != 2 && n_bits != 4) return PQ_ERR_BAD_BITS;
@@ -702,7 +711,7 @@ extern "C" int pq_compress(const void* x, int64_t n_vec, int head_dim, int n_bit
         if (jl_dim < 16 || jl_dim > 128 || (jl_dim % 16)) return PQ_ERR_BAD_JL_DIM;
         if (!qjl_bits_out || !qjl_norm_out) return PQ_ERR_NULL_POINTER;
         if (reinterpret_cast<uintptr_t>(jl_split) & 15) return PQ_ERR_MISALIGNED;
-        if (((jl_dim / 8) % 4 == 0) && (reinterpret_cast<uintptr_t>(qjl_bits_out) & 3)) return PQ_ERR_MISALIGNED;
+        if (reinterpret_cast<uintptr_t>(qjl_norm_out) & 1) return PQ_ERR_MISALIGNED;
     }
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(rot_split) & 15) ||
         (reinterpret_cast<uintptr_t>(blocks_out) & 3))
@@ -716,25 +725,25 @@ extern "C" int pq_compress(const void* x, int64_t n_vec, int head_dim, int n_bit
     p.qjl_bits_out = static_cast<uint8_t*>(qjl_bits_out);
     p.qjl_norm_out = static_cast<__half*>(qjl_norm_out);
     p.n_vec = n_vec;
+    p.tokens_per_row = tokens_per_row;
+    p.row_capacity = row_capacity;
+    p.position = position;
     p.jl_dim = qjl ? jl_dim : 0;
     // thresholds / codebook are small HOST tables; they travel as kernel parameters.
     const int nlev = 1 << n_bits;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const float* thr_h = thresholds;
-    const float* cb_h = codebook;
-    for (int i = 0; i < 16; ++i) p.cb[i] = i < nlev ? cb_h[i] : 0.f;
+    for (int i = 0; i < 16; ++i) p.cb[i] = i < nlev ? codebook[i] : 0.f;
     // bucket(y), evaluated exactly as the kernel does (one fused multiply-add, then mantissa bits):
-    // round(64 y) + 64 with the sketch, floor(64 y + 64) (after rounding to 1/128) without it
-    p.floor_buckets = qjl ? 0 : 1;
+    // floor(64 y + 64) after rounding to 1/128
     for (int k = 0; k < 132; ++k) { p.bucket_t[k] = 3.0e38f; p.bucket_base[k] = 0; }
     for (int i = 0; i < nlev - 1; ++i) {
-        const float u = fmaf(thr_h[i], 64.f, qjl ? 8388672.f : 98368.f);
+        const float u = fmaf(thresholds[i], 64.f, 98368.f);
         uint32_t bits;
         memcpy(&bits, &u, sizeof(bits));
-        const int kb = qjl ? (int)(bits & 0xFFu) : (int)((bits >> 7) & 0xFFu);
-        if (!(thr_h[i] > -1.0f && thr_h[i] < 1.0f) || kb > 130 || p.bucket_t[kb] != 3.0e38f)
+        const int kb = (int)((bits >> 7) & 0xFFu);
+        if (!(thresholds[i] > -1.0f && thresholds[i] < 1.0f) || kb > 130 || p.bucket_t[kb] != 3.0e38f)
             return PQ_ERR_BAD_SHAPE;      // thresholds out of range or two of them in one bucket
-        p.bucket_t[kb] = thr_h[i];
+        p.bucket_t[kb] = thresholds[i];
         for (int k = kb + 1; k < 132; ++k) p.bucket_base[k] += 1;
     }
 
@@ -747,4 +756,14 @@ extern "C" int pq_compress(const void* x, int64_t n_vec, int head_dim, int n_bit
     PQ_DISPATCH(128, 2)
 #undef PQ_DISPATCH
     return PQ_ERR_BAD_HEAD_DIM;
+}
+
+extern "C" int pq_compress(const void* x, int64_t n_vec, int head_dim, int n_bits,
+                           const void* rot_split, const float* thresholds, const float* codebook,
+                           void* blocks_out,
+                           const void* jl_split, int jl_dim, void* qjl_bits_out, void* qjl_norm_out,
+                           void* stream) {
+    if (n_vec < 0) return PQ_ERR_BAD_SHAPE;
+    return pq_compress_rows(x, 1, n_vec, n_vec, 0, head_dim, n_bits, rot_split, thresholds, codebook, blocks_out,
+                            jl_split, jl_dim, qjl_bits_out, qjl_norm_out, stream);
 }

@@ -24,6 +24,8 @@ SIGNATURES = {
     "pq_poll_device_errors": (c_int, [ctypes.POINTER(ctypes.c_uint)]),
     "pq_compress": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_float_p, c_float_p, c_void_p,
                             c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "pq_compress_rows": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_float_p,
+                                 c_float_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "pq_dequant": (c_int, [c_void_p, c_int64, c_int, c_int, c_float_p, c_void_p, c_void_p, c_int, c_void_p]),
     "pq_decode_attn": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64,
                                c_int, c_int, c_int, c_float_p, c_float_p, c_void_p, c_float,
@@ -37,6 +39,7 @@ SIGNATURES = {
     "pq_decode_attn_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int64, c_int, c_int]),
     "pq_decode_attn_default_splits": (c_int, [c_int, c_int, c_int, c_int64, c_int]),
     "pq_lse_merge": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "pq_qjl_sketch": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "pq_prefill_attn": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64,
                                 c_int, c_int, c_int, c_float_p, c_float_p, c_void_p, c_float, c_int,
                                 c_void_p, c_int, c_void_p, c_size_t, c_void_p]),

@@ -105,10 +105,16 @@ class PreparedDecode:
     output buffer), for serving loops where the Python-side set-up of ``decode_attention``
     would sit on the critical path of every token.  The cache objects and the query buffer
     are captured by reference: update ``ck.seq_len`` / the cache contents / the query buffer in
-    place and call the object again.  Returns the (reused) output tensor."""
+    place and call the object again.  Returns the (reused) output tensor.
+
+    ``partial=True`` produces the float32 (m, l, o_rotated) records [B, Hq, D+2] of a
+    sequence-sharded decode instead of the finished output.  The QJL score correction is applied
+    when the plan carries a JL matrix, the key cache carries a sketch and ``enable_qjl`` is set
+    (the defaults of ``decode_attention``)."""
 
     def __init__(self, query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, plan,
-                 scale: float | None = None, out_dtype: torch.dtype = torch.float32, n_splits: int = 0):
+                 scale: float | None = None, out_dtype: torch.dtype = torch.float32, n_splits: int = 0,
+                 partial: bool = False, enable_qjl: bool = True):
         _require_cuda(query, "query")
         if query.dtype != torch.float16 or not query.is_contiguous():
             raise ValueError("the query buffer must be a contiguous float16 tensor [B, Hq, D]")
@@ -118,16 +124,26 @@ class PreparedDecode:
         B, Hq, D = query.shape
         Hkv = ck.blocks.shape[1]
         self.dev = query.device
-        self.out = torch.empty((B, Hq, D), dtype=out_dtype, device=self.dev)
+        if partial:
+            self.out = torch.empty((B, Hq, D + 2), dtype=torch.float32, device=self.dev)
+        else:
+            self.out = torch.empty((B, Hq, D), dtype=out_dtype, device=self.dev)
         lib = _ext.lib()
         self._fn = lib.pq_decode_attn
         need = lib.pq_decode_attn_scratch_bytes(B, Hq, Hkv, ck.max_seq_len, D, max(0, n_splits))
         self.scratch = torch.zeros(max(need, 256), dtype=torch.uint8, device=self.dev)   # private: no sharing
         cbk, cbv = tables(ck.n_bits)[0], tables(cv.n_bits)[0]
+        use_qjl = bool(enable_qjl and plan.jl is not None and ck.qjl_signs is not None)
+        if use_qjl and (not ck.qjl_signs.is_contiguous() or not ck.residual_norms.is_contiguous()):
+            raise ValueError("sketch tensors must be contiguous")
         self._head = (query.data_ptr(), ck.blocks.data_ptr(), cv.blocks.data_ptr(), B, Hq, Hkv)
         self._tail = (ck.max_seq_len, D, ck.n_bits, cv.n_bits, cbk, cbv, plan.rot.data_ptr(),
                       ctypes.c_float(scale if scale is not None else 1.0 / math.sqrt(D)),
-                      None, 0, None, None, self.out.data_ptr(), 1 if out_dtype == torch.float16 else 0, None,
+                      plan.jl.data_ptr() if use_qjl else None, plan.jl_dim if use_qjl else 0,
+                      ck.qjl_signs.data_ptr() if use_qjl else None,
+                      ck.residual_norms.data_ptr() if use_qjl else None,
+                      None if partial else self.out.data_ptr(), 1 if out_dtype == torch.float16 else 0,
+                      self.out.data_ptr() if partial else None,
                       max(0, n_splits), self.scratch.data_ptr(), self.scratch.numel())
         self._stream = torch.cuda.current_stream(self.dev)
 

@@ -1,0 +1,8 @@
+"""Inference-side users of the compressed cache (the reference's src/polarquant_kv_cuda/inference/
+package): configuration, the per-layer cache manager, and a decoder that attends through it."""
+
+from .config import PolarQuantConfig
+from .kv_cache import KVCacheManager
+from .model import CompressedAttention, DecoderConfig, DecoderLM
+
+__all__ = ["PolarQuantConfig", "KVCacheManager", "CompressedAttention", "DecoderConfig", "DecoderLM"]

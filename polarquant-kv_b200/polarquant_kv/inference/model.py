@@ -1,0 +1,175 @@
+"""A decoder-only language model that keeps its KV cache compressed.
+
+Successor of CompressedMultiHeadAttention / SimpleTransformer
+(src/polarquant_kv_cuda/inference/attention.py:13-92, transformer.py:11-66 of the reference), in the
+shape of a current decoder: RMSNorm, rotary position embedding, grouped-query attention with biases on
+the q/k/v projections, SwiGLU MLP.  Keys and values are compressed on write (after the rotary
+embedding) and read by the fused attention kernels; every layer has its own rotation, seeds 42 + layer
+as the reference's create_cache_managers (transformer.py:58-66).  The dense layers are plain torch
+(library GEMMs): they are not part of the compressed-cache path.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .config import PolarQuantConfig
+from .kv_cache import KVCacheManager
+
+
+@dataclass
+class DecoderConfig:
+    """Defaults: the Qwen2.5-0.5B architecture."""
+    num_layers: int = 24
+    hidden: int = 896
+    q_heads: int = 14
+    kv_heads: int = 2
+    head_dim: int = 64
+    intermediate: int = 4864
+    vocab: int = 151936
+    rope_theta: float = 1.0e6
+    rms_eps: float = 1.0e-6
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim: int, eps: float):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim))
+        self.eps = eps
+
+    def forward(self, x):
+        v = x.float()
+        return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype) * self.weight
+
+
+def rotary(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor:
+    """x [B, H, S, D], positions [S] -> rotated halves (the rotate_half convention)."""
+    D = x.shape[-1]
+    inv = 1.0 / (theta ** (torch.arange(0, D, 2, device=x.device, dtype=torch.float32) / D))
+    ang = positions.float()[:, None] * inv[None, :]
+    cos, sin = torch.cos(ang).repeat(1, 2), torch.sin(ang).repeat(1, 2)
+    xf = x.float()
+    rot = torch.cat([-xf[..., D // 2:], xf[..., :D // 2]], dim=-1)
+    return xf * cos + rot * sin
+
+
+class CompressedAttention(nn.Module):
+    """q/k/v projections, rotary embedding, cache append, attention over the cache, output projection."""
+
+    def __init__(self, cfg: DecoderConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.q_proj = nn.Linear(cfg.hidden, cfg.q_heads * cfg.head_dim, bias=True)
+        self.k_proj = nn.Linear(cfg.hidden, cfg.kv_heads * cfg.head_dim, bias=True)
+        self.v_proj = nn.Linear(cfg.hidden, cfg.kv_heads * cfg.head_dim, bias=True)
+        self.o_proj = nn.Linear(cfg.q_heads * cfg.head_dim, cfg.hidden, bias=False)
+
+    def forward(self, x: torch.Tensor, cache: KVCacheManager, timers=None) -> torch.Tensor:
+        c = self.cfg
+        B, S, _ = x.shape
+        pos = torch.arange(cache.seq_len, cache.seq_len + S, device=x.device)
+        q = self.q_proj(x).view(B, S, c.q_heads, c.head_dim).transpose(1, 2)
+        k = self.k_proj(x).view(B, S, c.kv_heads, c.head_dim).transpose(1, 2)
+        v = self.v_proj(x).view(B, S, c.kv_heads, c.head_dim).transpose(1, 2)
+        q = rotary(q, pos, c.rope_theta).to(torch.float16)
+        k = rotary(k, pos, c.rope_theta).to(torch.float16)
+        v = v.to(torch.float16)
+        if timers is not None:
+            timers.start()
+        cache.append(k.contiguous(), v.contiguous())
+        out = cache.attend(q.contiguous(), causal=True)
+        if timers is not None:
+            timers.stop()
+        out = out.to(x.dtype).transpose(1, 2).reshape(B, S, c.q_heads * c.head_dim)
+        return self.o_proj(out)
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: DecoderConfig):
+        super().__init__()
+        self.attn = CompressedAttention(cfg)
+        self.norm1, self.norm2 = RMSNorm(cfg.hidden, cfg.rms_eps), RMSNorm(cfg.hidden, cfg.rms_eps)
+        self.gate = nn.Linear(cfg.hidden, cfg.intermediate, bias=False)
+        self.up = nn.Linear(cfg.hidden, cfg.intermediate, bias=False)
+        self.down = nn.Linear(cfg.intermediate, cfg.hidden, bias=False)
+
+    def forward(self, x, cache, timers=None):
+        x = x + self.attn(self.norm1(x), cache, timers)
+        h = self.norm2(x)
+        return x + self.down(F.silu(self.gate(h)) * self.up(h))
+
+
+class KernelTimer:
+    """Accumulates device time spent between start() and stop() (the compressed-cache kernels)."""
+
+    def __init__(self):
+        self.pairs = []
+
+    def start(self):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        self._open = e
+
+    def stop(self):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        self.pairs.append((self._open, e))
+
+    def total_ms(self) -> float:
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in self.pairs)
+
+
+class DecoderLM(nn.Module):
+    def __init__(self, cfg: DecoderConfig, pq: PolarQuantConfig):
+        super().__init__()
+        self.cfg, self.pq = cfg, pq
+        self.embed = nn.Embedding(cfg.vocab, cfg.hidden)
+        self.layers = nn.ModuleList([DecoderLayer(cfg) for _ in range(cfg.num_layers)])
+        self.norm = RMSNorm(cfg.hidden, cfg.rms_eps)
+        self.head = nn.Linear(cfg.hidden, cfg.vocab, bias=False)
+
+    @torch.no_grad()
+    def init_random(self, seed: int = 0, dtype: torch.dtype = torch.bfloat16, device="cuda"):
+        """Random weights (normal, std 0.02; norm weights one) from ``seed``, cast to ``dtype``."""
+        gen = torch.Generator(device="cpu")
+        gen.manual_seed(seed)
+        for name, prm in self.named_parameters():
+            if name.endswith("norm1.weight") or name.endswith("norm2.weight") or name == "norm.weight":
+                prm.fill_(1.0)
+            else:
+                prm.copy_(torch.randn(prm.shape, generator=gen) * 0.02)
+        return self.to(device=device, dtype=dtype)
+
+    def create_cache_managers(self, max_seq_len: int, batch: int, device="cuda") -> list[KVCacheManager]:
+        c = self.cfg
+        return [KVCacheManager(self.pq, max_seq_len, batch, c.kv_heads, c.head_dim, device, rotation_seed=42 + i)
+                for i in range(c.num_layers)]
+
+    @torch.no_grad()
+    def forward(self, input_ids: torch.Tensor, caches: list[KVCacheManager], timers=None, last_only: bool = True):
+        """input_ids [B, S] (a prompt, or S == 1 for a decode step) -> logits of the last position
+        [B, vocab] (or of every position with last_only=False)."""
+        x = self.embed(input_ids)
+        for layer, cache in zip(self.layers, caches):
+            x = layer(x, cache, timers)
+        x = self.norm(x[:, -1:] if last_only else x)
+        return self.head(x).float().squeeze(1) if last_only else self.head(x).float()
+
+    @torch.no_grad()
+    def generate(self, prompt_ids: torch.Tensor, steps: int, caches: list[KVCacheManager], timers=None) -> torch.Tensor:
+        """Greedy decoding: one prefill pass over the prompt [B, S], then ``steps`` single-token steps.
+        Returns the generated ids [B, steps]."""
+        logits = self.forward(prompt_ids, caches, timers)
+        out = []
+        tok = logits.argmax(-1, keepdim=True)
+        for _ in range(steps):
+            out.append(tok)
+            logits = self.forward(tok, caches, timers)
+            tok = logits.argmax(-1, keepdim=True)
+        return torch.cat(out, dim=1)

@@ -18,6 +18,36 @@ def generate_jl_matrix(jl_dim: int, d: int, seed: int | None = None) -> np.ndarr
     return rng.standard_normal((jl_dim, d)).astype(np.float64) / np.sqrt(jl_dim)
 
 
+def compute_signatures(residual: torch.Tensor, jl_matrix):
+    """signs = (P e >= 0) and ||e|| of residual vectors [..., d] on the GPU, in float64 like the
+    reference (qjl.py:25-35) -> QJLSignatures(signs bool [..., jl_dim], jl_dim, residual_norm).
+    ``residual_norm`` is a Python float for a single vector (as in the reference), a float32 tensor
+    [...] for a batch.  (pq_compress sketches its own residual in-kernel; this serves residuals a
+    caller computed itself.)"""
+    import ctypes
+
+    from . import _ext
+    from .types import QJLSignatures
+    if not isinstance(residual, torch.Tensor) or not residual.is_cuda:
+        raise TypeError("residual must be a CUDA tensor: this package has no CPU path")
+    P = torch.as_tensor(np.asarray(jl_matrix, dtype=np.float64) if not isinstance(jl_matrix, torch.Tensor)
+                        else jl_matrix).to(device=residual.device, dtype=torch.float64).contiguous()
+    m, d = P.shape
+    if residual.shape[-1] != d:
+        raise ValueError(f"residual has {residual.shape[-1]} dims, the JL matrix {d}")
+    e = residual.reshape(-1, d).to(torch.float32).contiguous()
+    n = e.shape[0]
+    bits = torch.empty((n, (m + 7) // 8), dtype=torch.uint8, device=e.device)
+    norms = torch.empty((n,), dtype=torch.float32, device=e.device)
+    st = _ext.lib().pq_qjl_sketch(e.data_ptr(), P.data_ptr(), n, d, m, bits.data_ptr(), norms.data_ptr(),
+                                  ctypes.c_void_p(torch.cuda.current_stream(e.device).cuda_stream))
+    _ext.check(st, "pq_qjl_sketch")
+    signs = bit_unpack(bits, m).reshape(*residual.shape[:-1], m)
+    if residual.dim() == 1:
+        return QJLSignatures(signs=signs, jl_dim=m, residual_norm=float(norms[0].item()))
+    return QJLSignatures(signs=signs, jl_dim=m, residual_norm=norms.reshape(residual.shape[:-1]))
+
+
 def bit_pack(signs: torch.Tensor) -> torch.Tensor:
     """bool [..., m] -> uint8 [..., ceil(m/8)], bit k of byte j = sign[8j + k]
     (qjl_kernel.py:72-92, 110-123)."""

@@ -84,33 +84,31 @@ def compress(kv: torch.Tensor, rotation_matrix, n_bits: int = 4, group_size: int
         signs = torch.empty((B, H, S, jl_dim // 8), dtype=torch.uint8, device=dev) if jl_dim else None
         norms = torch.empty((B, H, S), dtype=torch.float16, device=dev) if jl_dim else None
         out = CompressedKV(blocks, signs, norms, n_bits, group_size, d, S, S)
-        targets = [(blocks.view(-1), signs.view(-1) if jl_dim else None,
-                    norms.view(-1) if jl_dim else None, kv4.reshape(-1, d))]
+        capacity, position = S, 0
     else:
         if out.n_bits != n_bits or out.original_dim != d or tuple(out.blocks.shape[:2]) != (B, H):
             raise ValueError("preallocated cache does not match the input")
-        if position + S > out.max_seq_len:
+        if position < 0 or position + S > out.max_seq_len:
             raise RuntimeError(f"cache full: {position}+{S} > {out.max_seq_len}")   # kv_cache.py:76-79
-        targets = []
-        for b in range(B):
-            for h in range(H):
-                targets.append((out.blocks[b, h, position:position + S].reshape(-1),
-                                out.qjl_signs[b, h, position:position + S].reshape(-1) if jl_dim else None,
-                                out.residual_norms[b, h, position:position + S] if jl_dim else None,
-                                kv4[b, h]))
+        if jl_dim and (out.qjl_signs is None or out.qjl_signs.shape[-1] != jl_dim // 8):
+            raise ValueError("preallocated cache has no sketch side band of this width")
+        if not out.blocks.is_contiguous():
+            raise ValueError("cache tensors must be contiguous")
+        capacity = out.blocks.shape[2]
         out.seq_len = max(out.seq_len, position + S)
     if kv4.numel() == 0:
         return out
 
     cb, thr, _ = tables(n_bits)
-    lib = _ext.lib()
-    for blk_t, sign_t, norm_t, x in targets:
-        x = x.to(torch.float16).contiguous()
-        st = lib.pq_compress(
-            x.data_ptr(), x.shape[0], d, n_bits, plan.rot_split.data_ptr(), thr, cb, blk_t.data_ptr(),
-            plan.jl_split.data_ptr() if jl_dim else None, jl_dim,
-            sign_t.data_ptr() if jl_dim else None, norm_t.data_ptr() if jl_dim else None, _stream(dev))
-        _ext.check(st, "pq_compress")
+    x = kv4.to(torch.float16).contiguous()
+    # one launch for all (batch, head) rows: row r of the input goes to tokens [position, position + S) of
+    # row r of the cache
+    st = _ext.lib().pq_compress_rows(
+        x.data_ptr(), B * H, S, capacity, position, d, n_bits, plan.rot_split.data_ptr(), thr, cb,
+        out.blocks.data_ptr(),
+        plan.jl_split.data_ptr() if jl_dim else None, jl_dim,
+        out.qjl_signs.data_ptr() if jl_dim else None, out.residual_norms.data_ptr() if jl_dim else None, _stream(dev))
+    _ext.check(st, "pq_compress_rows")
     return out
 
 

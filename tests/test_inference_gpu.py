@@ -1,0 +1,130 @@
+"""GPU tests of the inference-side users of the compressed cache: the in-place cache manager
+(successor of the reference's KVCacheManager) and the decoder harness that attends through it."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import inputs
+from oracle import pq_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _cuda():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    return torch.device("cuda:0")
+
+
+def test_one_launch_append_equals_one_shot_compress():
+    """Decode-style appends (one new token for every (batch, head) row, odd positions included) and a
+    prompt-sized append write exactly the bytes of a one-shot compress of the whole tensor."""
+    from polarquant_kv import quantizer
+    dev = _cuda()
+    B, H, S, D = 3, 2, 41, 128
+    K, _, _ = inputs.make_kvq(B, H, 4, S, D, seed=5)
+    R = O.rotation_matrix(D, 0)
+    P = O.jl_matrix(128, D, 1)
+    Kd = torch.from_numpy(K).to(dev)
+    for bits, jl in ((4, P), (2, None)):
+        full = quantizer.compress(Kd, R, bits, 32, jl)
+        cache = quantizer.allocate_cache(B, H, 64, D, bits, 128 if jl is not None else 0, dev)
+        quantizer.compress(Kd[:, :, :17], R, bits, 32, jl, out=cache, position=0)
+        for pos in range(17, S):
+            quantizer.compress(Kd[:, :, pos:pos + 1], R, bits, 32, jl, out=cache, position=pos)
+        assert cache.seq_len == S
+        assert torch.equal(cache.blocks[:, :, :S], full.blocks)
+        assert not cache.blocks[:, :, S:].any()                    # nothing written past the end
+        if jl is not None:
+            assert torch.equal(cache.qjl_signs[:, :, :S], full.qjl_signs)
+            assert torch.equal(cache.residual_norms[:, :, :S], full.residual_norms)
+
+
+def test_cache_manager_interface():
+    from polarquant_kv.inference import KVCacheManager, PolarQuantConfig
+    dev = _cuda()
+    B, H, D = 2, 2, 64
+    K, V, q = inputs.make_kvq(B, H, 14, 40, D, seed=3)
+    Kd, Vd = torch.from_numpy(K).to(dev), torch.from_numpy(V).to(dev)
+    cm = KVCacheManager(PolarQuantConfig(n_bits=4), max_seq_len=48, batch=B, num_heads=H, head_dim=D, device=dev,
+                        rotation_seed=42)
+    assert cm.seq_len == 0 and cm.memory_bytes == 0 and cm.compression_ratio == 0.0
+    cm.append(Kd[:, :, :39], Vd[:, :, :39])
+    cm.append(Kd[:, :, 39:40], Vd[:, :, 39:40])
+    assert cm.seq_len == 40
+    assert cm.memory_bytes == B * H * 40 * 2 * 36
+    assert abs(cm.compression_ratio - (D * 2 * 2) / 72) < 1e-9
+    with pytest.raises(RuntimeError):
+        cm.append(Kd[:, :, :9], Vd[:, :, :9])
+    out = cm.attend(torch.from_numpy(q).to(dev))[:, :, 0]
+    ck, cv = cm.get_kv()
+    R = O.rotation_matrix(D, 42)
+    cb, _ = O.lloyd_max_codebook(32, 4)
+    for b in range(B):
+        ref = O.attention_from_blocks(q[b], ck.blocks[b, :, :40].cpu().numpy(), cv.blocks[b, :, :40].cpu().numpy(), R, cb, cb)[:, 0]
+        assert np.abs(out[b].cpu().numpy() - ref).max() <= 2e-3
+    cm.reset()
+    assert cm.seq_len == 0 and cm.get_kv()[0].seq_len == 0
+
+
+class _OracleCache:
+    """Stands in for KVCacheManager in the comparison run: every appended key / value goes through the
+    numpy oracle's compress -> decompress, attention is float64 torch over the dequantised tensors."""
+
+    def __init__(self, kv_heads, head_dim, seed):
+        self.R = O.rotation_matrix(head_dim, seed)
+        self.cb, _ = O.lloyd_max_codebook(32, 4)
+        self.k = self.v = None
+        self.num_heads = kv_heads
+
+    @property
+    def seq_len(self):
+        return 0 if self.k is None else self.k.shape[2]
+
+    def append(self, key, value):
+        def qdq(x):
+            xn = x.cpu().numpy()
+            hat = O.decompress(O.compress(xn, self.R, self.cb, 4), self.R, self.cb, 4)
+            return torch.from_numpy(hat).to(x.device).double()
+        k, v = qdq(key), qdq(value)
+        self.k = k if self.k is None else torch.cat([self.k, k], dim=2)
+        self.v = v if self.v is None else torch.cat([self.v, v], dim=2)
+
+    def attend(self, query, causal=True):
+        B, Hq, Sq, D = query.shape
+        rep = Hq // self.num_heads
+        k, v = self.k.repeat_interleave(rep, dim=1), self.v.repeat_interleave(rep, dim=1)
+        s = query.double() @ k.transpose(-2, -1) / np.sqrt(D)
+        S = k.shape[2]
+        if causal and Sq > 1:
+            keep = torch.arange(S, device=query.device)[None, :] <= (S - Sq + torch.arange(Sq, device=query.device))[:, None]
+            s = s.masked_fill(~keep, float("-inf"))
+        return (torch.softmax(s, dim=-1) @ v).float()
+
+
+def test_decoder_over_compressed_cache_matches_oracle_cache():
+    """A small decoder (float32 weights, two layers) generates the same greedy tokens, and logits equal
+    to 1e-3, whether its attention runs through the compressed cache kernels or through the oracle's
+    quantise-dequantise + float64 attention."""
+    from polarquant_kv.inference import DecoderConfig, DecoderLM, PolarQuantConfig
+    dev = _cuda()
+    cfg = DecoderConfig(num_layers=2, hidden=128, q_heads=4, kv_heads=2, head_dim=64, intermediate=256, vocab=503)
+    model = DecoderLM(cfg, PolarQuantConfig(n_bits=4)).init_random(seed=0, dtype=torch.float32, device=dev)
+    gen = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, cfg.vocab, (2, 37), generator=gen).to(dev)
+    caches = model.create_cache_managers(64, 2, dev)
+    ref_caches = [_OracleCache(cfg.kv_heads, cfg.head_dim, 42 + i) for i in range(cfg.num_layers)]
+    logits = model(prompt, caches)
+    ref_logits = model(prompt, ref_caches)
+    worst = float((logits - ref_logits).abs().max())
+    toks = []
+    for _ in range(6):
+        tok, ref_tok = logits.argmax(-1, keepdim=True), ref_logits.argmax(-1, keepdim=True)
+        assert torch.equal(tok, ref_tok)
+        toks.append(tok)
+        logits, ref_logits = model(tok, caches), model(tok, ref_caches)
+        worst = max(worst, float((logits - ref_logits).abs().max()))
+    print(f"decoder over compressed cache vs oracle cache: max logit difference {worst:.2e}")
+    assert worst <= 1e-3
+    assert caches[0].seq_len == 37 + 6
