@@ -534,6 +534,54 @@ def prefill_measurement(w, sets, plan, dev, timer, steps):
     return prefill
 
 
+def e2e_model_measurement(dev, rank, world, timer, steps=256):
+    """End-to-end greedy decoding of a Qwen2.5-0.5B-architecture decoder with random bfloat16 weights
+    (seed 0): 64 prompts of 4096 random token ids (sharded by batch across the ranks), one prefill pass,
+    then `steps` single-token steps; keys and values are compressed on write and read by the fused
+    attention kernels.  The dense layers are plain torch; `cache_kernel_share` is the part of the
+    decode time spent between cache append and attention output (compress x2 + attention per layer)."""
+    import torch
+    from polarquant_kv import distributed
+    from polarquant_kv.inference import DecoderConfig, DecoderLM, PolarQuantConfig
+    from polarquant_kv.inference.model import KernelTimer
+    cfg = DecoderConfig()
+    B_total, S = 64, 4096
+    lo, hi = distributed.batch_shard(B_total, rank, world)
+    B = hi - lo
+    model = DecoderLM(cfg, PolarQuantConfig(n_bits=4)).init_random(seed=0, dtype=torch.bfloat16, device=dev)
+    gen = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (B_total, S), generator=gen)[lo:hi].to(dev)
+    caches = model.create_cache_managers(S + steps, max(B, 1), dev)
+    state = {}
+
+    def prefill(i):
+        for c in caches:
+            c.reset()
+        state["logits"] = model(prompt, caches)
+
+    def decode(i):
+        tok = state["logits"].argmax(-1, keepdim=True)
+        for _ in range(steps):
+            state["logits"] = model(tok, caches, state.get("timers"))
+            tok = state["logits"].argmax(-1, keepdim=True)
+
+    if B == 0:
+        prefill = decode = (lambda i: None)
+    ms_prefill, _ = timer.run(prefill, 1, repeats=1)
+    state["timers"] = KernelTimer()
+    ms_decode, per_rank = timer.run(decode, 1, repeats=1)
+    kernel_ms = state["timers"].total_ms() if B else 0.0
+    mem = sum(c.memory_bytes for c in caches) if B else 0
+    return {"model": "Qwen2.5-0.5B architecture, random bfloat16 weights (seed 0)", "batch": B_total, "prompt_len": S,
+            "decode_steps": steps, "batch_this_rank": B,
+            "prefill_s": round(ms_prefill / 1e3, 3), "decode_s": round(ms_decode / 1e3, 3),
+            "decode_tokens_per_s": round(B_total * steps / (ms_decode / 1e3), 1),
+            "ms_per_decode_step": round(ms_decode / steps, 3),
+            "cache_kernel_share_of_decode": round(kernel_ms / ms_decode, 3) if B else None,
+            "compressed_cache_bytes_this_rank": mem,
+            "note": "host-launch bound: one decode step issues about 25 small kernels per layer from Python"}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -590,6 +638,11 @@ def run_ours(args):
     prefill = None
     if not args.only_decode and sets is not None:
         prefill = prefill_measurement(w, sets, sets[0][0], dev, timer, args.steps)
+    sets = None
+    e2e_model = None
+    if not args.only_decode and not args.skip_model:
+        torch.cuda.empty_cache()
+        e2e_model = e2e_model_measurement(dev, rank, world, timer)
 
     if rank != 0:
         if world > 1:
@@ -643,6 +696,7 @@ def run_ours(args):
         "compress": comp,
         "dequant": dequant,
         "prefill": prefill,
+        "e2e_model": e2e_model,
         "cpu_baseline": cpu,
         "clocks": clocks,
     }
@@ -664,6 +718,7 @@ def main():
     ap.add_argument("--q-heads", type=int, default=0, help="query heads (default: the headline workload's)")
     ap.add_argument("--only-decode", action="store_true",
                     help="only the headline decode measurement (profiler captures)")
+    ap.add_argument("--skip-model", action="store_true", help="skip the end-to-end decoder measurement")
     ap.add_argument("--splits", type=int, default=0, help="sequence splits per (batch, kv head); 0 = library default")
     ap.add_argument("--compress-vecs", type=int, default=COMPRESS_VECS, help="vectors per tensor in the compress measurement")
     args = ap.parse_args()

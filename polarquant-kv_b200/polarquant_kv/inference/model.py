@@ -136,15 +136,16 @@ class DecoderLM(nn.Module):
 
     @torch.no_grad()
     def init_random(self, seed: int = 0, dtype: torch.dtype = torch.bfloat16, device="cuda"):
-        """Random weights (normal, std 0.02; norm weights one) from ``seed``, cast to ``dtype``."""
-        gen = torch.Generator(device="cpu")
+        """Random weights (normal, std 0.02; norm weights one) drawn on ``device`` from ``seed``, in ``dtype``."""
+        self.to(device=device, dtype=dtype)
+        gen = torch.Generator(device=device)
         gen.manual_seed(seed)
         for name, prm in self.named_parameters():
             if name.endswith("norm1.weight") or name.endswith("norm2.weight") or name == "norm.weight":
                 prm.fill_(1.0)
             else:
-                prm.copy_(torch.randn(prm.shape, generator=gen) * 0.02)
-        return self.to(device=device, dtype=dtype)
+                prm.copy_((torch.randn(prm.shape, generator=gen, device=device, dtype=torch.float32) * 0.02).to(dtype))
+        return self
 
     def create_cache_managers(self, max_seq_len: int, batch: int, device="cuda") -> list[KVCacheManager]:
         c = self.cfg

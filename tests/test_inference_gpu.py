@@ -128,3 +128,32 @@ def test_decoder_over_compressed_cache_matches_oracle_cache():
     print(f"decoder over compressed cache vs oracle cache: max logit difference {worst:.2e}")
     assert worst <= 1e-3
     assert caches[0].seq_len == 37 + 6
+
+
+def test_hf_cache_adapter_serves_a_transformers_decoder():
+    """A small random `transformers` Qwen2 decoder generates through the block_pq4-backed cache: the
+    cache grows in place, its logits stay close to the float cache's (the codec is lossy: cosine), and
+    greedy generation runs end to end."""
+    transformers = pytest.importorskip("transformers")
+    from polarquant_kv import hf_integration
+    dev = _cuda()
+    cfg = transformers.Qwen2Config(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                                   num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=512)
+    torch.manual_seed(0)
+    model = transformers.Qwen2ForCausalLM(cfg).to(dev).eval()
+    hf_integration.patch_model(model, n_bits=4)
+    ids = torch.randint(0, 512, (2, 300), generator=torch.Generator().manual_seed(1)).to(dev)
+    with torch.no_grad():
+        ref = model(ids).logits[:, -1]
+        cache = hf_integration.create_compressed_cache(model)
+        got = model(ids, past_key_values=cache, use_cache=True).logits[:, -1]
+        assert cache.get_seq_length() == 300 and cache.layers[0].capacity == 512       # grew 256 -> 512
+        cos = torch.nn.functional.cosine_similarity(ref.float(), got.float(), dim=-1).min().item()
+        step = model(ids[:, -1:], past_key_values=cache, use_cache=True).logits
+        assert cache.get_seq_length() == 301 and tuple(step.shape) == (2, 1, 512)
+        out = model.generate(ids[:, :40], max_new_tokens=8, do_sample=False,
+                             past_key_values=hf_integration.create_compressed_cache(model))
+    print(f"HF adapter: min cosine of last-token logits vs the float cache {cos:.4f}")
+    assert cos > 0.98
+    assert tuple(out.shape) == (2, 48)
+    assert cache.get_compressed_memory_bytes() * 3 < cache.get_standard_memory_bytes()
