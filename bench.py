@@ -476,8 +476,11 @@ def compress_measurement(dev, world, timer, steps, n, peak):
 
         for fn in (kstep, vstep):
             fn(0)
-        tk = timer.run(kstep, k, repeats=3)[0] / k
+        torch.cuda.synchronize()
+        time.sleep(0.25)           # every kernel is timed alone: let the previous one's power draw decay
         tv = timer.run(vstep, k, repeats=3)[0] / k
+        time.sleep(0.25)
+        tk = timer.run(kstep, k, repeats=3)[0] / k
         out_bytes = sum(share * (D // 32) * (2 + 4 * bits) for bits, share in parts)
         bk, bv = 2 * D + out_bytes + D // 8 + 2, 2 * D + out_bytes
         comp[label] = {

@@ -7,10 +7,9 @@ path  rotate -> per-32 block radius -> Lloyd-Max nearest centroid -> nibble pack
 Only the test-suite, the smoke check and the CPU-baseline leg of the benchmark may
 import it; the shipped package never does.
 
-Parity status: PINNED.  Every function here is checked against the reference's own
-Python code (imported in the build container) by ``oracle/check_against_reference.py``,
-and against the committed fixtures in ``tests/golden/`` (which were produced by calling
-the reference functions themselves, see ``tests/golden/make_golden.py``).
+Parity status: PINNED.  Every function here is checked (``tests/test_oracle_golden.py``) against the
+committed fixtures in ``tests/golden/``, which were produced by calling the reference's own Python
+functions (``tests/golden/make_golden.py`` imports the reference and calls nothing else).
 
 No single reference function emits block_pq4 (the layout exists only as prose in the
 reference's README.md:73-78); the oracle is the composition

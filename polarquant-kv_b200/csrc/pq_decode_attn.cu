@@ -868,20 +868,47 @@ pq_decode_attn_kernel(const DecodeParams p) {
         if (tid == 0) p.tickets[group] = 0;   // ready for the next call on this stream
         if (!p.partial_out) {
             __syncthreads();
-            // out[head][i] = sum_j o_fin[head][j] * R[j][i]
-            for (int e = tid; e < HPC * D; e += NT) {
-                const int head = e / D, i = e % D;
-                if (head >= Gp) continue;
-                float acc_o = 0.f;
-                // 32 independent loads in flight per thread: the column of R comes from L2, and with a short
-                // unroll the D dependent round trips dominate the merge
-#pragma unroll 32
-                for (int j = 0; j < D; ++j) acc_o = fmaf(o_fin[head * D + j], __ldg(p.rot + (size_t)j * D + i), acc_o);
-                const size_t off = ((size_t)b * p.Hq + head0 + head) * D + i;
-                if (p.out_is_fp16)
-                    static_cast<__half*>(p.out)[off] = __float2half_rn(fminf(fmaxf(acc_o, -65504.f), 65504.f));
-                else
-                    static_cast<float*>(p.out)[off] = acc_o;
+            // out[head][i] = sum_j o_fin[head][j] * R[j][i] on the tensor cores, eight output columns per
+            // warp step: rows g = hi term of head g, rows g+8 = its lo term (two float16 terms of the
+            // float32 result), B = R split into two float16 terms of 4096*R on the fly; the three product
+            // terms hi*hi + lo*hi + hi*lo land in rows g and g+8 of the same lane.  (|o| <= 0.46 * 65504:
+            // the hi term cannot overflow.)
+            for (int nt = warp; nt < D / 8; nt += NW) {
+                float c[4] = {0.f, 0.f, 0.f, 0.f};
+                const int n = nt * 8 + g;                               // B column of this lane
+#pragma unroll 4
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const int k0 = ks * 16 + 2 * t;
+                    const float x0 = __ldg(p.rot + (size_t)k0 * D + n) * 4096.f, x1 = __ldg(p.rot + (size_t)(k0 + 1) * D + n) * 4096.f;
+                    const float x2 = __ldg(p.rot + (size_t)(k0 + 8) * D + n) * 4096.f, x3 = __ldg(p.rot + (size_t)(k0 + 9) * D + n) * 4096.f;
+                    const __half2 h01 = __floats2half2_rn(x0, x1), h23 = __floats2half2_rn(x2, x3);
+                    const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+                    // A: row g = head g (hi), row g+8 = head g (lo); k slots 2t, 2t+1 | 2t+8, 2t+9
+                    uint32_t a0 = 0u, a1 = 0u, a2 = 0u, a3 = 0u;
+                    if (g < HPC) {
+                        const float* src = o_fin + g * D + k0;
+                        const __half2 p01 = __floats2half2_rn(src[0], src[1]), p23 = __floats2half2_rn(src[8], src[9]);
+                        const float2 q01 = __half22float2(p01), q23 = __half22float2(p23);
+                        a0 = *reinterpret_cast<const uint32_t*>(&p01);
+                        a2 = *reinterpret_cast<const uint32_t*>(&p23);
+                        a1 = pack_half2(src[0] - q01.x, src[1] - q01.y);
+                        a3 = pack_half2(src[8] - q23.x, src[9] - q23.y);
+                    }
+                    mma_16816(c, a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+                    mma_16816(c, a0, 0u, a2, 0u, pack_half2(x0 - f01.x, x1 - f01.y), pack_half2(x2 - f23.x, x3 - f23.y));
+                }
+                // C rows g (hi rows) and g+8 (lo rows) of head g; columns 2t, 2t+1 = outputs nt*8 + 2t, +1
+                if (g < Gp) {
+                    const float r0 = (c[0] + c[2]) * (1.0f / 4096.f), r1 = (c[1] + c[3]) * (1.0f / 4096.f);
+                    const size_t off = ((size_t)b * p.Hq + head0 + g) * D + nt * 8 + 2 * t;
+                    if (p.out_is_fp16) {
+                        static_cast<__half*>(p.out)[off] = __float2half_rn(fminf(fmaxf(r0, -65504.f), 65504.f));
+                        static_cast<__half*>(p.out)[off + 1] = __float2half_rn(fminf(fmaxf(r1, -65504.f), 65504.f));
+                    } else {
+                        static_cast<float*>(p.out)[off] = r0;
+                        static_cast<float*>(p.out)[off + 1] = r1;
+                    }
+                }
             }
         }
     }

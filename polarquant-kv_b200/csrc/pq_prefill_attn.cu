@@ -480,7 +480,7 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
             ok = mbar_wait(sm_addr(mbar + PF_S_FULL + sk), sk_par, abort_s) && ok;
             ok = mbar_wait(sm_addr(mbar + PF_K_FULL + sb), (i >> 1) & 1, abort_s) && ok;   // dmaxK[sb] is visible
             tc_fence_after();
-            float mx = -INFINITY;
+            float mx = -INFINITY, tile_dv = 0.f;
             float s[HT];
             {
                 float sl[HT];                                            // the q_hi * k_lo part of the same scores
@@ -511,29 +511,50 @@ __global__ void __launch_bounds__(pf_threads(PRE), 1) pq_prefill_attn_kernel(con
                         if (tok0 + t >= limit) s[t] = -INFINITY;
                 }
             }
+            // this thread's scores are in registers and the key radii are read: the S buffer and dmaxK[sb]
+            // are free as far as this thread is concerned
+            tc_fence_before();
+            mbar_arrive(sm_addr(mbar + PF_S_FREE + sk));
             {
                 // partial maximum of this thread's tokens; the threads of a row swap partials through shared
-                // memory (one set per tile parity) with the row group's named barrier in between.  After the
-                // barrier every thread of the row has its scores in registers: the S columns may be reused.
+                // memory (one set per tile parity) with the row group's named barrier in between
 #pragma unroll
                 for (int t = 0; t < HT; ++t) mx = fmaxf(mx, s[t]);
+                // ... together with the largest value radius of their tokens (the weights are probability
+                // times that radius, split into float16 terms: the lazy rescale below must leave room for it)
+                ok = mbar_wait(sm_addr(mbar + PF_V_FULL + sb), (i >> 1) & 1, abort_s) && ok;   // dmaxV[sb] is visible
+                float dvl = 0.f;
+                {
+                    const uint32_t dvx = dv_addr + (uint32_t)((sb * kPfTok + hf * HT) * 4);
+#pragma unroll
+                    for (int t4 = 0; t4 < HT / 4; ++t4) {
+                        const float4 d4 = lds_f4(dvx + t4 * 16);
+                        dvl = fmaxf(fmaxf(dvl, fmaxf(d4.x, d4.y)), fmaxf(d4.z, d4.w));
+                    }
+                }
                 float* xm = reinterpret_cast<float*>(Ph) + sb * 4 * kPfRows;          // [parity][part][row]
+                float* xd = reinterpret_cast<float*>(Ph) + 12 * kPfRows + sb * 4 * kPfRows;
                 xm[hf * kPfRows + r] = mx;
+                xd[hf * kPfRows + r] = dvl;
                 asm volatile("bar.sync %0, %1;\n" ::"r"(1 + q), "r"(32 * NSPLIT) : "memory");
 #pragma unroll
-                for (int k = 0; k < NSPLIT; ++k) mx = fmaxf(mx, xm[k * kPfRows + r]);
+                for (int k = 0; k < NSPLIT; ++k) {
+                    mx = fmaxf(mx, xm[k * kPfRows + r]);
+                    dvl = fmaxf(dvl, xd[k * kPfRows + r]);
+                }
+                tile_dv = dvl;
             }
-            tc_fence_before();
-            mbar_arrive(sm_addr(mbar + PF_S_FREE + sk));                // S buffer and dmaxK[sb] consumed
             m_run = fmaxf(m_run, mx);
             // Probabilities first (registers only), relative to the maximum this tile will use: that work
             // overlaps the previous tile's P V, which must be complete before P is rewritten or O rescaled.
-            const bool grow = m_run > m_used + kPfRescaleGap;           // also true on the first finite maximum
+            // The row maximum may run ahead of the one in use by up to 2^8, less when the tile holds large
+            // radii: probability * radius stays below 2^15, inside the float16 range.
+            const float gap = fminf(kPfRescaleGap, 15.0f - __log2f(tile_dv));
+            const bool grow = m_run > m_used + gap;                     // also true on the first finite maximum
             const bool rescale = __any_sync(0xffffffffu, grow);         // same outcome in every warp of a row group
             const float m_old = m_used;
             if (rescale) m_used = m_run;
             const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
-            ok = mbar_wait(sm_addr(mbar + PF_V_FULL + sb), (i >> 1) & 1, abort_s) && ok;   // dmaxV[sb] is visible
             const uint32_t dv4 = dv_addr + (uint32_t)((sb * kPfTok + hf * HT) * 4);
             float sum = 0.f;
             uint32_t ph[HT / 2], pl[HT / 2];
