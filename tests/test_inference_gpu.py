@@ -157,3 +157,48 @@ def test_hf_cache_adapter_serves_a_transformers_decoder():
     assert cos > 0.98
     assert tuple(out.shape) == (2, 48)
     assert cache.get_compressed_memory_bytes() * 3 < cache.get_standard_memory_bytes()
+
+
+def _oracle_mixed(q, K, V, R, runs, axis):
+    """float64 attention over keys / values quantised-dequantised run by run with the oracle."""
+    Hkv, S, D = K.shape
+    Kh, Vh = np.zeros((Hkv, S, D)), np.zeros((Hkv, S, D))
+    for b, e, bits in runs:
+        cb, _ = O.lloyd_max_codebook(32, bits)
+        sl = (slice(None), slice(b, e)) if axis == "token" else (slice(b, e),)
+        Kh[sl] = O.decompress(O.compress(K[sl], R, cb, bits), R, cb, bits)
+        Vh[sl] = O.decompress(O.compress(V[sl], R, cb, bits), R, cb, bits)
+    G = q.shape[0] // Hkv
+    out = np.zeros((q.shape[0], D))
+    for h in range(q.shape[0]):
+        s = Kh[h // G] @ q[h].astype(np.float64) / np.sqrt(D)
+        p = np.exp(s - s.max())
+        out[h] = (p / p.sum()) @ Vh[h // G]
+    return out
+
+
+def test_mixed_precision_policies_vs_oracle():
+    """Sink + window token policy (three runs merged by log-sum-exp) and a per-head policy, against the
+    oracle's run-by-run quantise-dequantise + float64 attention (2e-3)."""
+    from polarquant_kv import policy
+    dev = _cuda()
+    B, Hkv, Hq, S, D = 2, 4, 16, 333, 128
+    K, V, q = inputs.make_kvq(B, Hkv, Hq, S, D, seed=8)
+    R = O.rotation_matrix(D, 0)
+    Kd, Vd, qd = torch.from_numpy(K).to(dev), torch.from_numpy(V).to(dev), torch.from_numpy(q[:, :, 0]).to(dev)
+    tok_bits = policy.compute_token_bitwidths(S, sink_size=4, window_size=64)
+    assert policy.runs_of(tok_bits) == [(0, 4, 4), (4, S - 64, 2), (S - 64, S, 4)]
+    cache = policy.mixed_precision_compress(Kd, Vd, R, tok_bits, axis="token")
+    out = policy.mixed_precision_attention(qd, cache, R).cpu().numpy()
+    for b in range(B):
+        ref = _oracle_mixed(q[b, :, 0], K[b], V[b], R, cache.runs, "token")
+        assert np.abs(out[b] - ref).max() <= 2e-3
+    assert 2.0 < cache.average_bits < 2.5 and cache.memory_bytes() < B * Hkv * S * 2 * 72
+    head_bits = [4, 4, 2, 2]
+    cache_h = policy.mixed_precision_compress(Kd, Vd, R, head_bits, axis="head")
+    out_h = policy.mixed_precision_attention(qd, cache_h, R).cpu().numpy()
+    for b in range(B):
+        ref = _oracle_mixed(q[b, :, 0], K[b], V[b], R, cache_h.runs, "head")
+        assert np.abs(out_h[b] - ref).max() <= 2e-3
+    assert policy.compute_layer_bitwidths(24, 3.0) == [4] * 6 + [2] * 12 + [4] * 6
+    assert policy.compute_layer_bitwidths(2) == [4, 4]
