@@ -18,8 +18,10 @@ CSRC = os.path.join(os.path.dirname(PKG_DIR), "csrc")
 INCLUDE = os.path.join(os.path.dirname(os.path.dirname(PKG_DIR)), "include")
 LIB_PATH = os.path.join(PKG_DIR, "libpolarquant_b200.so")
 
-SOURCES = ["pq_compress.cu", "pq_dequant.cu", "pq_decode_attn.cu", "pq_prefill_attn.cu", "pq_lse_merge.cu", "pq_qjl.cu"]
-HEADERS = ["pq_common.cuh", "pq_tcgen05.cuh", os.path.join(INCLUDE, "polarquant_b200.h")]
+SOURCES = ["pq_compress.cu", "pq_dequant.cu", "pq_decode_attn.cu", "pq_prefill_attn.cu", "pq_lse_merge.cu", "pq_qjl.cu",
+           "pq_llama_abi.cu"]
+HEADERS = ["pq_common.cuh", "pq_tcgen05.cuh", os.path.join(INCLUDE, "polarquant_b200.h"),
+           os.path.join(INCLUDE, "polarquant_llama_abi.h")]
 
 
 def _nvcc() -> str:

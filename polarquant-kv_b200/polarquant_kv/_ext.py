@@ -17,7 +17,7 @@ c_void_p, c_int, c_int64, c_float, c_size_t = (ctypes.c_void_p, ctypes.c_int, ct
                                                ctypes.c_float, ctypes.c_size_t)
 c_float_p = ctypes.POINTER(ctypes.c_float)
 
-# name -> (restype, argtypes); must list every symbol include/polarquant_b200.h declares
+# name -> (restype, argtypes); must list every symbol the headers under include/ declare
 SIGNATURES = {
     "pq_version": (c_int, []),
     "pq_strerror": (ctypes.c_char_p, [c_int]),
@@ -44,6 +44,16 @@ SIGNATURES = {
                                 c_int, c_int, c_int, c_float_p, c_float_p, c_void_p, c_float, c_int,
                                 c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
     "pq_prefill_attn_workspace_bytes": (c_size_t, [c_int, c_int, c_int64, c_int]),
+    # include/polarquant_llama_abi.h: the llama.cpp bridge's entry points
+    "polarquant_init_c": (c_void_p, [c_int, c_int, c_int, c_int, c_int, c_int]),
+    "polarquant_free_c": (None, [c_void_p]),
+    "polarquant_compress_cuda_c": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                          c_void_p]),
+    "polarquant_rotate_query_cuda_c": (None, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "polarquant_fused_attention_cuda_c": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]),
+    "polarquant_inverse_rotate_cuda_c": (None, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "polarquant_last_error_c": (c_int, []),
 }
 
 _lib = None

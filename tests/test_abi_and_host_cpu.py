@@ -14,9 +14,12 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "polarquant_b200.h")).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(pq_[a-z0-9_]+)\s*\(", text)))
+    names = set()
+    for header in ("polarquant_b200.h", "polarquant_llama_abi.h"):
+        text = open(os.path.join(ROOT, "include", header)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names.update(re.findall(r"\b(pq_[a-z0-9_]+|polarquant_[a-z_]+_c)\s*\(", text))
+    return sorted(names)
 
 
 def test_library_exports_every_declared_symbol():
@@ -159,3 +162,46 @@ def test_cuda_only_api_refuses_cpu_tensors():
         quantizer.compress(torch.zeros((1, 1, 2, 64), dtype=torch.float16), R)
     with pytest.raises(TypeError):
         attention.compressed_attention(torch.zeros((1, 2, 1, 64), dtype=torch.float16), None, None, R)
+
+
+def test_llama_bridge_entry_points_reject_before_touching_the_device():
+    """include/polarquant_llama_abi.h: the void entry points record why they did not run."""
+    from polarquant_kv import _ext
+    lib = _ext.lib()
+    assert lib.polarquant_last_error_c() == 0
+    lib.polarquant_compress_cuda_c(None, None, None, None, None, 4, 128, 16, None)
+    assert lib.polarquant_last_error_c() == 1
+    assert lib.polarquant_last_error_c() == 0            # reading clears it
+    lib.polarquant_compress_cuda_c(None, None, None, None, None, 0, 128, 16, None)   # nothing to do
+    assert lib.polarquant_last_error_c() == 0
+    one = ctypes.c_void_p(256)
+    lib.polarquant_compress_cuda_c(one, one, one, one, one, 4, 127, 16, None)
+    assert lib.polarquant_last_error_c() == 2
+    lib.polarquant_compress_cuda_c(one, one, one, one, one, 4, 128, 17, None)
+    assert lib.polarquant_last_error_c() == 3
+    lib.polarquant_fused_attention_cuda_c(one, one, one, one, one, one, one, 6, 4, 10, 64, 16, 1.0, None)
+    assert lib.polarquant_last_error_c() == 4
+    lib.polarquant_rotate_query_cuda_c(one, one, one, 2, 2048, None)
+    assert lib.polarquant_last_error_c() == 2
+    lib.polarquant_free_c(None)
+
+
+def test_llama_bridge_oracle_known_answers():
+    from oracle import llama_bridge_oracle as LO
+    cb = np.array([-0.75, -0.25, 0.25, 0.75])
+    # ties go to the first centroid; directions are rotated / radius
+    assert LO.nearest_level(np.array([0.0, 0.5, -0.5, 1.0, -1.0]), cb).tolist() == [1, 2, 0, 3, 0]
+    x = np.array([[3.0, 0.0, -4.0, 0.0]])
+    radius, packed, direction = LO.compress(x, np.eye(4), cb)
+    assert radius[0] == 5.0 and direction[0].tolist() == [0.6, 0.0, -0.8, 0.0]
+    assert packed[0].tolist() == [3 | (1 << 4), 0 | (1 << 4)]
+    assert LO.unpack(packed, 4)[0].tolist() == [3, 1, 0, 1]
+    zero_radius, zero_packed, _ = LO.compress(np.zeros((1, 4)), np.eye(4), cb)
+    assert zero_radius[0] == 0.0 and zero_packed[0].tolist() == [1 | (1 << 4)] * 2
+    # attention over one token returns that token's value whatever the score is
+    out = LO.fused_attention(np.ones((2, 4)), packed[None], radius[None], packed[None], radius[None], cb, 4, 0.5)
+    np.testing.assert_allclose(out, np.tile(cb[[3, 1, 0, 1]] * 5.0, (2, 1)))
+    rng = np.random.default_rng(0)
+    R, _ = np.linalg.qr(rng.standard_normal((8, 8)))
+    y = rng.standard_normal((3, 8))
+    np.testing.assert_allclose(LO.inverse_rotate(LO.rotate(y, R), R), y, atol=1e-12)
