@@ -22,7 +22,7 @@
  * returned (or silently read out of bounds) on a shape they could not handle, these record
  * a code that polarquant_last_error_c() returns and clears, and enqueue nothing.
  * D must be even and at most 1024.  There is no limit on S (the patch's attention kernel
- * gave up above 12288 tokens: polarquant.cu part of the patch, lines 484-494).
+ * gave up above 12288 tokens: lines 487-496 of the decoded patch).
  */
 #ifndef POLARQUANT_LLAMA_ABI_H
 #define POLARQUANT_LLAMA_ABI_H
