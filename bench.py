@@ -537,6 +537,32 @@ def prefill_measurement(w, sets, plan, dev, timer, steps):
     return prefill
 
 
+def cache_kernels_per_step(model, caches, cfg, B, dev, timer):
+    """Device time of one decode step's compressed-cache kernels alone (per layer: append of the new key
+    and value rows, attention over the cache), replayed from a CUDA graph at the caches' current length."""
+    import torch
+    k = torch.randn(B, cfg.kv_heads, 1, cfg.head_dim, device=dev).to(torch.float16)
+    q = torch.randn(B, cfg.q_heads, 1, cfg.head_dim, device=dev).to(torch.float16)
+    position = torch.full((1,), caches[0].seq_len - 1, dtype=torch.int64, device=dev)
+    length = torch.full((1,), caches[0].seq_len, dtype=torch.int64, device=dev)
+
+    def one_step():
+        for cache in caches:
+            cache.append(k, k, position=position)          # overwrites the last token's slot
+            cache.attend(q, seq_len_tensor=length)
+
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        one_step()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        one_step()
+    ms, _ = timer.run(lambda i: graph.replay(), 10, repeats=3)
+    return ms / 10
+
+
 def e2e_model_measurement(dev, rank, world, timer, steps=256):
     """End-to-end greedy decoding of a Qwen2.5-0.5B-architecture decoder with random bfloat16 weights
     (seed 0): 64 prompts of 4096 random token ids (sharded by batch across the ranks), one prefill pass,
@@ -568,21 +594,39 @@ def e2e_model_measurement(dev, rank, world, timer, steps=256):
             state["logits"] = model(tok, caches, state.get("timers"))
             tok = state["logits"].argmax(-1, keepdim=True)
 
+    def decode_graph(i):
+        # the same steps, launched as one CUDA graph replay per token (position and cache length on the
+        # device); recording the graph is inside the timed region
+        state["graph_tokens"] = model.decode_graph(state["logits"].argmax(-1, keepdim=True), steps, caches)
+
     if B == 0:
-        prefill = decode = (lambda i: None)
+        prefill = decode = decode_graph = (lambda i: None)
     ms_prefill, _ = timer.run(prefill, 1, repeats=1)
     state["timers"] = KernelTimer()
     ms_decode, per_rank = timer.run(decode, 1, repeats=1)
     kernel_ms = state["timers"].total_ms() if B else 0.0
     mem = sum(c.memory_bytes for c in caches) if B else 0
+    state["timers"] = None
+    timer.run(prefill, 1, repeats=1)                       # fresh caches for the graph-replayed run
+    ms_graph, _ = timer.run(decode_graph, 1, repeats=1)
+    ms_cache_step = cache_kernels_per_step(model, caches, cfg, max(B, 1), dev, timer) if B else 0.0
     return {"model": "Qwen2.5-0.5B architecture, random bfloat16 weights (seed 0)", "batch": B_total, "prompt_len": S,
             "decode_steps": steps, "batch_this_rank": B,
             "prefill_s": round(ms_prefill / 1e3, 3), "decode_s": round(ms_decode / 1e3, 3),
             "decode_tokens_per_s": round(B_total * steps / (ms_decode / 1e3), 1),
             "ms_per_decode_step": round(ms_decode / steps, 3),
             "cache_kernel_share_of_decode": round(kernel_ms / ms_decode, 3) if B else None,
+            "graph_replay": {"decode_s": round(ms_graph / 1e3, 3),
+                             "decode_tokens_per_s": round(B_total * steps / (ms_graph / 1e3), 1),
+                             "ms_per_decode_step": round(ms_graph / steps, 3),
+                             "cache_kernels_ms_per_step": round(ms_cache_step, 3),
+                             "cache_kernel_share_of_decode": round(ms_cache_step / (ms_graph / steps), 3) if B else None,
+                             "note": "one CUDA graph launch per token (pq_compress_rows_dynamic + "
+                                     "pq_decode_attn_dynamic read position and length from device memory); "
+                                     "recording the graph is inside the timed region"},
             "compressed_cache_bytes_this_rank": mem,
-            "note": "host-launch bound: one decode step issues about 25 small kernels per layer from Python"}
+            "note": "decode_tokens_per_s is the eager loop (host-launch bound: one decode step issues about 25 "
+                    "small kernels per layer from Python); graph_replay is the same loop as graph launches"}
 
 
 def run_ours(args):

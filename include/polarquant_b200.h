@@ -106,13 +106,27 @@ int pq_compress_rows(const void* x, int64_t n_rows, int64_t tokens_per_row, int6
                      const void* jl_split, int jl_dim, void* qjl_bits_out, void* qjl_norm_out,
                      void* stream);
 
+/* pq_compress_rows_dynamic — pq_compress_rows with the sequence offset read from DEVICE memory when
+ * the kernel starts (*position_dev, int64, 8-byte aligned), for a decode step recorded once as a CUDA
+ * graph and replayed while the position advances on the device.  The host cannot check the offset:
+ * when position + tokens_per_row exceeds row_capacity (or position < 0) the kernel writes nothing and
+ * sets bit 5 of pq_poll_device_errors.  No counterpart in the reference (its append concatenates on
+ * the host, src/polarquant_kv_cuda/inference/kv_cache.py:93-116). */
+int pq_compress_rows_dynamic(const void* x, int64_t n_rows, int64_t tokens_per_row, int64_t row_capacity,
+                             const int64_t* position_dev, int head_dim, int n_bits,
+                             const void* rot_split, const float* thresholds, const float* codebook,
+                             void* blocks_out,
+                             const void* jl_split, int jl_dim, void* qjl_bits_out, void* qjl_norm_out,
+                             void* stream);
+
 /* pq_poll_device_errors — HOST-synchronising check for device-side failures of earlier launches on
  * the current device.  The tensor-core kernels wait for copies and MMAs through barriers with a time
  * limit (so that a lost completion can never hang the GPU); if a wait ever gives up a bit of
  * *flags_out is set and the output of that launch must be discarded: bit 0 compress (a wait gave
  * up), bit 1 compress (shared-memory window unusable), bit 2 prefill attention (a wait gave up),
  * bit 3 decode attention (shared-memory window unusable, nothing computed), bit 4 decode attention (a
- * wait for a tile copy gave up).
+ * wait for a tile copy gave up), bit 5 compress (pq_compress_rows_dynamic found its device-side
+ * position out of range; nothing was written).
  * The flags are cleared by the call.  No counterpart in the reference (its kernels report nothing). */
 int pq_poll_device_errors(unsigned int* flags_out);
 
@@ -230,6 +244,20 @@ int pq_decode_attn_static(const void* q, const void* k_blocks, const void* v_blo
                           const float* jl_matrix, int jl_dim, const void* qjl_bits, const void* qjl_norms,
                           void* out, int out_is_fp16, void* partial_out,
                           int n_splits, void* stream);
+
+/* pq_decode_attn_dynamic — pq_decode_attn with the sequence length read from DEVICE memory when the
+ * kernel starts (*seq_len_dev, int64, 8-byte aligned), clamped to [0, max_seq_len]; max_seq_len (>= 1,
+ * <= seq_capacity) is the length the work partition and the scratch are made for
+ * (pq_decode_attn_scratch_bytes with max_seq_len).  One recorded launch serves every length up to
+ * max_seq_len.  No counterpart in the reference. */
+int pq_decode_attn_dynamic(const void* q, const void* k_blocks, const void* v_blocks,
+                           int batch, int q_heads, int kv_heads, int64_t max_seq_len,
+                           const int64_t* seq_len_dev, int64_t seq_capacity,
+                           int head_dim, int k_bits, int v_bits,
+                           const float* codebook_k, const float* codebook_v, const float* rot, float scale,
+                           const float* jl_matrix, int jl_dim, const void* qjl_bits, const void* qjl_norms,
+                           void* out, int out_is_fp16, void* partial_out,
+                           int n_splits, void* scratch, size_t scratch_bytes, void* stream);
 
 /* Bytes of the built-in scratch array pq_decode_attn_static can use. */
 size_t pq_decode_attn_static_scratch_capacity(void);

@@ -73,6 +73,9 @@ struct CompressParams {
     // row * row_capacity + position + t of the output tensors (one row with capacity n_vec at position 0
     // is the plain contiguous case).
     int64_t tokens_per_row, row_capacity, position;
+    // When set, the position is read from device memory at kernel start (a step of a captured graph
+    // whose position advances on the device); out of range -> error flag, nothing written.
+    const int64_t* position_dev;
     int jl_dim;
     float cb[16];
     // Index search table: a normalised coordinate y falls into bucket k = floor(64 y + 64);
@@ -217,6 +220,14 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
     if (sm_addr(sp) + C::kLowBytes > C::kTabAddr) {
         if (threadIdx.x == 0) atomicOr(&g_compress_error, 2u);
         return;
+    }
+    int64_t position = p.position;
+    if (p.position_dev != nullptr) {
+        position = *p.position_dev;
+        if (position < 0 || position + p.tokens_per_row > p.row_capacity) {
+            if (threadIdx.x == 0) atomicOr(&g_compress_error, 32u);
+            return;
+        }
     }
     uint8_t* outs0 = sp;                        sp += C::kOutBufs * kTileVecs * VB;
     float* cb_s = reinterpret_cast<float*>(sp); sp += 64;
@@ -391,9 +402,9 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
     // token slot of input vector v in the output tensors
     const bool one_row = p.tokens_per_row >= p.n_vec;            // no 64-bit division on the common path
     auto slot_of = [&](int64_t v) -> int64_t {
-        if (one_row) return p.position + v;
+        if (one_row) return position + v;
         const int64_t r = v / p.tokens_per_row;
-        return r * p.row_capacity + p.position + (v - r * p.tokens_per_row);
+        return r * p.row_capacity + position + (v - r * p.tokens_per_row);
     };
     // signs of the sketch of the tile whose vector `row` sits in token slot `slot`: every thread reads 32
     // projections of its vector from the sketch accumulator and stores their sign bits
@@ -402,9 +413,13 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
         for (int cg = wg; cg * 32 < M; cg += WG) {
             float pr[32];
             tmem_ld32(pr, tmem_lane + C::kAccCol + cg * 32);
+            // bit j = (projection j >= 0).  One funnel shift per projection moves its sign bit into the
+            // word, last projection first; the complement turns "negative" into the stored convention.
+            // (A sum of products on a +0 accumulator is never -0, so the sign bit alone decides.)
             uint32_t w = 0;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) w |= (pr[j] >= 0.f ? 1u : 0u) << j;
+            for (int j = 31; j >= 0; --j) w = __funnelshift_l(__float_as_uint(pr[j]), w, 1);
+            w = ~w;
             if (!valid) continue;
             uint8_t* dst = p.qjl_bits_out + slot * M8 + cg * 4;
             if (cg * 32 + 32 <= M && (reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
@@ -417,7 +432,7 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
         }
     };
     auto store_rows = [&](int64_t g0, int rows, const uint8_t* src, int ln, int w, bool lead) {
-        store_rows_impl<VB, WG>(p.blocks_out, p.tokens_per_row, p.row_capacity, p.position, g0, rows, src, ln, w, lead);
+        store_rows_impl<VB, WG>(p.blocks_out, p.tokens_per_row, p.row_capacity, position, g0, rows, src, ln, w, lead);
     };
     uint32_t it = 0;
     int64_t slot_prev = 0;
@@ -496,7 +511,7 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
                     pw |= be.y & (((1u << BITS) - 1u) << sh);
                     if (up) pw += 1u << sh;
                     // residual in rotated space (scaled by 4096): coordinate minus radius * centroid
-                    const float ee = v[j] - __fmul_rn(dq, __uint_as_float(up ? be.w : be.z));
+                    const float ee = fmaf(-dq, __uint_as_float(up ? be.w : be.z), v[j]);
                     en2 = fmaf(ee, ee, en2);
                     v[j] = ee;
                 } else {
@@ -560,12 +575,14 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
                 p.qjl_norm_out[slot] = __float2half_rn(fminf(sqrtf(n2) * (1.0f / 4096.0f), 65504.0f));
             uint32_t ehi[16], elo[16];
 #pragma unroll
+            const float2 es2 = make_float2(es, es), neg1 = make_float2(-1.f, -1.f);
+#pragma unroll
             for (int j = 0; j < 32; j += 2) {
-                const float a0 = v[j] * es, a1 = v[j + 1] * es;
-                const __half2 h = __floats2half2_rn(a0, a1);
-                const float2 f = __half22float2(h);
+                const float2 a = mul2(v2[j >> 1], es2);
+                const __half2 h = __floats2half2_rn(a.x, a.y);
+                const float2 lo = fma2(__half22float2(h), neg1, a);          // exact: a - float(h)
                 ehi[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
-                elo[j >> 1] = pack_half2(a0 - f.x, a1 - f.y);
+                elo[j >> 1] = pack_half2(lo.x, lo.y);
             }
             // the residual columns and the sketch accumulator are in use until the previous tile's
             // sketch MMAs have completed
@@ -596,7 +613,7 @@ pq_compress_kernel(const CompressParams p, const __grid_constant__ CUtensorMap x
             const int64_t g0 = v0 + 32 * q;
             const uint8_t* src = outs + 32 * q * VB;
             if (one_row) {
-                uint8_t* dst = p.blocks_out + (p.position + g0) * VB;
+                uint8_t* dst = p.blocks_out + (position + g0) * VB;
                 if (rows == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
                     if (leader) bulk_store(dst, sm_addr(src), 32u * VB);
                 } else {                                             // ragged end or odd token offset
@@ -691,15 +708,18 @@ extern "C" int pq_poll_device_errors(unsigned int* flags_out) {
     return PQ_OK;
 }
 
-extern "C" int pq_compress_rows(const void* x, int64_t n_rows, int64_t tokens_per_row, int64_t row_capacity,
-                                int64_t position, int head_dim, int n_bits,
-                                const void* rot_split, const float* thresholds, const float* codebook,
-                                void* blocks_out,
-                                const void* jl_split, int jl_dim, void* qjl_bits_out, void* qjl_norm_out,
-                                void* stream) {
+// Shared body of pq_compress_rows (position on the host) and pq_compress_rows_dynamic (position in
+// device memory, checked by the kernel).
+static int compress_rows_impl(const void* x, int64_t n_rows, int64_t tokens_per_row, int64_t row_capacity,
+                              int64_t position, const int64_t* position_dev, int head_dim, int n_bits,
+                              const void* rot_split, const float* thresholds, const float* codebook,
+                              void* blocks_out,
+                              const void* jl_split, int jl_dim, void* qjl_bits_out, void* qjl_norm_out,
+                              void* stream) {
     using namespace pq;
     if (n_rows < 0 || tokens_per_row < 0 || position < 0 || row_capacity < position + tokens_per_row)
         return PQ_ERR_BAD_SHAPE;
+    if (position_dev != nullptr && (reinterpret_cast<uintptr_t>(position_dev) & 7)) return PQ_ERR_MISALIGNED;
     const int64_t n_vec = n_rows * tokens_per_row;
     if (n_vec > (int64_t)0x7FFFFF00) return PQ_ERR_TOO_LARGE;   // tile coordinates are 32-bit
     if (head_dim != 64 && head_dim != 128) return PQ_ERR_BAD_HEAD_DIM;
@@ -728,6 +748,7 @@ extern "C" int pq_compress_rows(const void* x, int64_t n_rows, int64_t tokens_pe
     p.tokens_per_row = tokens_per_row;
     p.row_capacity = row_capacity;
     p.position = position;
+    p.position_dev = position_dev;
     p.jl_dim = qjl ? jl_dim : 0;
     // thresholds / codebook are small HOST tables; they travel as kernel parameters.
     const int nlev = 1 << n_bits;
@@ -756,6 +777,27 @@ extern "C" int pq_compress_rows(const void* x, int64_t n_rows, int64_t tokens_pe
     PQ_DISPATCH(128, 2)
 #undef PQ_DISPATCH
     return PQ_ERR_BAD_HEAD_DIM;
+}
+
+extern "C" int pq_compress_rows(const void* x, int64_t n_rows, int64_t tokens_per_row, int64_t row_capacity,
+                                int64_t position, int head_dim, int n_bits,
+                                const void* rot_split, const float* thresholds, const float* codebook,
+                                void* blocks_out,
+                                const void* jl_split, int jl_dim, void* qjl_bits_out, void* qjl_norm_out,
+                                void* stream) {
+    return compress_rows_impl(x, n_rows, tokens_per_row, row_capacity, position, nullptr, head_dim, n_bits, rot_split,
+                              thresholds, codebook, blocks_out, jl_split, jl_dim, qjl_bits_out, qjl_norm_out, stream);
+}
+
+extern "C" int pq_compress_rows_dynamic(const void* x, int64_t n_rows, int64_t tokens_per_row, int64_t row_capacity,
+                                        const int64_t* position_dev, int head_dim, int n_bits,
+                                        const void* rot_split, const float* thresholds, const float* codebook,
+                                        void* blocks_out,
+                                        const void* jl_split, int jl_dim, void* qjl_bits_out, void* qjl_norm_out,
+                                        void* stream) {
+    if (position_dev == nullptr) return PQ_ERR_NULL_POINTER;
+    return compress_rows_impl(x, n_rows, tokens_per_row, row_capacity, 0, position_dev, head_dim, n_bits, rot_split,
+                              thresholds, codebook, blocks_out, jl_split, jl_dim, qjl_bits_out, qjl_norm_out, stream);
 }
 
 extern "C" int pq_compress(const void* x, int64_t n_vec, int head_dim, int n_bits,

@@ -68,7 +68,10 @@ struct DecodeParams {
     float* partial_out;        // [B, Hq, D+2] or null
     float* records;            // scratch: [rows*HG][splits][8][D+2]
     unsigned int* tickets;     // scratch: [rows*HG]
-    int64_t S, Scap;
+    int64_t S, Scap;           // S: the length the work plan is made for
+    // When set, the number of tokens attended to is read from device memory at kernel start and
+    // clamped to [0, S] (a step of a captured graph whose cache grows on the device).
+    const int64_t* seq_len_dev;
     int Hq, Hkv, G, HG, n_rows;
     int splits, tiles_per_split, max_segs;   // splits == 0: balanced contiguous partition
     int jl_dim;
@@ -325,7 +328,10 @@ pq_decode_attn_kernel(const DecodeParams p) {
     const uint32_t vconst = kTabAddr | (128 + (lane % (128 / VENT)) * VENT);
     const uint32_t sign_lane = smem_addr(signtab) + (lane & 15) * 8;
     const uint32_t qjl_frag_lane = smem_addr(qjl_frag) + lane * 16;
-    const int64_t tiles_total = (p.S + kTileTok - 1) / kTileTok;
+    const int64_t tiles_total = (p.S + kTileTok - 1) / kTileTok;          // of the plan
+    int64_t s_len = p.S;                                                  // tokens actually attended to
+    if (p.seq_len_dev != nullptr) s_len = max((int64_t)0, min(*p.seq_len_dev, p.S));
+    const int valid_tiles = (int)((s_len + kTileTok - 1) / kTileTok);
 
     // ---- value side: which bytes of a stored block this lane feeds into the MMAs.  Lane group g owns
     // the dims 4g .. 4g+3 of every 32-dim block: two packed bytes (4-bit) or one (2-bit).  The packed
@@ -356,8 +362,20 @@ pq_decode_attn_kernel(const DecodeParams p) {
     const int64_t n_vrows = (int64_t)p.n_rows * p.HG;
     const int64_t all_tiles = n_vrows * tiles_total;
     const int64_t n_cta = gridDim.x;
-    int64_t cur = p.splits ? (int64_t)blockIdx.x : (int64_t)blockIdx.x * all_tiles / n_cta;
-    const int64_t cur_end = p.splits ? n_vrows * p.splits : ((int64_t)blockIdx.x + 1) * all_tiles / n_cta;
+    // 64-bit divisions cost a few hundred cycles each and a segment needs half a dozen: when every
+    // product below fits 32 bits (all but extreme shapes) the same arithmetic runs on 32-bit values.
+    const bool small = all_tiles * (n_cta + 1) < (int64_t)0x7FFFFFFF;
+    int64_t cur, cur_end;
+    if (p.splits) {
+        cur = (int64_t)blockIdx.x;
+        cur_end = n_vrows * p.splits;
+    } else if (small) {
+        cur = (int64_t)((uint32_t)blockIdx.x * (uint32_t)all_tiles / (uint32_t)n_cta);
+        cur_end = (int64_t)(((uint32_t)blockIdx.x + 1u) * (uint32_t)all_tiles / (uint32_t)n_cta);
+    } else {
+        cur = (int64_t)blockIdx.x * all_tiles / n_cta;
+        cur_end = ((int64_t)blockIdx.x + 1) * all_tiles / n_cta;
+    }
     while (cur < cur_end) {
     int64_t vrow, tile_begin, tile_end;
     int seg_idx, n_segs;
@@ -368,6 +386,20 @@ pq_decode_attn_kernel(const DecodeParams p) {
         tile_begin = (int64_t)seg_idx * p.tiles_per_split;
         tile_end = min(tiles_total, tile_begin + p.tiles_per_split);
         cur += n_cta;
+    } else if (small) {
+        const uint32_t tt = (uint32_t)tiles_total, at = (uint32_t)all_tiles, nc = (uint32_t)n_cta;
+        const uint32_t c32 = (uint32_t)cur, vr = c32 / tt;
+        const uint32_t row_t0 = vr * tt, row_t1 = row_t0 + tt;
+        const uint32_t seg_end = min((uint32_t)cur_end, row_t1);
+        vrow = vr;
+        tile_begin = c32 - row_t0;
+        tile_end = seg_end - row_t0;
+        // CTA that owns tile x: largest c with floor(c * all_tiles / n_cta) <= x
+        const uint32_t c_first = ((row_t0 + 1u) * nc + at - 1u) / at - 1u;
+        const uint32_t c_last = (row_t1 * nc + at - 1u) / at - 1u;
+        seg_idx = (int)(blockIdx.x - c_first);
+        n_segs = (int)(c_last - c_first + 1u);
+        cur = seg_end;
     } else {
         vrow = cur / tiles_total;
         const int64_t row_t0 = vrow * tiles_total, row_t1 = row_t0 + tiles_total;
@@ -381,7 +413,7 @@ pq_decode_attn_kernel(const DecodeParams p) {
         n_segs = (int)(c_last - c_first + 1);
         cur = seg_end;
     }
-    const int row = (int)(vrow / p.HG), hg = (int)(vrow % p.HG);
+    const int row = (int)((uint32_t)vrow / (uint32_t)p.HG), hg = (int)((uint32_t)vrow % (uint32_t)p.HG);   // rows fit 32 bits
     const int b = row / p.Hkv, hkv = row % p.Hkv;
     const int Gp = min(HPC, p.G - hg * HPC);                             // query heads of this segment
     const int head0 = hkv * p.G + hg * HPC;                              // first query head
@@ -396,8 +428,8 @@ pq_decode_attn_kernel(const DecodeParams p) {
     const bool bulk_row = ((reinterpret_cast<uintptr_t>(k_row) | reinterpret_cast<uintptr_t>(v_row) |
                             (QJL ? reinterpret_cast<uintptr_t>(bits_row) | reinterpret_cast<uintptr_t>(norm_row) : 0)) & 15) == 0;
     // Tile numbers inside a row fit 32 bits (the host rejects longer sequences).
-    const int t_first = (int)tile_begin + warp, t_end = (int)tile_end;
-    const int full_tiles = (int)(p.S / kTileTok);                  // tiles below this number hold 16 tokens
+    const int t_first = (int)tile_begin + warp, t_end = min((int)tile_end, valid_tiles);
+    const int full_tiles = (int)(s_len / kTileTok);                // tiles below this number hold 16 tokens
     auto issue_tile = [&](int tile, int slot) {
         if (tile >= t_end) return;
         const size_t tok0 = (size_t)tile * kTileTok;
@@ -413,7 +445,7 @@ pq_decode_attn_kernel(const DecodeParams p) {
                 }
             }
         } else {
-            const int ntok = tile < full_tiles ? kTileTok : (int)(p.S - (int64_t)tok0);
+            const int ntok = tile < full_tiles ? kTileTok : (int)(s_len - (int64_t)tok0);
             uint8_t* st = my_stages + slot * stage_sz;
             copy_words(st, k_row + tok0 * C::TBK, ntok * C::TBK, C::kStageK, lane);
             copy_words(st + C::kStageK, v_row + tok0 * C::TBV, ntok * C::TBV, C::kStageV, lane);
@@ -633,7 +665,7 @@ pq_decode_attn_kernel(const DecodeParams p) {
 
         // mask tokens past the end of the sequence (only the ragged last tile of a row has any)
         if (!full) {
-            const int ntok = (int)(p.S - (int64_t)tile * kTileTok);
+            const int ntok = (int)(s_len - (int64_t)tile * kTileTok);
 #pragma unroll
             for (int h = 0; h < NH; ++h) {
                 if (2 * g >= ntok) sc[h][0] = -INFINITY;
@@ -835,31 +867,53 @@ pq_decode_attn_kernel(const DecodeParams p) {
         }
         __stcg(cta_rec + e, val);
     }
-    __threadfence();
+    // A row that lies inside this CTA has one record, written and read by this CTA alone: the barrier
+    // orders it; no fence, no ticket.
+    if (n_segs > 1) __threadfence();
     __syncthreads();
-    if (tid == 0) s_ticket = atomicAdd(p.tickets + group, 1u);
-    __syncthreads();
-    if (s_ticket == (unsigned)(n_segs - 1)) {
+    if (n_segs > 1) {
+        if (tid == 0) s_ticket = atomicAdd(p.tickets + group, 1u);
+        __syncthreads();
+    }
+    if (n_segs == 1 || s_ticket == (unsigned)(n_segs - 1)) {
         // ---- last segment of this virtual row to finish: merge the segment records
-        __threadfence();
+        if (n_segs > 1) __threadfence();
         const float* recs = p.records + group * p.max_segs * kRecHeads * (D + 2);
         for (int e = tid; e < HPC * D; e += NT) {
             const int head = e / D, dim = e % D;
-            float mx = -INFINITY;
-            for (int s = 0; s < n_segs; ++s) mx = fmaxf(mx, __ldcg(recs + (s * kRecHeads + head) * (D + 2)));
-            float l = 0.f, o = 0.f;
-            for (int s = 0; s < n_segs; ++s) {
-                const float* r = recs + (s * kRecHeads + head) * (D + 2);
-                const float ms = __ldcg(r);
-                const float sc = (ms == -INFINITY) ? 0.f : fast_exp2(ms - mx);
-                l = fmaf(sc, __ldcg(r + 1), l);
-                o = fmaf(sc, __ldcg(r + 2 + dim), o);
+            // four records per round trip to L2: the loads of a round do not depend on each other
+            float mx = -INFINITY, l = 0.f, o = 0.f;
+            for (int s0 = 0; s0 < n_segs; s0 += 4) {
+                float ms[4], ls[4], os[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float* r = recs + (min(s0 + u, n_segs - 1) * kRecHeads + head) * (D + 2);
+                    ms[u] = __ldcg(r);
+                    ls[u] = __ldcg(r + 1);
+                    os[u] = __ldcg(r + 2 + dim);
+                }
+                float m_new = mx;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (s0 + u >= n_segs) ms[u] = -INFINITY;
+                    m_new = fmaxf(m_new, ms[u]);
+                }
+                const float c = (mx == -INFINITY) ? 0.f : fast_exp2(mx - m_new);
+                l *= c;
+                o *= c;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float sc = (ms[u] == -INFINITY) ? 0.f : fast_exp2(ms[u] - m_new);
+                    l = fmaf(sc, ls[u], l);
+                    o = fmaf(sc, os[u], o);
+                }
+                mx = m_new;
             }
             if (p.partial_out) {
                 if (head < Gp) {
                     float* dst = p.partial_out + ((size_t)b * p.Hq + head0 + head) * (D + 2);
                     dst[2 + dim] = o;
-                    if (dim == 0) { dst[0] = mx; dst[1] = l; }
+                    if (dim == 0) { dst[0] = l > 0.f ? mx : 0.f; dst[1] = l; }   // empty: m = 0, l = 0 as the host path writes
                 }
             } else {
                 o_fin[e] = l > 0.f ? o / l : 0.f;
@@ -876,7 +930,7 @@ pq_decode_attn_kernel(const DecodeParams p) {
             for (int nt = warp; nt < D / 8; nt += NW) {
                 float c[4] = {0.f, 0.f, 0.f, 0.f};
                 const int n = nt * 8 + g;                               // B column of this lane
-#pragma unroll 4
+#pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const int k0 = ks * 16 + 2 * t;
                     const float x0 = __ldg(p.rot + (size_t)k0 * D + n) * 4096.f, x1 = __ldg(p.rot + (size_t)(k0 + 1) * D + n) * 4096.f;
@@ -1088,14 +1142,17 @@ static int check_decode_args(const void* q, const void* k_blocks, const void* v_
     return PQ_OK;
 }
 
-extern "C" int pq_decode_attn(const void* q, const void* k_blocks, const void* v_blocks,
-                              int batch, int q_heads, int kv_heads, int64_t seq_len, int64_t seq_capacity,
-                              int head_dim, int k_bits, int v_bits,
-                              const float* codebook_k, const float* codebook_v, const float* rot, float scale,
-                              const float* jl_matrix, int jl_dim, const void* qjl_bits, const void* qjl_norms,
-                              void* out, int out_is_fp16, void* partial_out,
-                              int n_splits, void* scratch, size_t scratch_bytes, void* stream) {
+// Shared body of pq_decode_attn (length on the host) and pq_decode_attn_dynamic (seq_len is the
+// upper bound the plan and the scratch are made for; the kernel reads the length from device memory).
+static int decode_attn_impl(const void* q, const void* k_blocks, const void* v_blocks,
+                            int batch, int q_heads, int kv_heads, int64_t seq_len, const int64_t* seq_len_dev,
+                            int64_t seq_capacity, int head_dim, int k_bits, int v_bits,
+                            const float* codebook_k, const float* codebook_v, const float* rot, float scale,
+                            const float* jl_matrix, int jl_dim, const void* qjl_bits, const void* qjl_norms,
+                            void* out, int out_is_fp16, void* partial_out,
+                            int n_splits, void* scratch, size_t scratch_bytes, void* stream) {
     using namespace pq;
+    if (seq_len_dev != nullptr && (reinterpret_cast<uintptr_t>(seq_len_dev) & 7)) return PQ_ERR_MISALIGNED;
     const int chk = check_decode_args(q, k_blocks, v_blocks, batch, q_heads, kv_heads, seq_len, seq_capacity, head_dim,
                                       k_bits, v_bits, codebook_k, codebook_v, rot, jl_matrix, jl_dim, qjl_bits,
                                       qjl_norms, out, partial_out, &n_splits);
@@ -1131,6 +1188,7 @@ extern "C" int pq_decode_attn(const void* q, const void* k_blocks, const void* v
     p.out = out;
     p.partial_out = static_cast<float*>(partial_out);
     p.S = seq_len;
+    p.seq_len_dev = seq_len_dev;
     p.Scap = seq_capacity;
     p.Hq = q_heads;
     p.Hkv = kv_heads;
@@ -1170,6 +1228,33 @@ extern "C" int pq_decode_attn(const void* q, const void* k_blocks, const void* v
     PQ_DEC(128, 4, 4) PQ_DEC(128, 4, 2) PQ_DEC(128, 2, 4) PQ_DEC(128, 2, 2)
 #undef PQ_DEC
     return PQ_ERR_BAD_HEAD_DIM;
+}
+
+extern "C" int pq_decode_attn(const void* q, const void* k_blocks, const void* v_blocks,
+                              int batch, int q_heads, int kv_heads, int64_t seq_len, int64_t seq_capacity,
+                              int head_dim, int k_bits, int v_bits,
+                              const float* codebook_k, const float* codebook_v, const float* rot, float scale,
+                              const float* jl_matrix, int jl_dim, const void* qjl_bits, const void* qjl_norms,
+                              void* out, int out_is_fp16, void* partial_out,
+                              int n_splits, void* scratch, size_t scratch_bytes, void* stream) {
+    return decode_attn_impl(q, k_blocks, v_blocks, batch, q_heads, kv_heads, seq_len, nullptr, seq_capacity, head_dim,
+                            k_bits, v_bits, codebook_k, codebook_v, rot, scale, jl_matrix, jl_dim, qjl_bits, qjl_norms,
+                            out, out_is_fp16, partial_out, n_splits, scratch, scratch_bytes, stream);
+}
+
+extern "C" int pq_decode_attn_dynamic(const void* q, const void* k_blocks, const void* v_blocks,
+                                      int batch, int q_heads, int kv_heads, int64_t max_seq_len,
+                                      const int64_t* seq_len_dev, int64_t seq_capacity,
+                                      int head_dim, int k_bits, int v_bits,
+                                      const float* codebook_k, const float* codebook_v, const float* rot, float scale,
+                                      const float* jl_matrix, int jl_dim, const void* qjl_bits, const void* qjl_norms,
+                                      void* out, int out_is_fp16, void* partial_out,
+                                      int n_splits, void* scratch, size_t scratch_bytes, void* stream) {
+    if (seq_len_dev == nullptr) return PQ_ERR_NULL_POINTER;
+    if (max_seq_len <= 0) return PQ_ERR_BAD_SHAPE;       // the plan needs at least one tile
+    return decode_attn_impl(q, k_blocks, v_blocks, batch, q_heads, kv_heads, max_seq_len, seq_len_dev, seq_capacity,
+                            head_dim, k_bits, v_bits, codebook_k, codebook_v, rot, scale, jl_matrix, jl_dim, qjl_bits,
+                            qjl_norms, out, out_is_fp16, partial_out, n_splits, scratch, scratch_bytes, stream);
 }
 
 // ------------------------------------------------------------------ no-allocation variant

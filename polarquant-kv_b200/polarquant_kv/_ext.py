@@ -27,6 +27,13 @@ SIGNATURES = {
     "pq_compress_rows": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p, c_float_p,
                                  c_float_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "pq_dequant": (c_int, [c_void_p, c_int64, c_int, c_int, c_float_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "pq_compress_rows_dynamic": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int, c_int, c_void_p,
+                                         c_float_p, c_float_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                         c_void_p]),
+    "pq_decode_attn_dynamic": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_void_p, c_int64,
+                                       c_int, c_int, c_int, c_float_p, c_float_p, c_void_p, c_float,
+                                       c_void_p, c_int, c_void_p, c_void_p,
+                                       c_void_p, c_int, c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
     "pq_decode_attn": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64,
                                c_int, c_int, c_int, c_float_p, c_float_p, c_void_p, c_float,
                                c_void_p, c_int, c_void_p, c_void_p,

@@ -53,10 +53,13 @@ def standard_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tens
 def decode_attention(query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, plan,
                      enable_qjl: bool = True, scale: float | None = None,
                      out_dtype: torch.dtype = torch.float32, n_splits: int = 0,
-                     partial: bool = False, seq_range: tuple[int, int] | None = None) -> torch.Tensor:
+                     partial: bool = False, seq_range: tuple[int, int] | None = None,
+                     seq_len_tensor: torch.Tensor | None = None) -> torch.Tensor:
     """One query token per sequence.  query [B, Hq, D] float16 -> [B, Hq, D] (or, with
     ``partial``, float32 [B, Hq, D+2] = (m, l, o_rotated) for a cross-GPU merge).
-    ``seq_range`` restricts attention to tokens [begin, end) of the cache."""
+    ``seq_range`` restricts attention to tokens [begin, end) of the cache.  With ``seq_len_tensor``
+    (one int64 on the device) the kernel reads the number of tokens when it runs, up to the cache's
+    capacity (pq_decode_attn_dynamic): the launch can be replayed from a CUDA graph as the cache grows."""
     _require_cuda(query, "query")
     B, Hq, D = query.shape
     Hkv = ck.blocks.shape[1]
@@ -81,6 +84,12 @@ def decode_attention(query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, pl
     q = query.to(torch.float16).contiguous()
     lib = _ext.lib()
     n_splits = max(0, int(n_splits))     # 0: the library balances the work itself
+    if seq_len_tensor is not None:
+        if seq_range is not None:
+            raise ValueError("seq_range and seq_len_tensor exclude each other")
+        if seq_len_tensor.dtype != torch.int64 or seq_len_tensor.numel() != 1 or seq_len_tensor.device != dev:
+            raise ValueError("seq_len_tensor must be a one-element int64 tensor on the query's device")
+        S = cap                              # the work partition and the scratch cover the capacity
     need = lib.pq_decode_attn_scratch_bytes(B, Hq, Hkv, S, D, n_splits)
     scratch = _scratch(dev, need)
     if partial:
@@ -89,8 +98,11 @@ def decode_attention(query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, pl
         out = torch.empty((B, Hq, D), dtype=out_dtype, device=dev)
     cbk, _, _ = tables(ck.n_bits)
     cbv, _, _ = tables(cv.n_bits)
-    st = lib.pq_decode_attn(
-        q.data_ptr(), kb.data_ptr(), vb.data_ptr(), B, Hq, Hkv, S, cap, D, ck.n_bits, cv.n_bits,
+    fn, length = lib.pq_decode_attn, (S,)
+    if seq_len_tensor is not None:
+        fn, length = lib.pq_decode_attn_dynamic, (S, seq_len_tensor.data_ptr())
+    st = fn(
+        q.data_ptr(), kb.data_ptr(), vb.data_ptr(), B, Hq, Hkv, *length, cap, D, ck.n_bits, cv.n_bits,
         cbk, cbv, plan.rot.data_ptr(), ctypes.c_float(scale if scale is not None else 1.0 / math.sqrt(D)),
         plan.jl.data_ptr() if use_qjl else None, plan.jl_dim if use_qjl else 0,
         bits_t.data_ptr() if use_qjl else None, norms_t.data_ptr() if use_qjl else None,
@@ -110,11 +122,15 @@ class PreparedDecode:
     ``partial=True`` produces the float32 (m, l, o_rotated) records [B, Hq, D+2] of a
     sequence-sharded decode instead of the finished output.  The QJL score correction is applied
     when the plan carries a JL matrix, the key cache carries a sketch and ``enable_qjl`` is set
-    (the defaults of ``decode_attention``)."""
+    (the defaults of ``decode_attention``).
+
+    ``seq_len_tensor`` (a one-element int64 tensor on the device) makes the kernel read the number
+    of tokens from device memory at every launch (pq_decode_attn_dynamic, clamped to the cache's
+    capacity), so the call can be recorded once in a CUDA graph and replayed while the cache grows."""
 
     def __init__(self, query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, plan,
                  scale: float | None = None, out_dtype: torch.dtype = torch.float32, n_splits: int = 0,
-                 partial: bool = False, enable_qjl: bool = True):
+                 partial: bool = False, enable_qjl: bool = True, seq_len_tensor: torch.Tensor | None = None):
         _require_cuda(query, "query")
         if query.dtype != torch.float16 or not query.is_contiguous():
             raise ValueError("the query buffer must be a contiguous float16 tensor [B, Hq, D]")
@@ -130,6 +146,11 @@ class PreparedDecode:
             self.out = torch.empty((B, Hq, D), dtype=out_dtype, device=self.dev)
         lib = _ext.lib()
         self._fn = lib.pq_decode_attn
+        self.seq_len_tensor = seq_len_tensor
+        if seq_len_tensor is not None:
+            if seq_len_tensor.dtype != torch.int64 or seq_len_tensor.numel() != 1 or seq_len_tensor.device != self.dev:
+                raise ValueError("seq_len_tensor must be a one-element int64 tensor on the query's device")
+            self._fn = lib.pq_decode_attn_dynamic
         need = lib.pq_decode_attn_scratch_bytes(B, Hq, Hkv, ck.max_seq_len, D, max(0, n_splits))
         self.scratch = torch.zeros(max(need, 256), dtype=torch.uint8, device=self.dev)   # private: no sharing
         cbk, cbv = tables(ck.n_bits)[0], tables(cv.n_bits)[0]
@@ -149,7 +170,11 @@ class PreparedDecode:
 
     def __call__(self, stream: torch.cuda.Stream | None = None) -> torch.Tensor:
         """Enqueue on the stream the object was prepared on, or on `stream`."""
-        st = self._fn(*self._head, self.ck.seq_len, *self._tail, (stream or self._stream).cuda_stream)
+        if self.seq_len_tensor is not None:
+            st = self._fn(*self._head, self.ck.max_seq_len, self.seq_len_tensor.data_ptr(), *self._tail,
+                          (stream or self._stream).cuda_stream)
+        else:
+            st = self._fn(*self._head, self.ck.seq_len, *self._tail, (stream or self._stream).cuda_stream)
         if st:
             _ext.check(st, "pq_decode_attn")
         return self.out

@@ -66,9 +66,19 @@ class KVCacheManager:
         used = self.memory_bytes
         return original / used if used > 0 else 0.0
 
-    def append(self, key: torch.Tensor, value: torch.Tensor) -> None:
-        """key, value: [batch, num_heads, new_seq, head_dim] float16; written at the current length."""
+    def append(self, key: torch.Tensor, value: torch.Tensor, position: torch.Tensor | None = None) -> None:
+        """key, value: [batch, num_heads, new_seq, head_dim] float16; written at the current length.
+
+        With ``position`` (one int64 on the device) the offset is read by the kernels when they run and
+        the host-side length is left alone: a decode step recorded once as a CUDA graph appends at a
+        position that advances on the device; call ``advance`` afterwards for the bookkeeping."""
         new_seq = key.shape[2]
+        if position is not None:
+            if not self.config.enable_compression:
+                raise ValueError("a device-side position needs the compressed cache")
+            quantizer.compress(key, self.plan, self.k_bits, 32, self.P, out=self._compressed_keys, position=position)
+            quantizer.compress(value, self.plan_v, self.v_bits, out=self._compressed_values, position=position)
+            return
         if self._seq_len + new_seq > self.max_seq_len:
             raise RuntimeError(f"KV cache full: {self._seq_len} + {new_seq} > {self.max_seq_len}")
         pos = self._seq_len
@@ -82,17 +92,33 @@ class KVCacheManager:
         if self.config.enable_compression:
             self._compressed_keys.seq_len = self._compressed_values.seq_len = self._seq_len
 
+    def advance(self, new_tokens: int) -> None:
+        """Account for tokens that were appended with a device-side position."""
+        if self._seq_len + new_tokens > self.max_seq_len:
+            raise RuntimeError(f"KV cache full: {self._seq_len} + {new_tokens} > {self.max_seq_len}")
+        self._seq_len += new_tokens
+        if self.config.enable_compression:
+            self._compressed_keys.seq_len = self._compressed_values.seq_len = self._seq_len
+
     def get_kv(self):
         """(CompressedKV, CompressedKV) in compressed mode, (key, value) float16 views otherwise."""
         if not self.config.enable_compression:
             return self._key_cache[:, :, :self._seq_len], self._value_cache[:, :, :self._seq_len]
         return self._compressed_keys, self._compressed_values
 
-    def attend(self, query: torch.Tensor, causal: bool = True) -> torch.Tensor:
+    def attend(self, query: torch.Tensor, causal: bool = True,
+               seq_len_tensor: torch.Tensor | None = None) -> torch.Tensor:
         """query [batch, q_heads, seq_q, head_dim] float16 over everything stored so far -> float32
         [batch, q_heads, seq_q, head_dim].  The last seq_q tokens of the cache are the queries' own
-        positions: with ``causal`` query i sees tokens [0, seq_len - seq_q + i]."""
+        positions: with ``causal`` query i sees tokens [0, seq_len - seq_q + i].  ``seq_len_tensor``
+        (one int64 on the device, seq_q == 1): the number of tokens is read by the kernel when it runs."""
         B, Hq, Sq, D = query.shape
+        if seq_len_tensor is not None:
+            if Sq != 1 or not self.config.enable_compression:
+                raise ValueError("a device-side length serves single-token steps over the compressed cache")
+            ck, cv = self.get_kv()
+            return decode_attention(query[:, :, 0].contiguous(), ck, cv, self.plan,
+                                    enable_qjl=self.config.enable_qjl, seq_len_tensor=seq_len_tensor).unsqueeze(2)
         if not self.config.enable_compression:
             k, v = self.get_kv()
             rep = Hq // self.num_heads

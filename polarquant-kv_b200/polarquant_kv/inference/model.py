@@ -69,10 +69,15 @@ class CompressedAttention(nn.Module):
         self.v_proj = nn.Linear(cfg.hidden, cfg.kv_heads * cfg.head_dim, bias=True)
         self.o_proj = nn.Linear(cfg.q_heads * cfg.head_dim, cfg.hidden, bias=False)
 
-    def forward(self, x: torch.Tensor, cache: KVCacheManager, timers=None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, cache: KVCacheManager, timers=None, device_step=None) -> torch.Tensor:
+        """``device_step`` = (position, length) one-element int64 device tensors: the step's token
+        position and the number of cached tokens after the append, both read on the device."""
         c = self.cfg
         B, S, _ = x.shape
-        pos = torch.arange(cache.seq_len, cache.seq_len + S, device=x.device)
+        if device_step is not None:
+            pos = device_step[0]
+        else:
+            pos = torch.arange(cache.seq_len, cache.seq_len + S, device=x.device)
         q = self.q_proj(x).view(B, S, c.q_heads, c.head_dim).transpose(1, 2)
         k = self.k_proj(x).view(B, S, c.kv_heads, c.head_dim).transpose(1, 2)
         v = self.v_proj(x).view(B, S, c.kv_heads, c.head_dim).transpose(1, 2)
@@ -81,8 +86,12 @@ class CompressedAttention(nn.Module):
         v = v.to(torch.float16)
         if timers is not None:
             timers.start()
-        cache.append(k.contiguous(), v.contiguous())
-        out = cache.attend(q.contiguous(), causal=True)
+        if device_step is not None:
+            cache.append(k.contiguous(), v.contiguous(), position=device_step[0])
+            out = cache.attend(q.contiguous(), seq_len_tensor=device_step[1])
+        else:
+            cache.append(k.contiguous(), v.contiguous())
+            out = cache.attend(q.contiguous(), causal=True)
         if timers is not None:
             timers.stop()
         out = out.to(x.dtype).transpose(1, 2).reshape(B, S, c.q_heads * c.head_dim)
@@ -98,8 +107,8 @@ class DecoderLayer(nn.Module):
         self.up = nn.Linear(cfg.hidden, cfg.intermediate, bias=False)
         self.down = nn.Linear(cfg.intermediate, cfg.hidden, bias=False)
 
-    def forward(self, x, cache, timers=None):
-        x = x + self.attn(self.norm1(x), cache, timers)
+    def forward(self, x, cache, timers=None, device_step=None):
+        x = x + self.attn(self.norm1(x), cache, timers, device_step)
         h = self.norm2(x)
         return x + self.down(F.silu(self.gate(h)) * self.up(h))
 
@@ -161,6 +170,64 @@ class DecoderLM(nn.Module):
             x = layer(x, cache, timers)
         x = self.norm(x[:, -1:] if last_only else x)
         return self.head(x).float().squeeze(1) if last_only else self.head(x).float()
+
+    @torch.no_grad()
+    def _device_step(self, token: torch.Tensor, caches, state) -> None:
+        """One greedy step whose position, cache length and output slot live on the device:
+        ``token`` [B, 1] is consumed and overwritten with the next token."""
+        position, length, step, out = state
+        out.index_copy_(1, step, token)
+        x = self.embed(token)
+        for layer, cache in zip(self.layers, caches):
+            x = layer(x, cache, None, (position, length))
+        logits = self.head(self.norm(x)).float().squeeze(1)
+        token.copy_(logits.argmax(-1, keepdim=True))
+        position.add_(1)
+        length.add_(1)
+        step.add_(1)
+
+    @torch.no_grad()
+    def decode_graph(self, token: torch.Tensor, steps: int, caches: list[KVCacheManager]) -> torch.Tensor:
+        """``steps`` greedy single-token steps after a prefill, starting from ``token`` [B, 1], replayed
+        from ONE CUDA graph: the position and the cache length advance in device memory
+        (pq_compress_rows_dynamic, pq_decode_attn_dynamic), so the ~25 kernels per layer are launched by
+        one graph launch per token instead of one Python call each.  The first step runs eagerly (it
+        also warms the libraries up), the second is recorded, the rest are replays.  Returns the ids
+        fed and generated, [B, steps]."""
+        B = token.shape[0]
+        start = caches[0].seq_len
+        if start + steps > caches[0].max_seq_len:
+            raise RuntimeError(f"KV cache full: {start} + {steps} > {caches[0].max_seq_len}")
+        dev = token.device
+        if steps == 0:
+            return token[:, :0]
+        token = token.clone()
+        state = (torch.full((1,), start, dtype=torch.int64, device=dev),
+                 torch.full((1,), start + 1, dtype=torch.int64, device=dev),
+                 torch.zeros(1, dtype=torch.int64, device=dev),
+                 torch.empty((B, steps), dtype=token.dtype, device=dev))
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            self._device_step(token, caches, state)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        if steps > 1:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._device_step(token, caches, state)
+            for _ in range(steps - 1):
+                graph.replay()
+        for cache in caches:
+            cache.advance(steps)
+        return state[3]
+
+    @torch.no_grad()
+    def generate_graph(self, prompt_ids: torch.Tensor, steps: int, caches: list[KVCacheManager]) -> torch.Tensor:
+        """``generate`` with the single-token steps served by ``decode_graph``."""
+        if prompt_ids.shape[1] + steps > caches[0].max_seq_len:
+            raise RuntimeError(f"KV cache full: {prompt_ids.shape[1]} + {steps} > {caches[0].max_seq_len}")
+        token = self.forward(prompt_ids, caches).argmax(-1, keepdim=True)
+        return self.decode_graph(token, steps, caches)
 
     @torch.no_grad()
     def generate(self, prompt_ids: torch.Tensor, steps: int, caches: list[KVCacheManager], timers=None) -> torch.Tensor:

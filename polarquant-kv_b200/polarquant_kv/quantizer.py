@@ -61,7 +61,9 @@ def compress(kv: torch.Tensor, rotation_matrix, n_bits: int = 4, group_size: int
 
     With ``jl_matrix`` the QJL sign sketch and residual norms are produced as well.
     ``out``/``position`` write the new tokens in place into a preallocated cache at
-    sequence offset ``position`` (append-on-write); otherwise a new cache is returned.
+    sequence offset ``position`` (append-on-write); otherwise a new cache is returned.  ``position``
+    may be a one-element int64 tensor on the device: the kernel then reads the offset when it runs
+    (pq_compress_rows_dynamic), which lets a decode step be recorded once as a CUDA graph.
     An empty input returns an empty cache (compress_kernel.py:108-124).
     """
     _require_cuda(kv, "kv")
@@ -88,14 +90,20 @@ def compress(kv: torch.Tensor, rotation_matrix, n_bits: int = 4, group_size: int
     else:
         if out.n_bits != n_bits or out.original_dim != d or tuple(out.blocks.shape[:2]) != (B, H):
             raise ValueError("preallocated cache does not match the input")
-        if position < 0 or position + S > out.max_seq_len:
+        if isinstance(position, torch.Tensor):
+            # the offset lives on the device (a decode step replayed from a CUDA graph): the kernel checks
+            # it against the capacity; the caller keeps out.seq_len up to date
+            if position.dtype != torch.int64 or position.numel() != 1 or position.device != dev:
+                raise ValueError("a device-side position must be a one-element int64 tensor on the cache's device")
+        elif position < 0 or position + S > out.max_seq_len:
             raise RuntimeError(f"cache full: {position}+{S} > {out.max_seq_len}")   # kv_cache.py:76-79
         if jl_dim and (out.qjl_signs is None or out.qjl_signs.shape[-1] != jl_dim // 8):
             raise ValueError("preallocated cache has no sketch side band of this width")
         if not out.blocks.is_contiguous():
             raise ValueError("cache tensors must be contiguous")
         capacity = out.blocks.shape[2]
-        out.seq_len = max(out.seq_len, position + S)
+        if not isinstance(position, torch.Tensor):
+            out.seq_len = max(out.seq_len, position + S)
     if kv4.numel() == 0:
         return out
 
@@ -103,12 +111,14 @@ def compress(kv: torch.Tensor, rotation_matrix, n_bits: int = 4, group_size: int
     x = kv4.to(torch.float16).contiguous()
     # one launch for all (batch, head) rows: row r of the input goes to tokens [position, position + S) of
     # row r of the cache
-    st = _ext.lib().pq_compress_rows(
-        x.data_ptr(), B * H, S, capacity, position, d, n_bits, plan.rot_split.data_ptr(), thr, cb,
-        out.blocks.data_ptr(),
+    dynamic = isinstance(position, torch.Tensor)
+    fn = _ext.lib().pq_compress_rows_dynamic if dynamic else _ext.lib().pq_compress_rows
+    st = fn(
+        x.data_ptr(), B * H, S, capacity, position.data_ptr() if dynamic else position, d, n_bits,
+        plan.rot_split.data_ptr(), thr, cb, out.blocks.data_ptr(),
         plan.jl_split.data_ptr() if jl_dim else None, jl_dim,
         out.qjl_signs.data_ptr() if jl_dim else None, out.residual_norms.data_ptr() if jl_dim else None, _stream(dev))
-    _ext.check(st, "pq_compress_rows")
+    _ext.check(st, "pq_compress_rows_dynamic" if dynamic else "pq_compress_rows")
     return out
 
 

@@ -202,3 +202,92 @@ def test_mixed_precision_policies_vs_oracle():
         assert np.abs(out_h[b] - ref).max() <= 2e-3
     assert policy.compute_layer_bitwidths(24, 3.0) == [4] * 6 + [2] * 12 + [4] * 6
     assert policy.compute_layer_bitwidths(2) == [4, 4]
+
+
+def test_device_side_position_and_length():
+    """pq_compress_rows_dynamic / pq_decode_attn_dynamic: the offset of the append and the length of
+    the attention come from device memory; results equal the host-argument entry points."""
+    from polarquant_kv import _ext, quantizer, rotation
+    from polarquant_kv.attention import PreparedDecode, decode_attention
+    dev = _cuda()
+    B, H, Hq, D, cap = 3, 2, 8, 128, 200
+    R = rotation.generate_rotation_matrix(D, seed=5)
+    plan = rotation.device_plan(R, dev)
+    gen = torch.Generator().manual_seed(3)
+    K = torch.randn(B, H, 150, D, generator=gen).to(dev, torch.float16)
+    V = torch.randn(B, H, 150, D, generator=gen).to(dev, torch.float16)
+    q = torch.randn(B, Hq, D, generator=gen).to(dev, torch.float16)
+    pos = torch.zeros(1, dtype=torch.int64, device=dev)
+    length = torch.zeros(1, dtype=torch.int64, device=dev)
+
+    ref_k = quantizer.allocate_cache(B, H, cap, D, 4, 0, dev)
+    ref_v = quantizer.allocate_cache(B, H, cap, D, 4, 0, dev)
+    dyn_k = quantizer.allocate_cache(B, H, cap, D, 4, 0, dev)
+    dyn_v = quantizer.allocate_cache(B, H, cap, D, 4, 0, dev)
+    prepared = PreparedDecode(q, dyn_k, dyn_v, plan, seq_len_tensor=length)
+    done = 0
+    for chunk in (1, 33, 1, 100, 15):                      # appends of one token and of many
+        ks, vs = K[:, :, done:done + chunk], V[:, :, done:done + chunk]
+        quantizer.compress(ks, plan, 4, out=ref_k, position=done)
+        quantizer.compress(vs, plan, 4, out=ref_v, position=done)
+        pos.fill_(done)
+        quantizer.compress(ks, plan, 4, out=dyn_k, position=pos)
+        quantizer.compress(vs, plan, 4, out=dyn_v, position=pos)
+        done += chunk
+        length.fill_(done)
+        assert torch.equal(ref_k.blocks, dyn_k.blocks) and torch.equal(ref_v.blocks, dyn_v.blocks)
+        want = decode_attention(q, ref_k, ref_v, plan)
+        got = decode_attention(q, dyn_k, dyn_v, plan, seq_len_tensor=length)
+        assert float((got - want).abs().max()) <= 2e-5      # another work partition, same arithmetic
+        assert float((prepared().clone() - want).abs().max()) <= 2e-5
+    # a length beyond the capacity is clamped, zero gives zeros
+    length.fill_(10 ** 6)
+    dyn_k.seq_len = dyn_v.seq_len = cap
+    full = decode_attention(q, dyn_k, dyn_v, plan)
+    assert float((decode_attention(q, dyn_k, dyn_v, plan, seq_len_tensor=length) - full).abs().max()) <= 2e-5
+    length.fill_(0)
+    assert float(decode_attention(q, dyn_k, dyn_v, plan, seq_len_tensor=length).abs().max()) == 0.0
+    # an append that would run past the capacity writes nothing and raises the device flag
+    _ext.poll_device_errors()
+    before = dyn_k.blocks.clone()
+    pos.fill_(cap - 3)
+    quantizer.compress(K[:, :, :4], plan, 4, out=dyn_k, position=pos)
+    flags = ctypes_flags()
+    assert flags & 32
+    assert torch.equal(before, dyn_k.blocks)
+    with pytest.raises(ValueError):
+        quantizer.compress(K[:, :, :4], plan, 4, out=dyn_k, position=pos.to(torch.int32))
+
+
+def ctypes_flags() -> int:
+    """pq_poll_device_errors without the raising wrapper."""
+    import ctypes
+    from polarquant_kv import _ext
+    flags = ctypes.c_uint(0)
+    assert _ext.lib().pq_poll_device_errors(ctypes.byref(flags)) == 0
+    return flags.value
+
+
+def test_graph_replayed_decode_steps_equal_eager_steps():
+    """generate_graph (one CUDA graph launch per token, position and length on the device) produces the
+    greedy tokens of generate (one Python call per kernel), with and without the key sketch."""
+    from polarquant_kv.inference import DecoderConfig, DecoderLM, PolarQuantConfig
+    dev = _cuda()
+    cfg = DecoderConfig(num_layers=3, hidden=128, q_heads=4, kv_heads=2, head_dim=64, intermediate=256, vocab=503)
+    for pq in (PolarQuantConfig(n_bits=4), PolarQuantConfig(n_bits=4, enable_qjl=True, jl_dim=64)):
+        model = DecoderLM(cfg, pq).init_random(seed=0, dtype=torch.float32, device=dev)
+        prompt = torch.randint(0, cfg.vocab, (2, 41), generator=torch.Generator().manual_seed(7)).to(dev)
+        eager_caches = model.create_cache_managers(96, 2, dev)
+        graph_caches = model.create_cache_managers(96, 2, dev)
+        eager = model.generate(prompt, 20, eager_caches)
+        replayed = model.generate_graph(prompt, 20, graph_caches)
+        assert torch.equal(eager, replayed)
+        assert graph_caches[0].seq_len == eager_caches[0].seq_len == 61
+        for a, b in zip(eager_caches, graph_caches):         # the prompt part is the same launch in both
+            assert torch.equal(a.get_kv()[0].blocks[:, :, :41], b.get_kv()[0].blocks[:, :, :41])
+            # the appended steps: same tokens in, inputs equal up to the attention's summation order
+            same = (a.get_kv()[0].blocks[:, :, 41:61] == b.get_kv()[0].blocks[:, :, 41:61]).float().mean().item()
+            assert same > 0.999
+        assert ctypes_flags() == 0
+        with pytest.raises(RuntimeError):
+            model.generate_graph(prompt, 80, model.create_cache_managers(96, 2, dev))
