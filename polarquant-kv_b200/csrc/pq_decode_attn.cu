@@ -49,6 +49,18 @@ constexpr int kTabBytes = 65536;    // 256 byte values x 256 B: K copies at +0, 
 // the output error near 5e-4 of the 2e-3 tolerance and halves the value-side lookups and MMAs;
 // 2: {hi, lo} pairs like the keys (float32-level accuracy).  One term fails the 2e-3 bar on short,
 // peaked sequences with large values (measured 2.9e-3), so two are used.
+// Launch shape, overridable on the compiler command line for timing experiments: warps per CTA, teams
+// of warps per CTA (see DecodeCfg), tile stages per warp.  Measured on the 32 x 8 x 8192-token workload:
+// 16 warps in 2 teams 141.8 us, 20 warps in 2 teams 143.8, 20 warps in one team 149.5, 4 teams 142-149.
+#ifndef PQ_DEC_TEAMS
+#define PQ_DEC_TEAMS 2
+#endif
+#ifndef PQ_DEC_STAGES
+#define PQ_DEC_STAGES 3
+#endif
+#ifndef PQ_DEC_WARPS
+#define PQ_DEC_WARPS 16
+#endif
 constexpr int kVTerms = 2;
 
 // Device error flags of this file (read and cleared through pq_poll_device_errors):
@@ -74,6 +86,7 @@ struct DecodeParams {
     const int64_t* seq_len_dev;
     int Hq, Hkv, G, HG, n_rows;
     int splits, tiles_per_split, max_segs;   // splits == 0: balanced contiguous partition
+    int n_workers;             // balanced mode: teams that own a range of tiles (<= teams in the grid)
     int jl_dim;
     int out_is_fp16;
     float scale_log2;          // softmax scale * log2(e)
@@ -192,11 +205,18 @@ template <int D, int KBITS, int VBITS, int NH, bool QJL>
 struct DecodeCfg {
     static constexpr int NBLK = D / 32;
     static constexpr int HPC = 4 * NH;                            // query heads per CTA
-    // Warps per CTA and tile stages per warp.  The loop is bound by instruction latency, so with four
-    // query heads per KV head 20 warps of at most 102 registers replace 16 of 128.
-    static constexpr int NWARPS = (NH == 1 && !QJL) ? 20 : 16;
+    // Warps per CTA and tile stages per warp (16 warps of at most 128 registers; 12, 16 and 20 warps run
+    // the tile loop at the same rate).
+    static constexpr int NWARPS = PQ_DEC_WARPS;
     static constexpr int NTHREADS = NWARPS * 32;
-    static constexpr int kStages = 3;
+    // The warps of a CTA form kTeams independent teams, each walking its own range of tiles with its own
+    // query buffers and barrier: while one team is between two segments (query rotation, record merge,
+    // final rotation) the other keeps the SM's pipes busy.  (A dozen warps already reach the tile rate of
+    // twenty, so a team alone nearly fills the SM.)
+    static constexpr int kTeams = QJL ? 1 : PQ_DEC_TEAMS;
+    static constexpr int kTeamWarps = NWARPS / kTeams;
+    static constexpr int kTeamThreads = kTeamWarps * 32;
+    static constexpr int kStages = PQ_DEC_STAGES;
     static constexpr int BBK = block_bytes(KBITS), BBV = block_bytes(VBITS);
     static constexpr int TBK = NBLK * BBK, TBV = NBLK * BBV;     // bytes per token
     static constexpr int kStageK = kTileTok * TBK;                // multiples of 64 bytes
@@ -211,7 +231,7 @@ struct DecodeCfg {
     }
     __host__ __device__ static int qjl_frag_bytes(int jl_dim) { return QJL ? (jl_dim / 16) * 32 * 16 : 0; }
     // Shared-memory plan (byte addresses in the shared window):
-    //   [base, 64K)        query buffers, split codebooks, the rings of the first n_low warps
+    //   [base, 64K)        the teams' query buffers, split codebooks, the rings of the first n_low warps
     //   [64K, 128K)        centroid table (its address is baked into the lookups)
     //   [128K, ...)        sign table, JL query fragments, the rings of the remaining warps
     // A ring = head (see kRingHead) + kStages tile stages; at the end of a work item the warp parks
@@ -221,7 +241,8 @@ struct DecodeCfg {
         return kRingHead + (((r > rec ? r : rec) + 15) & ~15);
     }
     __host__ __device__ static int low_fixed(int jl_dim) {
-        return ((HPC * (3 * D + (QJL ? jl_dim : 0)) * 4 + 2 * 16 * 4) + 15) & ~15;
+        // per team: rotated query and final-stage buffer [HPC][D] each (+ the projected query with QJL)
+        return ((kTeams * HPC * (2 * D + (QJL ? jl_dim : 0)) * 4 + 2 * 16 * 4) + 15) & ~15;
     }
     // rings that fit below the table when the dynamic window starts at or below 8 KB
     __host__ __device__ static int n_low(int jl_dim) {
@@ -257,7 +278,6 @@ template <int D, int KBITS, int VBITS, int NH, bool QJL>
 __global__ void __launch_bounds__(DecodeCfg<D, KBITS, VBITS, NH, QJL>::NTHREADS, 1)
 pq_decode_attn_kernel(const DecodeParams p) {
     using C = DecodeCfg<D, KBITS, VBITS, NH, QJL>;
-    constexpr int NW = C::NWARPS;
     constexpr int NT = C::NTHREADS;
     constexpr int kStages = C::kStages;
     constexpr int NBLK = C::NBLK;
@@ -265,11 +285,13 @@ pq_decode_attn_kernel(const DecodeParams p) {
     constexpr int VT = kVTerms;
     constexpr int VENT = (VBITS == 4 ? 4 : 8) * VT;                      // bytes per value-table entry
     extern __shared__ __align__(16) uint8_t smem[];
-    float* q_in = reinterpret_cast<float*>(smem);                        // [HPC][D] (spare)
-    float* q_rot = q_in + HPC * D;                                       // [HPC][D] rotated, scaled
+    constexpr int kTeams = C::kTeams, TW = C::kTeamWarps, TT = C::kTeamThreads;
+    const int team = (threadIdx.x >> 5) / TW;                            // this warp's team
+    const int team_buf = HPC * (2 * D + (QJL ? p.jl_dim : 0));           // floats per team
+    float* q_rot = reinterpret_cast<float*>(smem) + team * team_buf;     // [HPC][D] rotated, scaled
     float* o_fin = q_rot + HPC * D;                                      // [HPC][D] final stage
     float* q_jl = o_fin + HPC * D;                                       // [HPC][M] (QJL)
-    uint32_t* cs_k = reinterpret_cast<uint32_t*>(q_jl + (QJL ? HPC * p.jl_dim : 0));   // split centroids
+    uint32_t* cs_k = reinterpret_cast<uint32_t*>(reinterpret_cast<float*>(smem) + kTeams * team_buf);   // split centroids
     uint32_t* cs_v = cs_k + 16;
     const uint32_t smem_base = smem_addr(smem);
     uint8_t* low_ring = smem + C::low_fixed(QJL ? p.jl_dim : 0);
@@ -277,15 +299,23 @@ pq_decode_attn_kernel(const DecodeParams p) {
     uint8_t* signtab = tab + kTabBytes;
     uint8_t* qjl_frag = signtab + C::kSignTab;
     uint8_t* high_ring = qjl_frag + C::qjl_frag_bytes(QJL ? p.jl_dim : 0);
-    __shared__ unsigned int s_ticket;
+    __shared__ unsigned int s_ticket_all[kTeams];
+    unsigned int& s_ticket = s_ticket_all[team];
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tw = warp - team * TW;                                     // warp index inside the team
+    const int tid = threadIdx.x - team * TT;                             // thread index inside the team
     const int g = lane >> 2, t = lane & 3;
+    // barrier of the team (the whole CTA when there is one team)
+    auto team_sync = [&]() {
+        if (kTeams == 1) __syncthreads();
+        else asm volatile("bar.sync %0, %1;\n" ::"r"(1 + team), "r"(TT) : "memory");
+    };
     const int M = QJL ? p.jl_dim : 0;
     const int stage_sz = C::stage_bytes_total(M);
     const int n_low = C::n_low(M);
     if (smem_base + C::low_fixed(M) + n_low * C::ring_bytes(M) > kTabAddr) {   // window starts too high
-        if (tid == 0) atomicOr(&g_decode_error, 1u);
+        if (threadIdx.x == 0) atomicOr(&g_decode_error, 1u);
         return;
     }
     auto ring_of = [&](int w) -> uint8_t* {
@@ -304,15 +334,16 @@ pq_decode_attn_kernel(const DecodeParams p) {
 #pragma unroll
         for (int s = 0; s < kStages; ++s) mbar_init(mbar0 + 8 * s, 1);
     }
-    if (tid < 32) {
-        const float c = tid < 16 ? p.cbk[tid] * kCbScale : p.cbv[tid - 16] * p.v_scale;
+    if (threadIdx.x < 32) {
+        const int i = threadIdx.x;
+        const float c = i < 16 ? p.cbk[i] * kCbScale : p.cbv[i - 16] * p.v_scale;
         __half h, l;
         split_half(c, h, l);
-        cs_k[tid] = (uint32_t)__half_as_ushort(h) | ((uint32_t)__half_as_ushort(l) << 16);   // cs_v = cs_k + 16
+        cs_k[i] = (uint32_t)__half_as_ushort(h) | ((uint32_t)__half_as_ushort(l) << 16);   // cs_v = cs_k + 16
     }
     if (QJL) {
         // sign table: nibble -> 4 halves of +-1; entry 8 bytes, 16 lane copies
-        for (int e = tid; e < 16 * 16; e += NT) {
+        for (int e = threadIdx.x; e < 16 * 16; e += NT) {
             const int nib = e >> 4;
             __half2 a = __floats2half2_rn((nib & 1) ? 1.f : -1.f, (nib & 2) ? 1.f : -1.f);
             __half2 c = __floats2half2_rn((nib & 4) ? 1.f : -1.f, (nib & 8) ? 1.f : -1.f);
@@ -321,8 +352,9 @@ pq_decode_attn_kernel(const DecodeParams p) {
         }
     }
     __syncthreads();
-    build_table<KBITS, 2>(tab, 0, cs_k, tid, NT);
-    build_table<VBITS, VT>(tab, 128, cs_v, tid, NT);
+    build_table<KBITS, 2>(tab, 0, cs_k, threadIdx.x, NT);
+    build_table<VBITS, VT>(tab, 128, cs_v, threadIdx.x, NT);
+    __syncthreads();                                  // the last CTA-wide barrier: the teams part here
     // this lane's private table copies (shared-memory byte addresses)
     const uint32_t kconst = kTabAddr | (KBITS == 4 ? (lane & 15) * 8 : (lane & 7) * 16);
     const uint32_t vconst = kTabAddr | (128 + (lane % (128 / VENT)) * VENT);
@@ -356,25 +388,28 @@ pq_decode_attn_kernel(const DecodeParams p) {
 
     // ---- work distribution.  A "virtual row" is one (batch, kv head, head group); its tiles
     // are numbered 0..tiles_total-1.  Balanced mode (p.splits == 0): the tiles of all virtual
-    // rows form one sequence that is cut into gridDim.x equal contiguous ranges, one per CTA;
-    // a CTA walks the segments (pieces of rows) inside its range.  Split mode: every row is
-    // cut into p.splits equal segments that are dealt round-robin to the CTAs.
+    // rows form one sequence that is cut into p.n_workers equal contiguous ranges, one per team (a
+    // "worker"); a team walks the segments (pieces of rows) inside its range.  Split mode: every row
+    // is cut into p.splits equal segments that are dealt round-robin to the workers.
     const int64_t n_vrows = (int64_t)p.n_rows * p.HG;
     const int64_t all_tiles = n_vrows * tiles_total;
-    const int64_t n_cta = gridDim.x;
+    const uint32_t worker = blockIdx.x * kTeams + team;
+    const int64_t n_cta = p.splits ? (int64_t)gridDim.x * kTeams : (int64_t)p.n_workers;   // workers
     // 64-bit divisions cost a few hundred cycles each and a segment needs half a dozen: when every
     // product below fits 32 bits (all but extreme shapes) the same arithmetic runs on 32-bit values.
     const bool small = all_tiles * (n_cta + 1) < (int64_t)0x7FFFFFFF;
     int64_t cur, cur_end;
     if (p.splits) {
-        cur = (int64_t)blockIdx.x;
+        cur = (int64_t)worker;
         cur_end = n_vrows * p.splits;
+    } else if ((int64_t)worker >= n_cta) {
+        cur = cur_end = 0;                               // fewer tiles than workers: nothing for this team
     } else if (small) {
-        cur = (int64_t)((uint32_t)blockIdx.x * (uint32_t)all_tiles / (uint32_t)n_cta);
-        cur_end = (int64_t)(((uint32_t)blockIdx.x + 1u) * (uint32_t)all_tiles / (uint32_t)n_cta);
+        cur = (int64_t)(worker * (uint32_t)all_tiles / (uint32_t)n_cta);
+        cur_end = (int64_t)((worker + 1u) * (uint32_t)all_tiles / (uint32_t)n_cta);
     } else {
-        cur = (int64_t)blockIdx.x * all_tiles / n_cta;
-        cur_end = ((int64_t)blockIdx.x + 1) * all_tiles / n_cta;
+        cur = (int64_t)worker * all_tiles / n_cta;
+        cur_end = ((int64_t)worker + 1) * all_tiles / n_cta;
     }
     while (cur < cur_end) {
     int64_t vrow, tile_begin, tile_end;
@@ -397,7 +432,7 @@ pq_decode_attn_kernel(const DecodeParams p) {
         // CTA that owns tile x: largest c with floor(c * all_tiles / n_cta) <= x
         const uint32_t c_first = ((row_t0 + 1u) * nc + at - 1u) / at - 1u;
         const uint32_t c_last = (row_t1 * nc + at - 1u) / at - 1u;
-        seg_idx = (int)(blockIdx.x - c_first);
+        seg_idx = (int)(worker - c_first);
         n_segs = (int)(c_last - c_first + 1u);
         cur = seg_end;
     } else {
@@ -409,7 +444,7 @@ pq_decode_attn_kernel(const DecodeParams p) {
         // CTA that owns tile x: largest c with floor(c * all_tiles / n_cta) <= x
         const int64_t c_first = ((row_t0 + 1) * n_cta + all_tiles - 1) / all_tiles - 1;
         const int64_t c_last = (row_t1 * n_cta + all_tiles - 1) / all_tiles - 1;
-        seg_idx = (int)((int64_t)blockIdx.x - c_first);
+        seg_idx = (int)((int64_t)worker - c_first);
         n_segs = (int)(c_last - c_first + 1);
         cur = seg_end;
     }
@@ -428,7 +463,7 @@ pq_decode_attn_kernel(const DecodeParams p) {
     const bool bulk_row = ((reinterpret_cast<uintptr_t>(k_row) | reinterpret_cast<uintptr_t>(v_row) |
                             (QJL ? reinterpret_cast<uintptr_t>(bits_row) | reinterpret_cast<uintptr_t>(norm_row) : 0)) & 15) == 0;
     // Tile numbers inside a row fit 32 bits (the host rejects longer sequences).
-    const int t_first = (int)tile_begin + warp, t_end = min((int)tile_end, valid_tiles);
+    const int t_first = (int)tile_begin + tw, t_end = min((int)tile_end, valid_tiles);
     const int full_tiles = (int)(s_len / kTileTok);                // tiles below this number hold 16 tokens
     auto issue_tile = [&](int tile, int slot) {
         if (tile >= t_end) return;
@@ -457,13 +492,13 @@ pq_decode_attn_kernel(const DecodeParams p) {
     };
     // first tiles in flight before the prologue math
 #pragma unroll
-    for (int s = 0; s < kStages - 1; ++s) issue_tile(t_first + s * NW, s);
+    for (int s = 0; s < kStages - 1; ++s) issue_tile(t_first + s * TW, s);
 
     // ---- per item: query rotation (and JL projection of the query)
     // q_rot[h][i] = sum_j q[h][j] * R[i][j] (and the JL projection P q) on tensor cores: rows =
     // heads (the float16 query is exact), columns = 8 outputs per warp-step, R split into two
     // float16 terms of 4096*R on the fly.  Matrix rows are read as 32-byte pieces by 4 lanes.
-    for (int nt = warp; nt < (D + M) / 8; nt += NW) {
+    for (int nt = tw; nt < (D + M) / 8; nt += TW) {
         const int i = nt * 8 + g;                                        // this lane's output column
         const float* mrow = i < D ? p.rot + (size_t)i * D : p.jl + (size_t)(i - D) * D;
         const __half* qrow = p.q + ((size_t)b * p.Hq + head0 + g) * D;   // row g = head g (if it exists)
@@ -494,7 +529,7 @@ pq_decode_attn_kernel(const DecodeParams p) {
             }
         }
     }
-    __syncthreads();
+    team_sync();
 
     // ---- B fragments of the query.  MMA column n = lane group g.
     //   NH == 1: column g is head g>>1, term hi (g even) or lo (g odd);
@@ -523,7 +558,7 @@ pq_decode_attn_kernel(const DecodeParams p) {
             }
         if (QJL) {
             // fragments of the projected query, one uint4 per (k-step, lane): {b0, b1 | lo b0, lo b1}
-            for (int ks = warp; ks < M / 16; ks += NW) {
+            for (int ks = tw; ks < M / 16; ks += TW) {
                 const float* src = q_jl + hq * M + ks * 16 + 4 * t;
                 uint4 f;
                 if (NH == 1) {
@@ -540,7 +575,7 @@ pq_decode_attn_kernel(const DecodeParams p) {
             }
         }
     }
-    __syncthreads();
+    team_sync();
 
     // ---- running softmax state.  A lane holds the scores of its head(s) (NH == 1: head t;
     // NH == 2: heads t and t+4) for tokens 2g and 2g+1 of the tile.
@@ -565,8 +600,8 @@ pq_decode_attn_kernel(const DecodeParams p) {
                 for (int j = 0; j < 4; ++j) acc[blk][f][h][j] = 0.f;
 
     int slot = 0;
-    for (int tile = t_first; tile < t_end; tile += NW) {
-        issue_tile(tile + (kStages - 1) * NW, slot >= 1 ? slot - 1 : kStages - 1);
+    for (int tile = t_first; tile < t_end; tile += TW) {
+        issue_tile(tile + (kStages - 1) * TW, slot >= 1 ? slot - 1 : kStages - 1);
         const bool full = tile < full_tiles;
         if (bulk_row && full) {
             if (!dead && !mbar_wait(mbar0 + 8 * slot, (phase >> slot) & 1u)) {
@@ -844,21 +879,21 @@ pq_decode_attn_kernel(const DecodeParams p) {
                     rec[(t + 4 * h) * (D + 2) + 2 + dim] = v * p.v_inv;
                 }
     }
-    __syncthreads();
+    team_sync();
 
     // ---- item record = merge of the warp records
     const size_t group = (size_t)vrow;
     float* cta_rec = p.records + (group * p.max_segs + seg_idx) * kRecHeads * (D + 2);
-    for (int e = tid; e < HPC * (D + 2); e += NT) {
+    for (int e = tid; e < HPC * (D + 2); e += TT) {
         const int head = e / (D + 2), col = e % (D + 2);
         float mx = -INFINITY;
-        for (int w = 0; w < NW; ++w) mx = fmaxf(mx, rec_of(w)[head * (D + 2)]);
+        for (int w = team * TW; w < (team + 1) * TW; ++w) mx = fmaxf(mx, rec_of(w)[head * (D + 2)]);
         float val;
         if (col == 0) {
             val = mx;
         } else {
             val = 0.f;
-            for (int w = 0; w < NW; ++w) {
+            for (int w = team * TW; w < (team + 1) * TW; ++w) {
                 const float* r = rec_of(w) + head * (D + 2);
                 const float mw = r[0];
                 const float s = (mw == -INFINITY) ? 0.f : fast_exp2(mw - mx);
@@ -870,16 +905,16 @@ pq_decode_attn_kernel(const DecodeParams p) {
     // A row that lies inside this CTA has one record, written and read by this CTA alone: the barrier
     // orders it; no fence, no ticket.
     if (n_segs > 1) __threadfence();
-    __syncthreads();
+    team_sync();
     if (n_segs > 1) {
         if (tid == 0) s_ticket = atomicAdd(p.tickets + group, 1u);
-        __syncthreads();
+        team_sync();
     }
     if (n_segs == 1 || s_ticket == (unsigned)(n_segs - 1)) {
         // ---- last segment of this virtual row to finish: merge the segment records
         if (n_segs > 1) __threadfence();
         const float* recs = p.records + group * p.max_segs * kRecHeads * (D + 2);
-        for (int e = tid; e < HPC * D; e += NT) {
+        for (int e = tid; e < HPC * D; e += TT) {
             const int head = e / D, dim = e % D;
             // four records per round trip to L2: the loads of a round do not depend on each other
             float mx = -INFINITY, l = 0.f, o = 0.f;
@@ -921,13 +956,13 @@ pq_decode_attn_kernel(const DecodeParams p) {
         }
         if (tid == 0) p.tickets[group] = 0;   // ready for the next call on this stream
         if (!p.partial_out) {
-            __syncthreads();
+            team_sync();
             // out[head][i] = sum_j o_fin[head][j] * R[j][i] on the tensor cores, eight output columns per
             // warp step: rows g = hi term of head g, rows g+8 = its lo term (two float16 terms of the
             // float32 result), B = R split into two float16 terms of 4096*R on the fly; the three product
             // terms hi*hi + lo*hi + hi*lo land in rows g and g+8 of the same lane.  (|o| <= 0.46 * 65504:
             // the hi term cannot overflow.)
-            for (int nt = warp; nt < D / 8; nt += NW) {
+            for (int nt = tw; nt < D / 8; nt += TW) {
                 float c[4] = {0.f, 0.f, 0.f, 0.f};
                 const int n = nt * 8 + g;                               // B column of this lane
 #pragma unroll
@@ -969,7 +1004,7 @@ pq_decode_attn_kernel(const DecodeParams p) {
     // the next segment reuses the rings (bulk copies land where this segment wrote records and
     // slow-path tiles with ordinary stores) and the query buffers
     fence_async_smem();
-    __syncthreads();
+    team_sync();
     }   // segments
 }
 
@@ -986,6 +1021,8 @@ static int heads_per_cta(int G) { return G <= 4 ? 4 : 8; }
 
 static int head_groups(int G) { const int h = heads_per_cta(G); return (G + h - 1) / h; }
 
+constexpr int kMaxTeams = PQ_DEC_TEAMS > 2 ? PQ_DEC_TEAMS : 2;
+
 // Balanced mode: number of persistent CTAs and the largest number of segments a row can have.
 // A row of T tiles inside a sequence cut into n equal ranges of floor/ceil(all/n) tiles touches at
 // most ceil(n / n_vrows) + 1 ranges and never more than T; the bound does not shrink when T grows,
@@ -997,7 +1034,9 @@ static void balanced_plan(int64_t n_vrows, int64_t tiles_per_row, int sms, int* 
     int64_t n = all_tiles < sms ? all_tiles : sms;
     if (n < 1) n = 1;
     *n_cta = (int)n;
-    const int64_t by_cta = (sms + n_vrows - 1) / n_vrows + 1;
+    // ranges are per team of warps, at most kMaxTeams per CTA (the bound also serves kernels with one)
+    const int64_t workers = (int64_t)sms * kMaxTeams;
+    const int64_t by_cta = (workers + n_vrows - 1) / n_vrows + 1;
     int64_t segs = tiles_per_row < by_cta ? tiles_per_row : by_cta;
     if (segs < 1) segs = 1;
     *max_segs = (int)segs;
@@ -1076,15 +1115,19 @@ static int launch_decode(const DecodeParams& p, int rows, cudaStream_t st) {
         return PQ_ERR_CUDA;
     int sms = device_sms();
     if (sms <= 0) sms = 148;
-    int grid;
+    static_assert(C::kTeams <= kMaxTeams, "balanced_plan bounds the segments of a row with kMaxTeams");
+    DecodeParams pp = p;
+    int64_t workers;                                             // teams that get work
     if (p.splits) {
-        const int64_t n_items = (int64_t)p.splits * rows * p.HG;
-        grid = (int)(n_items < sms ? n_items : sms);             // persistent: one CTA per SM
+        workers = (int64_t)p.splits * rows * p.HG;               // items, dealt round-robin
     } else {
-        int ms = 0;
-        balanced_plan((int64_t)rows * p.HG, (p.S + kTileTok - 1) / kTileTok, sms, &grid, &ms);
+        workers = (int64_t)rows * p.HG * ((p.S + kTileTok - 1) / kTileTok);
     }
-    kern<<<grid, C::NTHREADS, smem, st>>>(p);
+    if (workers > (int64_t)sms * C::kTeams) workers = (int64_t)sms * C::kTeams;
+    if (workers < 1) workers = 1;
+    pp.n_workers = (int)workers;
+    const int grid = (int)((workers + C::kTeams - 1) / C::kTeams);   // persistent: at most one CTA per SM
+    kern<<<grid, C::NTHREADS, smem, st>>>(pp);
     return cudaGetLastError() == cudaSuccess ? PQ_OK : PQ_ERR_CUDA;
 }
 
