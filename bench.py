@@ -647,6 +647,14 @@ def run_ours(args):
     w = WORKLOAD
     timer = Timer(dev, world, args.repeats)
     peak, peak_kind = measured_peak()
+    if args.only_compress:
+        # the compress and dequantise launches alone (for profiler captures of those kernels)
+        comp, dequant = compress_measurement(dev, world, timer, args.steps, args.compress_vecs, peak)
+        if rank == 0:
+            print(json.dumps({"compress": comp, "dequant": dequant}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()          # nvidia-smi takes a moment to start: begin before the warm-up
@@ -765,6 +773,8 @@ def main():
     ap.add_argument("--q-heads", type=int, default=0, help="query heads (default: the headline workload's)")
     ap.add_argument("--only-decode", action="store_true",
                     help="only the headline decode measurement (profiler captures)")
+    ap.add_argument("--only-compress", action="store_true",
+                    help="run the compress and dequantise measurements alone and print them")
     ap.add_argument("--skip-model", action="store_true", help="skip the end-to-end decoder measurement")
     ap.add_argument("--splits", type=int, default=0, help="sequence splits per (batch, kv head); 0 = library default")
     ap.add_argument("--compress-vecs", type=int, default=COMPRESS_VECS, help="vectors per tensor in the compress measurement")

@@ -126,7 +126,7 @@ int pq_compress_rows_dynamic(const void* x, int64_t n_rows, int64_t tokens_per_r
  * up), bit 1 compress (shared-memory window unusable), bit 2 prefill attention (a wait gave up),
  * bit 3 decode attention (shared-memory window unusable, nothing computed), bit 4 decode attention (a
  * wait for a tile copy gave up), bit 5 compress (pq_compress_rows_dynamic found its device-side
- * position out of range; nothing was written).
+ * position out of range; nothing was written), bit 6 dequantise (a wait gave up).
  * The flags are cleared by the call.  No counterpart in the reference (its kernels report nothing). */
 int pq_poll_device_errors(unsigned int* flags_out);
 
@@ -154,7 +154,7 @@ int pq_qjl_sketch(const float* residual, const double* jl_matrix, int64_t n_vec,
  *   blocks     uint8 [n_vec, head_dim/32, block_bytes]
  *   codebook   HOST float32 [2^n_bits]
  *   rot        float32 [head_dim, head_dim] row-major R
- *   out        [n_vec, head_dim], float32 (out_is_fp16 == 0) or float16 clamped to +-65504
+ *   out        [n_vec, head_dim], float32 (out_is_fp16 == 0) or float16 clamped to +-65504; 16-byte aligned
  */
 int pq_dequant(const void* blocks, int64_t n_vec, int head_dim, int n_bits,
                const float* codebook, const float* rot, void* out, int out_is_fp16,

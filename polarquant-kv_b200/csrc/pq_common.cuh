@@ -73,5 +73,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 int prefill_error_flags(unsigned int* flags);
 // Device error flags of the decode kernel, read and cleared (defined in pq_decode_attn.cu).
 int decode_error_flags(unsigned int* flags);
+// pq_dequant.cu: bit 0 a bounded wait gave up
+int dequant_error_flags(unsigned int* flags);
 
 }  // namespace pq

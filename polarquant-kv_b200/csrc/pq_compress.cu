@@ -704,7 +704,10 @@ extern "C" int pq_poll_device_errors(unsigned int* flags_out) {
     unsigned int df = 0;
     const int sd = pq::decode_error_flags(&df);
     if (sd != PQ_OK) return sd;
-    *flags_out = v | pf | (df << 3);
+    unsigned int qf = 0;
+    const int sq = pq::dequant_error_flags(&qf);
+    if (sq != PQ_OK) return sq;
+    *flags_out = v | pf | (df << 3) | (qf << 6);
     return PQ_OK;
 }
 

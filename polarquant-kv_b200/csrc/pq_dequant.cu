@@ -6,25 +6,32 @@
 // inverse_rotate (python/polarquant_kv/rotation.py:61); the float16 output is clamped to
 // +-65504 like decompress_gpu (src/polarquant_kv_cuda/decompress_kernel.py:47-51).
 //
-// The inverse rotation is a [vectors x D] . [D x D] contraction on the tensor cores
-// (mma.sync.m16n8k16, float32 accumulation) with both operands as two float16 terms and three
-// product terms (hi*hi + hi*lo + lo*hi), which keeps float32-level accuracy (2e-6 of a vector's largest
-// component against the float64 reference).  A CTA of 16 warps owns 128 vectors at a time:
-//   1. a thread dequantises one block (32 elements) of one vector: centroid * radius in float32 exactly
-//      as the reference, times a power of two per vector (so tiny vectors keep their precision), split
-//      into hi/lo float16 rows of a shared-memory tile (rows padded against bank conflicts); the stored
-//      bytes of the next tile are already in registers by then (loaded before the previous contraction);
-//   2. a warp multiplies 32 vectors by D/4 output columns: A fragments by ldmatrix from the tile,
-//      B fragments (R split on the fly at set-up, already in fragment order) from shared memory;
-//   3. results leave the accumulators as 8- or 4-byte stores, rescaled per vector.
-// Bound: 72 B in + 256 or 512 B out per vector (HBM); the three-term contraction on mma.sync costs
-// about as much tensor time as the bytes cost HBM time.
-#include "pq_common.cuh"
+// The inverse rotation is a [vectors x D] . [D x D] contraction on the 5th-generation tensor cores
+// (tcgen05.mma kind::f16, M = 128, accumulators in tensor memory) with both operands as two float16
+// terms and three product terms (hi*hi + hi*lo + lo*hi), which keeps float32-level accuracy (2e-6 of
+// a vector's largest component against the float64 reference).  A persistent CTA owns 128 vectors at a
+// time and runs the compress pipeline backwards:
+//   worker warps (4 per 32-dim block)  a thread dequantises one block of one vector - centroid * radius
+//       in float32 exactly as the reference, times a power of two per vector (so tiny vectors keep their
+//       precision) - and writes its hi and lo float16 terms as four 16-byte chunks each into the K-major
+//       A tiles in shared memory (two pairs of tiles: tile i+1 is produced while tile i is contracted);
+//       the stored bytes of the next tile are loaded before the epilogue so they are in flight;
+//   MMA warp  one lane issues, per tile, D/16 MMAs A_hi x [R_hi ; R_lo] (N = 2D: columns [0, D) receive
+//       hi*hi, [D, 2D) hi*lo) and D/16 MMAs A_lo x R_hi on top of the first D columns; tcgen05.commit
+//       releases the A tiles and hands the accumulator (one of two) to the epilogue;
+//   the same worker warps, one tile behind, read their 32 output columns of both halves from tensor
+//       memory (thread = vector), add, rescale and store 64 or 128 contiguous bytes per vector.
+// R is split into the two float16 terms of 4096 R and laid out as the B operand once per CTA.
+// All waits are bounded (a lost completion sets an error flag instead of hanging).
+// Bound: 72 B in + 256 or 512 B out per vector (HBM).
+#include "pq_tcgen05.cuh"
 
 namespace pq {
 
 constexpr int kDqVecs = 128;
-constexpr int kDqThreads = 512;
+
+// bit 0: a bounded wait gave up (read and cleared through pq_poll_device_errors, bit 6 there)
+static __device__ unsigned int g_dequant_error = 0;
 
 struct DequantParams {
     const uint8_t* blocks;
@@ -37,156 +44,233 @@ struct DequantParams {
 
 template <int D>
 struct DequantCfg {
-    static constexpr int LD = D + 8;                              // halves per tile row (16-byte skew)
-    static constexpr int kTileBytes = kDqVecs * LD * 2;           // one term of the dequantised tile
-    static constexpr int kRBytes = D * D * 2;                     // one term of R in fragment order
-    static constexpr size_t smem_bytes() { return 2 * (size_t)kTileBytes + 2 * (size_t)kRBytes + 16 * 32 * 4 + kDqVecs * 4; }
+    static constexpr int NBLK = D / 32;
+    static constexpr int kWorkers = 32 * 4 * NBLK;                // one thread per (vector, block)
+    static constexpr int kThreads = kWorkers + 32;                // + the MMA warp
+    static constexpr int kATile = kDqVecs * D * 2;                // one float16 term of a 128-vector tile
+    static constexpr int kBBytes = 2 * D * D * 2;                 // [R_hi ; R_lo] as the stacked B operand
+    static constexpr int kAccCols = 2 * D;                        // accumulator columns per buffer
+    // A tiles (2 buffers x 2 terms) | B | codebook copies | per-vector scales (4 tiles) | barriers | alignment
+    static constexpr size_t smem_bytes() { return 4 * (size_t)kATile + kBBytes + 16 * 32 * 4 + 4 * kDqVecs * 4 + 128 + 128; }
 };
 
+// Byte offset of 16-byte chunk `kc` of row `r` in a K-major operand tile with `rows` rows (8-row x 16-byte
+// core matrices, 128 bytes each; consecutive 8-row groups 128 bytes apart, consecutive K chunks rows/8 * 128).
+__device__ __forceinline__ uint32_t dq_chunk_off(int rows, int r, int kc) {
+    return (uint32_t)(kc * (rows / 8) * 128 + (r >> 3) * 128 + (r & 7) * 16);
+}
+
 template <int D, int BITS>
-__global__ void __launch_bounds__(kDqThreads, 1) pq_dequant_kernel(const DequantParams p) {
+__global__ void __launch_bounds__(DequantCfg<D>::kThreads, 1) pq_dequant_kernel(const DequantParams p) {
     using C = DequantCfg<D>;
-    constexpr int NBLK = D / 32;
+    constexpr int NBLK = C::NBLK;
     constexpr int BB = block_bytes(BITS);
     constexpr int VB = NBLK * BB;
-    constexpr int LD = C::LD;
-    constexpr int KS = D / 16;                                    // k-steps
-    constexpr int NTW = D / 32;                                   // 8-column n-tiles per warp (a quarter of D)
-    extern __shared__ __align__(16) uint8_t smem_raw[];
-    __half* xh = reinterpret_cast<__half*>(smem_raw);             // [128][LD] hi term
-    __half* xl = xh + kDqVecs * LD;                               // [128][LD] lo term
-    uint2* rh = reinterpret_cast<uint2*>(smem_raw + 2 * C::kTileBytes);   // [KS][D/8][32] B fragments, hi term of 4096 R
-    uint2* rl = rh + KS * (D / 8) * 32;                                     // lo term
-    float* cbs = reinterpret_cast<float*>(rl + KS * (D / 8) * 32);          // [16][32]: a copy of the codebook per lane
-    float* vscale = cbs + 16 * 32;                                          // [128] 1 / (power-of-two scale of a vector)
+    constexpr int WORKERS = C::kWorkers;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t* sp = smem_raw + ((128u - (sm_addr(smem_raw) & 127u)) & 127u);
+    uint8_t* a_tiles = sp;                      sp += 4 * C::kATile;      // [buffer][term]
+    uint8_t* b_tile = sp;                       sp += C::kBBytes;
+    float* cbs = reinterpret_cast<float*>(sp);  sp += 16 * 32 * 4;        // a copy of the codebook per lane
+    // [tile & 3][vector] power-of-two scale.  A worker may already produce tile i + 1 while another still
+    // reads the scales of tile i - 2 in its epilogue (tile i + 2 cannot start before that: its A tiles are
+    // free only after the MMAs of tile i, which need every worker's tile i), hence four slots.
+    float* vscale = reinterpret_cast<float*>(sp); sp += 4 * kDqVecs * 4;
+    uint64_t* mbar = reinterpret_cast<uint64_t*>(sp);
+    // [0], [1]: A tiles of buffer b written; [2], [3]: A tiles of buffer b consumed by their MMAs;
+    // [4], [5]: accumulator b complete; [6], [7]: accumulator b read out by every worker
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mbar + 8);
+    volatile uint32_t* abort_s = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    // ---- set-up: R as B fragments.  out[v][n] = sum_k x[v][k] R[k][n]: B[k][n] = R[k][n];
-    // fragment (ks, nt), lane (g, t): b0 = (R[16ks+2t][8nt+g], R[16ks+2t+1][8nt+g]), b1 = rows +8, +9.
-    for (int e = tid; e < KS * (D / 8) * 32; e += kDqThreads) {
-        const int ln = e & 31, nt = (e >> 5) % (D / 8), ks = (e >> 5) / (D / 8);
-        const int gg = ln >> 2, tt = ln & 3, n = nt * 8 + gg, k0 = ks * 16 + 2 * tt;
-        float v[4] = {p.rot[(size_t)k0 * D + n] * 4096.f, p.rot[(size_t)(k0 + 1) * D + n] * 4096.f,
-                      p.rot[(size_t)(k0 + 8) * D + n] * 4096.f, p.rot[(size_t)(k0 + 9) * D + n] * 4096.f};
-        const __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
-        const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
-        rh[e] = make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
-        rl[e] = make_uint2(pack_half2(v[0] - f0.x, v[1] - f0.y), pack_half2(v[2] - f1.x, v[3] - f1.y));
+
+    // ---- set-up: B = [R_hi ; R_lo] with B[n][k] = 4096 R[k][n] (out[v][n] = sum_k x[v][k] R[k][n])
+    for (int e = tid; e < D * D; e += C::kThreads) {
+        const int k = e / D, n = e - k * D;                               // coalesced along n
+        const float v = p.rot[e] * 4096.f;
+        const __half h = __float2half_rn(v);
+        const __half l = __float2half_rn(v - __half2float(h));
+        const uint32_t off = dq_chunk_off(2 * D, n, k >> 3) + (k & 7) * 2;
+        *reinterpret_cast<__half*>(b_tile + off) = h;
+        *reinterpret_cast<__half*>(b_tile + off + dq_chunk_off(2 * D, D, 0)) = l;      // rows D .. 2D-1
     }
-    for (int e = tid; e < 16 * 32; e += kDqThreads) cbs[e] = p.cb[e >> 5];
+    for (int e = tid; e < 16 * 32; e += C::kThreads) cbs[e] = p.cb[e >> 5];
+    if (tid == 0) {
+        for (int i = 0; i < 2; ++i) mbar_init(sm_addr(mbar + i), WORKERS);
+        for (int i = 2; i < 6; ++i) mbar_init(sm_addr(mbar + i), 1);
+        for (int i = 6; i < 8; ++i) mbar_init(sm_addr(mbar + i), WORKERS);
+        *abort_s = 0u;
+    }
+    if (warp == 0) tmem_alloc(sm_addr(tmem_slot), 2 * C::kAccCols);
+    fence_async_smem();          // B is read by the tensor core through the async proxy
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
 
     const int64_t n_tiles = (p.n_vec + kDqVecs - 1) / kDqVecs;
-    // this thread's (vector, block) of every tile; the NBLK threads of a vector are neighbouring lanes
-    const bool has_pair = tid < kDqVecs * NBLK;
-    const int vec = tid / NBLK, blk = tid % NBLK;
-    uint32_t words[BITS];                                         // 32 packed indices of the next tile's block
-    float d_next = 0.f;
-    auto fetch = [&](int64_t tile) {
-        d_next = 0.f;
+    const int64_t n_my = (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;      // tiles of this CTA
+    bool ok = true;
+
+    if (warp == WORKERS / 32) {
+        // ---- MMA warp: every lane runs the loop (uniform waits and descriptor arithmetic), lane 0 issues
+        constexpr uint32_t idesc_full = umma_idesc_f16(2 * D), idesc_half = umma_idesc_f16(D);
+        constexpr uint32_t kLboA = (kDqVecs / 8) * 128, kLboB = (2 * D / 8) * 128;   // K-chunk strides
+        constexpr uint32_t d_hi = (128u >> 4) | (1u << 14);                         // 8-row groups 128 B apart, no swizzle
+        const uint32_t b_lo0 = ((sm_addr(b_tile) >> 4) & 0x3FFFu) | ((kLboB >> 4) << 16);
+        const uint32_t issue = lane == 0 ? 1u : 0u;
+        for (int64_t i = 0; i < n_my && ok; ++i) {
+            const uint32_t b = (uint32_t)(i & 1), use = (uint32_t)(i >> 1);
+            ok = mbar_wait(sm_addr(mbar + b), use & 1u, abort_s, 32) && ok;                       // A written
+            if (i >= 2) ok = mbar_wait(sm_addr(mbar + 6 + b), (use - 1u) & 1u, abort_s, 32) && ok;   // accumulator free
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t acc = tmem_base + b * C::kAccCols;
+            const uint32_t ah0 = ((sm_addr(a_tiles + (2 * b) * C::kATile) >> 4) & 0x3FFFu) | ((kLboA >> 4) << 16);
+            const uint32_t al0 = ((sm_addr(a_tiles + (2 * b + 1) * C::kATile) >> 4) & 0x3FFFu) | ((kLboA >> 4) << 16);
 #pragma unroll
-        for (int w = 0; w < BITS; ++w) words[w] = 0u;
-        const int64_t v = tile * kDqVecs + vec;
-        if (has_pair && tile < n_tiles && v < p.n_vec) {
-            const uint16_t* src = reinterpret_cast<const uint16_t*>(p.blocks + v * VB + blk * BB);
-            d_next = __half2float(__ushort_as_half(__ldg(src)));
+            for (int ks = 0; ks < D / 16; ++ks)          // a k-step is two 16-byte chunks
+                umma_f16_split_pred(acc, ah0 + ks * ((2 * kLboA) >> 4), d_hi, b_lo0 + ks * ((2 * kLboB) >> 4), d_hi,
+                                    idesc_full, ks ? 1u : 0u, issue);
 #pragma unroll
-            for (int w = 0; w < BITS; ++w)
-                words[w] = (uint32_t)__ldg(src + 1 + 2 * w) | ((uint32_t)__ldg(src + 2 + 2 * w) << 16);
+            for (int ks = 0; ks < D / 16; ++ks)          // lo term of the vectors x hi term of R: the first D rows of B
+                umma_f16_split_pred(acc, al0 + ks * ((2 * kLboA) >> 4), d_hi, b_lo0 + ks * ((2 * kLboB) >> 4), d_hi,
+                                    idesc_half, 1u, issue);
+            umma_commit_pred(sm_addr(mbar + 2 + b), issue);      // the A tiles may be overwritten
+            umma_commit_pred(sm_addr(mbar + 4 + b), issue);      // the accumulator is complete
         }
-    };
-    fetch(blockIdx.x);
-    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        const int64_t v0 = tile * kDqVecs;
-        const int n_valid = (int)((p.n_vec - v0) < kDqVecs ? (p.n_vec - v0) : kDqVecs);
-        __syncthreads();                                          // the previous tile is consumed (and set-up done)
-        // ---- 1. dequantise this thread's block into the tile
-        if (has_pair) {
-            const float d = d_next;
-            // one power of two per vector: largest block radius -> [1, 2)
-            float dmax = d;
+        if (!ok && lane == 0) { *abort_s = 1u; atomicOr(&g_dequant_error, 1u); }
+    } else {
+        // ---- worker warps
+        // produce: this thread's (vector, block).  Eight neighbouring lanes own eight neighbouring vectors
+        // of the same block, so that their 16-byte chunk stores into the A tiles fill 128 contiguous bytes
+        // (a quarter warp per shared-memory wavefront, no bank conflicts); the blocks of a vector sit
+        // 32 / NBLK lanes apart.
+        constexpr int VPW = 32 / NBLK;                            // vectors per warp
+        const int vec = warp * VPW + (lane % VPW), blk = lane / VPW;
+        const int q = warp & 3, cc = warp >> 2;                   // epilogue: TMEM lane quarter, 32-column chunk
+        const int row = 32 * q + lane;
+        const uint32_t tmem_lane = tmem_base + ((uint32_t)(32 * q) << 16);
+        uint32_t words[BITS];                                     // 32 packed indices of the next tile's block
+        float d_next = 0.f;
+        auto fetch = [&](int64_t tile) {
+            d_next = 0.f;
 #pragma unroll
-            for (int o = 1; o < NBLK; o <<= 1) dmax = fmaxf(dmax, __shfl_xor_sync(0xffffffffu, dmax, o));
-            const uint32_t be = __float_as_uint(dmax) >> 23;
-            const float sc = (be > 0 && be < 255) ? __uint_as_float((254u - be) << 23) : 1.0f;
-            if (blk == 0) vscale[vec] = (be > 0 && be < 255) ? __uint_as_float(be << 23) : 1.0f;
-            __half* oh = xh + vec * LD + blk * 32;
-            __half* ol = xl + vec * LD + blk * 32;
+            for (int w = 0; w < BITS; ++w) words[w] = 0u;
+            const int64_t v = tile * kDqVecs + vec;
+            if (tile < n_tiles && v < p.n_vec) {
+                const uint16_t* src = reinterpret_cast<const uint16_t*>(p.blocks + v * VB + blk * BB);
+                d_next = __half2float(__ushort_as_half(__ldg(src)));
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-                uint32_t i0, i1;
-                if (BITS == 4) {
-                    i0 = (words[j >> 3] >> ((j & 7) * 4)) & 0xFu;
-                    i1 = (words[j >> 3] >> ((j & 7) * 4 + 4)) & 0xFu;
-                } else {
-                    i0 = (words[j >> 4] >> ((j & 15) * 2)) & 0x3u;
-                    i1 = (words[j >> 4] >> ((j & 15) * 2 + 2)) & 0x3u;
-                }
-                const float x0 = __fmul_rn(cbs[i0 * 32 + lane], d) * sc, x1 = __fmul_rn(cbs[i1 * 32 + lane], d) * sc;
-                const __half2 h = __floats2half2_rn(x0, x1);
-                const float2 f = __half22float2(h);
-                *reinterpret_cast<__half2*>(oh + j) = h;
-                *reinterpret_cast<uint32_t*>(ol + j) = pack_half2(x0 - f.x, x1 - f.y);
+                for (int w = 0; w < BITS; ++w)
+                    words[w] = (uint32_t)__ldg(src + 1 + 2 * w) | ((uint32_t)__ldg(src + 2 + 2 * w) << 16);
             }
-        }
-        fetch(tile + gridDim.x);                                  // in flight during the contraction
-        __syncthreads();
-        // ---- 2. contraction: warp -> rows 32*(warp & 3) .. +31, columns (D/4)*(warp >> 2) .. + D/4 - 1
-        const int r0 = 32 * (warp & 3), nt0 = (warp >> 2) * NTW;
-        float acc[2][NTW][4];
+        };
+        auto epilogue = [&](int64_t i) {                          // tile number i of this CTA
+            const uint32_t b = (uint32_t)(i & 1), use = (uint32_t)(i >> 1);
+            ok = mbar_wait(sm_addr(mbar + 4 + b), use & 1u, abort_s) && ok;
+            if (!ok) return;
+            tc_fence_after();
+            float hi[32], lo[32];
+            tmem_ld32(hi, tmem_lane + b * C::kAccCols + cc * 32);
+            tmem_ld32(lo, tmem_lane + b * C::kAccCols + D + cc * 32);
+            tc_fence_before();
+            mbar_arrive(sm_addr(mbar + 6 + b));                   // this thread's part of the accumulator is in registers
+            const int64_t tile = (int64_t)blockIdx.x + i * gridDim.x;
+            const int64_t v = tile * kDqVecs + row;
+            if (v >= p.n_vec) return;
+            const float s = vscale[(i & 3) * kDqVecs + row] * (1.0f / 4096.f);
+            const size_t off = (size_t)v * D + cc * 32;
+            if (p.out_is_fp16) {
+                uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(p.out) + off);
 #pragma unroll
-        for (int m = 0; m < 2; ++m)
+                for (int j = 0; j < 32; j += 8) {
+                    uint32_t w[4];
 #pragma unroll
-            for (int nt = 0; nt < NTW; ++nt)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) acc[m][nt][j] = 0.f;
-#pragma unroll 2
-        for (int ks = 0; ks < KS; ++ks) {
-            uint32_t ah[2][4], al[2][4];
-#pragma unroll
-            for (int m = 0; m < 2; ++m) {
-                // ldmatrix x4: matrices (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
-                const int row = r0 + 16 * m + (lane & 7) + ((lane >> 3) & 1) * 8, col = ks * 16 + (lane >> 4) * 8;
-                ldmatrix_x4(ah[m][0], ah[m][1], ah[m][2], ah[m][3], xh + row * LD + col);
-                ldmatrix_x4(al[m][0], al[m][1], al[m][2], al[m][3], xl + row * LD + col);
-            }
-#pragma unroll
-            for (int nt = 0; nt < NTW; ++nt) {
-                const uint2 bh = rh[(ks * (D / 8) + nt0 + nt) * 32 + lane], bl = rl[(ks * (D / 8) + nt0 + nt) * 32 + lane];
-#pragma unroll
-                for (int m = 0; m < 2; ++m) {
-                    mma_16816(acc[m][nt], ah[m][0], ah[m][1], ah[m][2], ah[m][3], bh.x, bh.y);
-                    mma_16816(acc[m][nt], ah[m][0], ah[m][1], ah[m][2], ah[m][3], bl.x, bl.y);
-                    mma_16816(acc[m][nt], al[m][0], al[m][1], al[m][2], al[m][3], bh.x, bh.y);
-                }
-            }
-        }
-        // ---- 3. store: C rows g / g+8, columns 2t, 2t+1 of every n-tile
-#pragma unroll
-        for (int m = 0; m < 2; ++m)
-#pragma unroll
-            for (int hrow = 0; hrow < 2; ++hrow) {
-                const int row = r0 + 16 * m + g + 8 * hrow;
-                if (row >= n_valid) continue;
-                const float s = vscale[row] * (1.0f / 4096.f);
-#pragma unroll
-                for (int nt = 0; nt < NTW; ++nt) {
-                    const float a = acc[m][nt][2 * hrow] * s, b = acc[m][nt][2 * hrow + 1] * s;
-                    const size_t off = (size_t)(v0 + row) * D + (nt0 + nt) * 8 + 2 * t;
-                    if (p.out_is_fp16) {
-                        *reinterpret_cast<__half2*>(static_cast<__half*>(p.out) + off) =
-                            __floats2half2_rn(fminf(fmaxf(a, -65504.f), 65504.f), fminf(fmaxf(b, -65504.f), 65504.f));
-                    } else {
-                        *reinterpret_cast<float2*>(static_cast<float*>(p.out) + off) = make_float2(a, b);
+                    for (int u = 0; u < 4; ++u) {
+                        const float a = (hi[j + 2 * u] + lo[j + 2 * u]) * s, c = (hi[j + 2 * u + 1] + lo[j + 2 * u + 1]) * s;
+                        w[u] = pack_half2(fminf(fmaxf(a, -65504.f), 65504.f), fminf(fmaxf(c, -65504.f), 65504.f));
                     }
+                    dst[j >> 3] = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            } else {
+                float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + off);
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    dst[j >> 2] = make_float4((hi[j] + lo[j]) * s, (hi[j + 1] + lo[j + 1]) * s, (hi[j + 2] + lo[j + 2]) * s,
+                                              (hi[j + 3] + lo[j + 3]) * s);
+            }
+        };
+        fetch(blockIdx.x);
+        for (int64_t i = 0; i < n_my && ok; ++i) {
+            const uint32_t b = (uint32_t)(i & 1), use = (uint32_t)(i >> 1);
+            // ---- produce tile i: its A tiles must have been consumed by the MMAs of tile i - 2
+            if (i >= 2) ok = mbar_wait(sm_addr(mbar + 2 + b), (use - 1u) & 1u, abort_s) && ok;
+            if (!ok) break;
+            {
+                const float d = d_next;
+                // one power of two per vector: largest block radius -> [1, 2)
+                float dmax = d;
+#pragma unroll
+                for (int o = VPW; o < 32; o <<= 1) dmax = fmaxf(dmax, __shfl_xor_sync(0xffffffffu, dmax, o));
+                const uint32_t be = __float_as_uint(dmax) >> 23;
+                const bool normal = be > 0 && be < 255;
+                const float sc = normal ? __uint_as_float((254u - be) << 23) : 1.0f;
+                if (blk == 0) vscale[(i & 3) * kDqVecs + vec] = normal ? __uint_as_float(be << 23) : 1.0f;
+                uint8_t* ah = a_tiles + (2 * b) * C::kATile;
+                uint8_t* al = ah + C::kATile;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {                     // four 16-byte chunks of 8 elements
+                    uint32_t wh[4], wl[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int j = 8 * c + 2 * u;
+                        uint32_t i0, i1;
+                        if (BITS == 4) {
+                            i0 = (words[j >> 3] >> ((j & 7) * 4)) & 0xFu;
+                            i1 = (words[j >> 3] >> ((j & 7) * 4 + 4)) & 0xFu;
+                        } else {
+                            i0 = (words[j >> 4] >> ((j & 15) * 2)) & 0x3u;
+                            i1 = (words[j >> 4] >> ((j & 15) * 2 + 2)) & 0x3u;
+                        }
+                        const float x0 = __fmul_rn(cbs[i0 * 32 + lane], d) * sc, x1 = __fmul_rn(cbs[i1 * 32 + lane], d) * sc;
+                        const __half2 h = __floats2half2_rn(x0, x1);
+                        const float2 f = __half22float2(h);
+                        wh[u] = *reinterpret_cast<const uint32_t*>(&h);
+                        wl[u] = pack_half2(x0 - f.x, x1 - f.y);
+                    }
+                    const uint32_t off = dq_chunk_off(kDqVecs, vec, blk * 4 + c);
+                    *reinterpret_cast<uint4*>(ah + off) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+                    *reinterpret_cast<uint4*>(al + off) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
                 }
             }
+            fence_async_smem();                                   // the tensor core reads the tiles through the async proxy
+            mbar_arrive(sm_addr(mbar + b));
+            fetch((int64_t)blockIdx.x + (i + 1) * gridDim.x);     // in flight during the epilogue below
+            // ---- epilogue of the tile before
+            if (i >= 1) epilogue(i - 1);
+        }
+        if (ok && n_my >= 1) epilogue(n_my - 1);
+        if (!ok && lane == 0) { *abort_s = 1u; atomicOr(&g_dequant_error, 1u); }
     }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, 2 * C::kAccCols);
+}
+
+// Read and clear this file's device error flag (for pq_poll_device_errors).
+int dequant_error_flags(unsigned int* flags) {
+    unsigned int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_dequant_error, sizeof(v)) != cudaSuccess) return PQ_ERR_CUDA;
+    if (v && cudaMemcpyToSymbol(g_dequant_error, &zero, sizeof(zero)) != cudaSuccess) return PQ_ERR_CUDA;
+    *flags = v;
+    return PQ_OK;
 }
 
 template <int D, int BITS>
 static int launch_dequant(const DequantParams& p, cudaStream_t st) {
-    const size_t smem = DequantCfg<D>::smem_bytes();
+    using C = DequantCfg<D>;
+    const size_t smem = C::smem_bytes();
     auto kern = pq_dequant_kernel<D, BITS>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return PQ_ERR_CUDA;
@@ -195,9 +279,8 @@ static int launch_dequant(const DequantParams& p, cudaStream_t st) {
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
         return PQ_ERR_CUDA;
     const int64_t n_tiles = (p.n_vec + kDqVecs - 1) / kDqVecs;
-    const int64_t cap = (int64_t)sms * (D == 128 ? 1 : 2);
-    const int grid = (int)(n_tiles < cap ? n_tiles : cap);
-    kern<<<grid, kDqThreads, smem, st>>>(p);
+    const int grid = (int)(n_tiles < sms ? n_tiles : sms);          // persistent: one CTA per SM (tensor memory)
+    kern<<<grid, C::kThreads, smem, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? PQ_OK : PQ_ERR_CUDA;
 }
 
@@ -213,7 +296,7 @@ extern "C" int pq_dequant(const void* blocks, int64_t n_vec, int head_dim, int n
     if (n_vec == 0) return PQ_OK;
     if (!blocks || !codebook || !rot || !out) return PQ_ERR_NULL_POINTER;
     if ((reinterpret_cast<uintptr_t>(blocks) & 3) || (reinterpret_cast<uintptr_t>(rot) & 15) ||
-        (reinterpret_cast<uintptr_t>(out) & 7))
+        (reinterpret_cast<uintptr_t>(out) & 15))
         return PQ_ERR_MISALIGNED;
     DequantParams p{};
     p.blocks = static_cast<const uint8_t*>(blocks);
