@@ -154,7 +154,7 @@ int pq_qjl_sketch(const float* residual, const double* jl_matrix, int64_t n_vec,
  *   blocks     uint8 [n_vec, head_dim/32, block_bytes]
  *   codebook   HOST float32 [2^n_bits]
  *   rot        float32 [head_dim, head_dim] row-major R
- *   out        [n_vec, head_dim], float32 (out_is_fp16 == 0) or float16 clamped to +-65504; 16-byte aligned
+ *   out        [n_vec, head_dim], float32 (out_is_fp16 == 0) or float16 clamped to +-65504; 32-byte aligned (blocks: 16-byte aligned)
  */
 int pq_dequant(const void* blocks, int64_t n_vec, int head_dim, int n_bits,
                const float* codebook, const float* rot, void* out, int out_is_fp16,

@@ -50,14 +50,25 @@ struct DequantCfg {
     static constexpr int kATile = kDqVecs * D * 2;                // one float16 term of a 128-vector tile
     static constexpr int kBBytes = 2 * D * D * 2;                 // [R_hi ; R_lo] as the stacked B operand
     static constexpr int kAccCols = 2 * D;                        // accumulator columns per buffer
-    // A tiles (2 buffers x 2 terms) | B | codebook copies | per-vector scales (4 tiles) | barriers | alignment
-    static constexpr size_t smem_bytes() { return 4 * (size_t)kATile + kBBytes + 16 * 32 * 4 + 4 * kDqVecs * 4 + 128 + 128; }
+    static constexpr int kWarpSegMax = (32 / NBLK) * NBLK * 18;   // packed bytes of a warp's vectors, 4-bit (576)
+    // A tiles (2 buffers x 2 terms) | B | codebook copies | per-vector scales (4 tiles) | the warps' packed
+    // bytes | barriers | alignment
+    static constexpr size_t smem_bytes() {
+        return 4 * (size_t)kATile + kBBytes + 16 * 32 * 4 + 4 * kDqVecs * 4 + (kWorkers / 32) * kWarpSegMax + 128 + 128;
+    }
 };
 
 // Byte offset of 16-byte chunk `kc` of row `r` in a K-major operand tile with `rows` rows (8-row x 16-byte
 // core matrices, 128 bytes each; consecutive 8-row groups 128 bytes apart, consecutive K chunks rows/8 * 128).
 __device__ __forceinline__ uint32_t dq_chunk_off(int rows, int r, int kc) {
     return (uint32_t)(kc * (rows / 8) * 128 + (r >> 3) * 128 + (r & 7) * 16);
+}
+
+// 32 bytes to global memory at a 32-byte boundary in one instruction
+__device__ __forceinline__ void stg_256(void* dst, const uint32_t (&w)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n" ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                 "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                 : "memory");
 }
 
 template <int D, int BITS>
@@ -76,6 +87,7 @@ __global__ void __launch_bounds__(DequantCfg<D>::kThreads, 1) pq_dequant_kernel(
     // reads the scales of tile i - 2 in its epilogue (tile i + 2 cannot start before that: its A tiles are
     // free only after the MMAs of tile i, which need every worker's tile i), hence four slots.
     float* vscale = reinterpret_cast<float*>(sp); sp += 4 * kDqVecs * 4;
+    uint8_t* segs = sp;                         sp += (C::kWorkers / 32) * C::kWarpSegMax;   // [warp] packed bytes
     uint64_t* mbar = reinterpret_cast<uint64_t*>(sp);
     // [0], [1]: A tiles of buffer b written; [2], [3]: A tiles of buffer b consumed by their MMAs;
     // [4], [5]: accumulator b complete; [6], [7]: accumulator b read out by every worker
@@ -151,19 +163,51 @@ __global__ void __launch_bounds__(DequantCfg<D>::kThreads, 1) pq_dequant_kernel(
         const int q = warp & 3, cc = warp >> 2;                   // epilogue: TMEM lane quarter, 32-column chunk
         const int row = 32 * q + lane;
         const uint32_t tmem_lane = tmem_base + ((uint32_t)(32 * q) << 16);
-        uint32_t words[BITS];                                     // 32 packed indices of the next tile's block
-        float d_next = 0.f;
+        // The stored bytes of a warp's VPW vectors are one contiguous segment of VPW * VB bytes (576 or 320):
+        // the warp loads it as 16-byte pieces, one or two per lane, a tile ahead, and passes it through a
+        // shared-memory slot from which every thread picks its block (18 or 10 bytes at a 2-byte boundary).
+        constexpr int kSeg = VPW * VB;                            // a multiple of 16
+        constexpr int kPieces = kSeg / 16;                        // 36 or 20
+        const int64_t total_bytes = p.n_vec * VB;
+        uint4 piece0 = make_uint4(0u, 0u, 0u, 0u), piece1 = make_uint4(0u, 0u, 0u, 0u);
+        auto load_piece = [&](int64_t byte0) -> uint4 {           // 16 bytes at a 16-byte boundary, zeros past the end
+            uint4 r = make_uint4(0u, 0u, 0u, 0u);
+            if (byte0 + 16 <= total_bytes) {
+                r = __ldg(reinterpret_cast<const uint4*>(p.blocks + byte0));
+            } else if (byte0 < total_bytes) {                     // the last piece of the tensor: 2-byte loads
+                uint32_t w[4] = {0u, 0u, 0u, 0u};
+                for (int h = 0; h < 8 && byte0 + 2 * h < total_bytes; ++h)
+                    w[h >> 1] |= (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(p.blocks + byte0) + h) << (16 * (h & 1));
+                r = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            return r;
+        };
         auto fetch = [&](int64_t tile) {
-            d_next = 0.f;
+            const int64_t seg0 = (tile * kDqVecs + (int64_t)warp * VPW) * VB;
+            piece0 = lane < kPieces ? load_piece(seg0 + 16 * lane) : make_uint4(0u, 0u, 0u, 0u);
+            piece1 = 32 + lane < kPieces ? load_piece(seg0 + 16 * (32 + lane)) : make_uint4(0u, 0u, 0u, 0u);
+        };
+        uint8_t* seg = segs + warp * C::kWarpSegMax;
+        uint32_t words[BITS];                                     // 32 packed indices of this thread's block
+        float d_cur = 0.f;
+        auto unpack_block = [&]() {                               // registers -> slot -> this thread's block
+            __syncwarp();
+            if (lane < kPieces) *reinterpret_cast<uint4*>(seg + 16 * lane) = piece0;
+            if (32 + lane < kPieces) *reinterpret_cast<uint4*>(seg + 16 * (32 + lane)) = piece1;
+            __syncwarp();
+            const int off = (lane % VPW) * VB + blk * BB;         // 2-byte aligned; 4-byte aligned for even blocks
+            const uint32_t* w32 = reinterpret_cast<const uint32_t*>(seg + (off & ~3));
+            uint32_t w[BITS + 1];
 #pragma unroll
-            for (int w = 0; w < BITS; ++w) words[w] = 0u;
-            const int64_t v = tile * kDqVecs + vec;
-            if (tile < n_tiles && v < p.n_vec) {
-                const uint16_t* src = reinterpret_cast<const uint16_t*>(p.blocks + v * VB + blk * BB);
-                d_next = __half2float(__ushort_as_half(__ldg(src)));
+            for (int k = 0; k <= BITS; ++k) w[k] = w32[k];
+            if (off & 2) {
+                d_cur = __half2float(__ushort_as_half((unsigned short)(w[0] >> 16)));
 #pragma unroll
-                for (int w = 0; w < BITS; ++w)
-                    words[w] = (uint32_t)__ldg(src + 1 + 2 * w) | ((uint32_t)__ldg(src + 2 + 2 * w) << 16);
+                for (int k = 0; k < BITS; ++k) words[k] = w[k + 1];
+            } else {
+                d_cur = __half2float(__ushort_as_half((unsigned short)(w[0] & 0xFFFFu)));
+#pragma unroll
+                for (int k = 0; k < BITS; ++k) words[k] = __funnelshift_r(w[k], w[k + 1], 16);
             }
         };
         auto epilogue = [&](int64_t i) {                          // tile number i of this CTA
@@ -181,24 +225,28 @@ __global__ void __launch_bounds__(DequantCfg<D>::kThreads, 1) pq_dequant_kernel(
             if (v >= p.n_vec) return;
             const float s = vscale[(i & 3) * kDqVecs + row] * (1.0f / 4096.f);
             const size_t off = (size_t)v * D + cc * 32;
+            // 32-byte stores: every store instruction of a thread fills a whole sector
             if (p.out_is_fp16) {
-                uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(p.out) + off);
+                __half* dst = static_cast<__half*>(p.out) + off;
 #pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                    uint32_t w[4];
+                for (int j = 0; j < 32; j += 16) {
+                    uint32_t w[8];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
+                    for (int u = 0; u < 8; ++u) {
                         const float a = (hi[j + 2 * u] + lo[j + 2 * u]) * s, c = (hi[j + 2 * u + 1] + lo[j + 2 * u + 1]) * s;
                         w[u] = pack_half2(fminf(fmaxf(a, -65504.f), 65504.f), fminf(fmaxf(c, -65504.f), 65504.f));
                     }
-                    dst[j >> 3] = make_uint4(w[0], w[1], w[2], w[3]);
+                    stg_256(dst + j, w);
                 }
             } else {
-                float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + off);
+                float* dst = static_cast<float*>(p.out) + off;
 #pragma unroll
-                for (int j = 0; j < 32; j += 4)
-                    dst[j >> 2] = make_float4((hi[j] + lo[j]) * s, (hi[j + 1] + lo[j + 1]) * s, (hi[j + 2] + lo[j + 2]) * s,
-                                              (hi[j + 3] + lo[j + 3]) * s);
+                for (int j = 0; j < 32; j += 8) {
+                    uint32_t w[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) w[u] = __float_as_uint((hi[j + u] + lo[j + u]) * s);
+                    stg_256(dst + j, w);
+                }
             }
         };
         fetch(blockIdx.x);
@@ -208,7 +256,8 @@ __global__ void __launch_bounds__(DequantCfg<D>::kThreads, 1) pq_dequant_kernel(
             if (i >= 2) ok = mbar_wait(sm_addr(mbar + 2 + b), (use - 1u) & 1u, abort_s) && ok;
             if (!ok) break;
             {
-                const float d = d_next;
+                unpack_block();
+                const float d = d_cur;
                 // one power of two per vector: largest block radius -> [1, 2)
                 float dmax = d;
 #pragma unroll
@@ -295,8 +344,8 @@ extern "C" int pq_dequant(const void* blocks, int64_t n_vec, int head_dim, int n
     if (n_bits != 2 && n_bits != 4) return PQ_ERR_BAD_BITS;
     if (n_vec == 0) return PQ_OK;
     if (!blocks || !codebook || !rot || !out) return PQ_ERR_NULL_POINTER;
-    if ((reinterpret_cast<uintptr_t>(blocks) & 3) || (reinterpret_cast<uintptr_t>(rot) & 15) ||
-        (reinterpret_cast<uintptr_t>(out) & 15))
+    if ((reinterpret_cast<uintptr_t>(blocks) & 15) || (reinterpret_cast<uintptr_t>(rot) & 15) ||
+        (reinterpret_cast<uintptr_t>(out) & 31))
         return PQ_ERR_MISALIGNED;
     DequantParams p{};
     p.blocks = static_cast<const uint8_t*>(blocks);
