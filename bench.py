@@ -563,6 +563,48 @@ def cache_kernels_per_step(model, caches, cfg, B, dev, timer):
     return ms / 10
 
 
+def bridge_measurement(dev, timer, steps):
+    """The llama.cpp bridge's entry points (include/polarquant_llama_abi.h; per-vector-radius codec): fused
+    attention of 32 query / 8 kv heads over 65 536 tokens and compress of 2^20 float32 vectors, head dim 128.
+    Two input sets alternate so that no step finds its data in L2 (151 MB per attention set)."""
+    import torch
+    from polarquant_kv import llama_bridge as LB
+    hq, hkv, S, D, n = 32, 8, 65536, 128, 1 << 20
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    cb = torch.sort(torch.randn(16, generator=gen, device=dev) * 0.09).values.contiguous()
+    sets = []
+    for _ in range(2):
+        pk = torch.randint(0, 256, (hkv, S, D // 2), dtype=torch.uint8, generator=gen, device=dev)
+        pv = torch.randint(0, 256, (hkv, S, D // 2), dtype=torch.uint8, generator=gen, device=dev)
+        kr = torch.rand(hkv, S, generator=gen, device=dev) + 0.5
+        vr = torch.rand(hkv, S, generator=gen, device=dev) + 0.5
+        sets.append((pk, kr, pv, vr))
+    q = torch.randn(hq, D, generator=gen, device=dev)
+    out = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(D)
+
+    def attend(i):
+        pk, kr, pv, vr = sets[i & 1]
+        LB.fused_attention(q, pk, kr, pv, vr, cb, scale, out=out)
+
+    attend(0), attend(1)
+    t_att = timer.run(attend, steps, repeats=5)[0] / steps
+    att_bytes = 2 * hkv * S * (D // 2 + 4)
+    xs = [torch.randn(n, D, generator=gen, device=dev) for _ in range(2)]
+    R = torch.linalg.qr(torch.randn(D, D, generator=gen, device=dev))[0].contiguous()
+    LB.compress(xs[0], R, cb)
+    t_cmp = timer.run(lambda i: LB.compress(xs[i & 1], R, cb), steps, repeats=5)[0] / steps
+    cmp_bytes = n * (D * 4 + D // 2 + 4)
+    peak, _ = measured_peak()
+    return {"attention": {"q_heads": hq, "kv_heads": hkv, "tokens": S, "head_dim": D, "us": round(t_att * 1e3, 1),
+                          "stored_bytes": att_bytes, "achieved_gbs": round(att_bytes / t_att / 1e6, 1),
+                          "frac_of_hbm_peak": round(att_bytes / t_att / 1e6 / peak, 4)},
+            "compress": {"vectors": n, "head_dim": D, "ms": round(t_cmp, 4), "mvec_per_s": round(n / t_cmp / 1e3, 1),
+                         "bytes_per_vector": D * 4 + D // 2 + 4, "achieved_gbs": round(cmp_bytes / t_cmp / 1e6, 1),
+                         "frac_of_hbm_peak": round(cmp_bytes / t_cmp / 1e6 / peak, 4)}}
+
+
 def e2e_model_measurement(dev, rank, world, timer, steps=256):
     """End-to-end greedy decoding of a Qwen2.5-0.5B-architecture decoder with random bfloat16 weights
     (seed 0): 64 prompts of 4096 random token ids (sharded by batch across the ranks), one prefill pass,
@@ -647,11 +689,15 @@ def run_ours(args):
     w = WORKLOAD
     timer = Timer(dev, world, args.repeats)
     peak, peak_kind = measured_peak()
-    if args.only_compress:
-        # the compress and dequantise launches alone (for profiler captures of those kernels)
-        comp, dequant = compress_measurement(dev, world, timer, args.steps, args.compress_vecs, peak)
+    if args.only_compress or args.only_bridge:
+        # the compress and dequantise launches, or the bridge's, alone (for profiler captures of those kernels)
+        if args.only_bridge:
+            res = {"llama_bridge": bridge_measurement(dev, timer, args.steps)}
+        else:
+            comp, dequant = compress_measurement(dev, world, timer, args.steps, args.compress_vecs, peak)
+            res = {"compress": comp, "dequant": dequant}
         if rank == 0:
-            print(json.dumps({"compress": comp, "dequant": dequant}))
+            print(json.dumps(res))
         if world > 1:
             dist.destroy_process_group()
         return
@@ -694,6 +740,10 @@ def run_ours(args):
     if not args.only_decode and sets is not None:
         prefill = prefill_measurement(w, sets, sets[0][0], dev, timer, args.steps)
     sets = None
+    bridge = None
+    if not args.only_decode:
+        torch.cuda.empty_cache()
+        bridge = bridge_measurement(dev, timer, args.steps)     # per GPU, like the compress figures
     e2e_model = None
     if not args.only_decode and not args.skip_model:
         torch.cuda.empty_cache()
@@ -751,6 +801,7 @@ def run_ours(args):
         "compress": comp,
         "dequant": dequant,
         "prefill": prefill,
+        "llama_bridge": bridge,
         "e2e_model": e2e_model,
         "cpu_baseline": cpu,
         "clocks": clocks,
@@ -775,6 +826,8 @@ def main():
                     help="only the headline decode measurement (profiler captures)")
     ap.add_argument("--only-compress", action="store_true",
                     help="run the compress and dequantise measurements alone and print them")
+    ap.add_argument("--only-bridge", action="store_true",
+                    help="run the llama.cpp bridge measurement alone and print it")
     ap.add_argument("--skip-model", action="store_true", help="skip the end-to-end decoder measurement")
     ap.add_argument("--splits", type=int, default=0, help="sequence splits per (batch, kv head); 0 = library default")
     ap.add_argument("--compress-vecs", type=int, default=COMPRESS_VECS, help="vectors per tensor in the compress measurement")
