@@ -276,11 +276,20 @@ __device__ __forceinline__ void load_row_bytes(const uint8_t* row, int row_bytes
     }
 }
 
+// Centroid pairs of a stored byte: entry (byte, copy) = {codebook[byte & mask], codebook[(byte >> 4) & mask]},
+// kPairCopies copies side by side (a lane uses copy lane % kPairCopies, which thins out bank conflicts).
+constexpr int kPairCopies = 4;
+
 template <int DPL>
-__device__ __forceinline__ void decode_row(const uint32_t (&w)[(DPL + 7) / 8], const float* cb, uint32_t mask,
-                                           float (&v)[DPL]) {
+__device__ __forceinline__ void decode_row(const uint32_t (&w)[(DPL + 7) / 8], uint32_t pair_lane, float (&v)[DPL]) {
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) v[i] = cb[(w[i >> 3] >> (4 * (i & 7))) & mask];
+    for (int i = 0; i < DPL / 2; ++i) {
+        const uint32_t byte = (w[i >> 2] >> (8 * (i & 3))) & 0xFFu;
+        float2 c;
+        asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];\n" : "=f"(c.x), "=f"(c.y) : "r"(pair_lane + byte * (kPairCopies * 8)));
+        v[2 * i] = c.x;
+        v[2 * i + 1] = c.y;
+    }
 }
 
 // A warp fetches the packed words of `kChunk` consecutive tokens before it touches any of them, so
@@ -299,7 +308,7 @@ __device__ __forceinline__ void load_chunk(const uint8_t* rows, int row_bytes, i
                                            uint32_t (&w)[Chunk<DPL>::kTokens][Chunk<DPL>::W]) {
 #pragma unroll
     for (int t = 0; t < Chunk<DPL>::kTokens; ++t)
-        load_row_bytes<DPL>(rows + (size_t)min(first + t, valid - 1) * row_bytes, row_bytes, lane, vec, w[t]);
+        load_row_bytes<DPL>(rows + (uint32_t)(min(first + t, valid - 1) * row_bytes), row_bytes, lane, vec, w[t]);
 }
 
 template <int DPL, int G>
@@ -308,8 +317,7 @@ struct TileScores {
     const uint8_t* rows;      // first row of the tile
     int row_bytes, valid, lane;
     bool vec;
-    const float* cb;
-    uint32_t mask;
+    uint32_t pair_lane;       // shared address of this lane's copy of the pair table
     const float (*q)[DPL];
 
     // Sums over the 32 lanes of `1 << L` fetched tokens starting at chunk position t; afterwards
@@ -318,7 +326,7 @@ struct TileScores {
     __device__ __forceinline__ void reduce(const uint32_t (&w)[C::kTokens][C::W], int t, float (&out)[G]) const {
         if constexpr (L == 0) {
             float kv[DPL];
-            decode_row<DPL>(w[t], cb, mask, kv);
+            decode_row<DPL>(w[t], pair_lane, kv);
 #pragma unroll
             for (int h = 0; h < G; ++h) {
                 float s = 0.0f;
@@ -374,7 +382,7 @@ template <int DPL, int G>
 __global__ void __launch_bounds__(kAttWarps * 32, 3) attention_kernel(const AttnParams p) {
     constexpr int DP = 32 * DPL;                      // padded head dim
     constexpr int REC = DP + 2;                       // partial record: m, l, acc[DP]
-    __shared__ float cb[16];
+    __shared__ __align__(16) float2 pair_tab[256 * kPairCopies];
     __shared__ float sm_m[kAttWarps][G], sm_l[kAttWarps][G];
     __shared__ float sm_acc[kAttWarps][G][DP];
     __shared__ unsigned sm_last;
@@ -384,8 +392,12 @@ __global__ void __launch_bounds__(kAttWarps * 32, 3) attention_kernel(const Attn
     const int hq0 = hkv * p.gqa + group * G;
     const int row_bytes = p.D >> 1;
     const uint32_t mask = (uint32_t)(p.n_levels - 1);
-    if (threadIdx.x < 16) cb[threadIdx.x] = threadIdx.x < p.n_levels ? p.codebook[threadIdx.x] : 0.0f;
+    for (int e = threadIdx.x; e < 256 * kPairCopies; e += blockDim.x) {
+        const uint32_t byte = (uint32_t)e / kPairCopies;
+        pair_tab[e] = make_float2(p.codebook[byte & mask], p.codebook[(byte >> 4) & mask]);
+    }
     __syncthreads();
+    const uint32_t pair_lane = (uint32_t)__cvta_generic_to_shared(pair_tab) + (lane % kPairCopies) * 8;
 
     float q[G][DPL];
 #pragma unroll
@@ -416,7 +428,7 @@ __global__ void __launch_bounds__(kAttWarps * 32, 3) attention_kernel(const Attn
         const float vr = lane < valid ? p.vr[kv_row0 + s0 + lane] : 0.0f;
 
         TileScores<DPL, G> ts{p.pk + (kv_row0 + s0) * row_bytes, row_bytes, valid, lane, p.vector_loads != 0,
-                              cb, mask, q};
+                              pair_lane, q};
         float sc[G];
         ts.template run<5>(0, sc);
 
@@ -446,7 +458,7 @@ __global__ void __launch_bounds__(kAttWarps * 32, 3) attention_kernel(const Attn
 #pragma unroll
             for (int t = 0; t < C::kTokens; ++t) {
                 float vv[DPL];
-                decode_row<DPL>(vw[t], cb, mask, vv);
+                decode_row<DPL>(vw[t], pair_lane, vv);
 #pragma unroll
                 for (int h = 0; h < G; ++h) {
                     const float wt = __shfl_sync(kFull, w[h], c0 + t);     // 0 for tokens past `valid`
