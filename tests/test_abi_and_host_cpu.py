@@ -205,3 +205,21 @@ def test_llama_bridge_oracle_known_answers():
     R, _ = np.linalg.qr(rng.standard_normal((8, 8)))
     y = rng.standard_normal((3, 8))
     np.testing.assert_allclose(LO.inverse_rotate(LO.rotate(y, R), R), y, atol=1e-12)
+
+
+def test_mixed_precision_plans_host_logic():
+    """policy.py: the per-layer and per-token width plans and their run-length form (no GPU)."""
+    from polarquant_kv import policy
+    assert policy.compute_layer_bitwidths(2) == [4, 4]
+    assert policy.compute_layer_bitwidths(24, 3.0) == [4] * 6 + [2] * 12 + [4] * 6
+    plan = policy.compute_layer_bitwidths(12, 2.5)
+    assert plan == [4, 4] + [2] * 9 + [4]            # three layers stay wide: the ends first, then inwards
+    assert sum(policy.compute_layer_bitwidths(32, 3.5)) / 32 == pytest.approx(3.5, abs=0.07)
+    tok = policy.compute_token_bitwidths(333)
+    assert policy.runs_of(tok) == [(0, 4, 4), (4, 269, 2), (269, 333, 4)]
+    assert policy.runs_of(policy.compute_token_bitwidths(50)) == [(0, 50, 4)]            # shorter than sink + window
+    assert policy.runs_of(policy.compute_token_bitwidths(3)) == [(0, 3, 4)]
+    assert policy.runs_of([]) == [] and policy.runs_of([2, 2, 4, 2]) == [(0, 2, 2), (2, 3, 4), (3, 4, 2)]
+    # 4 + 64 tokens at 72 bytes, 4028 at 40 bytes against 256 bytes of float16 per token
+    ratio = policy.estimate_mixed_compression_ratio(4096)
+    assert ratio == pytest.approx(256 * 4096 / (68 * 72 + 4028 * 40), rel=1e-12)
