@@ -95,13 +95,48 @@ def _digest(m) -> str:
     return hashlib.blake2b(a.tobytes(), digest_size=16).hexdigest() + str(a.shape)
 
 
+_QUICK: dict = {}
+_QUICK_LIMIT = 64
+
+
+def _quick_key(m):
+    """Identity of a matrix object without reading it: the object, where its data lives and, for arrays,
+    three probe values (for tensors the version counter) - enough to notice the in-place edits that the
+    content digest would notice, at no cost per call.  None when the object offers no such handle."""
+    if m is None:
+        return ("-",)
+    if isinstance(m, np.ndarray):
+        if m.size == 0:
+            return None
+        flat = m.reshape(-1) if m.flags.c_contiguous else None
+        if flat is None:
+            return None
+        return ("np", id(m), m.shape, m.dtype.str, m.ctypes.data, float(flat[0]), float(flat[m.size // 2]), float(flat[-1]))
+    if isinstance(m, torch.Tensor):
+        return ("pt", id(m), tuple(m.shape), str(m.dtype), m.data_ptr(), m._version)
+    return None
+
+
 def device_plan(rotation_matrix, device, jl_matrix=None) -> DevicePlan:
-    """Cached DevicePlan for (R, P, device); callers on a hot loop should hold the plan."""
+    """Cached DevicePlan for (R, P, device).  The same matrix OBJECTS are recognised without being read
+    (the usual case: a caller passes its R and P on every call); otherwise the plan is looked up by a digest
+    of the contents.  Callers on a hot loop can also hold the plan and pass it instead of R."""
     if isinstance(rotation_matrix, DevicePlan):
         return rotation_matrix
-    key = (_digest(rotation_matrix), _digest(jl_matrix), str(torch.device(device)))
+    dev = str(torch.device(device))
+    qr, qp = _quick_key(rotation_matrix), _quick_key(jl_matrix)
+    quick = (qr, qp, dev) if qr is not None and qp is not None else None
+    if quick is not None:
+        hit = _QUICK.get(quick)
+        if hit is not None:
+            return hit[0]
+    key = (_digest(rotation_matrix), _digest(jl_matrix), dev)
     plan = _PLANS.get(key)
     if plan is None:
         plan = DevicePlan(rotation_matrix, device, jl_matrix)
         _PLANS[key] = plan
+    if quick is not None:
+        if len(_QUICK) >= _QUICK_LIMIT:
+            _QUICK.pop(next(iter(_QUICK)))
+        _QUICK[quick] = (plan, rotation_matrix, jl_matrix)      # the references keep the ids from being reused
     return plan

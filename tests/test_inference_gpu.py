@@ -291,3 +291,28 @@ def test_graph_replayed_decode_steps_equal_eager_steps():
         assert ctypes_flags() == 0
         with pytest.raises(RuntimeError):
             model.generate_graph(prompt, 80, model.create_cache_managers(96, 2, dev))
+
+
+def test_device_plan_cache_recognises_objects_and_edits():
+    """rotation.device_plan: the same matrix objects give the cached plan without being hashed again; a
+    copy with equal contents gives the same plan through the digest; an in-place edit gives a new one."""
+    import numpy as np
+    from polarquant_kv import qjl, rotation
+    dev = _cuda()
+    R = rotation.generate_rotation_matrix(64, seed=3)
+    P = qjl.generate_jl_matrix(32, 64, seed=4)
+    plan = rotation.device_plan(R, dev, P)
+    assert rotation.device_plan(R, dev, P) is plan
+    assert rotation.device_plan(R.copy(), dev, P.copy()) is plan
+    assert rotation.device_plan(plan, dev) is plan
+    assert rotation.device_plan(R, dev) is not plan and rotation.device_plan(R, dev).jl is None
+    Rt = torch.from_numpy(R).to(dev)
+    plan_t = rotation.device_plan(Rt, dev, P)
+    assert plan_t is plan and rotation.device_plan(Rt, dev, P) is plan
+    Rt.mul_(-1.0)                                            # version counter moves: not the cached object any more
+    assert rotation.device_plan(Rt, dev, P) is not plan
+    R2 = R.copy()
+    first = rotation.device_plan(R2, dev)
+    R2[0, 0], R2[-1, -1] = R2[-1, -1], R2[0, 0]
+    assert rotation.device_plan(R2, dev) is not first
+    assert np.allclose(first.rot.cpu().numpy(), R.astype(np.float32))
