@@ -914,44 +914,60 @@ pq_decode_attn_kernel(const DecodeParams p) {
         // ---- last segment of this virtual row to finish: merge the segment records
         if (n_segs > 1) __threadfence();
         const float* recs = p.records + group * p.max_segs * kRecHeads * (D + 2);
-        for (int e = tid; e < HPC * D; e += TT) {
-            const int head = e / D, dim = e % D;
-            // four records per round trip to L2: the loads of a round do not depend on each other
-            float mx = -INFINITY, l = 0.f, o = 0.f;
-            for (int s0 = 0; s0 < n_segs; s0 += 4) {
-                float ms[4], ls[4], os[4];
+        // A thread merges its E = HPC * D / TT (head, dim) elements together, four records per round trip to
+        // L2: all loads of a round are independent, so a row cut into n segments costs ceil(n / 4) round trips
+        // (a long single sequence is cut into a few dozen).
+        constexpr int E = (HPC * D + TT - 1) / TT;
+        float mx[E], ml[E], mo[E];
+#pragma unroll
+        for (int j = 0; j < E; ++j) { mx[j] = -INFINITY; ml[j] = 0.f; mo[j] = 0.f; }
+        for (int s0 = 0; s0 < n_segs; s0 += 4) {
+            float ms[E][4], ls[E][4], os[E][4];
+#pragma unroll
+            for (int j = 0; j < E; ++j) {
+                const int e = min(tid + j * TT, HPC * D - 1);
+                const int head = e / D, dim = e % D;
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const float* r = recs + (min(s0 + u, n_segs - 1) * kRecHeads + head) * (D + 2);
-                    ms[u] = __ldcg(r);
-                    ls[u] = __ldcg(r + 1);
-                    os[u] = __ldcg(r + 2 + dim);
+                    ms[j][u] = __ldcg(r);
+                    ls[j][u] = __ldcg(r + 1);
+                    os[j][u] = __ldcg(r + 2 + dim);
                 }
-                float m_new = mx;
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    if (s0 + u >= n_segs) ms[u] = -INFINITY;
-                    m_new = fmaxf(m_new, ms[u]);
-                }
-                const float c = (mx == -INFINITY) ? 0.f : fast_exp2(mx - m_new);
-                l *= c;
-                o *= c;
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const float sc = (ms[u] == -INFINITY) ? 0.f : fast_exp2(ms[u] - m_new);
-                    l = fmaf(sc, ls[u], l);
-                    o = fmaf(sc, os[u], o);
-                }
-                mx = m_new;
             }
+#pragma unroll
+            for (int j = 0; j < E; ++j) {
+                float m_new = mx[j];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (s0 + u >= n_segs) ms[j][u] = -INFINITY;
+                    m_new = fmaxf(m_new, ms[j][u]);
+                }
+                const float c = (mx[j] == -INFINITY) ? 0.f : fast_exp2(mx[j] - m_new);
+                ml[j] *= c;
+                mo[j] *= c;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float sc = (ms[j][u] == -INFINITY) ? 0.f : fast_exp2(ms[j][u] - m_new);
+                    ml[j] = fmaf(sc, ls[j][u], ml[j]);
+                    mo[j] = fmaf(sc, os[j][u], mo[j]);
+                }
+                mx[j] = m_new;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < E; ++j) {
+            const int e = tid + j * TT;
+            if (e >= HPC * D) break;
+            const int head = e / D, dim = e % D;
             if (p.partial_out) {
                 if (head < Gp) {
                     float* dst = p.partial_out + ((size_t)b * p.Hq + head0 + head) * (D + 2);
-                    dst[2 + dim] = o;
-                    if (dim == 0) { dst[0] = l > 0.f ? mx : 0.f; dst[1] = l; }   // empty: m = 0, l = 0 as the host path writes
+                    dst[2 + dim] = mo[j];
+                    if (dim == 0) { dst[0] = ml[j] > 0.f ? mx[j] : 0.f; dst[1] = ml[j]; }   // empty: m = 0, l = 0 as the host path writes
                 }
             } else {
-                o_fin[e] = l > 0.f ? o / l : 0.f;
+                o_fin[e] = ml[j] > 0.f ? mo[j] / ml[j] : 0.f;
             }
         }
         if (tid == 0) p.tickets[group] = 0;   // ready for the next call on this stream
