@@ -64,6 +64,23 @@ __device__ __forceinline__ uint32_t dq_chunk_off(int rows, int r, int kc) {
     return (uint32_t)(kc * (rows / 8) * 128 + (r >> 3) * 128 + (r & 7) * 16);
 }
 
+// packed float32x2 arithmetic: two round-to-nearest operations per instruction
+__device__ __forceinline__ float2 dq_mul2(float2 a, float2 b) {
+    float2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;\n"
+        : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+    return d;
+}
+__device__ __forceinline__ float2 dq_fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n"
+        : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+          "l"(*reinterpret_cast<unsigned long long*>(&c)));
+    return d;
+}
+
 // 32 bytes to global memory at a 32-byte boundary in one instruction
 __device__ __forceinline__ void stg_256(void* dst, const uint32_t (&w)[8]) {
     asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n" ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]),
@@ -268,6 +285,7 @@ __global__ void __launch_bounds__(DequantCfg<D>::kThreads, 1) pq_dequant_kernel(
                 if (blk == 0) vscale[(i & 3) * kDqVecs + vec] = normal ? __uint_as_float(be << 23) : 1.0f;
                 uint8_t* ah = a_tiles + (2 * b) * C::kATile;
                 uint8_t* al = ah + C::kATile;
+                const float2 ds2 = make_float2(d * sc, d * sc), neg1 = make_float2(-1.f, -1.f);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {                     // four 16-byte chunks of 8 elements
                     uint32_t wh[4], wl[4];
@@ -282,11 +300,13 @@ __global__ void __launch_bounds__(DequantCfg<D>::kThreads, 1) pq_dequant_kernel(
                             i0 = (words[j >> 4] >> ((j & 15) * 2)) & 0x3u;
                             i1 = (words[j >> 4] >> ((j & 15) * 2 + 2)) & 0x3u;
                         }
-                        const float x0 = __fmul_rn(cbs[i0 * 32 + lane], d) * sc, x1 = __fmul_rn(cbs[i1 * 32 + lane], d) * sc;
-                        const __half2 h = __floats2half2_rn(x0, x1);
-                        const float2 f = __half22float2(h);
+                        // centroid * radius rounded once to float32 as the reference does; the power of two
+                        // rides on the radius (it commutes with that rounding)
+                        const float2 x = dq_mul2(make_float2(cbs[i0 * 32 + lane], cbs[i1 * 32 + lane]), ds2);
+                        const __half2 h = __floats2half2_rn(x.x, x.y);
+                        const float2 lo = dq_fma2(__half22float2(h), neg1, x);     // exact: x - float(h)
                         wh[u] = *reinterpret_cast<const uint32_t*>(&h);
-                        wl[u] = pack_half2(x0 - f.x, x1 - f.y);
+                        wl[u] = pack_half2(lo.x, lo.y);
                     }
                     const uint32_t off = dq_chunk_off(kDqVecs, vec, blk * 4 + c);
                     *reinterpret_cast<uint4*>(ah + off) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
