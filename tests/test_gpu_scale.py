@@ -158,3 +158,45 @@ def test_prepared_decode_growing_sequence():
         err = float((got - ref).abs().max())
         assert err <= 2e-4, (S, err)
     _check_rows(got, q, ck, cv, R, [(0, 1)], 8192, "prepared decode at capacity")
+
+
+@pytest.mark.parametrize("head_dim,n_bits,n", [(128, 4, 300_001), (64, 2, 211_003), (128, 2, 1 << 20)])
+def test_dequant_many_tiles_vs_float64(head_dim, n_bits, n):
+    """The dequantise kernel at sizes where a persistent CTA owns many tiles (operand and accumulator
+    buffers reused, a ragged last tile): every vector against float64 arithmetic on the same stored bytes
+    (centroid * radius in float32 as the reference rounds it, then v @ R), and a sample against the oracle."""
+    from polarquant_kv import quantizer
+    from polarquant_kv.rotation import device_plan
+    from polarquant_kv.types import CompressedKV
+    dev = _cuda()
+    R = O.rotation_matrix(head_dim, 5)
+    cb, _ = O.lloyd_max_codebook(32, n_bits)
+    plan = device_plan(R, dev)
+    x = _synthetic((1, 1, n, head_dim), dev, seed=29)
+    c = quantizer.compress(x, plan, n_bits)
+    # float32 output: three float16 product terms keep 2^-22 per term; over 10^8 outputs the largest deviation
+    # seen is 2.2e-6 of the vector's largest component (1.6e-6 over 4 * 10^7), so the bar here is 4e-6
+    for dtype, tol in ((torch.float32, 4e-6), (torch.float16, 2e-3)):
+        got = quantizer.decompress(c, plan, dtype)[0, 0]
+        torch.cuda.synchronize()
+        # float64 on the device from the stored bytes
+        blocks = c.blocks[0, 0]                                            # [n, nblk, bb]
+        d = blocks[..., :2].contiguous().view(torch.float16).to(torch.float32)[..., 0]      # [n, nblk]
+        packed = blocks[..., 2:].to(torch.int32)
+        if n_bits == 4:
+            idx = torch.stack([packed & 15, packed >> 4], dim=-1).reshape(n, head_dim // 32, 32)
+        else:
+            idx = torch.stack([(packed >> s) & 3 for s in (0, 2, 4, 6)], dim=-1).reshape(n, head_dim // 32, 32)
+        cbt = torch.from_numpy(cb.astype(np.float32)).to(dev)
+        rot = (cbt[idx.long()] * d[..., None]).reshape(n, head_dim)          # float32 product, as the reference
+        ref = rot.double() @ torch.from_numpy(R).to(dev)
+        scale = ref.abs().amax(dim=-1, keepdim=True) + 1e-30
+        err = ((got.double() - ref).abs() / scale).amax().item()
+        print(f"dequant D{head_dim} b{n_bits} n={n} -> {dtype}: worst error relative to the vector's largest component {err:.2e}")
+        assert err < tol
+    # and the oracle on a sample that includes the last tile
+    sel = np.concatenate([np.arange(5, n, 4099), np.arange(n - 130, n)])
+    ref_o = O.decompress(c.blocks[0, 0, torch.from_numpy(sel).to(dev)].cpu().numpy(), R, cb, n_bits)
+    got_o = quantizer.decompress(c, plan)[0, 0, torch.from_numpy(sel).to(dev)].cpu().numpy()
+    sc = np.abs(ref_o).max(axis=-1, keepdims=True) + 1e-30
+    assert (np.abs(got_o - ref_o) / sc).max() < 4e-6
