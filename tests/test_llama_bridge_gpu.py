@@ -39,8 +39,11 @@ def explained(direction, cb, got, want):
     return len(bad), unexplained, worst
 
 
+# n >= 4096 at head dim 64 / 128 takes the warp-per-four-vectors kernel (R transposed in shared memory), everything
+# else the CTA-per-vector kernel
 @pytest.mark.parametrize("d,n_levels,n", [(128, 16, 1000), (128, 4, 37), (64, 16, 513), (64, 8, 3),
-                                          (96, 16, 200), (256, 16, 65), (130, 8, 9), (128, 16, 1)])
+                                          (96, 16, 200), (256, 16, 65), (130, 8, 9), (128, 16, 1),
+                                          (128, 16, 20_003), (64, 4, 4096), (64, 16, 70_001), (128, 8, 4097)])
 def test_compress_vs_oracle(d, n_levels, n):
     from polarquant_kv import llama_bridge as LB
     rng = np.random.default_rng(d * 131 + n_levels * 7 + n)
