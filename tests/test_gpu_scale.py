@@ -200,3 +200,38 @@ def test_dequant_many_tiles_vs_float64(head_dim, n_bits, n):
     got_o = quantizer.decompress(c, plan)[0, 0, torch.from_numpy(sel).to(dev)].cpu().numpy()
     sc = np.abs(ref_o).max(axis=-1, keepdims=True) + 1e-30
     assert (np.abs(got_o - ref_o) / sc).max() < 4e-6
+
+
+@pytest.mark.parametrize("ws", [True, False])
+def test_prefill_bench_shape_vs_oracle(ws):
+    """The prefill shape the bench times (2 x 32 query / 8 KV heads x 512 queries x 4096 tokens, D 128):
+    two KV heads of one sequence against the oracle, all 512 query rows; and, with the causal mask the decoder
+    harness uses, sampled rows against a decode over their prefix."""
+    from polarquant_kv import attention
+    from polarquant_kv.types import CompressedKV
+    dev = _cuda()
+    B, Hkv, Hq, Sq, S, D = 2, 8, 32, 512, 4096, 128
+    R, plan, ck, cv = _build(B, Hkv, S, D, dev, seed=31)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(6)
+    q = torch.randn((B, Hq, Sq, D), generator=gen, device=dev).to(torch.float16)
+    out = attention.prefill_attention(q, ck, cv, plan, use_workspace=ws)
+    torch.cuda.synchronize()
+    cb, _ = O.lloyd_max_codebook(32, 4)
+    G = Hq // Hkv
+    for b, hkv in ((1, 0), (0, 5)):
+        kb = ck.blocks[b, hkv:hkv + 1, :S].cpu().numpy()
+        vb = cv.blocks[b, hkv:hkv + 1, :S].cpu().numpy()
+        qs = q[b, hkv * G:(hkv + 1) * G].cpu().numpy()
+        ref = O.attention_from_blocks(qs, kb, vb, R, cb, cb)
+        err = np.abs(out[b, hkv * G:(hkv + 1) * G].cpu().numpy() - ref).max()
+        print(f"prefill bench shape, workspace={ws}, batch {b} kv head {hkv}: max-abs {err:.3e}")
+        assert err <= 2e-3
+    causal = attention.prefill_attention(q, ck, cv, plan, causal=True, use_workspace=ws)
+    torch.cuda.synchronize()
+    for i in (0, 1, 127, 128, 300, 511):
+        n = S - Sq + i + 1
+        pk = CompressedKV(ck.blocks, None, None, 4, 32, D, n, ck.max_seq_len)
+        pv = CompressedKV(cv.blocks, None, None, 4, 32, D, n, cv.max_seq_len)
+        row = attention.decode_attention(q[:, :, i].contiguous(), pk, pv, plan, enable_qjl=False)
+        assert float((causal[:, :, i] - row).abs().max()) <= 2e-3, i
