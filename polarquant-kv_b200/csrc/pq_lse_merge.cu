@@ -9,6 +9,10 @@
 
 namespace pq {
 
+// One CTA per output row, D threads (thread i = output dim i).  The records of the parts are fetched eight
+// at a time with independent loads (one round trip to L2 for up to eight GPUs), and the inverse rotation
+// keeps 32 matrix loads in flight over four accumulators: the kernel is all latency, so what matters is how
+// few dependent round trips a row makes.
 template <int D>
 __global__ void __launch_bounds__(D) pq_lse_merge_kernel(const float* __restrict__ parts, int n_parts,
                                                          int64_t n_rows, const float* __restrict__ rot,
@@ -16,30 +20,51 @@ __global__ void __launch_bounds__(D) pq_lse_merge_kernel(const float* __restrict
     __shared__ float o_s[D];
     const int i = threadIdx.x;
     for (int64_t row = blockIdx.x; row < n_rows; row += gridDim.x) {
-        float mx = -INFINITY;
-        for (int s = 0; s < n_parts; ++s) {
-            const float* r = parts + ((size_t)s * n_rows + row) * (D + 2);
-            if (r[1] > 0.f) mx = fmaxf(mx, r[0]);
-        }
-        float l = 0.f, o = 0.f;
-        for (int s = 0; s < n_parts; ++s) {
-            const float* r = parts + ((size_t)s * n_rows + row) * (D + 2);
-            if (r[1] > 0.f) {
-                const float sc = fast_exp2(r[0] - mx);
-                l = fmaf(sc, r[1], l);
-                o = fmaf(sc, r[2 + i], o);
+        float mx = -INFINITY, l = 0.f, o = 0.f;
+        for (int s0 = 0; s0 < n_parts; s0 += 8) {
+            float ms[8], ls[8], os[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int s = min(s0 + u, n_parts - 1);
+                const float* r = parts + ((size_t)s * n_rows + row) * (D + 2);
+                ms[u] = __ldg(r);
+                ls[u] = __ldg(r + 1);
+                os[u] = __ldg(r + 2 + i);
             }
+            float m_new = mx;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (s0 + u >= n_parts || !(ls[u] > 0.f)) { ls[u] = 0.f; ms[u] = -INFINITY; }   // empty slices carry no weight
+                m_new = fmaxf(m_new, ms[u]);
+            }
+            const float c = (mx == -INFINITY) ? 0.f : fast_exp2(mx - m_new);
+            l *= c;
+            o *= c;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float sc = (ms[u] == -INFINITY) ? 0.f : fast_exp2(ms[u] - m_new);
+                l = fmaf(sc, ls[u], l);
+                o = fmaf(sc, os[u], o);
+            }
+            mx = m_new;
         }
         __syncthreads();
         o_s[i] = l > 0.f ? o / l : 0.f;
         __syncthreads();
-        float acc = 0.f;
-#pragma unroll 8
-        for (int j = 0; j < D; ++j) acc = fmaf(o_s[j], __ldg(rot + (size_t)j * D + i), acc);
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j0 = 0; j0 < D; j0 += 32) {
+            float r[32];
+#pragma unroll
+            for (int u = 0; u < 32; ++u) r[u] = __ldg(rot + (size_t)(j0 + u) * D + i);
+#pragma unroll
+            for (int u = 0; u < 32; ++u) acc[u & 3] = fmaf(o_s[j0 + u], r[u], acc[u & 3]);
+        }
+        const float res = (acc[0] + acc[1]) + (acc[2] + acc[3]);
         if (out_is_fp16)
-            static_cast<__half*>(out)[row * D + i] = __float2half_rn(fminf(fmaxf(acc, -65504.f), 65504.f));
+            static_cast<__half*>(out)[row * D + i] = __float2half_rn(fminf(fmaxf(res, -65504.f), 65504.f));
         else
-            static_cast<float*>(out)[row * D + i] = acc;
+            static_cast<float*>(out)[row * D + i] = res;
     }
 }
 
