@@ -379,9 +379,10 @@ def decode_measurement(w, batch, dev, rank, timer, steps, warmup, n_splits, with
     return res
 
 
-def long_context_measurement(dev, rank, world, timer, steps):
+def long_context_measurement(dev, rank, world, timer, steps, peer_exchange="auto"):
     """One long sequence split along the sequence across the ranks: per-rank partial decode
-    (m, l, o_rotated), all-gather of the records, log-sum-exp merge + inverse rotation on every rank."""
+    (m, l, o_rotated), exchange of the records and log-sum-exp merge + inverse rotation on every rank -
+    as one kernel over NVLink peer memory (PeerExchange), with the all-gather + pq_lse_merge path beside it."""
     import torch
     import torch.distributed as dist
     from polarquant_kv import attention, distributed
@@ -407,12 +408,29 @@ def long_context_measurement(dev, rank, world, timer, steps):
     else:
         prepared = [attention.prepare_decode(q, sets[j][1], sets[j][2], plan, partial=True) for j in range(2)]
         gathered = torch.empty((world, Hq, D + 2), dtype=torch.float32, device=dev)
+        merged = torch.empty((Hq, D), dtype=torch.float32, device=dev)
+        exchange = None
+        # the exchange + merge as one kernel over NVLink peer memory; "auto" uses it at the rank counts it
+        # has been run at (2 and 4) and the collective path above that
+        if peer_exchange == "on" or (peer_exchange == "auto" and world <= 4):
+            try:
+                exchange = distributed.PeerExchange(Hq, D, dev)
+            except Exception as exc:   # noqa: BLE001  (no peer mapping between these GPUs: the collective path serves)
+                out["peer_exchange_unavailable"] = repr(exc)[:200]
+        flags = torch.tensor([1 if exchange is not None else 0], device=dev)
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)          # every rank takes the same path
+        if int(flags.item()) == 0:
+            exchange = None
 
-        def step(i):
+        def step_nccl(i):
             part = prepared[i & 1]()
             dist.all_gather_into_tensor(gathered, part.reshape(Hq, D + 2))
             return distributed.lse_merge(gathered, plan)
 
+        def step_peer(i):
+            return exchange.merge(prepared[i & 1]().reshape(Hq, D + 2), plan, out=merged)
+
+        step = step_peer if exchange is not None else step_nccl
         for i in range(3):
             step(i)
         ms, per_rank = timer.run(step, steps)
@@ -421,11 +439,24 @@ def long_context_measurement(dev, rank, world, timer, steps):
         part = prepared[0]().reshape(Hq, D + 2)
         ms_gather, _ = timer.run(lambda i: dist.all_gather_into_tensor(gathered, part), steps, repeats=5)
         ms_merge, _ = timer.run(lambda i: distributed.lse_merge(gathered, plan), steps, repeats=5)
-        out["phases_us"] = {"partial_decode_kernel": round(1e3 * ms_part / steps, 2),
-                            "all_gather": round(1e3 * ms_gather / steps, 2),
-                            "lse_merge_kernel": round(1e3 * ms_merge / steps, 2)}
-        out["all_gather_share_of_step"] = round(ms_gather / ms, 3)
-        out["all_gather_payload_bytes_per_rank"] = Hq * (D + 2) * 4
+        out["phases_us"] = {"partial_decode_kernel": round(1e3 * ms_part / steps, 2)}
+        if exchange is not None:
+            ms_x, _ = timer.run(lambda i: exchange.merge(part, plan, out=merged), steps, repeats=5)
+            ms_nccl, _ = timer.run(step_nccl, steps)
+            out["phases_us"]["peer_exchange_merge_kernel"] = round(1e3 * ms_x / steps, 2)
+            out["exchange"] = "one kernel over NVLink peer memory (pq_lse_exchange_merge): stores into the peers' " \
+                              "buffers, system-scope arrival counters, merge + inverse rotation"
+            out["collective_path"] = {"us_per_step": round(1e3 * ms_nccl / steps, 2),
+                                      "all_gather": round(1e3 * ms_gather / steps, 2),
+                                      "lse_merge_kernel": round(1e3 * ms_merge / steps, 2),
+                                      "note": "the same step with torch.distributed all_gather_into_tensor (NCCL) + pq_lse_merge"}
+            _ext_poll = __import__("polarquant_kv._ext", fromlist=["poll_device_errors"]).poll_device_errors
+            _ext_poll()
+        else:
+            out["phases_us"]["all_gather"] = round(1e3 * ms_gather / steps, 2)
+            out["phases_us"]["lse_merge_kernel"] = round(1e3 * ms_merge / steps, 2)
+            out["all_gather_share_of_step"] = round(ms_gather / ms, 3)
+        out["exchange_payload_bytes_per_rank"] = Hq * (D + 2) * 4
     bytes_total = algorithmic_bytes(w)
     us = 1e3 * ms / steps
     out.update({"us_per_step": round(us, 2), "per_rank_ms": [round(x / steps, 5) for x in per_rank],
@@ -734,7 +765,8 @@ def run_ours(args):
                 "per_rank_ms": [round(x / args.steps, 5) for x in wper]}
         sets = wdec["_keep"][0]
 
-    long_ctx = None if args.only_decode else long_context_measurement(dev, rank, world, timer, args.steps)
+    long_ctx = None if args.only_decode else long_context_measurement(dev, rank, world, timer, args.steps,
+                                                                      args.peer_exchange)
     comp = dequant = None
     if not args.only_decode:
         comp, dequant = compress_measurement(dev, world, timer, args.steps, args.compress_vecs, peak)
@@ -828,6 +860,9 @@ def main():
                     help="only the headline decode measurement (profiler captures)")
     ap.add_argument("--only-compress", action="store_true",
                     help="run the compress and dequantise measurements alone and print them")
+    ap.add_argument("--peer-exchange", default="auto", choices=["auto", "on", "off"],
+                    help="long-context step: exchange + merge as one kernel over NVLink peer memory "
+                         "(auto: at 2 and 4 ranks; the all-gather + merge path otherwise)")
     ap.add_argument("--only-bridge", action="store_true",
                     help="run the llama.cpp bridge measurement alone and print it")
     ap.add_argument("--skip-model", action="store_true", help="skip the end-to-end decoder measurement")

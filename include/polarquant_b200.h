@@ -126,7 +126,9 @@ int pq_compress_rows_dynamic(const void* x, int64_t n_rows, int64_t tokens_per_r
  * up), bit 1 compress (shared-memory window unusable), bit 2 prefill attention (a wait gave up),
  * bit 3 decode attention (shared-memory window unusable, nothing computed), bit 4 decode attention (a
  * wait for a tile copy gave up), bit 5 compress (pq_compress_rows_dynamic found its device-side
- * position out of range; nothing was written), bit 6 dequantise (a wait gave up).
+ * position out of range; nothing was written), bit 6 dequantise (a wait gave up), bit 7
+ * pq_lse_exchange_merge (a peer's records did not arrive within about two seconds; the output rows of the
+ * waiting CTAs are left unwritten).
  * The flags are cleared by the call.  No counterpart in the reference (its kernels report nothing). */
 int pq_poll_device_errors(unsigned int* flags_out);
 
@@ -272,6 +274,27 @@ size_t pq_decode_attn_static_scratch_capacity(void);
  */
 int pq_lse_merge(const float* partials, int n_parts, int64_t n_rows, int head_dim,
                  const float* rot, void* out, int out_is_fp16, void* stream);
+
+/* ---------------------------------------------------------------------------------
+ * pq_lse_exchange_merge — the all-gather of the partial records and pq_lse_merge as ONE kernel over
+ * peer memory (GPUs of one node that can address each other: NVLink / NVSwitch peer mappings).  No
+ * counterpart in the reference.
+ *
+ *   peer_buffers  HOST array of `world` device pointers: entry s is rank s's exchange buffer as THIS
+ *                 process addresses it (its own entry is a local allocation); every buffer has
+ *                 pq_lse_exchange_bytes(world, n_rows, head_dim) bytes, is 128-byte aligned and was
+ *                 zeroed once before the first call (all ranks, then a host barrier)
+ *   epoch         1 for the first call on these buffers, then 2, 3, ... on every rank alike
+ *   local_partial this rank's records [n_rows, head_dim + 2] as written through partial_out
+ *
+ * Every rank enqueues the call once per step; a rank's kernel stores its records into the peers'
+ * buffers, counts itself in, waits (bounded, about two seconds -> bit 7 of pq_poll_device_errors) for
+ * the peers' records and merges.  At most `world` = 8 ranks.  Plain peer stores and system-scope
+ * atomics; no multicast. */
+size_t pq_lse_exchange_bytes(int world, int64_t n_rows, int head_dim);
+int pq_lse_exchange_merge(const float* local_partial, int world, int rank, void* const* peer_buffers,
+                          uint64_t epoch, int64_t n_rows, int head_dim, const float* rot,
+                          void* out, int out_is_fp16, void* stream);
 
 /* ---------------------------------------------------------------------------------
  * pq_prefill_attn — seq_q >= 1 query tokens per head against the compressed cache:

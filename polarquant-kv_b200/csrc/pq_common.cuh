@@ -75,5 +75,7 @@ int prefill_error_flags(unsigned int* flags);
 int decode_error_flags(unsigned int* flags);
 // pq_dequant.cu: bit 0 a bounded wait gave up
 int dequant_error_flags(unsigned int* flags);
+// pq_lse_merge.cu: bit 0 a wait for a peer's records gave up
+int exchange_error_flags(unsigned int* flags);
 
 }  // namespace pq

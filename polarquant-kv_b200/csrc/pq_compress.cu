@@ -707,7 +707,10 @@ extern "C" int pq_poll_device_errors(unsigned int* flags_out) {
     unsigned int qf = 0;
     const int sq = pq::dequant_error_flags(&qf);
     if (sq != PQ_OK) return sq;
-    *flags_out = v | pf | (df << 3) | (qf << 6);
+    unsigned int xf = 0;
+    const int sx = pq::exchange_error_flags(&xf);
+    if (sx != PQ_OK) return sx;
+    *flags_out = v | pf | (df << 3) | (qf << 6) | (xf << 7);
     return PQ_OK;
 }
 

@@ -46,6 +46,9 @@ SIGNATURES = {
     "pq_decode_attn_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int64, c_int, c_int]),
     "pq_decode_attn_default_splits": (c_int, [c_int, c_int, c_int, c_int64, c_int]),
     "pq_lse_merge": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "pq_lse_exchange_bytes": (c_size_t, [c_int, c_int64, c_int]),
+    "pq_lse_exchange_merge": (c_int, [c_void_p, c_int, c_int, ctypes.POINTER(c_void_p), ctypes.c_uint64, c_int64,
+                                      c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "pq_qjl_sketch": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "pq_prefill_attn": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64,
                                 c_int, c_int, c_int, c_float_p, c_float_p, c_void_p, c_float, c_int,

@@ -8,7 +8,8 @@ The reference has no multi-GPU code.  Two schemes cover the path:
   cache, computes the partial softmax state (m, l, o_rot) of its slice with
   ``pq_decode_attn(partial_out=...)``, the ranks all-gather those records
   (``q_heads * (head_dim + 2)`` floats each) and every rank merges them with
-  ``pq_lse_merge`` (log-sum-exp merge + inverse rotation).
+  ``pq_lse_merge`` (log-sum-exp merge + inverse rotation); ``PeerExchange`` does the exchange and the
+  merge in ONE kernel over NVLink peer memory instead (``pq_lse_exchange_merge``).
 """
 
 from __future__ import annotations
@@ -68,15 +69,70 @@ def lse_merge(partials: torch.Tensor, plan, out_dtype: torch.dtype = torch.float
     return out
 
 
+class PeerExchange:
+    """Exchange of the partial records and their merge as one kernel over peer memory
+    (pq_lse_exchange_merge): every rank's kernel stores its records into the peers' buffers with plain
+    NVLink stores, counts itself in with a system-scope atomic, waits (bounded) for the peers' records
+    and merges.  The buffers are symmetric allocations of torch.distributed (one per rank, addressable
+    by every rank of the node).  Every rank must call ``merge`` the same number of times, in the same
+    order; at most eight ranks.  ``close`` (or the end of the process) releases the buffers."""
+
+    def __init__(self, rows: int, head_dim: int, device, group=None):
+        import os
+        # plain peer stores only: keep the allocation off NVLink multicast objects
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if self.world > 8:
+            raise ValueError("PeerExchange serves at most eight ranks")
+        self.rows, self.head_dim, self.device = rows, head_dim, torch.device(device)
+        lib = _ext.lib()
+        nbytes = lib.pq_lse_exchange_bytes(self.world, rows, head_dim)
+        self.buf = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.buf.zero_()
+        self.handle = symm.rendezvous(self.buf, self.group.group_name)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)                     # every rank's counters read zero before anyone counts
+        ptrs = [int(x) for x in self.handle.buffer_ptrs]
+        self._ptrs = (ctypes.c_void_p * self.world)(*ptrs)
+        self.epoch = 0
+
+    def merge(self, partial: torch.Tensor, plan, out_dtype: torch.dtype = torch.float32,
+              out: torch.Tensor | None = None) -> torch.Tensor:
+        """partial float32 [rows, D+2] of this rank -> merged, rotated-back [rows, D] on every rank."""
+        if partial.dtype != torch.float32 or tuple(partial.shape) != (self.rows, self.head_dim + 2) \
+                or not partial.is_contiguous() or partial.device != self.device:
+            raise ValueError("partial must be a contiguous float32 [rows, head_dim + 2] tensor on the exchange's device")
+        if out is None:
+            out = torch.empty((self.rows, self.head_dim), dtype=out_dtype, device=self.device)
+        self.epoch += 1
+        st = _ext.lib().pq_lse_exchange_merge(
+            partial.data_ptr(), self.world, self.rank, self._ptrs, self.epoch, self.rows, self.head_dim,
+            plan.rot.data_ptr(), out.data_ptr(), 1 if out.dtype == torch.float16 else 0,
+            ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        _ext.check(st, "pq_lse_exchange_merge")
+        return out
+
+    def close(self) -> None:
+        self.handle = None
+        self.buf = None
+
+
 def sharded_decode_attention(query: torch.Tensor, ck_local, cv_local, plan, group=None,
                              enable_qjl: bool = True, scale: float | None = None,
-                             out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+                             out_dtype: torch.dtype = torch.float32,
+                             exchange: PeerExchange | None = None) -> torch.Tensor:
     """Decode attention over a sequence whose cache is split across the ranks of ``group``.
 
     query [B, Hq, D] (replicated); ck_local / cv_local hold this rank's slice of the
-    sequence (``seq_len`` may be 0).  Returns [B, Hq, D] on every rank."""
+    sequence (``seq_len`` may be 0).  Returns [B, Hq, D] on every rank.  With ``exchange`` (a
+    PeerExchange for B * Hq rows) the records travel and merge in one kernel over peer memory;
+    otherwise by an all-gather of the process group followed by ``pq_lse_merge``."""
     from .attention import decode_attention
     B, Hq, D = query.shape
     part = decode_attention(query, ck_local, cv_local, plan, enable_qjl=enable_qjl, scale=scale, partial=True)
+    if exchange is not None:
+        return exchange.merge(part.reshape(B * Hq, D + 2), plan, out_dtype).reshape(B, Hq, D)
     allp = gather_partials(part.reshape(B * Hq, D + 2), group)
     return lse_merge(allp, plan, out_dtype).reshape(B, Hq, D)

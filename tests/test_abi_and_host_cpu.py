@@ -223,3 +223,20 @@ def test_mixed_precision_plans_host_logic():
     # 4 + 64 tokens at 72 bytes, 4028 at 40 bytes against 256 bytes of float16 per token
     ratio = policy.estimate_mixed_compression_ratio(4096)
     assert ratio == pytest.approx(256 * 4096 / (68 * 72 + 4028 * 40), rel=1e-12)
+
+
+def test_peer_exchange_entry_rejects_bad_arguments_on_the_host():
+    from polarquant_kv import _ext
+    lib = _ext.lib()
+    assert lib.pq_lse_exchange_bytes(2, 64, 128) == ((2 * 2 * 64 * 130 * 4 + 127) // 128) * 128 + 128
+    assert lib.pq_lse_exchange_bytes(0, 64, 128) == 0
+    one = ctypes.c_void_p(256)
+    ptrs = (ctypes.c_void_p * 2)(256, 512)
+    assert lib.pq_lse_exchange_merge(one, 9, 0, ptrs, 1, 4, 128, one, one, 0, None) == 4      # more than eight ranks
+    assert lib.pq_lse_exchange_merge(one, 2, 2, ptrs, 1, 4, 128, one, one, 0, None) == 4      # rank outside the group
+    assert lib.pq_lse_exchange_merge(one, 2, 0, ptrs, 0, 4, 128, one, one, 0, None) == 4      # epochs start at 1
+    assert lib.pq_lse_exchange_merge(one, 2, 0, ptrs, 1, 4, 96, one, one, 0, None) == 2
+    assert lib.pq_lse_exchange_merge(one, 2, 0, ptrs, 1, 0, 128, one, one, 0, None) == 0      # nothing to do
+    assert lib.pq_lse_exchange_merge(None, 2, 0, ptrs, 1, 4, 128, one, one, 0, None) == 1
+    bad = (ctypes.c_void_p * 2)(256, 520)
+    assert lib.pq_lse_exchange_merge(one, 2, 0, bad, 1, 4, 128, one, one, 0, None) == 6       # 128-byte alignment
