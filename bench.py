@@ -410,9 +410,9 @@ def long_context_measurement(dev, rank, world, timer, steps, peer_exchange="auto
         gathered = torch.empty((world, Hq, D + 2), dtype=torch.float32, device=dev)
         merged = torch.empty((Hq, D), dtype=torch.float32, device=dev)
         exchange = None
-        # the exchange + merge as one kernel over NVLink peer memory; "auto" uses it at the rank counts it
-        # has been run at (2 and 4) and the collective path above that
-        if peer_exchange == "on" or (peer_exchange == "auto" and world <= 4):
+        # the exchange + merge as one kernel over NVLink peer memory (run at 2, 4 and 8 ranks); "off" and
+        # any failure to map the peers' buffers fall back to the collective path
+        if peer_exchange == "on" or (peer_exchange == "auto" and world <= 8):
             try:
                 exchange = distributed.PeerExchange(Hq, D, dev)
             except Exception as exc:   # noqa: BLE001  (no peer mapping between these GPUs: the collective path serves)
@@ -862,7 +862,7 @@ def main():
                     help="run the compress and dequantise measurements alone and print them")
     ap.add_argument("--peer-exchange", default="auto", choices=["auto", "on", "off"],
                     help="long-context step: exchange + merge as one kernel over NVLink peer memory "
-                         "(auto: at 2 and 4 ranks; the all-gather + merge path otherwise)")
+                         "(auto: up to 8 ranks of one node; the all-gather + merge path otherwise)")
     ap.add_argument("--only-bridge", action="store_true",
                     help="run the llama.cpp bridge measurement alone and print it")
     ap.add_argument("--skip-model", action="store_true", help="skip the end-to-end decoder measurement")
