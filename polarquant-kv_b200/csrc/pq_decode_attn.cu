@@ -201,6 +201,11 @@ __device__ __forceinline__ void copy_bytes(uint8_t* dst, const uint8_t* src, int
     for (int c = lane; c < cap; c += 32) dst[c] = c < n ? __ldg(src + c) : (uint8_t)0;
 }
 
+// Asks L2 for `bytes` (a multiple of 16) at a 16-byte aligned global address; nothing waits for it.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gsrc, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(gsrc), "r"(bytes) : "memory");
+}
+
 template <int D, int KBITS, int VBITS, int NH, bool QJL>
 struct DecodeCfg {
     static constexpr int NBLK = D / 32;
@@ -217,6 +222,13 @@ struct DecodeCfg {
     static constexpr int kTeamWarps = NWARPS / kTeams;
     static constexpr int kTeamThreads = kTeamWarps * 32;
     static constexpr int kStages = PQ_DEC_STAGES;
+    // Query rows rotated in one pass.  The rotation MMA has 16 rows and one segment fills HPC of them, so a
+    // team rotates the queries of up to 16 / HPC consecutive segments of its range together: the second
+    // and third segment of a team then start without the two memory round trips of a rotation.  (With the
+    // key sketch the projected query takes the room, and with eight heads per segment the registers of
+    // the second row set spill in the tile loop: there a pass serves one segment.)
+    static constexpr int kQRows = (QJL || NH == 2) ? HPC : 16;
+    static constexpr int kSegBatch = kQRows / HPC;
     static constexpr int BBK = block_bytes(KBITS), BBV = block_bytes(VBITS);
     static constexpr int TBK = NBLK * BBK, TBV = NBLK * BBV;     // bytes per token
     static constexpr int kStageK = kTileTok * TBK;                // multiples of 64 bytes
@@ -241,8 +253,8 @@ struct DecodeCfg {
         return kRingHead + (((r > rec ? r : rec) + 15) & ~15);
     }
     __host__ __device__ static int low_fixed(int jl_dim) {
-        // per team: rotated query and final-stage buffer [HPC][D] each (+ the projected query with QJL)
-        return ((kTeams * HPC * (2 * D + (QJL ? jl_dim : 0)) * 4 + 2 * 16 * 4) + 15) & ~15;
+        // per team: rotated queries [kQRows][D], final-stage buffer [HPC][D] (+ the projected query with QJL)
+        return ((kTeams * ((kQRows + HPC) * D + (QJL ? HPC * jl_dim : 0)) * 4 + 2 * 16 * 4) + 15) & ~15;
     }
     // rings that fit below the table when the dynamic window starts at or below 8 KB
     __host__ __device__ static int n_low(int jl_dim) {
@@ -287,9 +299,10 @@ pq_decode_attn_kernel(const DecodeParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     constexpr int kTeams = C::kTeams, TW = C::kTeamWarps, TT = C::kTeamThreads;
     const int team = (threadIdx.x >> 5) / TW;                            // this warp's team
-    const int team_buf = HPC * (2 * D + (QJL ? p.jl_dim : 0));           // floats per team
-    float* q_rot = reinterpret_cast<float*>(smem) + team * team_buf;     // [HPC][D] rotated, scaled
-    float* o_fin = q_rot + HPC * D;                                      // [HPC][D] final stage
+    constexpr int kQRows = C::kQRows, kSegBatch = C::kSegBatch;
+    const int team_buf = (kQRows + HPC) * D + (QJL ? HPC * p.jl_dim : 0);   // floats per team
+    float* q_rot_all = reinterpret_cast<float*>(smem) + team * team_buf; // [kQRows][D] rotated, scaled
+    float* o_fin = q_rot_all + kQRows * D;                               // [HPC][D] final stage
     float* q_jl = o_fin + HPC * D;                                       // [HPC][M] (QJL)
     uint32_t* cs_k = reinterpret_cast<uint32_t*>(reinterpret_cast<float*>(smem) + kTeams * team_buf);   // split centroids
     uint32_t* cs_v = cs_k + 16;
@@ -411,6 +424,75 @@ pq_decode_attn_kernel(const DecodeParams p) {
         cur = (int64_t)worker * all_tiles / n_cta;
         cur_end = ((int64_t)worker + 1) * all_tiles / n_cta;
     }
+    // q_rot[row][i] = sum_j q[row][j] * R[i][j] (and the JL projection P q) on tensor cores for the query
+    // heads of `n_seg` consecutive virtual rows starting at `vrow0`: MMA row r = head r % HPC of virtual
+    // row vrow0 + r / HPC (the float16 query is exact), columns = 8 outputs per warp-step, R split into two
+    // float16 terms of 4096*R on the fly.  Matrix rows are read as 32-byte pieces by 4 lanes.
+    auto rotate_queries = [&](int64_t vrow0, int n_seg) {
+        const __half* qrow[2];
+        bool have[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {                                    // this lane's MMA rows g and g + 8
+            const int mr = g + 8 * r, sg = mr / HPC, hd = mr % HPC;
+            have[r] = mr < kQRows && sg < n_seg;
+            qrow[r] = p.q;
+            if (have[r]) {
+                const uint32_t vr = (uint32_t)vrow0 + (uint32_t)sg;      // rows fit 32 bits
+                const int rw = (int)(vr / (uint32_t)p.HG), hgx = (int)(vr % (uint32_t)p.HG);
+                const int bb = rw / p.Hkv, hk = rw % p.Hkv;
+                have[r] = hd < min(HPC, p.G - hgx * HPC);
+                qrow[r] = p.q + ((size_t)bb * p.Hq + hk * p.G + hgx * HPC + hd) * D;
+            }
+        }
+        auto rotate_pass = [&](int nt) {                                 // eight output columns
+            const int i = nt * 8 + g;                                    // this lane's output column
+            const float* mrow = i < D ? p.rot + (size_t)i * D : p.jl + (size_t)(i - D) * D;
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                const float2 r0 = __ldg(reinterpret_cast<const float2*>(mrow + ks * 16 + 2 * t));
+                const float2 r1 = __ldg(reinterpret_cast<const float2*>(mrow + ks * 16 + 8 + 2 * t));
+                const uint32_t a0 = have[0] ? *reinterpret_cast<const uint32_t*>(qrow[0] + ks * 16 + 2 * t) : 0u;
+                const uint32_t a2 = have[0] ? *reinterpret_cast<const uint32_t*>(qrow[0] + ks * 16 + 8 + 2 * t) : 0u;
+                uint32_t a1 = 0u, a3 = 0u;
+                if (kQRows > 8) {
+                    a1 = have[1] ? *reinterpret_cast<const uint32_t*>(qrow[1] + ks * 16 + 2 * t) : 0u;
+                    a3 = have[1] ? *reinterpret_cast<const uint32_t*>(qrow[1] + ks * 16 + 8 + 2 * t) : 0u;
+                }
+                const float x0 = r0.x * 4096.f, x1 = r0.y * 4096.f, x2 = r1.x * 4096.f, x3 = r1.y * 4096.f;
+                const __half2 h01 = __floats2half2_rn(x0, x1), h23 = __floats2half2_rn(x2, x3);
+                const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+                mma_16816(c, a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+                mma_16816(c, a0, a1, a2, a3, pack_half2(x0 - f01.x, x1 - f01.y), pack_half2(x2 - f23.x, x3 - f23.y));
+            }
+            // C rows g and g + 8, columns 2t, 2t+1 = outputs nt*8 + 2t, +1
+            const int o0 = nt * 8 + 2 * t;
+            if (o0 < D) {
+                if (g < kQRows) {
+                    q_rot_all[g * D + o0] = c[0] * (p.scale_log2 / 4096.f);
+                    q_rot_all[g * D + o0 + 1] = c[1] * (p.scale_log2 / 4096.f);
+                }
+                if (kQRows > 8) {
+                    q_rot_all[(g + 8) * D + o0] = c[2] * (p.scale_log2 / 4096.f);
+                    q_rot_all[(g + 8) * D + o0 + 1] = c[3] * (p.scale_log2 / 4096.f);
+                }
+            } else if (g < HPC) {                                        // QJL: one segment per pass
+                const float sj = QJL ? p.scale_log2 / (4096.f * (float)p.jl_dim) : 0.f;
+                q_jl[g * M + o0 - D] = c[0] * sj;
+                q_jl[g * M + o0 - D + 1] = c[1] * sj;
+            }
+        };
+        if (QJL) {
+            for (int nt = tw; nt < (D + M) / 8; nt += TW) rotate_pass(nt);
+        } else {
+            // compile-time bounds: the passes of a warp unroll and their matrix loads are in flight together
+            constexpr int kRotPasses = (D / 8 + TW - 1) / TW;
+#pragma unroll
+            for (int it = 0; it < kRotPasses; ++it)
+                if (tw + it * TW < D / 8) rotate_pass(tw + it * TW);
+        }
+    };
+    int seg_no = 0;                                                      // segments this team has started
     while (cur < cur_end) {
     int64_t vrow, tile_begin, tile_end;
     int seg_idx, n_segs;
@@ -493,43 +575,50 @@ pq_decode_attn_kernel(const DecodeParams p) {
     // first tiles in flight before the prologue math
 #pragma unroll
     for (int s = 0; s < kStages - 1; ++s) issue_tile(t_first + s * TW, s);
-
-    // ---- per item: query rotation (and JL projection of the query)
-    // q_rot[h][i] = sum_j q[h][j] * R[i][j] (and the JL projection P q) on tensor cores: rows =
-    // heads (the float16 query is exact), columns = 8 outputs per warp-step, R split into two
-    // float16 terms of 4096*R on the fly.  Matrix rows are read as 32-byte pieces by 4 lanes.
-    for (int nt = tw; nt < (D + M) / 8; nt += TW) {
-        const int i = nt * 8 + g;                                        // this lane's output column
-        const float* mrow = i < D ? p.rot + (size_t)i * D : p.jl + (size_t)(i - D) * D;
-        const __half* qrow = p.q + ((size_t)b * p.Hq + head0 + g) * D;   // row g = head g (if it exists)
-        const bool have = g < Gp;
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
+    // The team's next segment starts at tile 0 of the next virtual row: once this warp has issued its last
+    // tile here, it asks L2 for the tiles it will start that segment with, so that they arrive from L2
+    // rather than from DRAM when nothing else of the team is in flight.
+    // (Not with eight heads per segment: the tile loop has no register to spare there.)
+    bool prefetch_pending = NH == 1 && !p.splits && cur < cur_end;
+    auto prefetch_next_segment = [&]() {
+        prefetch_pending = false;
+        if (lane != 0) return;
+        const uint32_t nv = (uint32_t)vrow + 1u;
+        const size_t nrow = nv / (uint32_t)p.HG;
+        const uint8_t* kn = p.kb + nrow * p.Scap * C::TBK;
+        const uint8_t* vn = p.vb + nrow * p.Scap * C::TBV;
+        if (((reinterpret_cast<uintptr_t>(kn) | reinterpret_cast<uintptr_t>(vn)) & 15) != 0) return;
+        const int n_next = (int)min(min(cur_end - cur, tiles_total), (int64_t)full_tiles);
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-            const float2 r0 = __ldg(reinterpret_cast<const float2*>(mrow + ks * 16 + 2 * t));
-            const float2 r1 = __ldg(reinterpret_cast<const float2*>(mrow + ks * 16 + 8 + 2 * t));
-            const uint32_t a0 = have ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t) : 0u;
-            const uint32_t a2 = have ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t) : 0u;
-            const float x0 = r0.x * 4096.f, x1 = r0.y * 4096.f, x2 = r1.x * 4096.f, x3 = r1.y * 4096.f;
-            const __half2 h01 = __floats2half2_rn(x0, x1), h23 = __floats2half2_rn(x2, x3);
-            const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-            mma_16816(c, a0, 0u, a2, 0u, *reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
-            mma_16816(c, a0, 0u, a2, 0u, pack_half2(x0 - f01.x, x1 - f01.y), pack_half2(x2 - f23.x, x3 - f23.y));
-        }
-        // C rows g = heads, columns 2t, 2t+1 = outputs nt*8 + 2t, +1
-        if (g < HPC) {
-            const int o0 = nt * 8 + 2 * t;
-            if (o0 < D) {
-                q_rot[g * D + o0] = c[0] * (p.scale_log2 / 4096.f);
-                q_rot[g * D + o0 + 1] = c[1] * (p.scale_log2 / 4096.f);
-            } else {
-                const float sj = QJL ? p.scale_log2 / (4096.f * (float)p.jl_dim) : 0.f;
-                q_jl[g * M + o0 - D] = c[0] * sj;
-                q_jl[g * M + o0 - D + 1] = c[1] * sj;
+        for (int s = 0; s < kStages - 1; ++s) {
+            const int tile = tw + s * TW;
+            if (tile < n_next) {
+                bulk_prefetch_l2(kn + (size_t)tile * kTileTok * C::TBK, C::kStageK);
+                bulk_prefetch_l2(vn + (size_t)tile * kTileTok * C::TBV, C::kStageV);
             }
         }
+    };
+
+    // ---- query rotation (and JL projection of the query), once per pass of up to kSegBatch segments
+    int qslot = 0;                                                       // this segment's slot in q_rot_all
+    bool rotate_now = true;
+    int n_batch = 1;
+    if (kSegBatch > 1 && !p.splits) {
+        qslot = seg_no % kSegBatch;
+        rotate_now = qslot == 0;
+        if (rotate_now) {
+            // the team's remaining segments are the consecutive virtual rows up to the one of its last tile
+            const int64_t last_vrow = small ? (int64_t)((uint32_t)(cur_end - 1) / (uint32_t)tiles_total)
+                                            : (cur_end - 1) / tiles_total;
+            n_batch = (int)min((int64_t)kSegBatch, last_vrow - vrow + 1);
+        }
     }
-    team_sync();
+    ++seg_no;
+    if (rotate_now) {
+        rotate_queries(vrow, n_batch);
+        team_sync();
+    }
+    const float* q_rot = q_rot_all + qslot * HPC * D;
 
     // ---- B fragments of the query.  MMA column n = lane group g.
     //   NH == 1: column g is head g>>1, term hi (g even) or lo (g odd);
@@ -575,7 +664,7 @@ pq_decode_attn_kernel(const DecodeParams p) {
             }
         }
     }
-    team_sync();
+    if (QJL) team_sync();                       // the shared fragments of the projected query are complete
 
     // ---- running softmax state.  A lane holds the scores of its head(s) (NH == 1: head t;
     // NH == 2: heads t and t+4) for tokens 2g and 2g+1 of the tile.
@@ -602,6 +691,7 @@ pq_decode_attn_kernel(const DecodeParams p) {
     int slot = 0;
     for (int tile = t_first; tile < t_end; tile += TW) {
         issue_tile(tile + (kStages - 1) * TW, slot >= 1 ? slot - 1 : kStages - 1);
+        if (NH == 1 && prefetch_pending && tile + (kStages - 1) * TW >= t_end) prefetch_next_segment();
         const bool full = tile < full_tiles;
         if (bulk_row && full) {
             if (!dead && !mbar_wait(mbar0 + 8 * slot, (phase >> slot) & 1u)) {
@@ -847,6 +937,7 @@ pq_decode_attn_kernel(const DecodeParams p) {
         slot = slot + 1 == kStages ? 0 : slot + 1;
     }
 
+    if (NH == 1 && prefetch_pending) prefetch_next_segment();            // a warp without tiles in this segment
     // ---- reduce the row sums over the 8 lanes that share a head
 #pragma unroll
     for (int h = 0; h < NH; ++h) {
@@ -978,7 +1069,11 @@ pq_decode_attn_kernel(const DecodeParams p) {
             // float32 result), B = R split into two float16 terms of 4096*R on the fly; the three product
             // terms hi*hi + lo*hi + hi*lo land in rows g and g+8 of the same lane.  (|o| <= 0.46 * 65504:
             // the hi term cannot overflow.)
-            for (int nt = tw; nt < D / 8; nt += TW) {
+            constexpr int kInvPasses = (D / 8 + TW - 1) / TW;
+#pragma unroll
+            for (int it = 0; it < kInvPasses; ++it) {
+                const int nt = tw + it * TW;
+                if (nt >= D / 8) break;
                 float c[4] = {0.f, 0.f, 0.f, 0.f};
                 const int n = nt * 8 + g;                               // B column of this lane
 #pragma unroll
