@@ -807,6 +807,11 @@ def run_ours(args):
                "sample": f"{rows} (batch, kv-head) rows of the workload in {cpu_dt:.1f} s, numpy oracle, one process",
                "reference_as_shipped": None if args.only_decode else reference_as_shipped()}
 
+    # DRAM bytes of one launch (dram__bytes_read.sum + dram__bytes_write.sum of a single-launch ncu capture of
+    # this very shape on one GPU: 302 813 184 read + 4 269 312 written); any other shape reports none.
+    captured_shape = world == 1 and (w["batch"], w["context"], w["q_heads"]) == (32, 8192, 32) and not args.splits
+    traffic = 307_082_496 if captured_shape else None
+
     line = {
         "metric": "PQ4 decode-attn compressed-byte throughput", "value": round(value, 1), "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(ms_step, 5),
@@ -820,11 +825,11 @@ def run_ours(args):
                    "timing": f"median of {args.repeats} blocks of {args.steps} steps per rank, maximum over ranks"},
         "per_rank_ms": [round(x / args.steps, 5) for x in per_rank],
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": f"of {peak_kind}",
+                     "frac": round(achieved / peak, 4), "traffic": traffic, "peak_kind": f"of {peak_kind}",
                      "kernel": "pq_decode_attn_kernel<128,4,4,1,false>",
                      "algorithmic_bytes_per_launch": per_gpu_bytes,
-                     "traffic_note": "dram bytes of one launch are in the ncu summary under profiles/ for the "
-                                     "kernel build it was captured on"},
+                     "traffic_note": "dram bytes read + written by one launch of this shape in a single-launch ncu "
+                                     "capture (1.017 x the algorithmic bytes); null for shapes that were not captured"},
         "e2e": {"value": round(e2e_val, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": round(ms_e2e_block / args.steps, 5),
                 "per_rank_ms": [round(x / args.steps, 5) for x in per_rank_e2e]},
