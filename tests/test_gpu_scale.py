@@ -98,6 +98,28 @@ def test_decode_multi_segment_vs_oracle(B, Hkv, Hq, S):
     _check_rows(out, q, ck, cv, R, rows, S, f"decode B{B} Hkv{Hkv} Hq{Hq} S{S}")
 
 
+def test_decode_many_short_rows_vs_oracle():
+    """1536 short (batch, kv head, head group) rows: every team of warps walks five or six segments, so it
+    rotates the queries of its segments in more than one pass (a pass holds four), rows start in the middle
+    of a team's range, and each KV head has two head groups (six query heads per KV head).  The last
+    tile of every row is ragged."""
+    from polarquant_kv import attention
+    dev = _cuda()
+    B, Hkv, Hq, S, D = 96, 8, 48, 40, 128
+    R, plan, ck, cv = _build(B, Hkv, S, D, dev, seed=17)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(6)
+    q = torch.randn((B, Hq, D), generator=gen, device=dev).to(torch.float16)
+    out = attention.decode_attention(q, ck, cv, plan, enable_qjl=False, n_splits=0)
+    one = attention.decode_attention(q, ck, cv, plan, enable_qjl=False, n_splits=1)
+    torch.cuda.synchronize()
+    diff = float((out - one).abs().max())
+    print(f"B{B} Hkv{Hkv} Hq{Hq} S{S}: balanced vs one segment per row: max-abs {diff:.3e}")
+    assert diff <= 2e-4
+    rows = [(0, 0), (0, 1), (1, 7), (37, 3), (38, 4), (64, 0), (95, 6), (95, 7)]
+    _check_rows(out, q, ck, cv, R, rows, S, f"decode B{B} Hkv{Hkv} Hq{Hq} S{S}")
+
+
 def test_decode_long_context_shape_vs_oracle():
     """One 131072-token sequence, 8 KV heads, 64 query heads (8 per KV head): two sampled KV heads."""
     from polarquant_kv import attention
