@@ -43,19 +43,47 @@ class RMSNorm(nn.Module):
         self.eps = eps
 
     def forward(self, x):
-        v = x.float()
-        return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype) * self.weight
+        return F.rms_norm(x, (x.shape[-1],), self.weight, self.eps)
+
+
+def rotary_tables(positions: torch.Tensor, head_dim: int, theta: float) -> tuple[torch.Tensor, torch.Tensor]:
+    """positions [S] -> (cos, sin), each [S, head_dim] float32 (the rotate_half convention: the angle
+    of pair i sits at columns i and i + head_dim / 2).  One pair of tables serves every layer of a step."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, device=positions.device, dtype=torch.float32) / head_dim))
+    ang = positions.float()[:, None] * inv[None, :]
+    return torch.cos(ang).repeat(1, 2), torch.sin(ang).repeat(1, 2)
+
+
+def apply_rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x [B, H, S, D] -> float32 x * cos + rotate_half(x) * sin."""
+    D = x.shape[-1]
+    xf = x.float()
+    rot = torch.cat([-xf[..., D // 2:], xf[..., :D // 2]], dim=-1)
+    return torch.addcmul(xf * cos, rot, sin)
 
 
 def rotary(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor:
     """x [B, H, S, D], positions [S] -> rotated halves (the rotate_half convention)."""
-    D = x.shape[-1]
-    inv = 1.0 / (theta ** (torch.arange(0, D, 2, device=x.device, dtype=torch.float32) / D))
-    ang = positions.float()[:, None] * inv[None, :]
-    cos, sin = torch.cos(ang).repeat(1, 2), torch.sin(ang).repeat(1, 2)
-    xf = x.float()
-    rot = torch.cat([-xf[..., D // 2:], xf[..., :D // 2]], dim=-1)
-    return xf * cos + rot * sin
+    return apply_rotary(x, *rotary_tables(positions, x.shape[-1], theta))
+
+
+class _FusedLinear:
+    """The weights (and biases) of several nn.Linear layers that read the same input, stacked so that one
+    GEMM serves them all; rebuilt when a layer's parameters were modified in place or moved."""
+
+    def __init__(self, *layers: nn.Linear):
+        self.layers = layers
+        self.key = None
+        self.weight = self.bias = None
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        key = tuple((l.weight._version, l.weight.data_ptr(), l.weight.dtype) for l in self.layers)
+        if key != self.key:
+            self.weight = torch.cat([l.weight.detach() for l in self.layers], dim=0)
+            self.bias = (torch.cat([l.bias.detach() for l in self.layers], dim=0)
+                         if self.layers[0].bias is not None else None)
+            self.key = key
+        return F.linear(x, self.weight, self.bias)
 
 
 class CompressedAttention(nn.Module):
@@ -68,22 +96,23 @@ class CompressedAttention(nn.Module):
         self.k_proj = nn.Linear(cfg.hidden, cfg.kv_heads * cfg.head_dim, bias=True)
         self.v_proj = nn.Linear(cfg.hidden, cfg.kv_heads * cfg.head_dim, bias=True)
         self.o_proj = nn.Linear(cfg.q_heads * cfg.head_dim, cfg.hidden, bias=False)
+        self._qkv = _FusedLinear(self.q_proj, self.k_proj, self.v_proj)
 
-    def forward(self, x: torch.Tensor, cache: KVCacheManager, timers=None, device_step=None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, cache: KVCacheManager, timers=None, device_step=None, rope=None) -> torch.Tensor:
         """``device_step`` = (position, length) one-element int64 device tensors: the step's token
-        position and the number of cached tokens after the append, both read on the device."""
+        position and the number of cached tokens after the append, both read on the device.
+        ``rope`` = (cos, sin) of the step's positions (rotary_tables); computed here when absent."""
         c = self.cfg
         B, S, _ = x.shape
-        if device_step is not None:
-            pos = device_step[0]
-        else:
-            pos = torch.arange(cache.seq_len, cache.seq_len + S, device=x.device)
-        q = self.q_proj(x).view(B, S, c.q_heads, c.head_dim).transpose(1, 2)
-        k = self.k_proj(x).view(B, S, c.kv_heads, c.head_dim).transpose(1, 2)
-        v = self.v_proj(x).view(B, S, c.kv_heads, c.head_dim).transpose(1, 2)
-        q = rotary(q, pos, c.rope_theta).to(torch.float16)
-        k = rotary(k, pos, c.rope_theta).to(torch.float16)
-        v = v.to(torch.float16)
+        if rope is None:
+            pos = device_step[0] if device_step is not None else \
+                torch.arange(cache.seq_len, cache.seq_len + S, device=x.device)
+            rope = rotary_tables(pos, c.head_dim, c.rope_theta)
+        # one GEMM for the three projections; the rotary embedding runs over the query and key heads together
+        qkv = self._qkv(x).view(B, S, c.q_heads + 2 * c.kv_heads, c.head_dim).transpose(1, 2)
+        qk = apply_rotary(qkv[:, :c.q_heads + c.kv_heads], *rope).to(torch.float16)
+        q, k = qk[:, :c.q_heads], qk[:, c.q_heads:]
+        v = qkv[:, c.q_heads + c.kv_heads:].to(torch.float16)
         if timers is not None:
             timers.start()
         if device_step is not None:
@@ -106,11 +135,12 @@ class DecoderLayer(nn.Module):
         self.gate = nn.Linear(cfg.hidden, cfg.intermediate, bias=False)
         self.up = nn.Linear(cfg.hidden, cfg.intermediate, bias=False)
         self.down = nn.Linear(cfg.intermediate, cfg.hidden, bias=False)
+        self._gate_up = _FusedLinear(self.gate, self.up)
 
-    def forward(self, x, cache, timers=None, device_step=None):
-        x = x + self.attn(self.norm1(x), cache, timers, device_step)
-        h = self.norm2(x)
-        return x + self.down(F.silu(self.gate(h)) * self.up(h))
+    def forward(self, x, cache, timers=None, device_step=None, rope=None):
+        x = x + self.attn(self.norm1(x), cache, timers, device_step, rope)
+        g, u = self._gate_up(self.norm2(x)).chunk(2, dim=-1)
+        return x + self.down(F.silu(g) * u)
 
 
 class KernelTimer:
@@ -166,8 +196,11 @@ class DecoderLM(nn.Module):
         """input_ids [B, S] (a prompt, or S == 1 for a decode step) -> logits of the last position
         [B, vocab] (or of every position with last_only=False)."""
         x = self.embed(input_ids)
+        start = caches[0].seq_len
+        rope = rotary_tables(torch.arange(start, start + input_ids.shape[1], device=input_ids.device),
+                             self.cfg.head_dim, self.cfg.rope_theta)
         for layer, cache in zip(self.layers, caches):
-            x = layer(x, cache, timers)
+            x = layer(x, cache, timers, None, rope)
         x = self.norm(x[:, -1:] if last_only else x)
         return self.head(x).float().squeeze(1) if last_only else self.head(x).float()
 
@@ -178,8 +211,9 @@ class DecoderLM(nn.Module):
         position, length, step, out = state
         out.index_copy_(1, step, token)
         x = self.embed(token)
+        rope = rotary_tables(position, self.cfg.head_dim, self.cfg.rope_theta)
         for layer, cache in zip(self.layers, caches):
-            x = layer(x, cache, None, (position, length))
+            x = layer(x, cache, None, (position, length), rope)
         logits = self.head(self.norm(x)).float().squeeze(1)
         token.copy_(logits.argmax(-1, keepdim=True))
         position.add_(1)
