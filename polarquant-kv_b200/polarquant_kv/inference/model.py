@@ -224,7 +224,7 @@ class DecoderLM(nn.Module):
     def decode_graph(self, token: torch.Tensor, steps: int, caches: list[KVCacheManager]) -> torch.Tensor:
         """``steps`` greedy single-token steps after a prefill, starting from ``token`` [B, 1], replayed
         from ONE CUDA graph: the position and the cache length advance in device memory
-        (pq_compress_rows_dynamic, pq_decode_attn_dynamic), so the ~25 kernels per layer are launched by
+        (pq_compress_rows_dynamic, pq_decode_attn_dynamic), so the 22 or so kernels per layer are launched by
         one graph launch per token instead of one Python call each.  The first step runs eagerly (it
         also warms the libraries up), the second is recorded, the rest are replays.  Returns the ids
         fed and generated, [B, steps]."""
