@@ -240,3 +240,37 @@ def test_peer_exchange_entry_rejects_bad_arguments_on_the_host():
     assert lib.pq_lse_exchange_merge(None, 2, 0, ptrs, 1, 4, 128, one, one, 0, None) == 1
     bad = (ctypes.c_void_p * 2)(256, 520)
     assert lib.pq_lse_exchange_merge(one, 2, 0, bad, 1, 4, 128, one, one, 0, None) == 6       # 128-byte alignment
+
+
+def test_decoder_harness_host_pieces():
+    """The dense-layer helpers of the decoder harness on the CPU: rotary tables against the closed form,
+    stacked projection weights that follow in-place edits of their layers, the RMS norm formula."""
+    import torch
+    from polarquant_kv.inference import model as M
+
+    torch.manual_seed(0)
+    x = torch.randn(2, 3, 4, 16)
+    pos = torch.tensor([5, 6, 7, 8])
+    cos, sin = M.rotary_tables(pos, 16, 1.0e6)
+    inv = 1.0 / (1.0e6 ** (torch.arange(0, 16, 2, dtype=torch.float32) / 16))
+    ang = pos.float()[:, None] * inv[None, :]
+    want = torch.empty_like(x)
+    want[..., :8] = x[..., :8] * torch.cos(ang) - x[..., 8:] * torch.sin(ang)
+    want[..., 8:] = x[..., 8:] * torch.cos(ang) + x[..., :8] * torch.sin(ang)
+    assert torch.allclose(M.apply_rotary(x, cos, sin), want, atol=1e-6)
+    assert torch.allclose(M.rotary(x, pos, 1.0e6), want, atol=1e-6)
+
+    a, b = torch.nn.Linear(8, 6), torch.nn.Linear(8, 4)
+    fused = M._FusedLinear(a, b)
+    v = torch.randn(5, 8)
+    with torch.no_grad():
+        out = fused(v)
+        assert torch.allclose(out[:, :6], a(v), atol=1e-6) and torch.allclose(out[:, 6:], b(v), atol=1e-6)
+        b.weight.mul_(3.0)                                  # an in-place edit is picked up
+        assert torch.allclose(fused(v)[:, 6:], b(v), atol=1e-6)
+
+    norm = M.RMSNorm(8, 1e-6)
+    with torch.no_grad():
+        norm.weight.copy_(torch.randn(8))
+        want_n = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-6) * norm.weight
+        assert torch.allclose(norm(v), want_n, atol=1e-6)
