@@ -60,8 +60,8 @@ def _row_view(cache, b):
     return CompressedKV(cache.blocks[b:b + 1], None, None, cache.n_bits, 32, cache.original_dim, 0, cache.max_seq_len)
 
 
-def _check_rows(out, q, ck, cv, R, rows, S, label):
-    cb, _ = O.lloyd_max_codebook(32, 4)
+def _check_rows(out, q, ck, cv, R, rows, S, label, bits=4):
+    cb, _ = O.lloyd_max_codebook(32, bits)
     Hq, Hkv = q.shape[1], ck.blocks.shape[1]
     G = Hq // Hkv
     worst = 0.0
@@ -69,7 +69,7 @@ def _check_rows(out, q, ck, cv, R, rows, S, label):
         kb = ck.blocks[b, h:h + 1, :S].cpu().numpy()
         vb = cv.blocks[b, h:h + 1, :S].cpu().numpy()
         qh = q[b, h * G:(h + 1) * G].cpu().numpy()[:, None, :]
-        ref = O.attention_from_blocks(qh, kb, vb, R, cb, cb)[:, 0]
+        ref = O.attention_from_blocks(qh, kb, vb, R, cb, cb, bits_k=bits, bits_v=bits)[:, 0]
         err = float(np.abs(out[b, h * G:(h + 1) * G].cpu().numpy() - ref).max())
         worst = max(worst, err)
     print(f"{label}: {len(rows)} sampled (batch, kv-head) rows, max-abs {worst:.3e}")
@@ -98,15 +98,15 @@ def test_decode_multi_segment_vs_oracle(B, Hkv, Hq, S):
     _check_rows(out, q, ck, cv, R, rows, S, f"decode B{B} Hkv{Hkv} Hq{Hq} S{S}")
 
 
-def test_decode_many_short_rows_vs_oracle():
-    """1536 short (batch, kv head, head group) rows: every team of warps walks five or six segments, so it
-    rotates the queries of its segments in more than one pass (a pass holds four), rows start in the middle
-    of a team's range, and each KV head has two head groups (six query heads per KV head).  The last
-    tile of every row is ragged."""
+@pytest.mark.parametrize("B,Hkv,Hq,S,D,bits", [(96, 8, 48, 40, 128, 4), (160, 8, 24, 56, 64, 2)])
+def test_decode_many_short_rows_vs_oracle(B, Hkv, Hq, S, D, bits):
+    """More than 1200 short (batch, kv head, head group) rows: every team of warps walks five or six
+    segments, so it rotates the queries of its segments in more than one pass (a pass holds four), rows
+    start in the middle of a team's range, and the last tile of every row is ragged.  First shape: six query
+    heads per KV head (two head groups); second: head dim 64 with 2-bit blocks (other tile sizes)."""
     from polarquant_kv import attention
     dev = _cuda()
-    B, Hkv, Hq, S, D = 96, 8, 48, 40, 128
-    R, plan, ck, cv = _build(B, Hkv, S, D, dev, seed=17)
+    R, plan, ck, cv = _build(B, Hkv, S, D, dev, seed=17, bits=bits)
     gen = torch.Generator(device=dev)
     gen.manual_seed(6)
     q = torch.randn((B, Hq, D), generator=gen, device=dev).to(torch.float16)
@@ -114,10 +114,10 @@ def test_decode_many_short_rows_vs_oracle():
     one = attention.decode_attention(q, ck, cv, plan, enable_qjl=False, n_splits=1)
     torch.cuda.synchronize()
     diff = float((out - one).abs().max())
-    print(f"B{B} Hkv{Hkv} Hq{Hq} S{S}: balanced vs one segment per row: max-abs {diff:.3e}")
+    print(f"B{B} Hkv{Hkv} Hq{Hq} S{S} D{D} b{bits}: balanced vs one segment per row: max-abs {diff:.3e}")
     assert diff <= 2e-4
-    rows = [(0, 0), (0, 1), (1, 7), (37, 3), (38, 4), (64, 0), (95, 6), (95, 7)]
-    _check_rows(out, q, ck, cv, R, rows, S, f"decode B{B} Hkv{Hkv} Hq{Hq} S{S}")
+    rows = [(0, 0), (0, 1), (1, 7), (37, 3), (38, 4), (64, 0), (B - 1, 6), (B - 1, 7)]
+    _check_rows(out, q, ck, cv, R, rows, S, f"decode B{B} Hkv{Hkv} Hq{Hq} S{S} D{D} b{bits}", bits=bits)
 
 
 def test_decode_long_context_shape_vs_oracle():
