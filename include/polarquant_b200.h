@@ -194,9 +194,15 @@ int pq_dequant(const void* blocks, int64_t n_vec, int head_dim, int n_bits,
  *              cut into one equal contiguous range per SM; >= 1: that many equal
  *              sequence ranges per (batch, kv head, head group), dealt to the SMs
  *   scratch    device buffer of at least pq_decode_attn_scratch_bytes(...) bytes,
- *              256-byte aligned, ZERO-FILLED ONCE before its first use; the kernel
- *              leaves its counters at zero again, so it can be reused by later calls
- *              on the same stream (concurrent calls need separate scratch buffers)
+ *              256-byte aligned, ZERO-FILLED before its first use.  It starts with one
+ *              32-bit counter per (batch, kv head, head group), at most batch * q_heads of
+ *              them, followed (on the next 256-byte boundary) by the segment records.  The
+ *              kernel leaves its counters at zero again, so later calls with the SAME batch,
+ *              q_heads and kv_heads on the same stream reuse the buffer as it is; before a
+ *              call with another batch or other head counts clear the first
+ *              4 * batch * q_heads bytes (rounded up to 256) again, because the records of
+ *              a call with fewer counters lie where a larger call keeps its counters
+ *              (concurrent calls need separate scratch buffers)
  */
 int pq_decode_attn(const void* q, const void* k_blocks, const void* v_blocks,
                    int batch, int q_heads, int kv_heads, int64_t seq_len, int64_t seq_capacity,

@@ -22,14 +22,23 @@ from .types import CompressedKV
 _SCRATCH: dict = {}
 
 
-def _scratch(device, nbytes: int) -> torch.Tensor:
-    """Zero-initialised scratch for pq_decode_attn, one per (device, stream); grown on demand.
-    The kernel leaves its tickets at zero, so the buffer is reused without clearing."""
+def _scratch(device, nbytes: int, batch: int, q_heads: int, kv_heads: int) -> torch.Tensor:
+    """Scratch for pq_decode_attn, one per (device, stream); grown on demand.
+
+    The buffer starts with one ticket counter per (batch, kv head, head group), which must read zero when
+    a launch starts; the segment records follow.  A kernel leaves its own counters at zero, so consecutive
+    calls of one shape reuse the buffer as it is.  A call of another shape has another number of counters:
+    where its counters lie, an earlier call with fewer of them may have written records, so the counter
+    region is cleared whenever the shape differs from the previous call's on this buffer."""
     key = (str(device), torch.cuda.current_stream(device).cuda_stream)
-    buf = _SCRATCH.get(key)
+    shape = (batch, q_heads, kv_heads)
+    buf, last = _SCRATCH.get(key, (None, None))
     if buf is None or buf.numel() < nbytes:
         buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _SCRATCH[key] = buf
+    elif last != shape:
+        # at most one counter per (batch, query head); rounded up to the 256 bytes the records start on
+        buf[:min(buf.numel(), (batch * q_heads * 4 + 255) // 256 * 256)].zero_()
+    _SCRATCH[key] = (buf, shape)
     return buf
 
 
@@ -91,7 +100,7 @@ def decode_attention(query: torch.Tensor, ck: CompressedKV, cv: CompressedKV, pl
             raise ValueError("seq_len_tensor must be a one-element int64 tensor on the query's device")
         S = cap                              # the work partition and the scratch cover the capacity
     need = lib.pq_decode_attn_scratch_bytes(B, Hq, Hkv, S, D, n_splits)
-    scratch = _scratch(dev, need)
+    scratch = _scratch(dev, need, B, Hq, Hkv)
     if partial:
         out = torch.empty((B, Hq, D + 2), dtype=torch.float32, device=dev)
     else:

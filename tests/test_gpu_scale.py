@@ -120,6 +120,28 @@ def test_decode_many_short_rows_vs_oracle(B, Hkv, Hq, S, D, bits):
     _check_rows(out, q, ck, cv, R, rows, S, f"decode B{B} Hkv{Hkv} Hq{Hq} S{S} D{D} b{bits}", bits=bits)
 
 
+def test_decode_shared_scratch_after_a_call_with_fewer_rows():
+    """decode_attention keeps one scratch buffer per stream.  A call over few (batch, kv head) rows writes
+    its segment records where a later call over many rows keeps its ticket counters: the later call must
+    still merge every row (the wrapper clears the counter region when the shape changes)."""
+    from polarquant_kv import attention
+    dev = _cuda()
+    D, S = 128, 96
+    R, plan, ck_small, cv_small = _build(2, 2, S, D, dev, seed=23)
+    _, _, ck_big, cv_big = _build(48, 8, S, D, dev, seed=29)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(8)
+    q_small = torch.randn((2, 8, D), generator=gen, device=dev).to(torch.float16)
+    q_big = torch.randn((48, 32, D), generator=gen, device=dev).to(torch.float16)
+    want = attention.prepare_decode(q_big, ck_big, cv_big, plan, n_splits=3)().clone()     # private scratch
+    for _ in range(2):
+        attention.decode_attention(q_small, ck_small, cv_small, plan, enable_qjl=False, n_splits=3)
+        got = attention.decode_attention(q_big, ck_big, cv_big, plan, enable_qjl=False, n_splits=3)
+        torch.cuda.synchronize()
+        assert float((got - want).abs().max()) <= 1e-5
+    _check_rows(got, q_big, ck_big, cv_big, R, [(0, 0), (47, 7), (20, 3)], S, "decode after a smaller call")
+
+
 def test_decode_long_context_shape_vs_oracle():
     """One 131072-token sequence, 8 KV heads, 64 query heads (8 per KV head): two sampled KV heads."""
     from polarquant_kv import attention
