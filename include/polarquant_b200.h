@@ -184,9 +184,8 @@ int pq_dequant(const void* blocks, int64_t n_vec, int head_dim, int n_bits,
  *   jl_matrix  NULL, or the JL matrix for the QJL score correction: float32
  *              [jl_dim, head_dim] row-major P (scores += corr * scale,
  *              attention.py:150-155); then qjl_bits [rows, seq_capacity, jl_dim/8] and
- *              qjl_norms float16 [rows, seq_capacity] are required, both 16-byte aligned,
- *              jl_dim a multiple of 16 in [16, 128] and seq_capacity even (every row of
- *              norms then starts on a 4-byte boundary); PQ_ERR_MISALIGNED otherwise
+ *              qjl_norms float16 [rows, seq_capacity] are required, both 16-byte aligned
+ *              (PQ_ERR_MISALIGNED otherwise), jl_dim a multiple of 16 in [16, 128]
  *   out        [batch, q_heads, head_dim] float32 (out_is_fp16 == 0) or float16
  *   partial_out NULL, or float32 [batch, q_heads, head_dim + 2]: when given, the kernel
  *              skips the final normalisation and inverse rotation and writes

@@ -1284,8 +1284,9 @@ static int check_decode_args(const void* q, const void* k_blocks, const void* v_
     if (jl_matrix != nullptr) {
         if (jl_dim < 16 || jl_dim > 128 || (jl_dim % 16)) return PQ_ERR_BAD_JL_DIM;
         if (!qjl_bits || !qjl_norms) return PQ_ERR_NULL_POINTER;
-        if ((reinterpret_cast<uintptr_t>(qjl_bits) & 15) || (reinterpret_cast<uintptr_t>(qjl_norms) & 15) ||
-            (seq_capacity & 1))
+        // (rows of the side band that do not start on a 16-byte boundary - any capacity that is not a
+        // multiple of 8 has some - are staged by the warps' own byte loads instead of bulk copies)
+        if ((reinterpret_cast<uintptr_t>(qjl_bits) & 15) || (reinterpret_cast<uintptr_t>(qjl_norms) & 15))
             return PQ_ERR_MISALIGNED;
     }
     if (seq_len == 0) return PQ_OK;

@@ -25,7 +25,7 @@ DECODE_SHAPES = [
     (64, 4, 2, 64, 64, 2, 2, 0, False),
     (1, 8, 8, 3000, 128, 4, 2, 0, False),
     (16, 2, 1, 500, 128, 2, 4, 3, False),
-    (5, 2, 4, 78, 128, 4, 4, 2, True),       # with the sketch the capacity must be even
+    (5, 2, 4, 77, 128, 4, 4, 2, True),       # an odd capacity with the sketch: side-band rows off the 16-byte grid
     (48, 8, 4, 96, 128, 4, 4, 3, False),
     (2, 2, 4, 100, 128, 4, 4, 4, False),
     (300, 4, 4, 40, 64, 4, 4, 0, False),
