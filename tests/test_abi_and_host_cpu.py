@@ -274,3 +274,61 @@ def test_decoder_harness_host_pieces():
         norm.weight.copy_(torch.randn(8))
         want_n = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-6) * norm.weight
         assert torch.allclose(norm(v), want_n, atol=1e-6)
+
+
+def _walk_balanced_partition(n_vrows, tiles_per_row, n_workers):
+    """The decode kernel's balanced work partition, restated: the tiles of all virtual rows form one
+    sequence cut into n_workers equal contiguous ranges; a worker walks the pieces of rows ("segments")
+    inside its range and derives, from its own numbers alone, which segment of the row it holds and how many
+    the row has (the row's ticket counter and record slots depend on every worker agreeing).
+    Yields (worker, virtual row, first tile, end tile, segment index, segments of the row)."""
+    all_tiles = n_vrows * tiles_per_row
+    for w in range(n_workers):
+        cur, cur_end = w * all_tiles // n_workers, (w + 1) * all_tiles // n_workers
+        while cur < cur_end:
+            vrow = cur // tiles_per_row
+            row_t0, row_t1 = vrow * tiles_per_row, (vrow + 1) * tiles_per_row
+            seg_end = min(cur_end, row_t1)
+            c_first = ((row_t0 + 1) * n_workers + all_tiles - 1) // all_tiles - 1
+            c_last = (row_t1 * n_workers + all_tiles - 1) // all_tiles - 1
+            yield w, vrow, cur - row_t0, seg_end - row_t0, w - c_first, c_last - c_first + 1
+            cur = seg_end
+
+
+def test_decode_partition_arithmetic():
+    """Invariants the kernel and the host-side scratch layout rely on, over many shapes: every tile is covered
+    once; the workers that share a row number their pieces 0..n-1 and agree on n; n never exceeds the number
+    of record slots per row the scratch is sized for; a worker's pieces are consecutive rows and every piece
+    after its first starts at tile 0 of its row (the query rotation of several pieces in one pass and the
+    look-ahead for the next piece's first tiles assume both)."""
+    from polarquant_kv import _ext
+    lib = _ext.lib()
+    rng = np.random.default_rng(3)
+    shapes = [(256, 512), (32, 512), (8, 8192), (1536, 3), (1280, 4), (1, 1), (1, 7), (296, 1), (297, 1), (5, 59),
+              (128, 272), (16, 272), (1000, 1), (3, 100000)]
+    shapes += [(int(rng.integers(1, 2000)), int(rng.integers(1, 700))) for _ in range(40)]
+    for n_vrows, tiles in shapes:
+        # scratch layout for this shape: batch = n_vrows rows of one KV head with four query heads (one group)
+        seq_len = tiles * 16
+        need = lib.pq_decode_attn_scratch_bytes(n_vrows, 4, 1, seq_len, 128, 0)
+        tickets = (n_vrows * 4 + 255) // 256 * 256
+        slots = (need - tickets) // (n_vrows * 8 * 130 * 4)
+        assert tickets + n_vrows * slots * 8 * 130 * 4 == need
+        # (the library sizes the scratch for the device it runs on: 148 SMs when there is none)
+        for sms, teams in ((148, 2), (148, 1), (132, 2)):
+            n_workers = max(1, min(n_vrows * tiles, sms * teams))
+            covered = np.zeros(n_vrows * tiles, dtype=np.int32)
+            seen, last = {}, {}
+            for w, vrow, t0, t1, idx, n in _walk_balanced_partition(n_vrows, tiles, n_workers):
+                assert 0 <= t0 < t1 <= tiles and 0 <= idx < n
+                covered[vrow * tiles + t0: vrow * tiles + t1] += 1
+                seen.setdefault(vrow, []).append((idx, n))
+                if w in last:
+                    assert vrow == last[w] + 1 and t0 == 0, (n_vrows, tiles, n_workers, w)
+                last[w] = vrow
+            assert (covered == 1).all()
+            for vrow, pieces in seen.items():
+                n = pieces[0][1]
+                assert sorted(i for i, _ in pieces) == list(range(n)) and all(m == n for _, m in pieces)
+                if sms == 148:
+                    assert n <= slots, (n_vrows, tiles, n_workers, n, slots)
