@@ -311,10 +311,11 @@ def compressed_attention(query: torch.Tensor, compressed_keys, compressed_values
         out = decode_attention(q4[:, :, 0], ck, cv, plan, enable_qjl, out_dtype=out_dtype).unsqueeze(2)
     else:
         if enable_qjl and jl_matrix is not None and ck.qjl_signs is not None:
-            # the sketch correction lives in the decode kernel: one decode per query position
-            # (non-causal, as the reference: every position sees the whole cache)
-            out = torch.stack([decode_attention(q4[:, :, i].contiguous(), ck, cv, plan, True, out_dtype=out_dtype)
-                               for i in range(Sq)], dim=2)
+            # The sketch correction lives in the decode kernel.  Every position sees the whole cache (non-causal,
+            # as the reference), so the Sq positions of a query head are Sq more heads of its KV head's group:
+            # one decode launch over Hq * Sq heads, [B, Hq, Sq, D] read as [B, Hq * Sq, D] (kv-head major as it is).
+            out = decode_attention(q4.reshape(B, Hq * Sq, D).contiguous(), ck, cv, plan, True,
+                                   out_dtype=out_dtype).reshape(B, Hq, Sq, D)
         else:
             out = prefill_attention(q4, ck, cv, plan, out_dtype=out_dtype)
     if return_scores:
