@@ -4,5 +4,7 @@ package): configuration, the per-layer cache manager, and a decoder that attends
 from .config import PolarQuantConfig
 from .kv_cache import KVCacheManager
 from .model import CompressedAttention, DecoderConfig, DecoderLM
+from .reference_layers import CompressedMultiHeadAttention, SimpleTransformer, SimpleTransformerLayer
 
-__all__ = ["PolarQuantConfig", "KVCacheManager", "CompressedAttention", "DecoderConfig", "DecoderLM"]
+__all__ = ["PolarQuantConfig", "KVCacheManager", "CompressedAttention", "DecoderConfig", "DecoderLM",
+           "CompressedMultiHeadAttention", "SimpleTransformer", "SimpleTransformerLayer"]

@@ -332,3 +332,43 @@ def test_decode_partition_arithmetic():
                 assert sorted(i for i, _ in pieces) == list(range(n)) and all(m == n for _, m in pieces)
                 if sms == 148:
                     assert n <= slots, (n_vrows, tiles, n_workers, n, slots)
+
+
+def test_reference_gpu_package_paths_resolve():
+    """Every module path and name the reference's tests import from polarquant_kv_cuda resolves (the functions
+    themselves need a GPU); the layer classes build and run without a cache on the CPU."""
+    import importlib
+
+    import torch
+    wanted = {
+        "polarquant_kv_cuda.rotation": ["generate_rotation_matrix", "rotate", "inverse_rotate"],
+        "polarquant_kv_cuda.lloyd_max": ["build_lloyd_max_codebook", "quantize_with_codebook",
+                                         "dequantize_with_codebook", "get_codebook_torch"],
+        "polarquant_kv_cuda.types": ["CompressedKVCacheGPU"],
+        "polarquant_kv_cuda.compress_kernel": ["compress_gpu"],
+        "polarquant_kv_cuda.decompress_kernel": ["decompress_gpu"],
+        "polarquant_kv_cuda.attention_kernel": ["compressed_attention_gpu"],
+        "polarquant_kv_cuda.qjl_kernel": ["compute_signatures_gpu", "compute_correction_gpu", "bit_pack", "bit_unpack"],
+        "polarquant_kv_cuda.compressor": ["compress", "decompress", "compressed_attention", "get_memory_bytes"],
+        "polarquant_kv_cuda.utils": ["cosine_similarity", "check_memory_warning"],
+        "polarquant_kv_cuda.hf_integration": ["CompressedDynamicCache", "patch_model", "create_compressed_cache"],
+        "polarquant_kv_cuda.inference.config": ["PolarQuantConfig"],
+        "polarquant_kv_cuda.inference.kv_cache": ["KVCacheManager"],
+        "polarquant_kv_cuda.inference.attention": ["CompressedMultiHeadAttention"],
+        "polarquant_kv_cuda.inference.transformer": ["SimpleTransformer", "SimpleTransformerLayer"],
+    }
+    for module, names in wanted.items():
+        mod = importlib.import_module(module)
+        assert [n for n in names if not hasattr(mod, n)] == [], module
+    from polarquant_kv_cuda.inference.config import PolarQuantConfig
+    from polarquant_kv_cuda.inference.transformer import SimpleTransformer
+    from polarquant_kv_cuda.rotation import generate_rotation_matrix, inverse_rotate, rotate
+    model = SimpleTransformer(PolarQuantConfig(), num_layers=2, embed_dim=64, num_heads=4, num_kv_heads=2, vocab_size=50)
+    with torch.no_grad():
+        assert model(torch.randint(0, 50, (2, 5))).shape == (2, 5, 50)
+    assert {"layers.0.attn.q_proj.weight", "layers.1.ffn.2.weight", "layers.0.norm2.bias", "embed.weight",
+            "head.weight"} <= set(model.state_dict())
+    R = generate_rotation_matrix(64, 3, device="cpu")
+    v = torch.randn(5, 64)
+    assert R.dtype == torch.float32 and torch.allclose(inverse_rotate(rotate(v, R), R), v, atol=1e-5)
+    assert np.allclose(R.numpy(), O.rotation_matrix(64, 3), atol=1e-7)

@@ -316,3 +316,44 @@ def test_device_plan_cache_recognises_objects_and_edits():
     R2[0, 0], R2[-1, -1] = R2[-1, -1], R2[0, 0]
     assert rotation.device_plan(R2, dev) is not first
     assert np.allclose(first.rot.cpu().numpy(), R.astype(np.float32))
+
+
+def test_reference_named_layers_and_gpu_package_functions():
+    """The reference's GPU package by its own names: compress_gpu / decompress_gpu / compressed_attention_gpu
+    give what the polarquant_kv functions give, and SimpleTransformer over compressed cache managers stays
+    close to the same model over plain float16 caches (prompt, then two single-token steps)."""
+    from polarquant_kv import quantizer, attention
+    from polarquant_kv_cuda.attention_kernel import compressed_attention_gpu
+    from polarquant_kv_cuda.compress_kernel import compress_gpu
+    from polarquant_kv_cuda.compressor import get_memory_bytes
+    from polarquant_kv_cuda.decompress_kernel import decompress_gpu
+    from polarquant_kv_cuda.inference.config import PolarQuantConfig
+    from polarquant_kv_cuda.inference.transformer import SimpleTransformer
+    from polarquant_kv_cuda.rotation import generate_rotation_matrix
+    dev = _cuda()
+    torch.manual_seed(0)
+    R = generate_rotation_matrix(64, 0)
+    kv = torch.randn(2, 2, 50, 64, device=dev).half()
+    q = torch.randn(2, 8, 1, 64, device=dev).half()
+    cache = compress_gpu(kv, R, 4, 32)
+    assert torch.equal(cache.blocks, quantizer.compress(kv, R, 4, 32).blocks)
+    back = decompress_gpu(cache, R)
+    assert back.dtype == torch.float16 and back.shape == kv.shape
+    cos = torch.nn.functional.cosine_similarity(back.float().flatten(), kv.float().flatten(), dim=0)
+    assert float(cos) > 0.99
+    assert get_memory_bytes(cache) == 2 * 2 * 50 * 2 * 18
+    out = compressed_attention_gpu(q, cache, cache, R)
+    assert torch.equal(out, attention.compressed_attention(q, cache, cache, R))
+
+    cfg_c, cfg_p = PolarQuantConfig(n_bits=4), PolarQuantConfig(enable_compression=False)
+    model = SimpleTransformer(cfg_c, num_layers=2, embed_dim=128, num_heads=4, num_kv_heads=2, vocab_size=97).to(dev)
+    plain = SimpleTransformer(cfg_p, num_layers=2, embed_dim=128, num_heads=4, num_kv_heads=2, vocab_size=97).to(dev)
+    plain.load_state_dict(model.state_dict())
+    ids = torch.randint(0, 97, (3, 20), device=dev)
+    with torch.no_grad():
+        cm_c, cm_p = model.create_cache_managers(32, 3, dev), plain.create_cache_managers(32, 3, dev)
+        for chunk in (ids[:, :18], ids[:, 18:19], ids[:, 19:20]):
+            a, b = model(chunk, cm_c), plain(chunk, cm_p)
+            cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0)
+            assert a.shape == (3, chunk.shape[1], 97) and float(cos) > 0.99, float(cos)
+        assert cm_c[0].seq_len == 20 and cm_c[1].compression_ratio > 3.0
