@@ -346,8 +346,8 @@ def test_reference_named_layers_and_gpu_package_functions():
     assert torch.equal(out, attention.compressed_attention(q, cache, cache, R))
 
     cfg_c, cfg_p = PolarQuantConfig(n_bits=4), PolarQuantConfig(enable_compression=False)
-    model = SimpleTransformer(cfg_c, num_layers=2, embed_dim=128, num_heads=4, num_kv_heads=2, vocab_size=97).to(dev)
-    plain = SimpleTransformer(cfg_p, num_layers=2, embed_dim=128, num_heads=4, num_kv_heads=2, vocab_size=97).to(dev)
+    model = SimpleTransformer(cfg_c, num_layers=2, embed_dim=256, num_heads=4, num_kv_heads=2, vocab_size=97).to(dev)
+    plain = SimpleTransformer(cfg_p, num_layers=2, embed_dim=256, num_heads=4, num_kv_heads=2, vocab_size=97).to(dev)
     plain.load_state_dict(model.state_dict())
     ids = torch.randint(0, 97, (3, 20), device=dev)
     with torch.no_grad():
