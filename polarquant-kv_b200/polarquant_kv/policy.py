@@ -126,3 +126,12 @@ def estimate_mixed_compression_ratio(seq_len: int, sink_size: int = 4, window_si
     bits = compute_token_bitwidths(seq_len, sink_size, window_size)
     per_tok = [(head_dim // 32) * (2 + 4 * int(b)) for b in bits.tolist()]
     return (2 * head_dim * seq_len) / max(sum(per_tok), 1)
+
+
+def estimate_adaptive_compression_ratio(bitwidths, head_dim: int = 128) -> float:
+    """float16 bits over the mean block_pq4 bits per value of a per-layer plan (adaptive_bitwidth.py:71-84
+    amortises a float32 radius per vector; here every 32 values carry one float16 radius: 0.5 bit each)."""
+    widths = [int(b) for b in bitwidths]
+    if not widths:
+        return 0.0
+    return 16.0 / (sum(b + 16.0 / 32.0 for b in widths) / len(widths))

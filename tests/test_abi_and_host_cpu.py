@@ -350,7 +350,9 @@ def test_reference_gpu_package_paths_resolve():
         "polarquant_kv_cuda.attention_kernel": ["compressed_attention_gpu"],
         "polarquant_kv_cuda.qjl_kernel": ["compute_signatures_gpu", "compute_correction_gpu", "bit_pack", "bit_unpack"],
         "polarquant_kv_cuda.compressor": ["compress", "decompress", "compressed_attention", "get_memory_bytes"],
-        "polarquant_kv_cuda.utils": ["cosine_similarity", "check_memory_warning"],
+        "polarquant_kv_cuda.utils": ["cosine_similarity", "check_memory_warning", "cosine_similarity_gpu"],
+        "polarquant_kv_cuda.adaptive_bitwidth": ["compute_layer_bitwidths", "estimate_adaptive_compression_ratio"],
+        "polarquant_kv_cuda.token_importance": ["compute_token_bitwidths", "estimate_mixed_compression_ratio"],
         "polarquant_kv_cuda.hf_integration": ["CompressedDynamicCache", "patch_model", "create_compressed_cache"],
         "polarquant_kv_cuda.inference.config": ["PolarQuantConfig"],
         "polarquant_kv_cuda.inference.kv_cache": ["KVCacheManager"],
@@ -368,6 +370,10 @@ def test_reference_gpu_package_paths_resolve():
         assert model(torch.randint(0, 50, (2, 5))).shape == (2, 5, 50)
     assert {"layers.0.attn.q_proj.weight", "layers.1.ffn.2.weight", "layers.0.norm2.bias", "embed.weight",
             "head.weight"} <= set(model.state_dict())
+    from polarquant_kv_cuda.adaptive_bitwidth import compute_layer_bitwidths, estimate_adaptive_compression_ratio
+    plan = compute_layer_bitwidths(24, 3.0)
+    assert plan[0] == plan[-1] == 4 and plan[12] == 2 and abs(sum(plan) / 24 - 3.0) <= 0.1
+    assert abs(estimate_adaptive_compression_ratio([4, 2]) - 16.0 / 3.5) < 1e-9
     R = generate_rotation_matrix(64, 3, device="cpu")
     v = torch.randn(5, 64)
     assert R.dtype == torch.float32 and torch.allclose(inverse_rotate(rotate(v, R), R), v, atol=1e-5)
