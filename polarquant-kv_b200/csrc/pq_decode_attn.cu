@@ -50,8 +50,10 @@ constexpr int kTabBytes = 65536;    // 256 byte values x 256 B: K copies at +0, 
 // 2: {hi, lo} pairs like the keys (float32-level accuracy).  One term fails the 2e-3 bar on short,
 // peaked sequences with large values (measured 2.9e-3), so two are used.
 // Launch shape, overridable on the compiler command line for timing experiments: warps per CTA, teams
-// of warps per CTA (see DecodeCfg), tile stages per warp.  Measured on the 32 x 8 x 8192-token workload:
-// 16 warps in 2 teams 141.8 us, 20 warps in 2 teams 143.8, 20 warps in one team 149.5, 4 teams 142-149.
+// of warps per CTA (see DecodeCfg), tile stages per warp.  Measured on the 32 x 8 x 8192-token workload with
+// one query rotation per segment: 16 warps in 2 teams 141.8 us, 20 warps in 2 teams 143.8, 20 warps in one
+// team 149.5, 4 teams 142-149.  (With the rotation shared by a team's segments - 137 us - the query buffers of
+// four teams or the rings of twenty warps no longer fit shared memory; two stages instead of three: 138.4.)
 #ifndef PQ_DEC_TEAMS
 #define PQ_DEC_TEAMS 2
 #endif
