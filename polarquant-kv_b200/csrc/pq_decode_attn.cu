@@ -23,14 +23,15 @@
 // per lane so lookups never bank-conflict; a byte is moved into address position with a
 // single byte-permute.
 //
-// Work split: persistent CTAs, one per SM, 16 warps each.  The 16-token tiles of all
-// (batch, kv head, head group) rows form one sequence that is cut into equal contiguous
-// ranges, one per CTA (n_splits == 0), or every row is cut into n_splits equal segments dealt
-// round-robin (n_splits > 0).  Inside a segment a warp owns every 16th tile, streamed through
-// a private 3-stage cp.async ring.  Per segment the CTA reduces its warps' partials in shared
-// memory and writes one (m, l, o) record per query head; the last segment of a row to
-// finish (atomic ticket, no spinning) merges the row's records, normalises, rotates back
-// and resets the ticket.
+// Work split: persistent CTAs, one per SM, 16 warps each, in two independent teams of 8 (one team with the
+// key sketch).  The 16-token tiles of all (batch, kv head, head group) rows form one sequence that is cut
+// into equal contiguous ranges, one per team (n_splits == 0), or every row is cut into n_splits equal
+// segments dealt round-robin (n_splits > 0).  A team rotates the queries of up to four consecutive
+// segments of its range in one pass.  Inside a segment a warp owns every 8th tile, staged through a private
+// 3-stage ring by bulk copies (rows off the 16-byte grid and ragged last tiles by the warp's own loads).
+// Per segment the team reduces its warps' partials in shared memory and writes one (m, l, o) record per
+// query head; the last segment of a row to finish (atomic ticket, no spinning) merges the row's records,
+// normalises, rotates back and resets the ticket.
 #include <atomic>
 #include <cmath>
 #include <cstring>
