@@ -19,11 +19,14 @@ Other objects on the JSON line: `roofline` (dominant kernel against the measured
 bandwidth), `e2e` (same step through the public API with host buffers: query copied from pinned host
 memory, output copied back), `parity_sample_max_abs` (one (batch, kv-head) row of the very cache that
 was timed, against the numpy oracle), `long_context` (one 131072-token sequence split along the
-sequence across the ranks: partial decode + all-gather + merge), `compress` (2^24 K vectors with the
+sequence across the ranks: partial decode, then the exchange and merge of the per-rank records as one kernel
+over NVLink peer memory, with the all-gather + merge path timed beside it), `compress` (2^24 K vectors with the
 QJL sketch + 2^24 V vectors, per variant), `dequant`, `prefill`, `llama_bridge` (the llama.cpp bridge's
 entry points), `e2e_model` (a Qwen2.5-0.5B-shaped decoder over the compressed cache: 64 prompts of 4096
 tokens, 256 greedy steps, one CUDA graph launch per token; the same steps issued kernel by kernel under
-`eager`), `cpu_baseline` and the clocks sampled during the timed region.
+`eager`), `cpu_baseline` (the numpy oracle on a bounded sample, and the reference's own CPU functions as
+shipped on its CPU-runnable case and on a 16384-vector sample of the bulk-compress workload) and the clocks
+sampled during the timed region.
 
 `--impl reference` times the CPU implementation of the same step (the numpy restatement of the
 reference algorithm, oracle/pq_oracle.py, on all host cores, on a bounded sample per step).
