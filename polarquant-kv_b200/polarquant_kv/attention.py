@@ -29,13 +29,15 @@ def _scratch(device, nbytes: int, batch: int, q_heads: int, kv_heads: int) -> to
     a launch starts; the segment records follow.  A kernel leaves its own counters at zero, so consecutive
     calls of one shape reuse the buffer as it is.  A call of another shape has another number of counters:
     where its counters lie, an earlier call with fewer of them may have written records, so the counter
-    region is cleared whenever the shape differs from the previous call's on this buffer."""
+    region is cleared whenever the shape differs from the previous call's on this buffer — and always
+    while the stream is being captured into a CUDA graph: the graph is replayed later, after calls this
+    function has not seen, so the clear has to be part of it."""
     key = (str(device), torch.cuda.current_stream(device).cuda_stream)
     shape = (batch, q_heads, kv_heads)
     buf, last = _SCRATCH.get(key, (None, None))
     if buf is None or buf.numel() < nbytes:
         buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-    elif last != shape:
+    elif last != shape or torch.cuda.is_current_stream_capturing():
         # at most one counter per (batch, query head); rounded up to the 256 bytes the records start on
         buf[:min(buf.numel(), (batch * q_heads * 4 + 255) // 256 * 256)].zero_()
     _SCRATCH[key] = (buf, shape)
