@@ -378,3 +378,33 @@ def test_reference_gpu_package_paths_resolve():
     v = torch.randn(5, 64)
     assert R.dtype == torch.float32 and torch.allclose(inverse_rotate(rotate(v, R), R), v, atol=1e-5)
     assert np.allclose(R.numpy(), O.rotation_matrix(64, 3), atol=1e-7)
+
+
+def test_decode_split_mode_partition_arithmetic():
+    """n_splits >= 1, restated from the decode kernel: every row is cut into n_splits pieces of
+    ceil(tiles / n_splits) tiles, the pieces of all rows are dealt round-robin to the workers.  Every
+    tile is covered once, pieces past the end of a row are empty (they deliver an empty record), and the
+    scratch holds n_splits record slots per row; the library's default split count stays within its bounds."""
+    from polarquant_kv import _ext
+    lib = _ext.lib()
+    rng = np.random.default_rng(4)
+    for _ in range(60):
+        n_vrows, tiles = int(rng.integers(1, 300)), int(rng.integers(1, 600))
+        n_splits = int(rng.integers(1, min(tiles, 40) + 1))
+        per = -(-tiles // n_splits)
+        covered = np.zeros(n_vrows * tiles, dtype=np.int32)
+        n_workers = 2 * 148
+        handled = 0
+        for w in range(n_workers):
+            for item in range(w, n_vrows * n_splits, n_workers):
+                vrow, seg = divmod(item, n_splits)
+                t0, t1 = seg * per, min(tiles, seg * per + per)
+                handled += 1
+                if t0 < t1:
+                    covered[vrow * tiles + t0: vrow * tiles + t1] += 1
+        assert handled == n_vrows * n_splits and (covered == 1).all()
+        need = lib.pq_decode_attn_scratch_bytes(n_vrows, 4, 1, tiles * 16, 64, n_splits)
+        assert need == (n_vrows * 4 + 255) // 256 * 256 + n_vrows * n_splits * 8 * 66 * 4
+    for batch, hq, hkv, s in ((1, 64, 8, 131072), (32, 32, 8, 8192), (1, 8, 8, 16), (4, 14, 2, 5000)):
+        d = lib.pq_decode_attn_default_splits(batch, hq, hkv, s, 128)
+        assert 1 <= d <= max(1, min(64, -(-s // 16) // 32))
